@@ -1,0 +1,216 @@
+/*
+ * mcop_b200 - C ABI of the B200 (sm_100a) implementation of mcoplib's per-token inference hot path.
+ *
+ * Every entry point takes raw DEVICE pointers, 64-bit sizes/strides and a CUDA stream, enqueues its
+ * kernels on that stream and returns at once:
+ *     0  (MCOP_OK)          launched
+ *    <0                     rejected before any launch (see the enum); mcop_last_error() has the text.
+ * No entry point allocates, frees or synchronises unless its comment says so.  Buffers are owned by the
+ * caller.  Entry points are safe to call from several host threads; the error text is per thread.
+ *
+ * Each declaration cites the operator of MetaX-MACA/mcoplib it replaces (path:line inside that project).
+ * Element type codes: MCOP_F32 / MCOP_BF16 / MCOP_F16.
+ */
+#ifndef MCOP_B200_H_
+#define MCOP_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* mcop_stream_t; /* == cudaStream_t */
+
+enum { MCOP_F32 = 0, MCOP_BF16 = 1, MCOP_F16 = 2 };
+
+enum {
+  MCOP_OK = 0,
+  MCOP_ERR_ARGUMENT = -1,    /* null pointer, negative size, bad stride or misaligned buffer */
+  MCOP_ERR_UNSUPPORTED = -2, /* a shape / dtype combination this build has no kernel for */
+  MCOP_ERR_WORKSPACE = -3,   /* workspace missing or too small */
+  MCOP_ERR_CUDA = -4         /* the launch itself was refused by the CUDA runtime */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+int mcop_version(void);
+/* Text of the last error on the calling thread ("" if none). */
+const char* mcop_last_error(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Part 1 - residual add + RMSNorm (+ per-token int8 quantisation)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* torch.ops._C.fused_add_rms_norm, op/vllm/layernorm_kernels.cu:243-292 (schema op/vllm/torch_bindings.cpp:161-164).
+ * In place: r = T(x + res); res := r; x := T(T(r * rsqrt(mean(r^2)+eps)) * w).
+ * x [tokens, hidden] with row stride x_row_stride (elements); residual, weight contiguous. */
+int mcop_fused_add_rmsnorm(void* x, int64_t x_row_stride, void* residual, const void* weight,
+                           int64_t tokens, int64_t hidden, float eps, int dtype, mcop_stream_t stream);
+
+/* torch.ops._C.rms_norm_dynamic_per_token_quant,
+ * op/vllm/quantization/fused_kernels/fused_layernorm_dynamic_per_token_quant.cu:163-192 (schema torch_bindings.cpp:216-221),
+ * and mcoplib.op.rms_norm_dynamic_per_token_quant_custom, op/rms_norm_dynamic_per_token_quant.cu:266-285.
+ * s = x (+ res); res := T(s) (if residual != NULL); n = T(T(s * rsqrt(mean(s^2)+eps)) * w);
+ * scale = max(min(max|n|, *scale_ub) / 127, FLT_EPSILON); out = int8(rne(n * (1/scale))).
+ * out [tokens, hidden] int8, scales [tokens] fp32, scale_ub NULL or one fp32 on the device. */
+int mcop_add_rmsnorm_quant_i8(int8_t* out, float* scales, const void* x, int64_t x_row_stride,
+                              const void* weight, void* residual, const float* scale_ub,
+                              int64_t tokens, int64_t hidden, float eps, int dtype, mcop_stream_t stream);
+
+/* mcoplib.op.rms_norm_dynamic_per_token_quant (9 arguments), op/fused_rms_norm_dq.cu:646-667
+ * (include/fused_rms_norm_dq.h:3-12).  Keeps the reference's convention of DIVIDING by rsqrt(mean+eps):
+ * after_res = T(x + res); after_norm = T(after_res / r * w); y = after_res / r * w * smooth;
+ * scales = max|y| / 127; out = int8(rne(y / scale)) clamped to +-127.  weight and smooth share wdtype
+ * (MCOP_BF16 or MCOP_F32).  residual may be NULL; after_res and after_norm are always written. */
+int mcop_rmsnorm_smooth_quant_i8(int8_t* out, float* scales, void* after_res, void* after_norm,
+                                 const void* x, const void* weight, const void* smooth, const void* residual,
+                                 int64_t tokens, int64_t hidden, float eps, int dtype, int wdtype,
+                                 mcop_stream_t stream);
+
+/* mcoplib.op.rms_norm, op/fused_rms_norm_dq.cu:980-999 (include/fused_rms_norm_dq.h:16-24).
+ * out = T((x [+ res]) * d * w), d = rsqrt(mean+eps) or, with rms_div != 0, 1/rsqrt(mean+eps).
+ * residual and after_res are both NULL or both set (after_res = T(x + res)). */
+int mcop_rmsnorm(void* out, const void* x, const void* weight, void* after_res, const void* residual,
+                 int64_t tokens, int64_t hidden, float eps, int rms_div, int dtype, int wdtype,
+                 mcop_stream_t stream);
+
+/* mcoplib.op.head_rms_norm, op/fused_rms_norm_dq.cu:804-812: per-head RMSNorm (divide-by-rsqrt form) of
+ * heads [head_offset, head_offset + head_norm) of x [tokens, heads, head_dim] into out (same layout; other
+ * heads of out are not touched); weight [heads, head_dim] in wdtype. */
+int mcop_head_rmsnorm(void* out, const void* x, const void* weight, int64_t tokens, int64_t heads,
+                      int64_t head_dim, float eps, int head_offset, int head_norm, int dtype, int wdtype,
+                      mcop_stream_t stream);
+
+/* mcoplib.op.scale_dynamic_quant, op/scale_dynamic_quant.cu:127-153: y = x * smooth (fp32 smooth [hidden]);
+ * scales = max|y| / 127; out = int8(rne(y / scale)).  The caller allocates out and scales. */
+int mcop_scale_dynamic_quant_i8(int8_t* out, float* scales, const void* x, const float* smooth,
+                                int64_t tokens, int64_t hidden, int dtype, mcop_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Part 2 - rotary embedding and the int8 KV-cache store
+ * ---------------------------------------------------------------------------------------------- */
+
+/* torch.ops._C.rotary_embedding, op/vllm/pos_encoding_kernels.cu:135-217 (schema torch_bindings.cpp:233-237).
+ * In-place RoPE of query (and key unless NULL).  cos_sin_cache [max_pos, rot_dim] = cos || sin, in the
+ * activation dtype (arithmetic in T, rounded after every operation) or in fp32 (fp32 arithmetic, one rounding).
+ * Strides are in elements: token strides of query/key, and the stride between heads. */
+int mcop_rope_inplace(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
+                      int cache_dtype, int64_t tokens, int num_heads, int num_kv_heads, int head_size,
+                      int rot_dim, int64_t query_stride, int64_t key_stride, int64_t head_stride,
+                      int is_neox, int dtype, mcop_stream_t stream);
+
+/* mcoplib.op.rotary_embedding, op/rotary_embedding.cu:99-121 (include/rotary_embedding.h:3-5).
+ * NeoX RoPE of the Q and K heads of packed_qkv [tokens, Hq+2Hkv, D] into output (same layout, V heads not
+ * touched); position of token t of sequence b = cache_lens[b] + t - accum_q_lens[b];
+ * cos, sin fp32 [max_pos, D/2]; fp32 arithmetic, one rounding. */
+int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, const float* sin,
+                     const int32_t* accum_q_lens, const int32_t* cache_lens, int batch, int64_t tokens,
+                     int q_heads, int kv_heads, int head_dim, int dtype, mcop_stream_t stream);
+
+/* mcoplib.op.fused_rope_fwd, op/fused_rope.cu:13-74 (kernel/fused_rope_kernel.h:6-96).
+ * In-place NeoX RoPE of the Q and K planes of qkv [seq, planes>=2, heads, D]; cos, sin [*, D/2] in the
+ * activation dtype; row = indexes[s] (int64) or s when indexes is NULL; fp32 arithmetic, one rounding. */
+int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
+                        int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
+
+/* mcoplib.op.store_kv_cache_cuda_interface, op/store_kv.cu:220-350 (include/store_kv.h:2-15).
+ * code = clamp(rne(x * scale[h, d]), -127, 127) for the K and V heads of packed_qkv
+ * (strides qkv_stride_token / qkv_stride_head, elements) written to cache[slot_ids[b], h, cache_lens[b] + i, :]
+ * with cache strides in bytes-as-elements (int8): stride_slot, stride_head, stride_pos. */
+int mcop_kv_store_i8(const void* packed_qkv, int64_t qkv_stride_token, int64_t qkv_stride_head,
+                     const int32_t* q_lens, const int32_t* accum_q_lens, const int32_t* cache_lens,
+                     const int32_t* cache_slot_ids, int8_t* k_cache, int8_t* v_cache,
+                     int64_t k_stride_slot, int64_t k_stride_head, int64_t k_stride_pos,
+                     int64_t v_stride_slot, int64_t v_stride_head, int64_t v_stride_pos,
+                     const float* k_scale, const float* v_scale, int batch, int64_t tokens, int q_heads,
+                     int kv_heads, int head_dim, int dtype, mcop_stream_t stream);
+
+/* torch.ops._C_cache_ops.reshape_and_cache_flash / reshape_and_cache with kv_cache_dtype "auto",
+ * op/vllm/cache_kernels.cu:564-650 (schemas torch_bindings.cpp:403-420).
+ * Copies key/value [tokens, kv_heads, head_size] (token stride given) to the paged cache at
+ * slot_mapping[t] (block = slot / block_size, offset = slot % block_size; negative = skip).
+ * The cache is addressed by strides (elements): block, in-block position, head; head_size contiguous. */
+int mcop_reshape_and_cache_flash(const void* key, const void* value, int64_t key_stride, int64_t value_stride,
+                                 void* key_cache, void* value_cache, int64_t block_stride, int64_t page_stride,
+                                 int64_t head_stride, const int64_t* slot_mapping, int64_t tokens,
+                                 int kv_heads, int head_size, int block_size, int elem_bytes,
+                                 mcop_stream_t stream);
+
+/* Fused RoPE + int8 paged KV store.  No single reference operator: the composition of
+ * rotary_embedding (op/vllm/pos_encoding_kernels.cu:135-217) -> int8 quantisation of the ROUNDED rotated K
+ * and of V as in op/store_kv.cu:188-216 with per-head dequantisation scales (code = clamp(rne(v * (1/scale[h])), +-127))
+ * -> paged addressing of op/vllm/cache_kernels.cu:204-222.  query and key are rotated in place.
+ * key_cache/value_cache int8 [num_blocks, block_size, kv_heads, head_size] contiguous;
+ * k_scale, v_scale fp32 [kv_heads]. */
+int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query, void* key, const void* value,
+                                const void* cos_sin_cache, int cache_dtype, int8_t* key_cache,
+                                int8_t* value_cache, const int64_t* slot_mapping, const float* k_scale,
+                                const float* v_scale, int64_t tokens, int num_heads, int num_kv_heads,
+                                int head_size, int rot_dim, int64_t query_stride, int64_t key_stride,
+                                int64_t value_stride, int block_size, int64_t num_blocks, int is_neox,
+                                int dtype, mcop_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Part 3 - MoE routing, dispatch (scatter + quant) and combine (gather)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* mcoplib.op.moe_softmax_topk, op/moe_softmax_topk.cu:216-235 (include/moe_softmax_topk.h:3-7).
+ * fp32 logits [tokens, experts] -> softmax -> top-k (ties to the lowest index, descending order) ->
+ * weights renormalised to sum 1.  experts <= 1024, 1 <= k <= min(experts, 32). */
+int mcop_moe_softmax_topk(float* topk_weights, int32_t* topk_ids, const float* logits, int64_t tokens,
+                          int experts, int k, mcop_stream_t stream);
+
+/* mcoplib.op.fused_moe_gate_deepseek (moegate_type 0), op/fused_moe_gate_deepseek.cu:63-138
+ * (include/fused_moe_gate_deepseek.h:6-18).  Sigmoid scores + bias, group score = two best biased scores,
+ * keep topk_group groups, top-k experts of the kept groups (ties to the lower index, descending biased
+ * score), weights = score / sum(selected scores) (if renormalize) * routed_scaling.
+ * experts % 32 == 0, experts <= 512; groups == 1, or experts/groups a multiple of experts/32 spanning a
+ * power-of-two number of lanes.  group_mask (nullable) int32 [tokens]: bit g set iff group g was kept. */
+int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bias, float* topk_weights,
+                                  int32_t* topk_ids, int32_t* group_mask, int64_t tokens, int experts,
+                                  int groups, int topk_group, int topk, int renormalize,
+                                  float routed_scaling, int logits_dtype, int bias_dtype,
+                                  mcop_stream_t stream);
+
+/* Bytes of scratch mcop_moe_scatter_quant_i8 needs (contents need no initialisation). */
+size_t mcop_moe_scatter_workspace_bytes(int64_t tokens, int topk, int experts_per_rank);
+
+/* mcoplib.op.moe_scatter_dynamic_quant with no shared experts, op/moe_scatter_dynamic_quant.cu:312-341
+ * (include/moe_scatter_dynamic_quant.h:3-5).  Rows ordered by (expert, token); ids outside
+ * [0, experts_per_rank) are dropped.  row = int8(rne(x[t] * w[t,j] * smooth[e] * (127 / absmax))),
+ * row_scales = absmax / 127.  hidden bf16 [tokens, hidden]; ids int32 / weights fp32 [tokens, topk];
+ * smooth fp32 [experts_per_rank, hidden]; rows int8 [tokens*topk, hidden]; row_scales fp32 and row2tok
+ * int32 [tokens*topk]; counts, starts int32 [experts_per_rank]; tok2row (nullable) int32 [tokens, topk]
+ * receives the row of every (token, slot), -1 if dropped.  Entries of rows / row_scales / row2tok past the
+ * last routed row are left as they are. */
+int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids, const float* weights,
+                              const float* smooth, int8_t* rows, float* row_scales, int32_t* row2tok,
+                              int32_t* counts, int32_t* starts, int32_t* tok2row, int64_t tokens,
+                              int64_t hidden_size, int topk, int experts_per_rank, void* workspace,
+                              size_t workspace_bytes, mcop_stream_t stream);
+
+/* Bytes of scratch the gathers need when tok2row is NULL (0 otherwise). */
+size_t mcop_moe_gather_workspace_bytes(int64_t tokens, int64_t rows);
+
+/* mcoplib.op.moe_gather, op/moe_gather.cu:137-150 (include/moe_gather.h:3-6): out[row2tok[r]] += y[r].
+ * Deterministic: acc = float(out[t]); acc += y[r] for the rows of t in ascending r; out[t] = bf16(acc).
+ * y bf16 [rows, hidden], out bf16 [tokens, hidden].  tok2row (nullable) int32 [tokens, topk] as written by
+ * mcop_moe_scatter_quant_i8 avoids the inversion pre-pass (then workspace may be NULL). */
+int mcop_moe_gather(const void* y, const int32_t* row2tok, void* out, const int32_t* tok2row, int topk,
+                    int64_t tokens, int64_t rows, int64_t hidden_size, void* workspace,
+                    size_t workspace_bytes, mcop_stream_t stream);
+
+/* Weighted combine (no reference counterpart; weight lookup as op/moe_scatter_dynamic_quant.cu:240-247):
+ * out[t] = bf16((accumulate ? float(out[t]) : 0) + sum over the rows r of t, ascending, of w[t, j(r)] * y[r]),
+ * j(r) = first slot of t whose id equals the expert owning row r (from starts). */
+int mcop_moe_gather_weighted(const void* y, const int32_t* row2tok, const int32_t* topk_ids,
+                             const float* topk_weights, const int32_t* starts, void* out,
+                             const int32_t* tok2row, int accumulate, int64_t tokens, int64_t rows,
+                             int64_t hidden_size, int topk, int experts, void* workspace,
+                             size_t workspace_bytes, mcop_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MCOP_B200_H_ */

@@ -1,0 +1,446 @@
+// Part 1 of the hot path: residual add + RMSNorm (+ per-token int8 quantisation).
+//
+// One CTA per token row.  The row (and the residual row) is read ONCE with 16-byte loads and kept in
+// registers as fp32 across the sum-of-squares reduction, the abs-max reduction and the quantise step, so
+// the HBM traffic is the algorithmic minimum: read x and residual, write residual and the int8 codes.
+// Rows whose length is not a multiple of 8 elements (or that are not 16-byte aligned) take a scalar
+// multi-pass kernel with the same arithmetic.
+#include <math.h>
+
+#include <initializer_list>
+
+#include "common.cuh"
+
+namespace mcop {
+namespace {
+
+enum NormMode {
+  kQuant = 0,       // rms_norm_dynamic_per_token_quant: n = T(T(s*r)*w), codes + scale, residual in place
+  kFusedAdd = 1,    // fused_add_rms_norm: s = T(x+res), x := n, res := s
+  kSmoothQuant = 2, // 9-argument op: divide by r, after_res / after_norm / codes / scale
+  kPlain = 3        // rms_norm: out = T(s*d*w)
+};
+
+struct NormParams {
+  const void* x;
+  int64_t x_stride;
+  const void* weight;
+  const void* smooth;
+  const void* residual_in;  // nullable
+  void* residual_out;       // where T(x+res) goes (may alias residual_in); nullable
+  void* out;                // T output (kFusedAdd: == x; kSmoothQuant: after_norm; kPlain: out)
+  int64_t out_stride;
+  int8_t* q;
+  float* scales;
+  const float* scale_ub;
+  int hidden;
+  float eps;
+  int rms_div;
+};
+
+// Per-row scalar from the sum of squares: IEEE division and square root (matches 1/sqrt on the host).
+__device__ __forceinline__ float inv_rms(float ss, int hidden, float eps) {
+  return 1.0f / sqrtf(ss / (float)hidden + eps);
+}
+
+template <typename T, typename WT, int MODE, int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const int nv = p.hidden >> 3;
+  const T* x = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
+  const T* rin = p.residual_in ? reinterpret_cast<const T*>(p.residual_in) + row * (int64_t)p.hidden : nullptr;
+  T* rout = p.residual_out ? reinterpret_cast<T*>(p.residual_out) + row * (int64_t)p.hidden : nullptr;
+  const WT* w = reinterpret_cast<const WT*>(p.weight);
+
+  float s[NVEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nv) {
+      // x is overwritten by this kernel only in kFusedAdd: use the coherent load there.
+      if (MODE == kFusedAdd) Vec8<T>::load(x + v * 8, s[i]); else Vec8<T>::load_nc(x + v * 8, s[i]);
+      if (rin) {
+        float r[8];
+        Vec8<T>::load(rin + v * 8, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[i][j] += r[j];
+      }
+      if (MODE == kFusedAdd) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[i][j] = round_to<T>(s[i][j]);
+      }
+      if (rout) Vec8<T>::store(rout + v * 8, s[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += s[i][j] * s[i][j];
+      if (MODE == kSmoothQuant) {
+        // the later phases of the reference read the ROUNDED after_res back
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[i][j] = round_to<T>(s[i][j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[i][j] = 0.f;
+    }
+  }
+  ss = block_reduce<false>(ss, red);
+  const float r = inv_rms(ss, p.hidden, p.eps);
+
+  if (MODE == kPlain) {
+    const float d = p.rms_div ? 1.0f / r : r;
+    T* out = reinterpret_cast<T*>(p.out) + row * p.out_stride;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nv) {
+        float wv[8];
+        Vec8<WT>::load_nc(w + v * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[i][j] = s[i][j] * d * wv[j];
+        Vec8<T>::store(out + v * 8, s[i]);
+      }
+    }
+    return;
+  }
+
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nv) {
+      float wv[8];
+      Vec8<WT>::load_nc(w + v * 8, wv);
+      if (MODE == kSmoothQuant) {
+        float sm[8];
+        Vec8<WT>::load_nc(reinterpret_cast<const WT*>(p.smooth) + v * 8, sm);
+        float nw[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          nw[j] = s[i][j] / r * wv[j];
+          s[i][j] = nw[j] * sm[j];
+          amax = fmaxf(amax, fabsf(s[i][j]));
+        }
+        Vec8<T>::store(reinterpret_cast<T*>(p.out) + row * p.out_stride + v * 8, nw);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s[i][j] = round_to<T>(round_to<T>(s[i][j] * r) * wv[j]);
+          amax = fmaxf(amax, fabsf(s[i][j]));
+        }
+        if (MODE == kFusedAdd) Vec8<T>::store(reinterpret_cast<T*>(p.out) + row * p.out_stride + v * 8, s[i]);
+      }
+    }
+  }
+  if (MODE == kFusedAdd) return;
+
+  amax = block_reduce<true>(amax, red);
+  float scale, inv;
+  int lo;
+  if (MODE == kSmoothQuant) {
+    scale = (float)((double)amax / 127.0);
+    lo = -127;
+  } else {
+    if (p.scale_ub) amax = fminf(amax, *p.scale_ub);
+    scale = fmaxf(amax / 127.0f, FLT_EPSILON);
+    lo = -128;
+  }
+  inv = 1.0f / scale;
+  if (threadIdx.x == 0) p.scales[row] = scale;
+  int8_t* q = p.q + row * (int64_t)p.hidden;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nv) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(s[i][j] * inv, lo, 127);
+      st_cs_u2(q + v * 8, pack_i8x8(c));
+    }
+  }
+}
+
+// Scalar multi-pass form: any hidden size, any alignment.  Same arithmetic, re-reading the row.
+template <typename T, typename WT, int MODE>
+__global__ void __launch_bounds__(256) norm_rows_any(NormParams p) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const int H = p.hidden;
+  const T* x = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
+  const T* rin = p.residual_in ? reinterpret_cast<const T*>(p.residual_in) + row * (int64_t)H : nullptr;
+  T* rout = p.residual_out ? reinterpret_cast<T*>(p.residual_out) + row * (int64_t)H : nullptr;
+  const WT* w = reinterpret_cast<const WT*>(p.weight);
+  const WT* sm = reinterpret_cast<const WT*>(p.smooth);
+  T* out = p.out ? reinterpret_cast<T*>(p.out) + row * p.out_stride : nullptr;
+  // x (kFusedAdd) and the residual row are overwritten in place while later passes need the sum again,
+  // so the fp32 sum of the row is parked in shared memory and global memory is read only once.
+  extern __shared__ float keep[];  // hidden floats
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float s = ElemTraits<T>::to_float(x[i]);
+    if (rin) s += ElemTraits<T>::to_float(rin[i]);
+    if (MODE == kFusedAdd) s = round_to<T>(s);
+    if (rout) rout[i] = ElemTraits<T>::from_float(s);
+    ss += s * s;
+    if (MODE == kSmoothQuant) s = round_to<T>(s);
+    keep[i] = s;
+  }
+  ss = block_reduce<false>(ss, red);
+  const float r = inv_rms(ss, H, p.eps);
+  if (MODE == kPlain) {
+    const float d = p.rms_div ? 1.0f / r : r;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      out[i] = ElemTraits<T>::from_float(keep[i] * d * ElemTraits<WT>::to_float(w[i]));
+    return;
+  }
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v;
+    if (MODE == kSmoothQuant) {
+      const float nw = keep[i] / r * ElemTraits<WT>::to_float(w[i]);
+      out[i] = ElemTraits<T>::from_float(nw);
+      v = nw * ElemTraits<WT>::to_float(sm[i]);
+    } else {
+      v = round_to<T>(round_to<T>(keep[i] * r) * ElemTraits<WT>::to_float(w[i]));
+      if (MODE == kFusedAdd) out[i] = ElemTraits<T>::from_float(v);
+    }
+    keep[i] = v;
+    amax = fmaxf(amax, fabsf(v));
+  }
+  if (MODE == kFusedAdd) return;
+  amax = block_reduce<true>(amax, red);
+  float scale;
+  int lo;
+  if (MODE == kSmoothQuant) {
+    scale = (float)((double)amax / 127.0);
+    lo = -127;
+  } else {
+    if (p.scale_ub) amax = fminf(amax, *p.scale_ub);
+    scale = fmaxf(amax / 127.0f, FLT_EPSILON);
+    lo = -128;
+  }
+  const float inv = 1.0f / scale;
+  if (threadIdx.x == 0) p.scales[row] = scale;
+  int8_t* q = p.q + row * (int64_t)H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) q[i] = (int8_t)q_rn_clamp(keep[i] * inv, lo, 127);
+}
+
+template <typename T, typename WT, int MODE>
+int launch_norm(const NormParams& p, int64_t tokens, bool vec_ok, cudaStream_t stream) {
+  if (tokens == 0) return MCOP_OK;
+  MCOP_REQUIRE(tokens <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "norm: %lld tokens exceed the grid limit", (long long)tokens);
+  const int nv = p.hidden >> 3;
+  const dim3 grid((unsigned)tokens);
+  if (vec_ok && nv <= 4096) {
+    if (nv <= 256) norm_rows_vec<T, WT, MODE, 128, 2><<<grid, 128, 0, stream>>>(p);
+    else if (nv <= 1024) norm_rows_vec<T, WT, MODE, 256, 4><<<grid, 256, 0, stream>>>(p);
+    else if (nv <= 2048) norm_rows_vec<T, WT, MODE, 512, 4><<<grid, 512, 0, stream>>>(p);
+    else norm_rows_vec<T, WT, MODE, 1024, 4><<<grid, 1024, 0, stream>>>(p);
+  } else {
+    const size_t smem = (size_t)p.hidden * sizeof(float);
+    MCOP_REQUIRE(smem <= 200 * 1024, MCOP_ERR_UNSUPPORTED, "norm: hidden %d too large for the unaligned path", p.hidden);
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(norm_rows_any<T, WT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "norm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
+    norm_rows_any<T, WT, MODE><<<grid, 256, smem, stream>>>(p);
+  }
+  return check_launch("norm");
+}
+
+// Weight type choices: same as the activation type, or fp32.
+template <typename T, int MODE>
+int dispatch_wt(const NormParams& p, int64_t tokens, bool vec_ok, int dtype, int wdtype, cudaStream_t stream) {
+  if (wdtype == dtype) return launch_norm<T, T, MODE>(p, tokens, vec_ok, stream);
+  if (wdtype == MCOP_F32) return launch_norm<T, float, MODE>(p, tokens, vec_ok, stream);
+  return set_error(MCOP_ERR_UNSUPPORTED, "norm: weight dtype %d with activation dtype %d", wdtype, dtype);
+}
+
+template <int MODE>
+int dispatch_norm(const NormParams& p, int64_t tokens, bool vec_ok, int dtype, int wdtype, cudaStream_t stream) {
+  constexpr bool same_only = (MODE == kQuant || MODE == kFusedAdd);
+  if (same_only) {
+    MCOP_REQUIRE(wdtype == dtype, MCOP_ERR_UNSUPPORTED, "norm: weight dtype must equal the activation dtype");
+    switch (dtype) {
+      case MCOP_BF16: return launch_norm<__nv_bfloat16, __nv_bfloat16, MODE>(p, tokens, vec_ok, stream);
+      case MCOP_F16: return launch_norm<__half, __half, MODE>(p, tokens, vec_ok, stream);
+      case MCOP_F32: return launch_norm<float, float, MODE>(p, tokens, vec_ok, stream);
+    }
+  } else {
+    switch (dtype) {
+      case MCOP_BF16: return dispatch_wt<__nv_bfloat16, MODE>(p, tokens, vec_ok, dtype, wdtype, stream);
+      case MCOP_F16: return dispatch_wt<__half, MODE>(p, tokens, vec_ok, dtype, wdtype, stream);
+      case MCOP_F32: return dispatch_wt<float, MODE>(p, tokens, vec_ok, dtype, wdtype, stream);
+    }
+  }
+  return set_error(MCOP_ERR_UNSUPPORTED, "norm: unknown dtype code %d", dtype);
+}
+
+inline int elem_size(int dtype) { return dtype == MCOP_F32 ? 4 : 2; }
+
+bool rows_vectorisable(int64_t hidden, int dtype, int wdtype, const void* x, int64_t x_stride,
+                       std::initializer_list<const void*> contiguous_t, std::initializer_list<const void*> w_ptrs,
+                       const void* q) {
+  if (hidden % 8) return false;
+  if (!aligned16(x) || (x_stride * elem_size(dtype)) % 16) return false;
+  for (const void* p : contiguous_t) if (p && !aligned16(p)) return false;
+  for (const void* p : w_ptrs) if (p && !aligned16(p)) return false;
+  if (q && (reinterpret_cast<uintptr_t>(q) & 7u)) return false;
+  (void)wdtype;
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// head_rms_norm: one warp per (token, head); divide-by-rsqrt convention.
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename WT>
+__global__ void head_rmsnorm_kernel(T* out, const T* x, const WT* w, int64_t tokens, int heads, int head_dim,
+                                    float eps, int head_offset, int head_norm) {
+  const int warps = blockDim.x >> 5;
+  const int64_t item = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5);
+  if (item >= tokens * head_norm) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = item / head_norm;
+  const int h = head_offset + (int)(item % head_norm);
+  const T* src = x + (t * heads + h) * (int64_t)head_dim;
+  T* dst = out + (t * heads + h) * (int64_t)head_dim;
+  const WT* wh = w + (int64_t)h * head_dim;
+  float ss = 0.f;
+  for (int i = lane; i < head_dim; i += 32) {
+    const float v = ElemTraits<T>::to_float(src[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = inv_rms(ss, head_dim, eps);
+  for (int i = lane; i < head_dim; i += 32)
+    dst[i] = ElemTraits<T>::from_float(ElemTraits<T>::to_float(src[i]) / r * ElemTraits<WT>::to_float(wh[i]));
+}
+
+// ---------------------------------------------------------------------------------------------
+// scale_dynamic_quant: y = x * smooth; scale = max|y| / 127; q = rne(y / scale).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) scale_quant_kernel(int8_t* q, float* scales, const T* x, const float* smooth, int hidden) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * (int64_t)hidden;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    amax = fmaxf(amax, fabsf(ElemTraits<T>::to_float(xr[i]) * smooth[i]));
+  amax = block_reduce<true>(amax, red);
+  const float scale = amax / 127.0f;
+  if (threadIdx.x == 0) scales[row] = scale;
+  int8_t* qr = q + row * (int64_t)hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    qr[i] = (int8_t)q_rn_clamp(ElemTraits<T>::to_float(xr[i]) * smooth[i] / scale, -128, 127);
+}
+
+}  // namespace
+}  // namespace mcop
+
+using namespace mcop;
+
+extern "C" int mcop_fused_add_rmsnorm(void* x, int64_t x_row_stride, void* residual, const void* weight,
+                                      int64_t tokens, int64_t hidden, float eps, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(x && residual && weight, MCOP_ERR_ARGUMENT, "fused_add_rmsnorm: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && hidden > 0 && hidden <= 0x7fffffff && x_row_stride >= hidden, MCOP_ERR_ARGUMENT,
+               "fused_add_rmsnorm: bad sizes tokens=%lld hidden=%lld stride=%lld", (long long)tokens, (long long)hidden, (long long)x_row_stride);
+  NormParams p{};
+  p.x = x; p.x_stride = x_row_stride; p.weight = weight; p.residual_in = residual; p.residual_out = residual;
+  p.out = x; p.out_stride = x_row_stride; p.hidden = (int)hidden; p.eps = eps;
+  const bool vec = rows_vectorisable(hidden, dtype, dtype, x, x_row_stride, {residual}, {weight}, nullptr);
+  return dispatch_norm<kFusedAdd>(p, tokens, vec, dtype, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_add_rmsnorm_quant_i8(int8_t* out, float* scales, const void* x, int64_t x_row_stride,
+                                         const void* weight, void* residual, const float* scale_ub,
+                                         int64_t tokens, int64_t hidden, float eps, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(out && scales && x && weight, MCOP_ERR_ARGUMENT, "add_rmsnorm_quant_i8: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && hidden > 0 && hidden <= 0x7fffffff && x_row_stride >= hidden, MCOP_ERR_ARGUMENT,
+               "add_rmsnorm_quant_i8: bad sizes tokens=%lld hidden=%lld stride=%lld", (long long)tokens, (long long)hidden, (long long)x_row_stride);
+  NormParams p{};
+  p.x = x; p.x_stride = x_row_stride; p.weight = weight; p.residual_in = residual; p.residual_out = residual;
+  p.q = out; p.scales = scales; p.scale_ub = scale_ub; p.hidden = (int)hidden; p.eps = eps;
+  const bool vec = rows_vectorisable(hidden, dtype, dtype, x, x_row_stride, {residual}, {weight}, out);
+  return dispatch_norm<kQuant>(p, tokens, vec, dtype, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_rmsnorm_smooth_quant_i8(int8_t* out, float* scales, void* after_res, void* after_norm,
+                                            const void* x, const void* weight, const void* smooth, const void* residual,
+                                            int64_t tokens, int64_t hidden, float eps, int dtype, int wdtype,
+                                            mcop_stream_t stream) {
+  MCOP_REQUIRE(out && scales && after_res && after_norm && x && weight && smooth, MCOP_ERR_ARGUMENT,
+               "rmsnorm_smooth_quant_i8: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && hidden > 0 && hidden <= 0x7fffffff, MCOP_ERR_ARGUMENT, "rmsnorm_smooth_quant_i8: bad sizes");
+  NormParams p{};
+  p.x = x; p.x_stride = hidden; p.weight = weight; p.smooth = smooth; p.residual_in = residual; p.residual_out = after_res;
+  p.out = after_norm; p.out_stride = hidden; p.q = out; p.scales = scales; p.hidden = (int)hidden; p.eps = eps;
+  const bool vec = rows_vectorisable(hidden, dtype, wdtype, x, hidden, {residual, after_res, after_norm}, {weight, smooth}, out) &&
+                   (wdtype != MCOP_F32 || dtype == MCOP_F32 || hidden % 8 == 0);
+  return dispatch_norm<kSmoothQuant>(p, tokens, vec, dtype, wdtype, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_rmsnorm(void* out, const void* x, const void* weight, void* after_res, const void* residual,
+                            int64_t tokens, int64_t hidden, float eps, int rms_div, int dtype, int wdtype,
+                            mcop_stream_t stream) {
+  MCOP_REQUIRE(out && x && weight, MCOP_ERR_ARGUMENT, "rmsnorm: null pointer");
+  MCOP_REQUIRE((after_res == nullptr) == (residual == nullptr), MCOP_ERR_ARGUMENT,
+               "rmsnorm: residual and after_res must be given together");
+  MCOP_REQUIRE(tokens >= 0 && hidden > 0 && hidden <= 0x7fffffff, MCOP_ERR_ARGUMENT, "rmsnorm: bad sizes");
+  NormParams p{};
+  p.x = x; p.x_stride = hidden; p.weight = weight; p.residual_in = residual; p.residual_out = after_res;
+  p.out = out; p.out_stride = hidden; p.hidden = (int)hidden; p.eps = eps; p.rms_div = rms_div;
+  const bool vec = rows_vectorisable(hidden, dtype, wdtype, x, hidden, {residual, after_res, out}, {weight}, nullptr);
+  return dispatch_norm<kPlain>(p, tokens, vec, dtype, wdtype, (cudaStream_t)stream);
+}
+
+template <typename T>
+static int head_rmsnorm_wt(void* out, const void* x, const void* weight, int64_t tokens, int64_t heads, int64_t head_dim,
+                           float eps, int head_offset, int head_norm, int dtype, int wdtype, cudaStream_t stream) {
+  const int64_t items = tokens * head_norm;
+  if (items == 0) return MCOP_OK;
+  const int warps = 8;
+  const int64_t blocks = (items + warps - 1) / warps;
+  MCOP_REQUIRE(blocks <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "head_rmsnorm: too many rows");
+  if (wdtype == dtype)
+    head_rmsnorm_kernel<T, T><<<(unsigned)blocks, warps * 32, 0, stream>>>((T*)out, (const T*)x, (const T*)weight, tokens,
+                                                                           (int)heads, (int)head_dim, eps, head_offset, head_norm);
+  else if (wdtype == MCOP_F32)
+    head_rmsnorm_kernel<T, float><<<(unsigned)blocks, warps * 32, 0, stream>>>((T*)out, (const T*)x, (const float*)weight, tokens,
+                                                                               (int)heads, (int)head_dim, eps, head_offset, head_norm);
+  else
+    return set_error(MCOP_ERR_UNSUPPORTED, "head_rmsnorm: weight dtype %d with activation dtype %d", wdtype, dtype);
+  return check_launch("head_rmsnorm");
+}
+
+extern "C" int mcop_head_rmsnorm(void* out, const void* x, const void* weight, int64_t tokens, int64_t heads,
+                                 int64_t head_dim, float eps, int head_offset, int head_norm, int dtype, int wdtype,
+                                 mcop_stream_t stream) {
+  MCOP_REQUIRE(out && x && weight, MCOP_ERR_ARGUMENT, "head_rmsnorm: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && heads > 0 && head_dim > 0 && head_offset >= 0 && head_norm >= 0 &&
+                   (int64_t)head_offset + head_norm <= heads,
+               MCOP_ERR_ARGUMENT, "head_rmsnorm: bad sizes");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case MCOP_BF16: return head_rmsnorm_wt<__nv_bfloat16>(out, x, weight, tokens, heads, head_dim, eps, head_offset, head_norm, dtype, wdtype, s);
+    case MCOP_F16: return head_rmsnorm_wt<__half>(out, x, weight, tokens, heads, head_dim, eps, head_offset, head_norm, dtype, wdtype, s);
+    case MCOP_F32: return head_rmsnorm_wt<float>(out, x, weight, tokens, heads, head_dim, eps, head_offset, head_norm, dtype, wdtype, s);
+  }
+  return set_error(MCOP_ERR_UNSUPPORTED, "head_rmsnorm: unknown dtype code %d", dtype);
+}
+
+extern "C" int mcop_scale_dynamic_quant_i8(int8_t* out, float* scales, const void* x, const float* smooth,
+                                           int64_t tokens, int64_t hidden, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(out && scales && x && smooth, MCOP_ERR_ARGUMENT, "scale_dynamic_quant_i8: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && tokens <= 0x7fffffffLL && hidden > 0 && hidden <= 0x7fffffff, MCOP_ERR_ARGUMENT,
+               "scale_dynamic_quant_i8: bad sizes");
+  if (tokens == 0) return MCOP_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case MCOP_BF16: scale_quant_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __nv_bfloat16*)x, smooth, (int)hidden); break;
+    case MCOP_F16: scale_quant_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __half*)x, smooth, (int)hidden); break;
+    case MCOP_F32: scale_quant_kernel<float><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const float*)x, smooth, (int)hidden); break;
+    default: return set_error(MCOP_ERR_UNSUPPORTED, "scale_dynamic_quant_i8: unknown dtype code %d", dtype);
+  }
+  return check_launch("scale_dynamic_quant_i8");
+}

@@ -1,0 +1,409 @@
+// Part 2 of the hot path: rotary embedding on Q/K and the int8 KV-cache store.
+//
+// One CTA per token.  A "slice" is 8 consecutive elements of the first half of a head together with
+// the 8 paired elements of the second half (NeoX pairs i, i + rot/2), so both accesses are 16-byte
+// vectors and the cos/sin values a thread needs are the same for every head it touches: they are loaded
+// once per token into registers.  With the fused store, the thread that rotated a K slice also
+// quantises it (the bf16-ROUNDED rotated value) into the paged int8 cache, and V slices are read once
+// and written once as int8: K and V never make a second trip through HBM.
+#include "common.cuh"
+
+namespace mcop {
+namespace {
+
+struct RopeParams {
+  // sources / destinations of the rotated heads
+  const void* q_src; void* q_dst; int64_t q_stride;   // token stride, elements
+  const void* k_src; void* k_dst; int64_t k_stride;
+  int64_t head_stride;
+  int num_heads, num_kv_heads, head_size, rot_dim;
+  // cos / sin rows
+  const void* cos; const void* sin; int64_t cs_row_stride;  // elements of the table type
+  // positions: explicit, or derived from packed sequence bounds
+  const int64_t* positions;
+  const int32_t* accum_q_lens; const int32_t* cache_lens; int batch;
+  // fused int8 paged store (nullable)
+  const void* v_src; int64_t v_stride;
+  int8_t* k_cache; int8_t* v_cache;
+  const int64_t* slot_mapping; const float* k_scale; const float* v_scale;
+  int block_size; int64_t num_slots;
+};
+
+__device__ __forceinline__ int64_t token_position(const RopeParams& p, int64_t t) {
+  if (p.positions) return p.positions[t];
+  if (!p.accum_q_lens) return t;
+  // first sequence b with accum[b+1] > t
+  int lo = 0, hi = p.batch - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (p.accum_q_lens[mid + 1] > t) hi = mid; else lo = mid + 1;
+  }
+  return (int64_t)p.cache_lens[lo] + (t - p.accum_q_lens[lo]);
+}
+
+// PER_OP: arithmetic in T (a rounding after every product and after the sum); else fp32 with one rounding.
+template <typename T, bool PER_OP>
+__device__ __forceinline__ void rotate8(const float (&x)[8], const float (&y)[8], const float (&c)[8],
+                                        const float (&s)[8], float (&xo)[8], float (&yo)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (PER_OP) {
+      xo[j] = round_to<T>(__fsub_rn(round_to<T>(__fmul_rn(x[j], c[j])), round_to<T>(__fmul_rn(y[j], s[j]))));
+      yo[j] = round_to<T>(__fadd_rn(round_to<T>(__fmul_rn(y[j], c[j])), round_to<T>(__fmul_rn(x[j], s[j]))));
+    } else {
+      xo[j] = round_to<T>(__fsub_rn(__fmul_rn(x[j], c[j]), __fmul_rn(y[j], s[j])));
+      yo[j] = round_to<T>(__fadd_rn(__fmul_rn(y[j], c[j]), __fmul_rn(x[j], s[j])));
+    }
+  }
+}
+
+__device__ __forceinline__ uint2 quant8(const float (&v)[8], float inv) {
+  int c[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(__fmul_rn(v[j], inv), -127, 127);
+  return pack_i8x8(c);
+}
+
+// NeoX, rot_dim == head_size, head_size % 16 == 0, all rows 16-byte aligned.
+template <typename T, typename CT, bool PER_OP, bool STORE>
+__global__ void __launch_bounds__(256) rope_neox_vec(RopeParams p) {
+  const int64_t t = blockIdx.x;
+  const int half = p.rot_dim >> 1;
+  const int hv = half >> 3;                 // slices per head
+  const int j = threadIdx.x % hv;           // slice index: constant per thread (blockDim % hv == 0)
+  const int64_t pos = token_position(p, t);
+  float c[8], s[8];
+  Vec8<CT>::load_nc(reinterpret_cast<const CT*>(p.cos) + pos * p.cs_row_stride + j * 8, c);
+  Vec8<CT>::load_nc(reinterpret_cast<const CT*>(p.sin) + pos * p.cs_row_stride + j * 8, s);
+
+  int64_t slot = -1;
+  if (STORE) {
+    slot = p.slot_mapping[t];
+    if (slot >= p.num_slots) slot = -1;     // out-of-range slots are skipped like negative ones
+  }
+  const int heads_per_iter = blockDim.x / hv;
+  const int nqk = p.num_heads + p.num_kv_heads;
+  for (int h = threadIdx.x / hv; h < nqk; h += heads_per_iter) {
+    const bool is_k = h >= p.num_heads;
+    const int hh = is_k ? h - p.num_heads : h;
+    const T* src = (is_k ? reinterpret_cast<const T*>(p.k_src) + t * p.k_stride
+                         : reinterpret_cast<const T*>(p.q_src) + t * p.q_stride) + hh * p.head_stride;
+    T* dst = (is_k ? reinterpret_cast<T*>(p.k_dst) + t * p.k_stride
+                   : reinterpret_cast<T*>(p.q_dst) + t * p.q_stride) + hh * p.head_stride;
+    float x[8], y[8], xo[8], yo[8];
+    Vec8<T>::load(src + j * 8, x);
+    Vec8<T>::load(src + half + j * 8, y);
+    rotate8<T, PER_OP>(x, y, c, s, xo, yo);
+    Vec8<T>::store(dst + j * 8, xo);
+    Vec8<T>::store(dst + half + j * 8, yo);
+    if (STORE && is_k && slot >= 0) {
+      const float inv = 1.0f / p.k_scale[hh];
+      int8_t* kc = p.k_cache + (slot * p.num_kv_heads + hh) * (int64_t)p.head_size;
+      st_cs_u2(kc + j * 8, quant8(xo, inv));
+      st_cs_u2(kc + half + j * 8, quant8(yo, inv));
+    }
+  }
+  if (STORE && slot >= 0) {
+    // V: 16 consecutive elements per thread -> one 16-byte int8 store
+    const int vper = p.head_size >> 4;
+    const int nitems = p.num_kv_heads * vper;
+    for (int it = threadIdx.x; it < nitems; it += blockDim.x) {
+      const int hh = it / vper, e = (it % vper) * 16;
+      const T* src = reinterpret_cast<const T*>(p.v_src) + t * p.v_stride + hh * (int64_t)p.head_size + e;
+      float a[8], b[8];
+      Vec8<T>::load_nc(src, a);
+      Vec8<T>::load_nc(src + 8, b);
+      const float inv = 1.0f / p.v_scale[hh];
+      const uint2 qa = quant8(a, inv), qb = quant8(b, inv);
+      st_cs_u4(p.v_cache + (slot * p.num_kv_heads + hh) * (int64_t)p.head_size + e, make_uint4(qa.x, qa.y, qb.x, qb.y));
+    }
+  }
+}
+
+// Any rot_dim <= head_size, NeoX or GPT-J pairing, any alignment.  One thread per rotated pair.
+template <typename T, typename CT, bool PER_OP, bool STORE>
+__global__ void __launch_bounds__(256) rope_any(RopeParams p, int is_neox) {
+  const int64_t t = blockIdx.x;
+  const int half = p.rot_dim >> 1;
+  const int64_t pos = token_position(p, t);
+  const CT* cr = reinterpret_cast<const CT*>(p.cos) + pos * p.cs_row_stride;
+  const CT* sr = reinterpret_cast<const CT*>(p.sin) + pos * p.cs_row_stride;
+  int64_t slot = -1;
+  if (STORE) {
+    slot = p.slot_mapping[t];
+    if (slot >= p.num_slots) slot = -1;
+  }
+  const int nqk = p.num_heads + p.num_kv_heads;
+  for (int i = threadIdx.x; i < nqk * half; i += blockDim.x) {
+    const int h = i / half, r = i % half;
+    const bool is_k = h >= p.num_heads;
+    const int hh = is_k ? h - p.num_heads : h;
+    const T* src = (is_k ? reinterpret_cast<const T*>(p.k_src) + t * p.k_stride
+                         : reinterpret_cast<const T*>(p.q_src) + t * p.q_stride) + hh * p.head_stride;
+    T* dst = (is_k ? reinterpret_cast<T*>(p.k_dst) + t * p.k_stride
+                   : reinterpret_cast<T*>(p.q_dst) + t * p.q_stride) + hh * p.head_stride;
+    const int xi = is_neox ? r : 2 * r, yi = is_neox ? half + r : 2 * r + 1;
+    const float x = ElemTraits<T>::to_float(src[xi]), y = ElemTraits<T>::to_float(src[yi]);
+    const float c = ElemTraits<CT>::to_float(cr[r]), s = ElemTraits<CT>::to_float(sr[r]);
+    float xo, yo;
+    if (PER_OP) {
+      xo = round_to<T>(__fsub_rn(round_to<T>(__fmul_rn(x, c)), round_to<T>(__fmul_rn(y, s))));
+      yo = round_to<T>(__fadd_rn(round_to<T>(__fmul_rn(y, c)), round_to<T>(__fmul_rn(x, s))));
+    } else {
+      xo = round_to<T>(__fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s)));
+      yo = round_to<T>(__fadd_rn(__fmul_rn(y, c), __fmul_rn(x, s)));
+    }
+    dst[xi] = ElemTraits<T>::from_float(xo);
+    dst[yi] = ElemTraits<T>::from_float(yo);
+  }
+  if (STORE && slot >= 0) {
+    __syncthreads();  // the rotated K of this token is re-read from global memory below
+    __threadfence_block();
+    const int nkv = p.num_kv_heads * p.head_size;
+    for (int i = threadIdx.x; i < nkv; i += blockDim.x) {
+      const int hh = i / p.head_size, e = i % p.head_size;
+      const float kv = ElemTraits<T>::to_float(reinterpret_cast<const T*>(p.k_dst)[t * p.k_stride + hh * p.head_stride + e]);
+      const float vv = ElemTraits<T>::to_float(reinterpret_cast<const T*>(p.v_src)[t * p.v_stride + hh * (int64_t)p.head_size + e]);
+      const int64_t o = (slot * p.num_kv_heads + hh) * (int64_t)p.head_size + e;
+      p.k_cache[o] = (int8_t)q_rn_clamp(__fmul_rn(kv, 1.0f / p.k_scale[hh]), -127, 127);
+      p.v_cache[o] = (int8_t)q_rn_clamp(__fmul_rn(vv, 1.0f / p.v_scale[hh]), -127, 127);
+    }
+  }
+}
+
+inline int esize(int dtype) { return dtype == MCOP_F32 ? 4 : 2; }
+
+template <typename T, typename CT, bool PER_OP, bool STORE>
+int launch_rope_t(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok, cudaStream_t stream) {
+  if (tokens == 0) return MCOP_OK;
+  MCOP_REQUIRE(tokens <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "rope: %lld tokens exceed the grid limit", (long long)tokens);
+  if (vec_ok) {
+    const int hv = p.rot_dim >> 4;
+    const int threads = hv * (256 / hv > 0 ? 256 / hv : 1);
+    rope_neox_vec<T, CT, PER_OP, STORE><<<(unsigned)tokens, threads, 0, stream>>>(p);
+  } else {
+    rope_any<T, CT, PER_OP, STORE><<<(unsigned)tokens, 256, 0, stream>>>(p, is_neox);
+  }
+  return check_launch("rope");
+}
+
+// cache_dtype == dtype -> arithmetic in T unless force_fp32_math; cache fp32 -> fp32 math.
+template <bool STORE>
+int launch_rope(const RopeParams& p, int64_t tokens, int is_neox, int dtype, int cache_dtype, bool fp32_math,
+                cudaStream_t stream) {
+  const int half = p.rot_dim / 2;
+  bool vec_ok = is_neox && p.rot_dim == p.head_size && (half % 8 == 0) && (p.head_size % 16 == 0) && half / 8 <= 256 &&
+                aligned16(p.q_src) && aligned16(p.q_dst) && (p.q_stride * esize(dtype)) % 16 == 0 &&
+                (p.head_stride * esize(dtype)) % 16 == 0 && aligned16(p.cos) && aligned16(p.sin) &&
+                (p.cs_row_stride * esize(cache_dtype)) % 16 == 0;
+  if (p.k_src) vec_ok = vec_ok && aligned16(p.k_src) && aligned16(p.k_dst) && (p.k_stride * esize(dtype)) % 16 == 0;
+  if (STORE) vec_ok = vec_ok && aligned16(p.v_src) && (p.v_stride * esize(dtype)) % 16 == 0 && aligned16(p.k_cache) && aligned16(p.v_cache);
+#define MCOP_ROPE_CASE(T, CT, PER)  return launch_rope_t<T, CT, PER, STORE>(p, tokens, is_neox, vec_ok, stream)
+  if (cache_dtype == MCOP_F32) {
+    if (dtype == MCOP_BF16) MCOP_ROPE_CASE(__nv_bfloat16, float, false);
+    if (dtype == MCOP_F16) MCOP_ROPE_CASE(__half, float, false);
+    if (dtype == MCOP_F32) MCOP_ROPE_CASE(float, float, false);
+  } else if (cache_dtype == dtype) {
+    if (fp32_math) {
+      if (dtype == MCOP_BF16) MCOP_ROPE_CASE(__nv_bfloat16, __nv_bfloat16, false);
+      if (dtype == MCOP_F16) MCOP_ROPE_CASE(__half, __half, false);
+    } else {
+      if (dtype == MCOP_BF16) MCOP_ROPE_CASE(__nv_bfloat16, __nv_bfloat16, true);
+      if (dtype == MCOP_F16) MCOP_ROPE_CASE(__half, __half, true);
+    }
+  }
+#undef MCOP_ROPE_CASE
+  return set_error(MCOP_ERR_UNSUPPORTED, "rope: activation dtype %d with cos/sin dtype %d", dtype, cache_dtype);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Unpaged int8 store with per-(head, dim) multipliers (store_kv_cache_cuda_interface).
+// ---------------------------------------------------------------------------------------------
+struct KvStoreParams {
+  const void* qkv; int64_t stride_token, stride_head;
+  const int32_t* q_lens; const int32_t* accum; const int32_t* cache_lens; const int32_t* slot_ids;
+  int8_t* k_cache; int8_t* v_cache;
+  int64_t ks_slot, ks_head, ks_pos, vs_slot, vs_head, vs_pos;
+  const float* k_scale; const float* v_scale;
+  int batch, q_heads, kv_heads, head_dim;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) kv_store_kernel(KvStoreParams p) {
+  const int64_t t = blockIdx.x;
+  int lo = 0, hi = p.batch - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (p.accum[mid + 1] > t) hi = mid; else lo = mid + 1;
+  }
+  const int b = lo;
+  const int64_t i = t - p.accum[b];
+  if (i < 0 || i >= p.q_lens[b]) return;   // token outside every sequence
+  const int64_t pos = (int64_t)p.cache_lens[b] + i;
+  const int64_t slot = p.slot_ids[b];
+  const T* tok = reinterpret_cast<const T*>(p.qkv) + t * p.stride_token;
+  const int n = p.kv_heads * p.head_dim;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const int h = e / p.head_dim, d = e % p.head_dim;
+    const float kv = ElemTraits<T>::to_float(tok[(p.q_heads + h) * p.stride_head + d]);
+    const float vv = ElemTraits<T>::to_float(tok[(p.q_heads + p.kv_heads + h) * p.stride_head + d]);
+    p.k_cache[slot * p.ks_slot + h * p.ks_head + pos * p.ks_pos + d] =
+        (int8_t)q_rn_clamp(__fmul_rn(kv, p.k_scale[h * p.head_dim + d]), -127, 127);
+    p.v_cache[slot * p.vs_slot + h * p.vs_head + pos * p.vs_pos + d] =
+        (int8_t)q_rn_clamp(__fmul_rn(vv, p.v_scale[h * p.head_dim + d]), -127, 127);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Paged copy (reshape_and_cache_flash / reshape_and_cache with kv_cache_dtype "auto").
+// ---------------------------------------------------------------------------------------------
+struct CacheCopyParams {
+  const char* key; const char* value; int64_t key_stride, value_stride;   // bytes
+  char* key_cache; char* value_cache; int64_t block_stride, page_stride, head_stride;  // bytes
+  const int64_t* slot_mapping; int kv_heads, head_bytes, block_size;
+};
+
+template <typename V>
+__global__ void __launch_bounds__(256) cache_copy_kernel(CacheCopyParams p) {
+  const int64_t t = blockIdx.x;
+  const int64_t slot = p.slot_mapping[t];
+  if (slot < 0) return;
+  const int64_t blk = slot / p.block_size, off = slot % p.block_size;
+  const int per_head = p.head_bytes / (int)sizeof(V);
+  const int n = p.kv_heads * per_head;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int h = i / per_head, e = i % per_head;
+    const int64_t dst = blk * p.block_stride + off * p.page_stride + h * p.head_stride + (int64_t)e * sizeof(V);
+    const int64_t src = (int64_t)h * p.head_bytes + (int64_t)e * sizeof(V);
+    *reinterpret_cast<V*>(p.key_cache + dst) = *reinterpret_cast<const V*>(p.key + t * p.key_stride + src);
+    *reinterpret_cast<V*>(p.value_cache + dst) = *reinterpret_cast<const V*>(p.value + t * p.value_stride + src);
+  }
+}
+
+}  // namespace
+}  // namespace mcop
+
+using namespace mcop;
+
+extern "C" int mcop_rope_inplace(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
+                                 int cache_dtype, int64_t tokens, int num_heads, int num_kv_heads, int head_size,
+                                 int rot_dim, int64_t query_stride, int64_t key_stride, int64_t head_stride,
+                                 int is_neox, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(positions && query && cos_sin_cache, MCOP_ERR_ARGUMENT, "rope_inplace: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && num_heads > 0 && num_kv_heads >= 0 && head_size > 0 && rot_dim > 0 && rot_dim % 2 == 0 &&
+                   rot_dim <= head_size, MCOP_ERR_ARGUMENT, "rope_inplace: bad sizes");
+  RopeParams p{};
+  p.q_src = query; p.q_dst = query; p.q_stride = query_stride;
+  p.k_src = key; p.k_dst = key; p.k_stride = key_stride; p.head_stride = head_stride;
+  p.num_heads = num_heads; p.num_kv_heads = key ? num_kv_heads : 0; p.head_size = head_size; p.rot_dim = rot_dim;
+  const int cs = cache_dtype == MCOP_F32 ? 4 : 2;
+  p.cos = cos_sin_cache; p.sin = reinterpret_cast<const char*>(cos_sin_cache) + (size_t)(rot_dim / 2) * cs;
+  p.cs_row_stride = rot_dim; p.positions = positions;
+  return launch_rope<false>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, const float* sin,
+                                const int32_t* accum_q_lens, const int32_t* cache_lens, int batch, int64_t tokens,
+                                int q_heads, int kv_heads, int head_dim, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(packed_qkv && output && cos && sin && accum_q_lens && cache_lens, MCOP_ERR_ARGUMENT, "rope_packed: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && batch > 0 && q_heads > 0 && kv_heads >= 0 && head_dim > 0 && head_dim % 2 == 0,
+               MCOP_ERR_ARGUMENT, "rope_packed: bad sizes");
+  const int64_t tok_stride = (int64_t)(q_heads + 2 * kv_heads) * head_dim;
+  const int es = dtype == MCOP_F32 ? 4 : 2;
+  RopeParams p{};
+  p.q_src = packed_qkv; p.q_dst = output; p.q_stride = tok_stride;
+  p.k_src = reinterpret_cast<const char*>(packed_qkv) + (size_t)q_heads * head_dim * es;
+  p.k_dst = reinterpret_cast<char*>(output) + (size_t)q_heads * head_dim * es;
+  p.k_stride = tok_stride; p.head_stride = head_dim;
+  p.num_heads = q_heads; p.num_kv_heads = kv_heads; p.head_size = head_dim; p.rot_dim = head_dim;
+  p.cos = cos; p.sin = sin; p.cs_row_stride = head_dim / 2;
+  p.accum_q_lens = accum_q_lens; p.cache_lens = cache_lens; p.batch = batch;
+  return launch_rope<false>(p, tokens, 1, dtype, MCOP_F32, true, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
+                                   int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(qkv && cos && sin, MCOP_ERR_ARGUMENT, "fused_rope_fwd: null pointer");
+  MCOP_REQUIRE(seq >= 0 && planes >= 2 && heads > 0 && head_dim > 0 && head_dim % 2 == 0, MCOP_ERR_ARGUMENT, "fused_rope_fwd: bad sizes");
+  MCOP_REQUIRE(dtype == MCOP_BF16 || dtype == MCOP_F16, MCOP_ERR_UNSUPPORTED, "fused_rope_fwd: only f16 and bf16");
+  const int64_t tok_stride = (int64_t)planes * heads * head_dim;
+  RopeParams p{};
+  p.q_src = qkv; p.q_dst = qkv; p.q_stride = tok_stride;
+  p.k_src = reinterpret_cast<char*>(qkv) + (size_t)heads * head_dim * 2;
+  p.k_dst = reinterpret_cast<char*>(qkv) + (size_t)heads * head_dim * 2;
+  p.k_stride = tok_stride; p.head_stride = head_dim;
+  p.num_heads = heads; p.num_kv_heads = heads; p.head_size = head_dim; p.rot_dim = head_dim;
+  p.cos = cos; p.sin = sin; p.cs_row_stride = head_dim / 2; p.positions = indexes;
+  return launch_rope<false>(p, seq, 1, dtype, dtype, true, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query, void* key, const void* value,
+                                           const void* cos_sin_cache, int cache_dtype, int8_t* key_cache,
+                                           int8_t* value_cache, const int64_t* slot_mapping, const float* k_scale,
+                                           const float* v_scale, int64_t tokens, int num_heads, int num_kv_heads,
+                                           int head_size, int rot_dim, int64_t query_stride, int64_t key_stride,
+                                           int64_t value_stride, int block_size, int64_t num_blocks, int is_neox,
+                                           int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(positions && query && key && value && cos_sin_cache && key_cache && value_cache && slot_mapping && k_scale && v_scale,
+               MCOP_ERR_ARGUMENT, "rope_kv_store_i8_paged: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && head_size > 0 && rot_dim > 0 && rot_dim % 2 == 0 &&
+                   rot_dim <= head_size && block_size > 0 && num_blocks >= 0,
+               MCOP_ERR_ARGUMENT, "rope_kv_store_i8_paged: bad sizes");
+  RopeParams p{};
+  p.q_src = query; p.q_dst = query; p.q_stride = query_stride;
+  p.k_src = key; p.k_dst = key; p.k_stride = key_stride; p.head_stride = head_size;
+  p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_size = head_size; p.rot_dim = rot_dim;
+  const int cs = cache_dtype == MCOP_F32 ? 4 : 2;
+  p.cos = cos_sin_cache; p.sin = reinterpret_cast<const char*>(cos_sin_cache) + (size_t)(rot_dim / 2) * cs;
+  p.cs_row_stride = rot_dim; p.positions = positions;
+  p.v_src = value; p.v_stride = value_stride; p.k_cache = key_cache; p.v_cache = value_cache;
+  p.slot_mapping = slot_mapping; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.block_size = block_size; p.num_slots = num_blocks * block_size;
+  return launch_rope<true>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_kv_store_i8(const void* packed_qkv, int64_t qkv_stride_token, int64_t qkv_stride_head,
+                                const int32_t* q_lens, const int32_t* accum_q_lens, const int32_t* cache_lens,
+                                const int32_t* cache_slot_ids, int8_t* k_cache, int8_t* v_cache,
+                                int64_t k_stride_slot, int64_t k_stride_head, int64_t k_stride_pos,
+                                int64_t v_stride_slot, int64_t v_stride_head, int64_t v_stride_pos,
+                                const float* k_scale, const float* v_scale, int batch, int64_t tokens, int q_heads,
+                                int kv_heads, int head_dim, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(packed_qkv && q_lens && accum_q_lens && cache_lens && cache_slot_ids && k_cache && v_cache && k_scale && v_scale,
+               MCOP_ERR_ARGUMENT, "kv_store_i8: null pointer");
+  MCOP_REQUIRE(batch > 0 && tokens >= 0 && tokens <= 0x7fffffffLL && q_heads >= 0 && kv_heads > 0 && head_dim > 0,
+               MCOP_ERR_ARGUMENT, "kv_store_i8: bad sizes");
+  if (tokens == 0) return MCOP_OK;
+  KvStoreParams p{packed_qkv, qkv_stride_token, qkv_stride_head, q_lens, accum_q_lens, cache_lens, cache_slot_ids,
+                  k_cache, v_cache, k_stride_slot, k_stride_head, k_stride_pos, v_stride_slot, v_stride_head, v_stride_pos,
+                  k_scale, v_scale, batch, q_heads, kv_heads, head_dim};
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == MCOP_BF16) kv_store_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(p);
+  else if (dtype == MCOP_F16) kv_store_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(p);
+  else return set_error(MCOP_ERR_UNSUPPORTED, "kv_store_i8: only f16 and bf16");
+  return check_launch("kv_store_i8");
+}
+
+extern "C" int mcop_reshape_and_cache_flash(const void* key, const void* value, int64_t key_stride, int64_t value_stride,
+                                            void* key_cache, void* value_cache, int64_t block_stride, int64_t page_stride,
+                                            int64_t head_stride, const int64_t* slot_mapping, int64_t tokens,
+                                            int kv_heads, int head_size, int block_size, int elem_bytes,
+                                            mcop_stream_t stream) {
+  MCOP_REQUIRE(key && value && key_cache && value_cache && slot_mapping, MCOP_ERR_ARGUMENT, "reshape_and_cache_flash: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && tokens <= 0x7fffffffLL && kv_heads > 0 && head_size > 0 && block_size > 0 &&
+                   (elem_bytes == 1 || elem_bytes == 2 || elem_bytes == 4),
+               MCOP_ERR_ARGUMENT, "reshape_and_cache_flash: bad sizes");
+  if (tokens == 0) return MCOP_OK;
+  CacheCopyParams p{(const char*)key, (const char*)value, key_stride * elem_bytes, value_stride * elem_bytes,
+                    (char*)key_cache, (char*)value_cache, block_stride * elem_bytes, page_stride * elem_bytes,
+                    head_stride * elem_bytes, slot_mapping, kv_heads, head_size * elem_bytes, block_size};
+  const bool v16 = p.head_bytes % 16 == 0 && aligned16(key) && aligned16(value) && aligned16(key_cache) && aligned16(value_cache) &&
+                   p.key_stride % 16 == 0 && p.value_stride % 16 == 0 && p.block_stride % 16 == 0 && p.page_stride % 16 == 0 &&
+                   p.head_stride % 16 == 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (v16) cache_copy_kernel<uint4><<<(unsigned)tokens, 256, 0, s>>>(p);
+  else if (elem_bytes == 4) cache_copy_kernel<uint32_t><<<(unsigned)tokens, 256, 0, s>>>(p);
+  else if (elem_bytes == 2) cache_copy_kernel<uint16_t><<<(unsigned)tokens, 256, 0, s>>>(p);
+  else cache_copy_kernel<uint8_t><<<(unsigned)tokens, 256, 0, s>>>(p);
+  return check_launch("reshape_and_cache_flash");
+}

@@ -1,0 +1,541 @@
+// Host shims: the operator surface of mcoplib for the hot path, over the mcop_b200 C ABI.
+//
+// Two surfaces are reproduced with the reference's argument order, in-place conventions and checks:
+//   * the pybind11 module `op`  (mcoplib.op, op/pybind.cpp:30-104 of MetaX-MACA/mcoplib);
+//   * torch library operators   (torch.ops._C.* and torch.ops._C_cache_ops.*, op/vllm/torch_bindings.cpp),
+//     registered under the namespaces MCOP_TORCH_NS / MCOP_TORCH_NS_cache_ops (default mcop_C) because the
+//     name `_C` is taken by any vLLM wheel present in the same process.
+// Every function validates its tensors (TORCH_CHECK -> RuntimeError before any launch), takes the current
+// CUDA stream and calls one extern "C" entry point.  No computation happens on the host and there is no
+// fallback: without a CUDA device these functions raise.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+#include <torch/library.h>
+
+#include <optional>
+#include <string>
+#include <tuple>
+
+#include "mcop_b200.h"
+
+#ifndef MCOP_TORCH_NS
+#define MCOP_TORCH_NS mcop_C
+#endif
+#define MCOP_CAT_(a, b) a##b
+#define MCOP_CAT(a, b) MCOP_CAT_(a, b)
+#define MCOP_TORCH_NS_CACHE MCOP_CAT(MCOP_TORCH_NS, _cache_ops)
+
+namespace {
+
+using at::Tensor;
+
+int dtype_code(const Tensor& t, const char* what) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return MCOP_F32;
+    case at::kBFloat16: return MCOP_BF16;
+    case at::kHalf: return MCOP_F16;
+    default: TORCH_CHECK(false, what, ": unsupported dtype ", t.scalar_type());
+  }
+}
+
+void check_rc(int rc) { TORCH_CHECK(rc == MCOP_OK, "mcop_b200: ", mcop_last_error()); }
+
+void check_cuda(const Tensor& t, const char* name) { TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor"); }
+
+mcop_stream_t cur_stream() { return reinterpret_cast<mcop_stream_t>(at::cuda::getCurrentCUDAStream().stream()); }
+
+Tensor scratch_bytes(size_t bytes, const Tensor& like) {
+  return at::empty({(int64_t)((bytes + 15) / 16 * 16)}, like.options().dtype(at::kByte));
+}
+
+// ---------------------------------------------------------------- part 1
+
+// torch.ops._C.fused_add_rms_norm (op/vllm/layernorm_kernels.cu:243-292)
+void fused_add_rms_norm(Tensor& input, Tensor& residual, Tensor& weight, double epsilon) {
+  check_cuda(input, "input");
+  TORCH_CHECK(weight.scalar_type() == input.scalar_type());
+  TORCH_CHECK(input.scalar_type() == residual.scalar_type());
+  TORCH_CHECK(residual.is_contiguous());
+  TORCH_CHECK(weight.is_contiguous());
+  const int64_t hidden = input.size(-1);
+  TORCH_CHECK(input.stride(-1) == 1 && input.dim() >= 1);
+  const int64_t tokens = hidden ? input.numel() / hidden : 0;
+  int64_t stride = hidden;
+  if (input.dim() >= 2) {
+    stride = input.stride(-2);
+    // leading dims must collapse onto one row stride
+    Tensor v = input.dim() > 2 ? input.view({-1, hidden}) : input;
+    stride = v.stride(0);
+  }
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_fused_add_rmsnorm(input.data_ptr(), stride, residual.data_ptr(), weight.data_ptr(), tokens, hidden,
+                                  (float)epsilon, dtype_code(input, "fused_add_rms_norm"), cur_stream()));
+}
+
+// torch.ops._C.rms_norm_dynamic_per_token_quant
+// (op/vllm/quantization/fused_kernels/fused_layernorm_dynamic_per_token_quant.cu:163-192) and
+// mcoplib.op.rms_norm_dynamic_per_token_quant_custom (op/rms_norm_dynamic_per_token_quant.cu:266-285)
+void rms_norm_dynamic_per_token_quant_vllm(Tensor& out, const Tensor& input, const Tensor& weight, Tensor& scales,
+                                           double var_epsilon, std::optional<Tensor> scale_ub,
+                                           std::optional<Tensor> residual) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == at::kChar, "only int8 output is built");
+  TORCH_CHECK(out.is_contiguous() && input.is_contiguous());
+  TORCH_CHECK(weight.scalar_type() == input.scalar_type());
+  TORCH_CHECK(scales.scalar_type() == at::kFloat);
+  if (scale_ub.has_value()) TORCH_CHECK(scale_ub->scalar_type() == at::kFloat);
+  if (residual.has_value()) TORCH_CHECK(residual->scalar_type() == input.scalar_type() && residual->is_contiguous());
+  const int64_t hidden = input.size(-1);
+  const int64_t tokens = hidden ? input.numel() / hidden : 0;
+  TORCH_CHECK(scales.numel() >= tokens && scales.is_contiguous(), "scales must hold one fp32 per token");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_add_rmsnorm_quant_i8(out.data_ptr<int8_t>(), scales.data_ptr<float>(), input.data_ptr(), hidden,
+                                     weight.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr,
+                                     scale_ub.has_value() ? scale_ub->data_ptr<float>() : nullptr, tokens, hidden,
+                                     (float)var_epsilon, dtype_code(input, "rms_norm_dynamic_per_token_quant"), cur_stream()));
+}
+
+// mcoplib.op.rms_norm_dynamic_per_token_quant, 9 arguments (op/fused_rms_norm_dq.cu:646-667)
+void rms_norm_dynamic_per_token_quant_9(Tensor& out, const Tensor& input, const Tensor& weight, const Tensor& smooth_scale,
+                                        Tensor& scales, double var_epsilon, Tensor& after_res, Tensor& after_norm,
+                                        std::optional<Tensor> residual) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == at::kChar);
+  TORCH_CHECK(out.is_contiguous() && input.is_contiguous());
+  TORCH_CHECK(scales.scalar_type() == at::kFloat);
+  TORCH_CHECK(weight.scalar_type() == smooth_scale.scalar_type(), "weight and smooth_scale must share a dtype");
+  TORCH_CHECK(weight.scalar_type() == at::kBFloat16 || weight.scalar_type() == at::kFloat, "weight must be bf16 or fp32");
+  TORCH_CHECK(after_res.is_contiguous() && after_norm.is_contiguous() && weight.is_contiguous() && smooth_scale.is_contiguous());
+  TORCH_CHECK(after_res.scalar_type() == input.scalar_type() && after_norm.scalar_type() == input.scalar_type());
+  if (residual.has_value()) TORCH_CHECK(residual->scalar_type() == input.scalar_type() && residual->is_contiguous());
+  const int64_t hidden = input.size(-1);
+  const int64_t tokens = hidden ? input.numel() / hidden : 0;
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_rmsnorm_smooth_quant_i8(out.data_ptr<int8_t>(), scales.data_ptr<float>(), after_res.data_ptr(),
+                                        after_norm.data_ptr(), input.data_ptr(), weight.data_ptr(), smooth_scale.data_ptr(),
+                                        residual.has_value() ? residual->data_ptr() : nullptr, tokens, hidden,
+                                        (float)var_epsilon, dtype_code(input, "rms_norm_dynamic_per_token_quant"),
+                                        dtype_code(weight, "rms_norm_dynamic_per_token_quant weight"), cur_stream()));
+}
+
+// mcoplib.op.rms_norm (op/fused_rms_norm_dq.cu:980-999)
+void rms_norm(Tensor& out, const Tensor& input, const Tensor& weight, double var_epsilon, std::optional<Tensor> after_res,
+              std::optional<Tensor> residual, bool rms_div) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.is_contiguous() && input.is_contiguous() && weight.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == input.scalar_type());
+  TORCH_CHECK(after_res.has_value() == residual.has_value(), "after_res and residual go together");
+  if (residual.has_value())
+    TORCH_CHECK(residual->is_contiguous() && after_res->is_contiguous() && residual->scalar_type() == input.scalar_type() &&
+                after_res->scalar_type() == input.scalar_type());
+  const int64_t hidden = input.size(-1);
+  const int64_t tokens = hidden ? input.numel() / hidden : 0;
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_rmsnorm(out.data_ptr(), input.data_ptr(), weight.data_ptr(), after_res.has_value() ? after_res->data_ptr() : nullptr,
+                        residual.has_value() ? residual->data_ptr() : nullptr, tokens, hidden, (float)var_epsilon, rms_div ? 1 : 0,
+                        dtype_code(input, "rms_norm"), dtype_code(weight, "rms_norm weight"), cur_stream()));
+}
+
+// mcoplib.op.head_rms_norm (op/fused_rms_norm_dq.cu:804-812)
+void head_rms_norm(Tensor& out, const Tensor& hidden_states, const Tensor& weight, double var_epsilon, int head_offset, int head_norm) {
+  check_cuda(hidden_states, "hidden_states");
+  TORCH_CHECK(hidden_states.dim() == 3, "hidden_states must be [tokens, heads, head_dim]");
+  TORCH_CHECK(out.is_contiguous() && hidden_states.is_contiguous() && weight.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == hidden_states.scalar_type());
+  const c10::cuda::OptionalCUDAGuard guard(device_of(hidden_states));
+  check_rc(mcop_head_rmsnorm(out.data_ptr(), hidden_states.data_ptr(), weight.data_ptr(), hidden_states.size(0), hidden_states.size(1),
+                             hidden_states.size(2), (float)var_epsilon, head_offset, head_norm, dtype_code(hidden_states, "head_rms_norm"),
+                             dtype_code(weight, "head_rms_norm weight"), cur_stream()));
+}
+
+// mcoplib.op.scale_dynamic_quant (op/scale_dynamic_quant.cu:127-153): allocates and returns (codes, scales)
+std::tuple<Tensor, Tensor> scale_dynamic_quant(const Tensor& hidden_states, const Tensor& smooth_scales, at::ScalarType dst) {
+  check_cuda(hidden_states, "hidden_states");
+  TORCH_CHECK(dst == at::kChar, "only int8 output is built");
+  TORCH_CHECK(hidden_states.is_contiguous() && smooth_scales.is_contiguous());
+  TORCH_CHECK(smooth_scales.scalar_type() == at::kFloat);
+  const int64_t hidden = hidden_states.size(-1);
+  const int64_t tokens = hidden ? hidden_states.numel() / hidden : 0;
+  const c10::cuda::OptionalCUDAGuard guard(device_of(hidden_states));
+  Tensor q = at::empty(hidden_states.sizes(), hidden_states.options().dtype(at::kChar));
+  Tensor s = at::empty({tokens}, hidden_states.options().dtype(at::kFloat));
+  check_rc(mcop_scale_dynamic_quant_i8(q.data_ptr<int8_t>(), s.data_ptr<float>(), hidden_states.data_ptr(), smooth_scales.data_ptr<float>(),
+                                       tokens, hidden, dtype_code(hidden_states, "scale_dynamic_quant"), cur_stream()));
+  return {q, s};
+}
+
+// ---------------------------------------------------------------- part 2
+
+// torch.ops._C.rotary_embedding (op/vllm/pos_encoding_kernels.cu:135-217); the cos/sin cache may also be fp32
+void rotary_embedding_vllm(Tensor& positions, Tensor& query, std::optional<Tensor> key, int64_t head_size, Tensor& cos_sin_cache,
+                           bool is_neox) {
+  check_cuda(query, "query");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous());
+  const int64_t num_tokens = positions.numel();
+  const int positions_ndim = positions.dim();
+  TORCH_CHECK(positions_ndim == 1 || positions_ndim == 2, "positions must have shape [num_tokens] or [batch_size, seq_len]");
+  if (positions_ndim == 1) {
+    TORCH_CHECK(query.size(0) == positions.size(0) && (!key.has_value() || key->size(0) == positions.size(0)),
+                "query, key and positions must have the same number of tokens");
+  } else {
+    TORCH_CHECK(query.size(0) == positions.size(0) && (!key.has_value() || key->size(0) == positions.size(0)) &&
+                    query.size(1) == positions.size(1) && (!key.has_value() || key->size(1) == positions.size(1)),
+                "query, key and positions must have the same batch_size and seq_len");
+  }
+  const int64_t query_hidden = num_tokens ? query.numel() / num_tokens : 0;
+  const int64_t key_hidden = key.has_value() && num_tokens ? key->numel() / num_tokens : 0;
+  TORCH_CHECK(head_size > 0 && query_hidden % head_size == 0);
+  TORCH_CHECK(key_hidden % head_size == 0);
+  const int num_heads = (int)(query_hidden / head_size);
+  const int num_kv_heads = key.has_value() ? (int)(key_hidden / head_size) : num_heads;
+  TORCH_CHECK(num_kv_heads == 0 || num_heads % num_kv_heads == 0);
+  const int rot_dim = (int)cos_sin_cache.size(1);
+  TORCH_CHECK(cos_sin_cache.is_contiguous());
+  TORCH_CHECK(cos_sin_cache.scalar_type() == query.scalar_type() || cos_sin_cache.scalar_type() == at::kFloat,
+              "cos_sin_cache must have the activation dtype or fp32");
+  const int seq_dim_idx = positions_ndim - 1;
+  const int64_t query_stride = query.stride(seq_dim_idx);
+  const int64_t key_stride = key.has_value() ? key->stride(seq_dim_idx) : 0;
+  const int query_ndim = query.dim();
+  const int64_t head_stride = (query_ndim == positions_ndim + 2) ? query.stride(-2) : head_size;
+  if (key.has_value()) TORCH_CHECK(key->scalar_type() == query.scalar_type());
+  const c10::cuda::OptionalCUDAGuard guard(device_of(query));
+  check_rc(mcop_rope_inplace(positions.data_ptr<int64_t>(), query.data_ptr(), key.has_value() ? key->data_ptr() : nullptr,
+                             cos_sin_cache.data_ptr(), dtype_code(cos_sin_cache, "cos_sin_cache"), num_tokens, num_heads,
+                             num_kv_heads, (int)head_size, rot_dim, query_stride, key_stride, head_stride, is_neox ? 1 : 0,
+                             dtype_code(query, "rotary_embedding"), cur_stream()));
+}
+
+// mcoplib.op.rotary_embedding (op/rotary_embedding.cu:99-121)
+void rotary_embedding_packed(Tensor packed_qkv, Tensor q_len, Tensor accum_q_lens, Tensor cache_lens, Tensor cos, Tensor sin,
+                             Tensor output, int q_head_num, int kv_head_num, int rope_offset) {
+  (void)rope_offset;  // accepted and unused, as in the reference (op/rotary_embedding.cu:68-70)
+  (void)q_len;
+  check_cuda(packed_qkv, "packed_qkv");
+  TORCH_CHECK(packed_qkv.scalar_type() == at::kBFloat16, "Only bfloat16 are supported");
+  TORCH_CHECK(packed_qkv.dim() == 3 && packed_qkv.is_contiguous() && output.is_contiguous());
+  TORCH_CHECK(output.scalar_type() == packed_qkv.scalar_type() && output.sizes() == packed_qkv.sizes());
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat && cos.is_contiguous() && sin.is_contiguous());
+  TORCH_CHECK(accum_q_lens.scalar_type() == at::kInt && cache_lens.scalar_type() == at::kInt);
+  const int64_t tokens = packed_qkv.size(0);
+  const int head_dim = (int)packed_qkv.size(2);
+  TORCH_CHECK(packed_qkv.size(1) == q_head_num + 2 * kv_head_num, "head count mismatch");
+  TORCH_CHECK(cos.size(-1) * 2 == head_dim && sin.size(-1) * 2 == head_dim, "cos/sin must be [max_pos, head_dim/2]");
+  const int batch = (int)cache_lens.numel();
+  TORCH_CHECK(accum_q_lens.numel() >= batch + 1, "accum_q_lens must hold batch+1 entries");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(packed_qkv));
+  check_rc(mcop_rope_packed(packed_qkv.data_ptr(), output.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(),
+                            accum_q_lens.data_ptr<int32_t>(), cache_lens.data_ptr<int32_t>(), batch, tokens, q_head_num, kv_head_num,
+                            head_dim, MCOP_BF16, cur_stream()));
+}
+
+// mcoplib.op.fused_rope_fwd (op/fused_rope.cu:13-74)
+Tensor fused_rope_fwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> indexes, bool force_bf16_attn) {
+  check_cuda(qkv, "qkv"); check_cuda(cos, "cos"); check_cuda(sin, "sin");
+  TORCH_CHECK(qkv.is_contiguous() && cos.is_contiguous() && sin.is_contiguous());
+  if (indexes.has_value()) {
+    check_cuda(*indexes, "indexes");
+    TORCH_CHECK(indexes->is_contiguous() && indexes->scalar_type() == at::kLong);
+  }
+  TORCH_CHECK(qkv.dim() == 4, "qkv must be [seq, 3, heads, head_dim]");
+  TORCH_CHECK(qkv.scalar_type() == at::kHalf || qkv.scalar_type() == at::kBFloat16, "Only float16 and bfloat16 are supported");
+  TORCH_CHECK(!(force_bf16_attn && qkv.scalar_type() == at::kHalf), "the half -> bf16 reinterpreting output is not built");
+  TORCH_CHECK(cos.scalar_type() == qkv.scalar_type() && sin.scalar_type() == qkv.scalar_type());
+  TORCH_CHECK(cos.size(-1) * 2 == qkv.size(3));
+  const c10::cuda::OptionalCUDAGuard guard(device_of(qkv));
+  check_rc(mcop_fused_rope_fwd(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), indexes.has_value() ? indexes->data_ptr<int64_t>() : nullptr,
+                               qkv.size(0), (int)qkv.size(1), (int)qkv.size(2), (int)qkv.size(3), dtype_code(qkv, "fused_rope_fwd"), cur_stream()));
+  return qkv;
+}
+
+// mcoplib.op.store_kv_cache_cuda_interface (op/store_kv.cu:220-350)
+void store_kv_cache_cuda_interface(Tensor packed_qkv, Tensor q_lens, Tensor accum_q_lens, Tensor cache_lens, Tensor cache_slot_ids,
+                                   Tensor& k_cache, Tensor& v_cache, Tensor k_scale, Tensor v_scale, int batch_size, int q_head_num,
+                                   int kv_head_num) {
+  check_cuda(packed_qkv, "packed_qkv"); check_cuda(q_lens, "q_lens"); check_cuda(accum_q_lens, "accum_q_lens");
+  check_cuda(cache_lens, "cache_lens"); check_cuda(cache_slot_ids, "cache_slot_ids"); check_cuda(k_cache, "k_cache");
+  check_cuda(v_cache, "v_cache"); check_cuda(k_scale, "k_scale"); check_cuda(v_scale, "v_scale");
+  TORCH_CHECK(packed_qkv.scalar_type() == at::kHalf || packed_qkv.scalar_type() == at::kBFloat16, "Only float16, bfloat16 are supported");
+  TORCH_CHECK(packed_qkv.dim() == 3 && packed_qkv.stride(2) == 1);
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.stride(3) == 1 && v_cache.stride(3) == 1);
+  TORCH_CHECK(k_cache.scalar_type() == at::kChar && v_cache.scalar_type() == at::kChar);
+  TORCH_CHECK(k_scale.scalar_type() == at::kFloat && v_scale.scalar_type() == at::kFloat && k_scale.is_contiguous() && v_scale.is_contiguous());
+  TORCH_CHECK(q_lens.scalar_type() == at::kInt && accum_q_lens.scalar_type() == at::kInt && cache_lens.scalar_type() == at::kInt &&
+              cache_slot_ids.scalar_type() == at::kInt);
+  const int head_dim = (int)packed_qkv.size(2);
+  TORCH_CHECK(k_scale.numel() == (int64_t)kv_head_num * head_dim && v_scale.numel() == (int64_t)kv_head_num * head_dim,
+              "k_scale / v_scale must be [kv_heads, head_dim]");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(packed_qkv));
+  check_rc(mcop_kv_store_i8(packed_qkv.data_ptr(), packed_qkv.stride(0), packed_qkv.stride(1), q_lens.data_ptr<int32_t>(),
+                            accum_q_lens.data_ptr<int32_t>(), cache_lens.data_ptr<int32_t>(), cache_slot_ids.data_ptr<int32_t>(),
+                            k_cache.data_ptr<int8_t>(), v_cache.data_ptr<int8_t>(), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
+                            v_cache.stride(0), v_cache.stride(1), v_cache.stride(2), k_scale.data_ptr<float>(), v_scale.data_ptr<float>(),
+                            batch_size, packed_qkv.size(0), q_head_num, kv_head_num, head_dim, dtype_code(packed_qkv, "store_kv"), cur_stream()));
+}
+
+// torch.ops._C_cache_ops.reshape_and_cache_flash (op/vllm/cache_kernels.cu:610-650): only kv_cache_dtype "auto"
+void reshape_and_cache_flash(Tensor& key, Tensor& value, Tensor& key_cache, Tensor& value_cache, Tensor& slot_mapping,
+                             const std::string& kv_cache_dtype, Tensor& k_scale, Tensor& v_scale) {
+  (void)k_scale; (void)v_scale;
+  check_cuda(key, "key");
+  TORCH_CHECK(kv_cache_dtype == "auto", "only kv_cache_dtype \"auto\" is built (as in the reference)");
+  TORCH_CHECK(key.dim() == 3 && value.dim() == 3 && key_cache.dim() == 4 && value_cache.dim() == 4);
+  TORCH_CHECK(key_cache.scalar_type() == key.scalar_type() && value_cache.scalar_type() == value.scalar_type());
+  TORCH_CHECK(slot_mapping.scalar_type() == at::kLong && slot_mapping.is_contiguous());
+  TORCH_CHECK(key.stride(2) == 1 && value.stride(2) == 1 && key_cache.stride(3) == 1 && value_cache.stride(3) == 1);
+  TORCH_CHECK(key.stride(1) == key.size(2) && value.stride(1) == value.size(2), "heads of key/value must be contiguous");
+  TORCH_CHECK(key_cache.strides() == value_cache.strides(), "key_cache and value_cache must share a layout");
+  const int64_t tokens = slot_mapping.size(0);
+  const int kv_heads = (int)key.size(1), head_size = (int)key.size(2), block_size = (int)key_cache.size(1);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(key));
+  check_rc(mcop_reshape_and_cache_flash(key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0), key_cache.data_ptr(),
+                                        value_cache.data_ptr(), key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+                                        slot_mapping.data_ptr<int64_t>(), tokens, kv_heads, head_size, block_size,
+                                        (int)key.element_size(), cur_stream()));
+}
+
+// Fused RoPE + int8 paged store (addition of this build, composition of the three ops above)
+void rope_kv_store_int8(Tensor& positions, Tensor& query, Tensor& key, Tensor& value, int64_t head_size, Tensor& cos_sin_cache,
+                        bool is_neox, Tensor& key_cache, Tensor& value_cache, Tensor& slot_mapping, Tensor& k_scale, Tensor& v_scale) {
+  check_cuda(query, "query");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.dim() == 1);
+  TORCH_CHECK(slot_mapping.scalar_type() == at::kLong && slot_mapping.is_contiguous());
+  const int64_t tokens = positions.numel();
+  TORCH_CHECK(query.dim() == 2 && key.dim() == 2 && value.dim() == 2, "query/key/value must be [tokens, heads*head_size]");
+  TORCH_CHECK(query.size(0) == tokens && key.size(0) == tokens && value.size(0) == tokens && slot_mapping.numel() == tokens);
+  TORCH_CHECK(query.stride(1) == 1 && key.stride(1) == 1 && value.stride(1) == 1);
+  TORCH_CHECK(key.scalar_type() == query.scalar_type() && value.scalar_type() == query.scalar_type());
+  TORCH_CHECK(head_size > 0 && query.size(1) % head_size == 0 && key.size(1) % head_size == 0 && value.size(1) == key.size(1));
+  TORCH_CHECK(key_cache.scalar_type() == at::kChar && value_cache.scalar_type() == at::kChar);
+  TORCH_CHECK(key_cache.dim() == 4 && key_cache.is_contiguous() && value_cache.is_contiguous() && key_cache.sizes() == value_cache.sizes(),
+              "caches must be contiguous int8 [num_blocks, block_size, kv_heads, head_size]");
+  const int num_heads = (int)(query.size(1) / head_size), num_kv_heads = (int)(key.size(1) / head_size);
+  TORCH_CHECK(key_cache.size(2) == num_kv_heads && key_cache.size(3) == head_size);
+  TORCH_CHECK(k_scale.scalar_type() == at::kFloat && v_scale.scalar_type() == at::kFloat && k_scale.numel() == num_kv_heads &&
+              v_scale.numel() == num_kv_heads && k_scale.is_contiguous() && v_scale.is_contiguous());
+  TORCH_CHECK(cos_sin_cache.is_contiguous() && cos_sin_cache.dim() == 2);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(query));
+  check_rc(mcop_rope_kv_store_i8_paged(positions.data_ptr<int64_t>(), query.data_ptr(), key.data_ptr(), value.data_ptr(),
+                                       cos_sin_cache.data_ptr(), dtype_code(cos_sin_cache, "cos_sin_cache"), key_cache.data_ptr<int8_t>(),
+                                       value_cache.data_ptr<int8_t>(), slot_mapping.data_ptr<int64_t>(), k_scale.data_ptr<float>(),
+                                       v_scale.data_ptr<float>(), tokens, num_heads, num_kv_heads, (int)head_size, (int)cos_sin_cache.size(1),
+                                       query.stride(0), key.stride(0), value.stride(0), (int)key_cache.size(1), key_cache.size(0),
+                                       is_neox ? 1 : 0, dtype_code(query, "rope_kv_store_int8"), cur_stream()));
+}
+
+// ---------------------------------------------------------------- part 3
+
+// mcoplib.op.moe_softmax_topk (op/moe_softmax_topk.cu:216-235)
+void moe_softmax_topk(Tensor topk_weights, Tensor topk_indices, Tensor gating_output, bool pre_softmax) {
+  (void)pre_softmax;  // unused on this path in the reference as well: the weights are always renormalised
+  check_cuda(gating_output, "gating_output");
+  TORCH_CHECK(gating_output.scalar_type() == at::kFloat, "gating_output must be float32");
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat && topk_indices.scalar_type() == at::kInt);
+  TORCH_CHECK(gating_output.is_contiguous() && topk_weights.is_contiguous() && topk_indices.is_contiguous());
+  const int experts = (int)gating_output.size(-1);
+  const int64_t tokens = experts ? gating_output.numel() / experts : 0;
+  const int k = (int)topk_weights.size(-1);
+  TORCH_CHECK(topk_weights.numel() == tokens * k && topk_indices.numel() == tokens * k);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(gating_output));
+  check_rc(mcop_moe_softmax_topk(topk_weights.data_ptr<float>(), topk_indices.data_ptr<int32_t>(), gating_output.data_ptr<float>(), tokens,
+                                 experts, k, cur_stream()));
+}
+
+// mcoplib.op.fused_moe_gate_deepseek (op/fused_moe_gate_deepseek.cu:63-138)
+int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Tensor& out_routing_weights, Tensor& out_selected_experts,
+                            int topk, bool renormalize, int num_expert_group, int topk_group,
+                            std::optional<int> num_fused_shared_experts, std::optional<float> routed_scaling_factor,
+                            std::optional<int> moegate_type, std::optional<Tensor> debug_group_mask) {
+  check_cuda(gating_outputs, "gating_outputs");
+  TORCH_CHECK(gating_outputs.dim() == 2 && gating_outputs.is_contiguous() && correction_bias.is_contiguous());
+  TORCH_CHECK(out_routing_weights.scalar_type() == at::kFloat && out_routing_weights.is_contiguous());
+  TORCH_CHECK(out_selected_experts.scalar_type() == at::kInt && out_selected_experts.is_contiguous(), "selected experts must be int32");
+  TORCH_CHECK(num_fused_shared_experts.value_or(0) == 0, "fused shared experts are not built");
+  TORCH_CHECK(moegate_type.value_or(0) == 0, "only moegate_type 0 is built");
+  const int64_t tokens = gating_outputs.size(0);
+  const int experts = (int)gating_outputs.size(1);
+  TORCH_CHECK(correction_bias.numel() == experts);
+  TORCH_CHECK(out_routing_weights.numel() == tokens * topk && out_selected_experts.numel() == tokens * topk);
+  int32_t* gm = nullptr;
+  if (debug_group_mask.has_value()) {
+    TORCH_CHECK(debug_group_mask->scalar_type() == at::kInt && debug_group_mask->numel() == tokens && debug_group_mask->is_contiguous());
+    gm = debug_group_mask->data_ptr<int32_t>();
+  }
+  const c10::cuda::OptionalCUDAGuard guard(device_of(gating_outputs));
+  check_rc(mcop_moe_gate_grouped_sigmoid(gating_outputs.data_ptr(), correction_bias.data_ptr(), out_routing_weights.data_ptr<float>(),
+                                         out_selected_experts.data_ptr<int32_t>(), gm, tokens, experts, num_expert_group, topk_group, topk,
+                                         renormalize ? 1 : 0, routed_scaling_factor.value_or(1.0f), dtype_code(gating_outputs, "gating_outputs"),
+                                         dtype_code(correction_bias, "correction_bias"), cur_stream()));
+  return 0;
+}
+
+// mcoplib.op.moe_scatter_dynamic_quant (op/moe_scatter_dynamic_quant.cu:312-341)
+void moe_scatter_dynamic_quant(Tensor hidden_status, Tensor selected_experts, Tensor moe_weights, Tensor smooth_scale, Tensor scatter_tokens,
+                               Tensor scatter_per_token_scale, Tensor scatter_tokens_offset, Tensor experts_token_count,
+                               Tensor experts_token_start, int experts_per_rank, int shared_experts_per_rank, int shared_tokens_per_sp,
+                               std::optional<Tensor> tok2row) {
+  check_cuda(hidden_status, "hidden_status"); check_cuda(selected_experts, "selected_experts"); check_cuda(smooth_scale, "smooth_scale");
+  TORCH_CHECK(hidden_status.is_contiguous() && selected_experts.is_contiguous() && smooth_scale.is_contiguous());
+  TORCH_CHECK(hidden_status.scalar_type() == at::kBFloat16, "Only float16, bfloat16 are supported");
+  TORCH_CHECK(shared_experts_per_rank == 0 && shared_tokens_per_sp == 0, "shared experts are not built");
+  TORCH_CHECK(experts_per_rank <= 256, "Unsupported, num_experts_per_rank should less than or equal to 256");
+  TORCH_CHECK(selected_experts.scalar_type() == at::kInt && moe_weights.scalar_type() == at::kFloat && smooth_scale.scalar_type() == at::kFloat);
+  TORCH_CHECK(scatter_tokens.scalar_type() == at::kChar && scatter_per_token_scale.scalar_type() == at::kFloat &&
+              scatter_tokens_offset.scalar_type() == at::kInt && experts_token_count.scalar_type() == at::kInt &&
+              experts_token_start.scalar_type() == at::kInt);
+  TORCH_CHECK(moe_weights.is_contiguous() && scatter_tokens.is_contiguous() && scatter_per_token_scale.is_contiguous() &&
+              scatter_tokens_offset.is_contiguous() && experts_token_count.is_contiguous() && experts_token_start.is_contiguous());
+  const int64_t hidden = hidden_status.size(-1);
+  const int64_t tokens = hidden ? hidden_status.numel() / hidden : 0;
+  const int topk = (int)selected_experts.size(-1);
+  TORCH_CHECK(selected_experts.numel() == tokens * topk && moe_weights.numel() == tokens * topk);
+  TORCH_CHECK(smooth_scale.numel() >= (int64_t)experts_per_rank * hidden);
+  TORCH_CHECK(scatter_tokens.numel() >= tokens * topk * hidden && scatter_per_token_scale.numel() >= tokens * topk &&
+              scatter_tokens_offset.numel() >= tokens * topk);
+  TORCH_CHECK(experts_token_count.numel() >= experts_per_rank && experts_token_start.numel() >= experts_per_rank);
+  int32_t* t2r = nullptr;
+  if (tok2row.has_value()) {
+    TORCH_CHECK(tok2row->scalar_type() == at::kInt && tok2row->is_contiguous() && tok2row->numel() == tokens * topk);
+    t2r = tok2row->data_ptr<int32_t>();
+  }
+  const c10::cuda::OptionalCUDAGuard guard(device_of(hidden_status));
+  const size_t ws_bytes = mcop_moe_scatter_workspace_bytes(tokens, topk, experts_per_rank);
+  Tensor ws = scratch_bytes(ws_bytes, hidden_status);
+  check_rc(mcop_moe_scatter_quant_i8(hidden_status.data_ptr(), selected_experts.data_ptr<int32_t>(), moe_weights.data_ptr<float>(),
+                                     smooth_scale.data_ptr<float>(), scatter_tokens.data_ptr<int8_t>(), scatter_per_token_scale.data_ptr<float>(),
+                                     scatter_tokens_offset.data_ptr<int32_t>(), experts_token_count.data_ptr<int32_t>(),
+                                     experts_token_start.data_ptr<int32_t>(), t2r, tokens, hidden, topk, experts_per_rank, ws.data_ptr(),
+                                     (size_t)ws.numel(), cur_stream()));
+}
+
+// mcoplib.op.moe_gather (op/moe_gather.cu:137-150)
+void moe_gather(Tensor scatter_tokens, Tensor scatter_tokens_offset, Tensor convergent_tokens, std::optional<Tensor> tok2row) {
+  check_cuda(scatter_tokens, "scatter_tokens");
+  TORCH_CHECK(scatter_tokens.scalar_type() == at::kBFloat16 && convergent_tokens.scalar_type() == at::kBFloat16,
+              "Only float16, bfloat16 are supported");
+  TORCH_CHECK(scatter_tokens.is_contiguous() && scatter_tokens_offset.is_contiguous() && convergent_tokens.is_contiguous());
+  TORCH_CHECK(scatter_tokens_offset.scalar_type() == at::kInt);
+  const int64_t hidden = scatter_tokens.size(-1);
+  const int64_t rows = hidden ? scatter_tokens.numel() / hidden : 0;
+  TORCH_CHECK(convergent_tokens.size(-1) == hidden);
+  const int64_t tokens = hidden ? convergent_tokens.numel() / hidden : 0;
+  TORCH_CHECK(scatter_tokens_offset.numel() >= rows);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(scatter_tokens));
+  const int32_t* t2r = nullptr;
+  int topk = 0;
+  Tensor ws;
+  void* wsp = nullptr;
+  size_t ws_bytes = 0;
+  if (tok2row.has_value()) {
+    TORCH_CHECK(tok2row->scalar_type() == at::kInt && tok2row->is_contiguous() && tok2row->dim() == 2 && tok2row->size(0) == tokens);
+    t2r = tok2row->data_ptr<int32_t>();
+    topk = (int)tok2row->size(1);
+  } else {
+    ws_bytes = mcop_moe_gather_workspace_bytes(tokens, rows);
+    ws = scratch_bytes(ws_bytes, scatter_tokens);
+    wsp = ws.data_ptr();
+    ws_bytes = (size_t)ws.numel();
+  }
+  check_rc(mcop_moe_gather(scatter_tokens.data_ptr(), scatter_tokens_offset.data_ptr<int32_t>(), convergent_tokens.data_ptr(), t2r, topk,
+                           tokens, rows, hidden, wsp, ws_bytes, cur_stream()));
+}
+
+// Weighted combine (addition of this build)
+void moe_gather_weighted(Tensor y, Tensor row2tok, Tensor topk_ids, Tensor topk_weights, Tensor experts_token_start, Tensor out,
+                         bool accumulate, std::optional<Tensor> tok2row) {
+  check_cuda(y, "y");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "Only bfloat16 is supported");
+  TORCH_CHECK(y.is_contiguous() && row2tok.is_contiguous() && topk_ids.is_contiguous() && topk_weights.is_contiguous() &&
+              experts_token_start.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(row2tok.scalar_type() == at::kInt && topk_ids.scalar_type() == at::kInt && topk_weights.scalar_type() == at::kFloat &&
+              experts_token_start.scalar_type() == at::kInt);
+  const int64_t hidden = y.size(-1);
+  const int64_t rows = hidden ? y.numel() / hidden : 0;
+  const int64_t tokens = hidden ? out.numel() / hidden : 0;
+  const int topk = (int)topk_ids.size(-1);
+  TORCH_CHECK(out.size(-1) == hidden && topk_ids.numel() == tokens * topk && topk_weights.numel() == tokens * topk && row2tok.numel() >= rows);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(y));
+  const int32_t* t2r = nullptr;
+  Tensor ws;
+  void* wsp = nullptr;
+  size_t ws_bytes = 0;
+  if (tok2row.has_value()) {
+    TORCH_CHECK(tok2row->scalar_type() == at::kInt && tok2row->is_contiguous() && tok2row->numel() == tokens * topk);
+    t2r = tok2row->data_ptr<int32_t>();
+  } else {
+    ws_bytes = mcop_moe_gather_workspace_bytes(tokens, rows);
+    ws = scratch_bytes(ws_bytes, y);
+    wsp = ws.data_ptr();
+    ws_bytes = (size_t)ws.numel();
+  }
+  check_rc(mcop_moe_gather_weighted(y.data_ptr(), row2tok.data_ptr<int32_t>(), topk_ids.data_ptr<int32_t>(), topk_weights.data_ptr<float>(),
+                                    experts_token_start.data_ptr<int32_t>(), out.data_ptr(), t2r, accumulate ? 1 : 0, tokens, rows, hidden,
+                                    topk, (int)experts_token_start.numel(), wsp, ws_bytes, cur_stream()));
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- registration
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  namespace py = pybind11;
+  m.doc() = "mcoplib.op operator surface of the per-token inference hot path, B200 (sm_100a) kernels";
+  m.def("rms_norm_dynamic_per_token_quant", &rms_norm_dynamic_per_token_quant_9);
+  m.def("rms_norm_dynamic_per_token_quant_custom", &rms_norm_dynamic_per_token_quant_vllm);
+  m.def("rms_norm", &rms_norm);
+  m.def("head_rms_norm", &head_rms_norm);
+  m.def("scale_dynamic_quant", &scale_dynamic_quant, py::arg("hidden_states"), py::arg("smooth_scales"),
+        py::arg("dst_torch_dtype") = at::ScalarType::Char);
+  m.def("rotary_embedding", &rotary_embedding_packed, py::arg("packed_qkv"), py::arg("q_len"), py::arg("accum_q_lens"),
+        py::arg("cache_lens"), py::arg("cos"), py::arg("sin"), py::arg("output"), py::arg("q_head_num"), py::arg("kv_head_num"),
+        py::arg("rope_offset") = 0);
+  m.def("fused_rope_fwd", &fused_rope_fwd, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("indexes"),
+        py::arg("force_bf16_attn") = false);
+  m.def("store_kv_cache_cuda_interface", &store_kv_cache_cuda_interface);
+  m.def("moe_softmax_topk", &moe_softmax_topk);
+  m.def("fused_moe_gate_deepseek", &fused_moe_gate_deepseek, py::arg("gating_outputs"), py::arg("correction_bias"),
+        py::arg("out_routing_weights"), py::arg("out_selected_experts"), py::arg("topk"), py::arg("renormalize"),
+        py::arg("num_expert_group"), py::arg("topk_group"), py::arg("num_fused_shared_experts") = py::none(),
+        py::arg("routed_scaling_factor") = py::none(), py::arg("moegate_type") = py::none(), py::arg("debug_group_mask") = py::none());
+  m.def("moe_scatter_dynamic_quant", &moe_scatter_dynamic_quant, py::arg("hidden_status"), py::arg("selected_experts"),
+        py::arg("moe_weights"), py::arg("smooth_scale"), py::arg("scatter_tokens"), py::arg("scatter_per_token_scale"),
+        py::arg("scatter_tokens_offset"), py::arg("experts_token_count"), py::arg("experts_token_start"), py::arg("experts_per_rank"),
+        py::arg("shared_experts_per_rank"), py::arg("shared_tokens_per_sp"), py::arg("tok2row") = py::none());
+  m.def("moe_gather", &moe_gather, py::arg("scatter_tokens"), py::arg("scatter_tokens_offset"), py::arg("convergent_tokens"),
+        py::arg("tok2row") = py::none());
+  // additions of this build (no reference counterpart)
+  m.def("rope_kv_store_int8", &rope_kv_store_int8);
+  m.def("moe_gather_weighted", &moe_gather_weighted, py::arg("y"), py::arg("row2tok"), py::arg("topk_ids"), py::arg("topk_weights"),
+        py::arg("experts_token_start"), py::arg("out"), py::arg("accumulate"), py::arg("tok2row") = py::none());
+  // torch-library functions also reachable directly (same objects the dispatcher calls)
+  m.def("fused_add_rms_norm", &fused_add_rms_norm);
+  m.def("vllm_rotary_embedding", &rotary_embedding_vllm);
+  m.def("reshape_and_cache_flash", &reshape_and_cache_flash);
+#define MCOP_STR_(x) #x
+#define MCOP_STR(x) MCOP_STR_(x)
+  m.attr("torch_namespace") = MCOP_STR(MCOP_TORCH_NS);
+}
+
+TORCH_LIBRARY(MCOP_TORCH_NS, ops) {
+  ops.def("fused_add_rms_norm(Tensor! input, Tensor! residual, Tensor weight, float epsilon) -> ()");
+  ops.impl("fused_add_rms_norm", torch::kCUDA, &fused_add_rms_norm);
+  ops.def(
+      "rms_norm_dynamic_per_token_quant(Tensor! result, Tensor input, Tensor weight, Tensor! scale, float epsilon, "
+      "Tensor? scale_ub, Tensor!? residual) -> ()");
+  ops.impl("rms_norm_dynamic_per_token_quant", torch::kCUDA, &rms_norm_dynamic_per_token_quant_vllm);
+  ops.def(
+      "rotary_embedding(Tensor positions, Tensor! query, Tensor!? key, int head_size, Tensor cos_sin_cache, bool is_neox) -> ()");
+  ops.impl("rotary_embedding", torch::kCUDA, &rotary_embedding_vllm);
+  ops.def(
+      "rope_kv_store_int8(Tensor positions, Tensor! query, Tensor! key, Tensor value, int head_size, Tensor cos_sin_cache, "
+      "bool is_neox, Tensor! key_cache, Tensor! value_cache, Tensor slot_mapping, Tensor k_scale, Tensor v_scale) -> ()");
+  ops.impl("rope_kv_store_int8", torch::kCUDA, &rope_kv_store_int8);
+}
+
+TORCH_LIBRARY(MCOP_TORCH_NS_CACHE, cache_ops) {
+  cache_ops.def(
+      "reshape_and_cache_flash(Tensor key, Tensor value, Tensor! key_cache, Tensor! value_cache, Tensor slot_mapping, "
+      "str kv_cache_dtype, Tensor k_scale, Tensor v_scale) -> ()");
+  cache_ops.impl("reshape_and_cache_flash", torch::kCUDA, &reshape_and_cache_flash);
+}
