@@ -1,0 +1,492 @@
+#!/usr/bin/env python
+"""Benchmark of the per-token hot path (default: benchmark configuration 5, the token-sharded chain).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload chain5|chain4|route3|rope2]
+
+A step is one pass of the chain over the rank's token shard:
+    chain5 : add+RMSNorm+int8 quant -> softmax top-2 of 8 -> scatter with per-row int8 quant -> weighted gather
+For N > 1 launch with torchrun (one rank per GPU); tokens are split evenly by rank, there is no collective on
+the data path, and the step time is the maximum over ranks of the device time between CUDA events.
+Rank 0 prints ONE JSON line.  `--impl reference` times the CPU restatement of the reference path (oracle/)
+on the host cores instead; it is a reported baseline, not a target.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+METRIC = "fused_chain_tokens_per_s"
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per token of the norm+quant kernel at hidden 7168,
+# from the ncu capture summarised in profiles/norm_quant_7168.md; None until such a capture exists.
+NORM_QUANT_DRAM_BYTES_PER_TOKEN = None
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+class Chain5:
+    """Configuration 5: T tokens x hidden 7168, softmax top-2 of 8 experts."""
+    name = "config5 token_sharded_chain_262144: add+rmsnorm+int8 quant -> softmax top2/8 -> scatter+int8 quant -> weighted gather"
+    kernels = ["norm_quant", "softmax_topk", "scatter", "gather"]
+    launches_per_step = 5  # norm, softmax, scatter rank + scatter quant, gather (tok2row given: no inversion pass)
+
+    def __init__(self, tokens, hidden=7168, experts=8, topk=2, t0=0, device="cuda", gen_device="cuda", pinned_host=False):
+        from mcoplib_b200 import workloads as W
+        self.T, self.H, self.E, self.k, self.W = tokens, hidden, experts, topk, W
+        self.dev = device
+        d = W.norm_quant_inputs(tokens, hidden, t0, 0, gen_device, device)
+        self.x, self.res, self.w = d["x"], d["residual"], d["weight"]
+        self.logits = W.router_inputs(tokens, experts, t0, 0, gen_device, device)["logits"]
+        dd = W.dispatch_inputs(tokens, hidden, experts, topk, t0, 0, gen_device, device, with_hidden=False)
+        self.smooth, self.y = dd["smooth"], dd["y"]
+        R = tokens * topk
+        o = dict(device=device)
+        self.codes = torch.empty(tokens, hidden, dtype=torch.int8, **o)
+        self.scales = torch.empty(tokens, 1, dtype=torch.float32, **o)
+        self.topk_w = torch.empty(tokens, topk, dtype=torch.float32, **o)
+        self.topk_ids = torch.empty(tokens, topk, dtype=torch.int32, **o)
+        self.rows = torch.empty(R, hidden, dtype=torch.int8, **o)
+        self.row_scales = torch.empty(R, dtype=torch.float32, **o)
+        self.row2tok = torch.empty(R, dtype=torch.int32, **o)
+        self.counts = torch.empty(experts, dtype=torch.int32, **o)
+        self.starts = torch.empty(experts, dtype=torch.int32, **o)
+        self.tok2row = torch.empty(tokens, topk, dtype=torch.int32, **o)
+        self.out = torch.empty(tokens, hidden, dtype=torch.bfloat16, **o)
+
+    def bytes_per_kernel(self):
+        return self.W.chain5_bytes(self.T, self.H, self.E, self.k)
+
+    def stages(self, ops):
+        return [
+            lambda: ops.rms_norm_dynamic_per_token_quant_custom(self.codes, self.x, self.w, self.scales, 1e-6, None, self.res),
+            lambda: ops.moe_softmax_topk(self.topk_w, self.topk_ids, self.logits, False),
+            lambda: ops.moe_scatter_dynamic_quant(self.x, self.topk_ids, self.topk_w, self.smooth, self.rows, self.row_scales,
+                                                  self.row2tok, self.counts, self.starts, self.E, 0, 0, self.tok2row),
+            lambda: ops.moe_gather_weighted(self.y, self.row2tok, self.topk_ids, self.topk_w, self.starts, self.out, False, self.tok2row),
+        ]
+
+    def inputs(self):
+        return [self.x, self.res, self.logits, self.y]
+
+    def outputs(self):
+        return [self.codes, self.scales, self.res, self.topk_w, self.topk_ids, self.rows, self.row_scales, self.row2tok,
+                self.counts, self.starts, self.out]
+
+
+class Chain4:
+    """Configuration 4: add+RMSNorm+quant at hidden 8192, then RoPE (64 Q / 8 KV heads) + int8 paged KV store."""
+    name = "config4 llama70b_prefill_chunk_32768: add+rmsnorm+int8 quant -> neox rope + int8 paged kv store"
+    kernels = ["norm_quant", "rope_kv_store"]
+    launches_per_step = 2
+
+    def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
+        from mcoplib_b200 import op as ops
+        from mcoplib_b200 import workloads as W
+        self.T, self.H, self.W = tokens, 8192, W
+        d = W.norm_quant_inputs(tokens, 8192, t0, 0, gen_device, device)
+        self.x, self.res, self.w = d["x"], d["residual"], d["weight"]
+        nb = max(2048, (tokens + 15) // 16)
+        self.r = W.rope_kv_inputs(tokens, 64, 8, 128, 131072, 500000.0, 16, nb, t0, 0, gen_device, device)
+        self.codes = torch.empty(tokens, 8192, dtype=torch.int8, device=device)
+        self.scales = torch.empty(tokens, 1, dtype=torch.float32, device=device)
+        kr = self.r["key"].clone()
+        ops.vllm_rotary_embedding(self.r["positions"], self.r["query"].clone(), kr, 128, self.r["cos_sin_cache"], True)
+        self.ks, self.vs = W.kv_scales(kr, self.r["value"], 8, 128)
+
+    def bytes_per_kernel(self):
+        return {"norm_quant": self.W.norm_quant_bytes(self.T, self.H), "rope_kv_store": self.W.rope_kv_bytes(self.T, 64, 8, 128)}
+
+    def stages(self, ops):
+        r = self.r
+        return [
+            lambda: ops.rms_norm_dynamic_per_token_quant_custom(self.codes, self.x, self.w, self.scales, 1e-6, None, self.res),
+            lambda: ops.rope_kv_store_int8(r["positions"], r["query"], r["key"], r["value"], 128, r["cos_sin_cache"], True,
+                                           r["key_cache"], r["value_cache"], r["slot_mapping"], self.ks, self.vs),
+        ]
+
+
+class Route3:
+    """Configuration 3: DeepSeek-V3-shaped gate (256 experts, 8 groups, top-8) + scatter + weighted gather, hidden 7168."""
+    name = "config3 deepseek_route_dispatch_8192: grouped sigmoid gate -> scatter+int8 quant -> weighted gather"
+    kernels = ["gate", "scatter", "gather"]
+    launches_per_step = 4
+
+    def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
+        from mcoplib_b200 import workloads as W
+        self.T, self.H, self.E, self.k, self.W = tokens, 7168, 256, 8, W
+        r = W.router_inputs(tokens, 256, t0, 0, gen_device, device)
+        self.logits, self.bias = r["logits"], r["bias"]
+        d = W.dispatch_inputs(tokens, 7168, 256, 8, t0, 0, gen_device, device)
+        self.hidden, self.smooth, self.y = d["hidden"], d["smooth"], d["y"]
+        R = tokens * 8
+        o = dict(device=device)
+        self.topk_w = torch.empty(tokens, 8, dtype=torch.float32, **o)
+        self.topk_ids = torch.empty(tokens, 8, dtype=torch.int32, **o)
+        self.rows = torch.empty(R, 7168, dtype=torch.int8, **o)
+        self.row_scales = torch.empty(R, dtype=torch.float32, **o)
+        self.row2tok = torch.empty(R, dtype=torch.int32, **o)
+        self.counts = torch.empty(256, dtype=torch.int32, **o)
+        self.starts = torch.empty(256, dtype=torch.int32, **o)
+        self.tok2row = torch.empty(tokens, 8, dtype=torch.int32, **o)
+        self.out = torch.empty(tokens, 7168, dtype=torch.bfloat16, **o)
+
+    def bytes_per_kernel(self):
+        W = self.W
+        return {"gate": W.gate_bytes(self.T, 256, 8), "scatter": W.scatter_bytes(self.T, 7168, 256, 8),
+                "gather": W.gather_bytes(self.T, 7168, 8, False)}
+
+    def stages(self, ops):
+        return [
+            lambda: ops.fused_moe_gate_deepseek(self.logits, self.bias, self.topk_w, self.topk_ids, 8, True, 8, 4, None, 2.5, 0),
+            lambda: ops.moe_scatter_dynamic_quant(self.hidden, self.topk_ids, self.topk_w, self.smooth, self.rows, self.row_scales,
+                                                  self.row2tok, self.counts, self.starts, 256, 0, 0, self.tok2row),
+            lambda: ops.moe_gather_weighted(self.y, self.row2tok, self.topk_ids, self.topk_w, self.starts, self.out, False, self.tok2row),
+        ]
+
+
+class Rope2:
+    """Configuration 2: NeoX RoPE + int8 paged KV store, 32 Q / 8 KV heads."""
+    name = "config2 rope_kv_4096: neox rope + int8 paged kv store"
+    kernels = ["rope_kv_store"]
+    launches_per_step = 1
+
+    def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
+        from mcoplib_b200 import op as ops
+        from mcoplib_b200 import workloads as W
+        self.T, self.W = tokens, W
+        nb = max(2048, (tokens + 15) // 16)
+        self.r = W.rope_kv_inputs(tokens, 32, 8, 128, 8192, 500000.0, 16, nb, t0, 0, gen_device, device)
+        kr = self.r["key"].clone()
+        ops.vllm_rotary_embedding(self.r["positions"], self.r["query"].clone(), kr, 128, self.r["cos_sin_cache"], True)
+        self.ks, self.vs = W.kv_scales(kr, self.r["value"], 8, 128)
+
+    def bytes_per_kernel(self):
+        return {"rope_kv_store": self.W.rope_kv_bytes(self.T, 32, 8, 128)}
+
+    def stages(self, ops):
+        r = self.r
+        return [lambda: ops.rope_kv_store_int8(r["positions"], r["query"], r["key"], r["value"], 128, r["cos_sin_cache"], True,
+                                               r["key_cache"], r["value_cache"], r["slot_mapping"], self.ks, self.vs)]
+
+
+WORKLOADS = {"chain5": (Chain5, 262144), "chain4": (Chain4, 32768), "route3": (Route3, 8192), "rope2": (Rope2, 4096)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle restatement of the reference path on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_chain5(sample_tokens: int, reps: int = 1, warm: bool = True):
+    """Times the CPU restatement (oracle/ref_ops.py) of configuration 5's chain on `sample_tokens` tokens."""
+    from mcoplib_b200 import workloads as W
+    from oracle import ref_ops as R
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+
+    def make(n):
+        d = W.norm_quant_inputs(n, 7168)
+        d["logits"] = W.router_inputs(n, 8)["logits"]
+        d.update(W.dispatch_inputs(n, 7168, 8, 2, with_hidden=False))
+        return d
+
+    def run(d, n):
+        R.rms_norm_dynamic_per_token_quant(d["x"], d["weight"], 1e-6, residual=d["residual"])
+        w, ids = R.moe_softmax_topk(d["logits"], 2)
+        _, _, row2tok, _, starts, _ = R.moe_scatter_dynamic_quant(d["x"], ids, w, d["smooth"], 8)
+        R.moe_gather_weighted(d["y"], row2tok, ids, w, starts, torch.empty(n, 7168, dtype=torch.bfloat16), False)
+
+    if warm:
+        run(make(512), 512)
+    d = make(sample_tokens)
+    times = []
+    for _ in range(reps):
+        t = time.perf_counter()
+        run(d, sample_tokens)
+        times.append(time.perf_counter() - t)
+    return {"seconds": times, "tokens": sample_tokens, "threads": threads}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    sample = args.cpu_sample
+    r = cpu_chain5(sample, reps=max(1, args.steps), warm=args.warmup > 0)
+    total = sum(r["seconds"])
+    value = sample * len(r["seconds"]) / total
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(r["seconds"]), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": Chain5.name, "tokens_per_step_sample": sample, "hidden": 7168, "experts": 8, "topk": 2},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": r["threads"], "kind": "port",
+                         "sample": f"{sample} tokens of the config-5 chain per step, torch CPU oracle, {r['threads']} threads"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def e2e_chain5(ops, tokens_rank, chunk, steps, warmup, device):
+    """The same chain driven from HOST buffers: the rank's batch is streamed in `chunk`-token pieces from pinned
+    host memory (H2D), through the operators, and every output is copied back (D2H), on two alternating streams.
+    Returns (seconds per step, h2d bytes per step, d2h bytes per step)."""
+    chunk = min(chunk, tokens_rank)
+    nchunks = (tokens_rank + chunk - 1) // chunk
+    slots = []
+    host_in = None
+    for s in range(2):
+        c = Chain5(chunk, device=device, gen_device=device)
+        if host_in is None:
+            host_in = [t.cpu().pin_memory() for t in c.inputs()]
+        host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in c.outputs()]
+        slots.append((c, host_out, torch.cuda.Stream(device=device)))
+    h2d = sum(t.numel() * t.element_size() for t in host_in) * nchunks
+    d2h = sum(t.numel() * t.element_size() for t in slots[0][1]) * nchunks
+    main = torch.cuda.current_stream()
+
+    def one_step():
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record(main)
+        for _, _, st in slots:
+            st.wait_event(start)
+        for i in range(nchunks):
+            c, host_out, st = slots[i % 2]
+            with torch.cuda.stream(st):
+                for dst, src in zip(c.inputs(), host_in):
+                    dst.copy_(src, non_blocking=True)
+                for f in c.stages(ops):
+                    f()
+                for dst, src in zip(host_out, c.outputs()):
+                    dst.copy_(src, non_blocking=True)
+        for _, _, st in slots:
+            ev = torch.cuda.Event()
+            ev.record(st)
+            main.wait_event(ev)
+        stop.record(main)
+        return start, stop
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    evs = [one_step() for _ in range(steps)]
+    torch.cuda.synchronize()
+    secs = sum(a.elapsed_time(b) for a, b in evs) / 1e3 / steps
+    return secs, h2d, d2h
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from mcoplib_b200 import op as ops  # raises if the extension is not built: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py --impl ours needs a CUDA device (the kernels have no CPU fallback)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    n = max(world, 1)
+
+    cls, tokens_global = WORKLOADS[args.workload]
+    if args.tokens:
+        tokens_global = args.tokens
+    if args.scaling == "weak":
+        tokens_rank, t0 = tokens_global, rank * tokens_global
+        tokens_total = tokens_global * n
+    else:
+        tokens_rank = tokens_global // n
+        t0 = rank * tokens_rank
+        tokens_total = tokens_rank * n
+    wl = cls(tokens_rank, t0=t0, device=device, gen_device=device)
+    stages = wl.stages(ops)
+    nst = len(stages)
+
+    def step(events=None):
+        if events is not None:
+            events[0].record()
+        for i, f in enumerate(stages):
+            f()
+            if events is not None:
+                events[i + 1].record()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(nst + 1)] for _ in range(args.steps)]
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_stop = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for s in range(args.steps):
+        step(evs[s])
+    t_stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    elapsed_ms = t_start.elapsed_time(t_stop)
+    per_kernel_ms = [sum(evs[s][i].elapsed_time(evs[s][i + 1]) for s in range(args.steps)) / args.steps for i in range(nst)]
+    if world > 1:
+        t = torch.tensor([elapsed_ms] + per_kernel_ms, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, per_kernel_ms = float(t[0]), [float(v) for v in t[1:]]
+
+    e2e = None
+    if args.workload == "chain5" and not args.no_e2e:
+        secs, h2d, d2h = e2e_chain5(ops, tokens_rank, args.e2e_chunk, max(1, min(args.steps, 3)), 1, device)
+        if world > 1:
+            t = torch.tensor([secs], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            secs = float(t[0])
+        e2e = {"value": tokens_total / secs, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": secs * 1e3,
+               "how": f"host pinned buffers -> H2D -> operators -> D2H of every output, streamed in {min(args.e2e_chunk, tokens_rank)}-token "
+                      "chunks on two streams per rank"}
+    if world > 1:
+        dist.barrier()
+
+    if rank == 0:
+        ms_per_step = elapsed_ms / args.steps
+        peak, peak_kind = measured_peak()
+        bpk = wl.bytes_per_kernel()
+        kernels = {}
+        for name, ms in zip(wl.kernels, per_kernel_ms):
+            gbs = bpk[name] / (ms * 1e-3) / 1e9
+            kernels[name] = {"ms": ms, "algorithmic_bytes": bpk[name], "gb_per_s": gbs, "frac_of_measured_copy_peak": gbs / peak,
+                             "frac_of_8TBps_nominal": gbs / NOMINAL_HBM_GBS}
+        dom = max(wl.kernels, key=lambda k: bpk[k])
+        traffic = None
+        if dom == "norm_quant" and NORM_QUANT_DRAM_BYTES_PER_TOKEN is not None and wl.H == 7168:
+            traffic = NORM_QUANT_DRAM_BYTES_PER_TOKEN * tokens_rank
+        line = {
+            "metric": METRIC, "value": tokens_total / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl.name, "tokens_global": tokens_total, "tokens_per_gpu": tokens_rank,
+                       "parallelism": f"token-sharded x{n}, no collective on the data path",
+                       "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gb_per_s"], "peak": peak, "peak_kind": f"of {peak_kind}",
+                         "unit": "GB/s", "frac": kernels[dom]["gb_per_s"] / peak, "traffic": traffic},
+            "kernels": kernels,
+            "gpu_launches": wl.launches_per_step * args.steps,
+            "clocks": clocks,
+            "impl": "ours",
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if n == 1 and args.workload == "chain5" and not args.no_cpu_baseline:
+            r = cpu_chain5(args.cpu_sample, reps=1)
+            v = r["tokens"] / r["seconds"][0]
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": r["threads"], "kind": "port",
+                                    "sample": f"{r['tokens']} tokens of the same chain, torch CPU oracle, {r['threads']} threads, "
+                                              f"{r['seconds'][0]:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="chain5", choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=0, help="override the global token count of the workload")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="strong: the configuration's tokens are split across ranks (as configuration 5 states); weak: each rank gets all of them")
+    ap.add_argument("--e2e-chunk", type=int, default=16384)
+    ap.add_argument("--cpu-sample", type=int, default=0,
+                    help="tokens per CPU sample (default 16384 for the cpu_baseline of the GPU arm, 8192 per step of --impl reference)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3  # timing rule: at least three untimed steps
+    if args.impl == "reference":
+        args.cpu_sample = args.cpu_sample or 8192
+        return run_reference(args)
+    args.cpu_sample = args.cpu_sample or 16384
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -38,14 +38,32 @@ struct NormParams {
   int rms_div;
 };
 
-// Per-row scalar from the sum of squares: IEEE division and square root (matches 1/sqrt on the host).
-__device__ __forceinline__ float inv_rms(float ss, int hidden, float eps) {
-  return 1.0f / sqrtf(ss / (float)hidden + eps);
+// Per-row scalar from the sum of squares.  The squares are accumulated in double, so the mean is the
+// correctly rounded fp32 value whatever the summation order; then IEEE fp32 add, sqrt and division
+// (the sequence 1/sqrt(var + eps) a host evaluates).
+__device__ __forceinline__ float inv_rms(double ss, int hidden, float eps) {
+  const float var = (float)(ss / (double)hidden);
+  return 1.0f / sqrtf(var + eps);
+}
+
+__device__ __forceinline__ double block_sum_f64(double v, double* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (nwarp == 1) return v;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  double r = (lane < nwarp) ? red[lane] : 0.0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  __syncthreads();
+  return r;
 }
 
 template <typename T, typename WT, int MODE, int THREADS, int NVEC>
 __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
   __shared__ float red[33];
+  __shared__ double red64[33];
   const int64_t row = blockIdx.x;
   const int nv = p.hidden >> 3;
   const T* x = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
@@ -54,7 +72,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
   const WT* w = reinterpret_cast<const WT*>(p.weight);
 
   float s[NVEC][8];
-  float ss = 0.f;
+  double ss = 0.0;
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * THREADS;
@@ -73,7 +91,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
       }
       if (rout) Vec8<T>::store(rout + v * 8, s[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += s[i][j] * s[i][j];
+      for (int j = 0; j < 8; ++j) ss += (double)s[i][j] * (double)s[i][j];
       if (MODE == kSmoothQuant) {
         // the later phases of the reference read the ROUNDED after_res back
 #pragma unroll
@@ -84,7 +102,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
       for (int j = 0; j < 8; ++j) s[i][j] = 0.f;
     }
   }
-  ss = block_reduce<false>(ss, red);
+  ss = block_sum_f64(ss, red64);
   const float r = inv_rms(ss, p.hidden, p.eps);
 
   if (MODE == kPlain) {
@@ -164,6 +182,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
 template <typename T, typename WT, int MODE>
 __global__ void __launch_bounds__(256) norm_rows_any(NormParams p) {
   __shared__ float red[33];
+  __shared__ double red64[33];
   const int64_t row = blockIdx.x;
   const int H = p.hidden;
   const T* x = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
@@ -175,17 +194,17 @@ __global__ void __launch_bounds__(256) norm_rows_any(NormParams p) {
   // x (kFusedAdd) and the residual row are overwritten in place while later passes need the sum again,
   // so the fp32 sum of the row is parked in shared memory and global memory is read only once.
   extern __shared__ float keep[];  // hidden floats
-  float ss = 0.f;
+  double ss = 0.0;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float s = ElemTraits<T>::to_float(x[i]);
     if (rin) s += ElemTraits<T>::to_float(rin[i]);
     if (MODE == kFusedAdd) s = round_to<T>(s);
     if (rout) rout[i] = ElemTraits<T>::from_float(s);
-    ss += s * s;
+    ss += (double)s * (double)s;
     if (MODE == kSmoothQuant) s = round_to<T>(s);
     keep[i] = s;
   }
-  ss = block_reduce<false>(ss, red);
+  ss = block_sum_f64(ss, red64);
   const float r = inv_rms(ss, H, p.eps);
   if (MODE == kPlain) {
     const float d = p.rms_div ? 1.0f / r : r;
@@ -305,12 +324,13 @@ __global__ void head_rmsnorm_kernel(T* out, const T* x, const WT* w, int64_t tok
   const T* src = x + (t * heads + h) * (int64_t)head_dim;
   T* dst = out + (t * heads + h) * (int64_t)head_dim;
   const WT* wh = w + (int64_t)h * head_dim;
-  float ss = 0.f;
+  double ss = 0.0;
   for (int i = lane; i < head_dim; i += 32) {
     const float v = ElemTraits<T>::to_float(src[i]);
-    ss += v * v;
+    ss += (double)v * (double)v;
   }
-  ss = warp_sum(ss);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   const float r = inv_rms(ss, head_dim, eps);
   for (int i = lane; i < head_dim; i += 32)
     dst[i] = ElemTraits<T>::from_float(ElemTraits<T>::to_float(src[i]) / r * ElemTraits<WT>::to_float(wh[i]));

@@ -42,6 +42,12 @@ def _rsqrt(v: torch.Tensor) -> torch.Tensor:
     return 1.0 / torch.sqrt(v)
 
 
+def _mean_sq(s: torch.Tensor) -> torch.Tensor:
+    """mean(s^2) over the last dim as the correctly rounded fp32 value (accumulated in float64): the result
+    every fp32 summation order of the reference kernels approximates, and independent of any order."""
+    return (s.double() * s.double()).mean(dim=-1, keepdim=True).float()
+
+
 # --------------------------------------------------------------------------------------
 # Part 1: residual add + RMSNorm (+ per-token int8 quant)
 # --------------------------------------------------------------------------------------
@@ -55,7 +61,7 @@ def fused_add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Te
     Returns (out, new_residual) in T."""
     T = x.dtype
     r = rt(x.float() + residual.float(), T)
-    var = (r * r).mean(dim=-1, keepdim=True)
+    var = _mean_sq(r)
     inv = _rsqrt(var + eps)
     n = rt(rt(r * inv, T) * weight.float(), T)
     return n.to(T), r.to(T)
@@ -81,7 +87,7 @@ def rms_norm_dynamic_per_token_quant(
     if residual is not None:
         s = s + residual.float()
         new_res = s.to(T)
-    var = (s * s).mean(dim=-1, keepdim=True)
+    var = _mean_sq(s)
     inv = _rsqrt(var + eps)
     n = rt(rt(s * inv, T) * weight.float(), T)
     a = n.abs().amax(dim=-1, keepdim=True)
@@ -111,7 +117,7 @@ def fused_rms_norm_dq(
     if residual is not None:
         s = s + residual.float()
     after_res = s.to(T)
-    var = (s * s).mean(dim=-1, keepdim=True)
+    var = _mean_sq(s)
     r = _rsqrt(var + eps)
     a = after_res.float()
     nw = a / r * weight.float()
@@ -136,7 +142,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float,
     if residual is not None:
         s = s + residual.float()
         after_res = s.to(T)
-    var = (s * s).mean(dim=-1, keepdim=True)
+    var = _mean_sq(s)
     r = _rsqrt(var + eps)
     d = (1.0 / r) if rms_div else r
     out = (s * d * weight.float()).to(T)
@@ -152,7 +158,7 @@ def head_rms_norm(hidden: torch.Tensor, weight: torch.Tensor, eps: float, head_o
     T = hidden.dtype
     out = hidden.clone()
     sel = hidden[:, head_offset:head_offset + head_norm, :].float()
-    var = (sel * sel).mean(dim=-1, keepdim=True)
+    var = _mean_sq(sel)
     r = _rsqrt(var + eps)
     w = weight.float().reshape(-1, hidden.shape[-1])[head_offset:head_offset + head_norm]
     out[:, head_offset:head_offset + head_norm, :] = (sel / r * w.unsqueeze(0)).to(T)

@@ -1,0 +1,268 @@
+"""GPU parity of part 1 (residual add + RMSNorm + per-token int8 quant) against the CPU oracle and the
+golden vectors.  Every call goes through the operator shims, i.e. through the C ABI of libmcop_b200.so.
+
+Tolerances (oracle/compare.py): int8 codes +-1 LSB on <= 0.01 % of elements; scales and bf16 outputs
+1e-2 relative / 1e-3 absolute; the in-place residual is bit-exact."""
+import pytest
+import torch
+
+from mcoplib_b200 import workloads as W
+from oracle import compare as C
+from oracle import ref_ops as R
+from tests.golden_io import records
+from tests.gpu_util import DEV, Canary, bits
+
+pytestmark = pytest.mark.gpu
+
+FLT_EPSILON = 1.1920928955078125e-07
+
+
+@pytest.fixture(scope="module")
+def op():
+    from mcoplib_b200 import op as _op
+    return _op
+
+
+def _run_a2(op, x, w, res, scale_ub=None):
+    T, H = x.shape
+    out = Canary((T, H), torch.int8)
+    sc = Canary((T, 1), torch.float32)
+    xg, wg = x.to(DEV), w.to(DEV)
+    rg = res.to(DEV) if res is not None else None
+    x_before = xg.clone()
+    op.rms_norm_dynamic_per_token_quant_custom(out.t, xg, wg, sc.t, 1e-6, scale_ub.to(DEV) if scale_ub is not None else None, rg)
+    torch.cuda.synchronize()
+    out.check("codes"); sc.check("scales")
+    assert torch.equal(xg, x_before), "input must not be modified"
+    return out.t.cpu(), sc.t.cpu(), (rg.cpu() if rg is not None else None)
+
+
+# shapes of the reference test (unit_test/test_fused_rms_norm_dq.py:17-22, token counts trimmed) + the benchmark shapes
+SHAPES = [(1, 1), (1, 64), (1, 1024), (1, 1025), (1, 1026), (1, 1027), (1, 1028), (1, 1029), (1, 5120), (1, 5137),
+          (83, 1), (83, 1033), (83, 2048), (83, 5120), (300, 64), (129, 5137), (256, 4096), (64, 7168), (48, 8192),
+          (3, 16384), (2, 32768), (2, 40000)]
+
+
+@pytest.mark.parametrize("T,H", SHAPES)
+@pytest.mark.parametrize("add_residual", [False, True])
+def test_norm_quant_bf16_matches_oracle(op, T, H, add_residual):
+    d = W.norm_quant_inputs(T, H)
+    res = d["residual"] if add_residual else None
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(d["x"], d["weight"], 1e-6, residual=res)
+    q, s, r = _run_a2(op, d["x"], d["weight"], res)
+    C.assert_codes(q, q_ref, f"codes {T}x{H}")
+    C.assert_close(s, s_ref, "scales")
+    if add_residual:
+        C.assert_equal(bits(r), bits(r_ref), "residual (bit-exact)")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("T,H", [(1, 64), (83, 1033), (17, 2048), (5, 5137)])
+def test_norm_quant_other_dtypes(op, dtype, T, H):
+    d = W.norm_quant_inputs(T, H, dtype=dtype)
+    scale = 1.0 / H  # the reference test scales its inputs by 1/hidden
+    x, res = (d["x"].float() * scale).to(dtype), (d["residual"].float() * scale).to(dtype)
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(x, d["weight"], 1e-6, residual=res)
+    q, s, r = _run_a2(op, x, d["weight"], res)
+    C.assert_codes(q, q_ref, f"codes {dtype}")
+    C.assert_close(s, s_ref, "scales", abs_=1e-6)
+    C.assert_equal(bits(r), bits(r_ref), "residual")
+
+
+def test_norm_quant_against_golden(op, golden):
+    """The reference's own test tolerances: allclose on scales, int8 atol=1, allclose on the residual."""
+    n = 0
+    for key, r in records(golden, "formula:unit_test/test_fused_rms_norm_dq.py:77-117"):
+        q, s, res = _run_a2(op, r["x"], r["weight"], r.get("residual"))
+        assert torch.allclose(s, r["scales"]), key
+        assert C.code_stats(q, r["codes"])["max_abs"] <= 1, key
+        if "residual_out" in r:
+            assert torch.allclose(res.float(), r["residual_out"].float()), key
+        n += 1
+    assert n >= 20
+
+
+def test_norm_quant_degenerate_rows(op):
+    T, H = 8, 1024
+    d = W.norm_quant_inputs(T, H)
+    x, res = d["x"].clone(), d["residual"].clone()
+    x[0] = 0; res[0] = 0                       # all-zero row: scale floors at FLT_EPSILON, codes are 0
+    x[1] = 0; res[1] = 0; x[1, 5] = 3.0        # one-hot row
+    x[2] = 60000.0; res[2] = 60000.0           # large values: the fp32 sum of squares must not overflow
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(x, d["weight"], 1e-6, residual=res)
+    q, s, r = _run_a2(op, x, d["weight"], res)
+    assert float(s[0]) == pytest.approx(FLT_EPSILON) and int(q[0].abs().max()) == 0
+    C.assert_codes(q, q_ref); C.assert_close(s, s_ref, abs_=1e-7); C.assert_equal(bits(r), bits(r_ref))
+    assert torch.isfinite(s).all()
+
+
+def test_norm_quant_scale_ub(op):
+    d = W.norm_quant_inputs(16, 2048)
+    ub = torch.tensor([1.5])
+    q_ref, s_ref, _ = R.rms_norm_dynamic_per_token_quant(d["x"], d["weight"], 1e-6, residual=d["residual"], scale_ub=ub)
+    q, s, _ = _run_a2(op, d["x"], d["weight"], d["residual"], scale_ub=ub)
+    assert float(s.max()) <= 1.5 / 127 + 1e-9
+    C.assert_codes(q, q_ref); C.assert_close(s, s_ref)
+    assert int(q.min()) == -128 or int(q.max()) == 127   # clamped values saturate
+
+
+def test_norm_quant_is_deterministic(op):
+    d = W.norm_quant_inputs(512, 7168)
+    a = _run_a2(op, d["x"], d["weight"], d["residual"])
+    b = _run_a2(op, d["x"], d["weight"], d["residual"])
+    for u, v in zip(a, b):
+        assert torch.equal(bits(u), bits(v))
+
+
+def test_custom_ops_wrapper(op):
+    from mcoplib_b200 import custom_ops
+    d = W.norm_quant_inputs(32, 4096)
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(d["x"], d["weight"], 1e-6, residual=d["residual"])
+    res = d["residual"].to(DEV)
+    q, s = custom_ops.rms_norm_dynamic_per_token_quant(d["x"].to(DEV), d["weight"].to(DEV), 1e-6, torch.int8, None, res)
+    assert q.dtype == torch.int8 and tuple(s.shape) == (32, 1) and s.dtype == torch.float32
+    C.assert_codes(q, q_ref); C.assert_close(s, s_ref); C.assert_equal(bits(res), bits(r_ref))
+
+
+def test_torch_library_ops(op):
+    d = W.norm_quant_inputs(64, 4096)
+    ns = getattr(torch.ops, op.torch_namespace)
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(d["x"], d["weight"], 1e-6, residual=d["residual"])
+    out = torch.empty(64, 4096, dtype=torch.int8, device=DEV); sc = torch.empty(64, 1, device=DEV); res = d["residual"].to(DEV)
+    ns.rms_norm_dynamic_per_token_quant(out, d["x"].to(DEV), d["weight"].to(DEV), sc, 1e-6, None, res)
+    C.assert_codes(out, q_ref); C.assert_close(sc, s_ref); C.assert_equal(bits(res), bits(r_ref))
+    o_ref, r2_ref = R.fused_add_rms_norm(d["x"], d["residual"], d["weight"], 1e-6)
+    x, res = d["x"].to(DEV), d["residual"].to(DEV)
+    ns.fused_add_rms_norm(x, res, d["weight"].to(DEV), 1e-6)
+    C.assert_equal(bits(res), bits(r2_ref)); C.assert_close(x, o_ref)
+
+
+@pytest.mark.parametrize("T,H", [(1, 8), (64, 4096), (7, 1030), (33, 8192), (5, 777)])
+def test_fused_add_rms_norm(op, T, H):
+    d = W.norm_quant_inputs(T, H)
+    o_ref, r_ref = R.fused_add_rms_norm(d["x"], d["residual"], d["weight"], 1e-6)
+    x, res = d["x"].to(DEV), d["residual"].to(DEV)
+    op.fused_add_rms_norm(x, res, d["weight"].to(DEV), 1e-6)
+    C.assert_equal(bits(res), bits(r_ref), "residual"); C.assert_close(x, o_ref, "out")
+    # at most a handful of bf16 roundings may flip through a 1-ulp difference of the row scalar
+    assert int((bits(x) != bits(o_ref)).sum()) <= max(2, x.numel() // 2000)
+
+
+def test_fused_add_rms_norm_strided_input(op):
+    d = W.norm_quant_inputs(40, 2048)
+    big = torch.zeros(40, 3 * 2048, dtype=torch.bfloat16, device=DEV)
+    view = big[:, 2048:4096]
+    view.copy_(d["x"])
+    res = d["residual"].to(DEV)
+    o_ref, r_ref = R.fused_add_rms_norm(d["x"], d["residual"], d["weight"], 1e-6)
+    op.fused_add_rms_norm(view, res, d["weight"].to(DEV), 1e-6)
+    C.assert_equal(bits(res), bits(r_ref)); C.assert_close(view, o_ref)
+    assert float(big[:, :2048].abs().max()) == 0 and float(big[:, 4096:].abs().max()) == 0
+    (key, g), = records(pytest.importorskip("tests.golden_io").load_golden(),
+                        "formula:benchmark/runners/mcoplib_mxbenchmark_fused_add_rms_norm_runners.py:36-49")
+    x, r = g["x"].to(DEV), g["residual"].to(DEV)
+    op.fused_add_rms_norm(x, r, g["weight"].to(DEV), 1e-6)
+    C.assert_equal(bits(r), bits(g["residual_out"]), key); C.assert_close(x, g["out"], key, rel=2e-2, abs_=2e-2)
+
+
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("T,H,with_res", [(16, 4096, True), (9, 1030, True), (16, 7168, False), (3, 333, False)])
+def test_fused_rms_norm_dq_nine_arguments(op, wdtype, T, H, with_res):
+    """PARITY UNPINNED in the reference; checked against the restatement of op/fused_rms_norm_dq.cu:69-186."""
+    d = W.norm_quant_inputs(T, H)
+    g = torch.Generator().manual_seed(3)
+    w = d["weight"].to(wdtype)
+    smooth = (0.5 + torch.rand(H, generator=g)).to(wdtype)
+    res = d["residual"] if with_res else None
+    q_ref, s_ref, ar_ref, an_ref = R.fused_rms_norm_dq(d["x"], w, smooth, 1e-6, residual=res)
+    out = torch.empty(T, H, dtype=torch.int8, device=DEV); sc = torch.empty(T, device=DEV)
+    ar = torch.empty(T, H, dtype=torch.bfloat16, device=DEV); an = torch.empty_like(ar)
+    op.rms_norm_dynamic_per_token_quant(out, d["x"].to(DEV), w.to(DEV), smooth.to(DEV), sc, 1e-6, ar, an,
+                                        res.to(DEV) if with_res else None)
+    C.assert_equal(bits(ar), bits(ar_ref), "after_res"); C.assert_close(an, an_ref, "after_norm")
+    C.assert_close(sc.reshape(-1, 1), s_ref, "scales"); C.assert_codes(out, q_ref)
+
+
+@pytest.mark.parametrize("rms_div", [False, True])
+@pytest.mark.parametrize("T,H,with_res", [(8, 1024, True), (5, 4096, False), (4, 999, True)])
+def test_rms_norm(op, rms_div, T, H, with_res, golden):
+    d = W.norm_quant_inputs(T, H)
+    res = d["residual"] if with_res else None
+    o_ref, ar_ref = R.rms_norm(d["x"], d["weight"], 1e-6, residual=res, rms_div=rms_div)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    ar = torch.empty_like(out) if with_res else None
+    op.rms_norm(out, d["x"].to(DEV), d["weight"].to(DEV), 1e-6, ar, res.to(DEV) if with_res else None, rms_div)
+    C.assert_close(out, o_ref)
+    if with_res:
+        C.assert_equal(bits(ar), bits(ar_ref))
+    if rms_div and with_res and H == 1024:
+        (key, g), = records(golden, "ref:unit_test/test_rms_norm.py:rms_norm_ref")
+        out = torch.empty(8, 1024, dtype=torch.bfloat16, device=DEV); ar = torch.empty_like(out)
+        op.rms_norm(out, g["x"].to(DEV), g["weight"].to(DEV), 1e-6, ar, g["residual"].to(DEV), True)
+        C.assert_close(out, g["out"], key, rel=2e-2, abs_=2e-2)
+
+
+def test_head_rms_norm_and_scale_dynamic_quant(op, golden):
+    (key, g), = records(golden, "ref:unit_test/test_head_rms_norm.py:head_rms_norm_ref")
+    hid = g["hidden"].to(DEV)
+    out = hid.clone()
+    op.head_rms_norm(out, hid, g["weight"].to(DEV), 1e-5, 0, g["head_norm"])
+    ref = R.head_rms_norm(g["hidden"], g["weight"], 1e-5, 0, g["head_norm"])
+    C.assert_close(out, ref, key); C.assert_close(out, g["out"], key, rel=2e-2, abs_=2e-2)
+    for key, g in records(golden, "ref:unit_test/test_scale_dynamic_quant.py:scale_dynamic_quant_cpu"):
+        q, s = op.scale_dynamic_quant(g["hidden"].to(DEV), g["smooth"].to(DEV))
+        assert q.shape == g["hidden"].shape and s.numel() == g["scales"].numel()
+        assert torch.allclose(s.cpu(), g["scales"].reshape(-1), rtol=1e-5), key
+        assert C.code_stats(q.cpu(), g["codes"])["max_abs"] <= 1, key
+
+
+def test_norm_quant_full_size_properties(op):
+    """Benchmark configuration 4 (32768 x 8192): size-independent properties on the whole output, and the oracle
+    on a sample of rows."""
+    T, H = 32768, 8192
+    d = W.norm_quant_inputs(T, H, gen_device=DEV)
+    x, res, w = d["x"], d["residual"], d["weight"]
+    res0 = res.clone()
+    codes = torch.empty(T, H, dtype=torch.int8, device=DEV); sc = torch.empty(T, 1, device=DEV)
+    op.rms_norm_dynamic_per_token_quant_custom(codes, x, w, sc, 1e-6, None, res)
+    # residual == bf16(x + residual) exactly
+    assert torch.equal(res, (x.float() + res0.float()).bfloat16())
+    # every row uses the full code range: its abs-max element maps to +-127, nothing beyond
+    amax = codes.to(torch.int16).abs().amax(dim=1)
+    assert int(amax.min()) == 127 and int(amax.max()) == 127
+    # scale * 127 equals the abs-max of the normalised row (checked with torch on the GPU in fp32)
+    s = x.float() + res0.float()
+    n = ((s * torch.rsqrt((s * s).mean(-1, keepdim=True) + 1e-6)).bfloat16() * w).float()
+    assert torch.allclose(sc * 127.0, n.abs().amax(-1, keepdim=True), rtol=1e-2, atol=1e-3)
+    # dequantised codes reproduce the normalised row to half a code
+    # (torch's rsqrt may move n by one bf16 ulp, 2^-8 relative, on some elements)
+    assert bool(((codes.float() * sc - n).abs() <= 0.51 * sc + 0.008 * n.abs()).all())
+    # oracle on 256 sampled rows
+    idx = torch.arange(0, T, T // 256, device=DEV)
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(x[idx].cpu(), w.cpu(), 1e-6, residual=res0[idx].cpu())
+    C.assert_codes(codes[idx], q_ref); C.assert_close(sc[idx], s_ref); C.assert_equal(bits(res[idx]), bits(r_ref))
+
+
+def test_c_abi_called_directly(op):
+    """One call through ctypes with raw pointers: the binding a non-torch host would use."""
+    from mcoplib_b200 import cabi
+    from tests.gpu_util import stream_ptr
+    lib = cabi.load()
+    d = W.norm_quant_inputs(96, 4096)
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(d["x"], d["weight"], 1e-6, residual=d["residual"])
+    x, w, res = d["x"].to(DEV), d["weight"].to(DEV), d["residual"].to(DEV)
+    out = torch.empty(96, 4096, dtype=torch.int8, device=DEV); sc = torch.empty(96, device=DEV)
+    rc = lib.mcop_add_rmsnorm_quant_i8(out.data_ptr(), sc.data_ptr(), x.data_ptr(), 4096, w.data_ptr(), res.data_ptr(), None,
+                                       96, 4096, 1e-6, cabi.BF16_CODE, stream_ptr())
+    cabi.check(rc, lib)
+    torch.cuda.synchronize()
+    C.assert_codes(out, q_ref); C.assert_close(sc.reshape(-1, 1), s_ref); C.assert_equal(bits(res), bits(r_ref))
+    # a misaligned row stride falls back to the scalar kernel and still matches
+    xs = torch.zeros(96, 4099, dtype=torch.bfloat16, device=DEV)
+    xs[:, :4096] = d["x"].to(DEV)
+    res = d["residual"].to(DEV)
+    rc = lib.mcop_add_rmsnorm_quant_i8(out.data_ptr(), sc.data_ptr(), xs.data_ptr(), 4099, w.data_ptr(), res.data_ptr(), None,
+                                       96, 4096, 1e-6, cabi.BF16_CODE, stream_ptr())
+    cabi.check(rc, lib)
+    torch.cuda.synchronize()
+    C.assert_codes(out, q_ref); C.assert_equal(bits(res), bits(r_ref))

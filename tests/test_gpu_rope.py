@@ -1,0 +1,245 @@
+"""GPU parity of part 2 (RoPE on Q/K, int8 KV stores, paged copy, and the fused RoPE + int8 paged store)
+against the CPU oracle and the golden vectors, through the operator shims over the C ABI.
+
+Rotated bf16 outputs are compared bit-exactly where the oracle evaluates the same fp32 operation sequence
+(products and sums rounded separately); int8 codes: +-1 LSB on <= 0.01 %."""
+import pytest
+import torch
+
+from mcoplib_b200 import workloads as W
+from oracle import compare as C
+from oracle import ref_ops as R
+from tests.golden_io import records
+from tests.gpu_util import DEV, Canary, bits, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def op():
+    from mcoplib_b200 import op as _op
+    return _op
+
+
+def _fused(op, d, ks, vs, is_neox=True):
+    g = to_dev(d)
+    kc = Canary(tuple(d["key_cache"].shape), torch.int8)
+    vc = Canary(tuple(d["value_cache"].shape), torch.int8)
+    v_before = g["value"].clone()
+    op.rope_kv_store_int8(g["positions"], g["query"], g["key"], g["value"], d["head_size"], g["cos_sin_cache"], is_neox,
+                          kc.t, vc.t, g["slot_mapping"], ks.to(DEV), vs.to(DEV))
+    torch.cuda.synchronize()
+    kc.check("key cache"); vc.check("value cache")
+    assert torch.equal(g["value"], v_before)
+    return g["query"].cpu(), g["key"].cpu(), kc.t.cpu(), vc.t.cpu()
+
+
+def _oracle_fused(d, is_neox=True):
+    Hkv, D = d["key_cache"].shape[2], d["head_size"]
+    _, kr = R.rotary_embedding(d["positions"], d["query"], d["key"], D, d["cos_sin_cache"], is_neox)
+    ks, vs = W.kv_scales(kr, d["value"], Hkv, D)
+    q, k, kc, vc = R.rope_kv_store_int8(d["positions"], d["query"], d["key"], d["value"], D, d["cos_sin_cache"], is_neox,
+                                        d["key_cache"], d["value_cache"], d["slot_mapping"], ks, vs)
+    return ks, vs, q, k, kc, vc
+
+
+def test_config2_fused_rope_kv_store(op):
+    """Benchmark configuration 2 in full: 4096 tokens, 32/8 heads, D 128, fp32 cos/sin cache, 2048 blocks of 16."""
+    d = W.rope_kv_inputs(4096, 32, 8, 128, 8192)
+    ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
+    q, k, kc, vc = _fused(op, d, ks, vs)
+    C.assert_equal(bits(q), bits(q_ref), "query"); C.assert_equal(bits(k), bits(k_ref), "key")
+    C.assert_codes(kc, kc_ref, "key cache"); C.assert_codes(vc, vc_ref, "value cache")
+    # untouched slots stay zero; every written slot reaches the full code range for at least one head overall
+    used = torch.zeros(2048 * 16, dtype=torch.bool); used[d["slot_mapping"]] = True
+    assert int(kc.reshape(-1, 8 * 128)[~used].abs().max()) == 0
+    assert int(kc.abs().max()) == 127 and int(vc.abs().max()) == 127
+
+
+@pytest.mark.parametrize("tokens,hq,hkv,D", [(1, 1, 1, 64), (37, 4, 4, 128), (130, 8, 2, 96), (64, 16, 1, 256), (50, 6, 2, 32)])
+@pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
+def test_fused_shapes_and_cache_dtypes(op, tokens, hq, hkv, D, cache_dtype):
+    d = W.rope_kv_inputs(tokens, hq, hkv, D, 512, num_blocks=16)
+    d["cos_sin_cache"] = d["cos_sin_cache"].to(cache_dtype)
+    ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
+    q, k, kc, vc = _fused(op, d, ks, vs)
+    C.assert_equal(bits(q), bits(q_ref)); C.assert_equal(bits(k), bits(k_ref))
+    C.assert_codes(kc, kc_ref); C.assert_codes(vc, vc_ref)
+
+
+def test_fused_skips_negative_and_out_of_range_slots(op):
+    d = W.rope_kv_inputs(64, 4, 2, 128, 512, num_blocks=8)
+    d["slot_mapping"][::3] = -1
+    ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
+    q, k, kc, vc = _fused(op, d, ks, vs)
+    C.assert_equal(bits(q), bits(q_ref)); C.assert_equal(bits(k), bits(k_ref))   # rotation still happens
+    C.assert_equal(kc, kc_ref); C.assert_equal(vc, vc_ref)
+    d2 = W.rope_kv_inputs(64, 4, 2, 128, 512, num_blocks=8)
+    d2["slot_mapping"][5] = 8 * 16 + 3                                              # beyond the cache: skipped, not written
+    keep = torch.ones(64, dtype=torch.bool); keep[5] = False
+    ks, vs = W.kv_scales(R.rotary_embedding(d2["positions"], d2["query"], d2["key"], 128, d2["cos_sin_cache"], True)[1], d2["value"], 2, 128)
+    _fused(op, d2, ks, vs)
+
+
+def test_fused_gptj_and_partial_rotation_use_the_generic_kernel(op):
+    for is_neox, rot in [(False, 128), (True, 64), (False, 64)]:
+        d = W.rope_kv_inputs(40, 4, 2, 128, 256, num_blocks=8)
+        d["cos_sin_cache"] = W.cos_sin_cache(256, rot, 10000.0)
+        ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d, is_neox)
+        q, k, kc, vc = _fused(op, d, ks, vs, is_neox)
+        C.assert_equal(bits(q), bits(q_ref)); C.assert_equal(bits(k), bits(k_ref))
+        C.assert_codes(kc, kc_ref); C.assert_codes(vc, vc_ref)
+
+
+@pytest.mark.parametrize("is_neox", [True, False])
+@pytest.mark.parametrize("cache_dtype", [torch.bfloat16, torch.float32])
+def test_vllm_rotary_embedding(op, is_neox, cache_dtype, golden):
+    ns = getattr(torch.ops, op.torch_namespace)
+    d = W.rope_kv_inputs(100, 8, 2, 128, 1024, num_blocks=8)
+    cache = d["cos_sin_cache"].to(cache_dtype)
+    q_ref, k_ref = R.rotary_embedding(d["positions"], d["query"], d["key"], 128, cache, is_neox)
+    q, k = d["query"].to(DEV), d["key"].to(DEV)
+    ns.rotary_embedding(d["positions"].to(DEV), q, k, 128, cache.to(DEV), is_neox)
+    C.assert_equal(bits(q), bits(q_ref)); C.assert_equal(bits(k), bits(k_ref))
+    # key=None, 3-D query view, 2-D positions
+    q3 = d["query"].to(DEV).view(4, 25, 8, 128)
+    ns.rotary_embedding(d["positions"].to(DEV).view(4, 25), q3, None, 128, cache.to(DEV), is_neox)
+    C.assert_equal(bits(q3.reshape(100, -1)), bits(q_ref))
+    # golden vectors produced by the reference's apply_rope_ref (fp32 form)
+    if cache_dtype == torch.float32:
+        for key, g in records(golden, "ref:benchmark/runners/mcoplib_mxbenchmark_batched_rotary_embedding_runners.py:apply_rope_ref"):
+            if bool(g["is_neox"]) != is_neox:
+                continue
+            qq = g["query"].reshape(g["query"].shape[0], -1).to(DEV)
+            ns.rotary_embedding(g["positions"].to(DEV), qq, None, 128, g["cos_sin_cache"].to(DEV), is_neox)
+            C.assert_equal(bits(qq.reshape(g["out"].shape)), bits(g["out"]), key)
+
+
+def test_packed_rotary_embedding(op, golden):
+    (key, g), = records(golden, "ref:benchmark/runners/mcoplib_mxbenchmark_rotary_embeding_runners.py:_torch_rope_impl")
+    n = g["packed_qkv"].shape[0]
+    out = torch.full_like(g["packed_qkv"], 7.0).to(DEV)
+    op.rotary_embedding(g["packed_qkv"].to(DEV), torch.tensor([n], dtype=torch.int32, device=DEV),
+                        torch.tensor([0, n], dtype=torch.int32, device=DEV), torch.tensor([0], dtype=torch.int32, device=DEV),
+                        g["cos"].to(DEV), g["sin"].to(DEV), out, g["q_head_num"], g["kv_head_num"])
+    nqk = g["q_head_num"] + g["kv_head_num"]
+    C.assert_equal(bits(out[:, :nqk]), bits(g["out"][:, :nqk]), key)
+    assert bool((out[:, nqk:] == 7.0).all()), "V heads of the output must not be touched"
+    # several sequences with cache offsets
+    T, Hq, Hkv, D = 90, 6, 2, 128
+    packed = W.per_token("randn", 30, 0, T, (Hq + 2 * Hkv) * D, torch.bfloat16).reshape(T, Hq + 2 * Hkv, D)
+    accum = torch.tensor([0, 20, 21, 90], dtype=torch.int32); q_len = torch.tensor([20, 1, 69], dtype=torch.int32)
+    cache_lens = torch.tensor([5, 400, 0], dtype=torch.int32)
+    cs = W.cos_sin_cache(512, D, 500000.0)
+    cos, sin = cs[:, :D // 2].contiguous(), cs[:, D // 2:].contiguous()
+    base = torch.zeros_like(packed)
+    ref = R.rotary_embedding_packed(packed, q_len, accum, cache_lens, cos, sin, base, Hq, Hkv)
+    out = base.to(DEV)
+    op.rotary_embedding(packed.to(DEV), q_len.to(DEV), accum.to(DEV), cache_lens.to(DEV), cos.to(DEV), sin.to(DEV), out, Hq, Hkv, 0)
+    C.assert_equal(bits(out), bits(ref))
+
+
+def test_fused_rope_fwd(op):
+    S, H, D = 70, 8, 128
+    qkv = W.per_token("randn", 31, 0, S, 3 * H * D, torch.bfloat16).reshape(S, 3, H, D)
+    cs = W.cos_sin_cache(256, D, 10000.0)
+    cos, sin = cs[:, :D // 2].bfloat16().contiguous(), cs[:, D // 2:].bfloat16().contiguous()
+    idx = torch.randint(0, 256, (S,), generator=torch.Generator().manual_seed(1))
+    for indexes in (None, idx):
+        ref = R.fused_rope_fwd(qkv, cos, sin, indexes)
+        g = qkv.to(DEV)
+        ret = op.fused_rope_fwd(g, cos.to(DEV), sin.to(DEV), indexes.to(DEV) if indexes is not None else None, False)
+        assert ret.data_ptr() == g.data_ptr()
+        C.assert_equal(bits(g), bits(ref))
+    with pytest.raises(RuntimeError):
+        op.fused_rope_fwd(qkv.float().to(DEV), cos.to(DEV), sin.to(DEV), None, False)
+
+
+def test_store_kv_cache_against_golden(op, golden):
+    for key, g in records(golden, "ref:unit_test/test_store_kv.py:run_reference_impl"):
+        kc = torch.zeros_like(g["k_cache"]).to(DEV); vc = torch.zeros_like(kc)
+        op.store_kv_cache_cuda_interface(g["packed_qkv"].to(DEV), g["q_lens"].to(DEV), g["accum_q_lens"].to(DEV),
+                                         g["cache_lens"].to(DEV), g["cache_slot_ids"].to(DEV), kc, vc, g["k_scale"].to(DEV),
+                                         g["v_scale"].to(DEV), len(g["q_lens"]), g["q_head_num"], g["kv_head_num"])
+        # reference tolerance atol=0.5 on integers == exact
+        C.assert_equal(kc, g["k_cache"], key + " k"); C.assert_equal(vc, g["v_cache"], key + " v")
+    # strided cache view
+    g = records(golden, "ref:unit_test/test_store_kv.py:run_reference_impl")[1][1]
+    big = torch.zeros(2, g["kv_head_num"], 48, 256, dtype=torch.int8, device=DEV)
+    kc, vc = big[..., :128], big[..., 128:]
+    op.store_kv_cache_cuda_interface(g["packed_qkv"].to(DEV), g["q_lens"].to(DEV), g["accum_q_lens"].to(DEV), g["cache_lens"].to(DEV),
+                                     g["cache_slot_ids"].to(DEV), kc, vc, g["k_scale"].to(DEV), g["v_scale"].to(DEV), 2,
+                                     g["q_head_num"], g["kv_head_num"])
+    C.assert_equal(kc, g["k_cache"]); C.assert_equal(vc, g["v_cache"])
+
+
+def test_reshape_and_cache_flash(op):
+    ns = getattr(torch.ops, op.torch_namespace + "_cache_ops")
+    T, Hkv, D, bs, nb = 200, 4, 128, 16, 32
+    key = W.per_token("randn", 40, 0, T, Hkv * D, torch.bfloat16).reshape(T, Hkv, D)
+    val = W.per_token("randn", 41, 0, T, Hkv * D, torch.bfloat16).reshape(T, Hkv, D)
+    slots = torch.randperm(nb * bs, generator=torch.Generator().manual_seed(2))[:T].to(torch.int64)
+    slots[7] = -1
+    kc0 = torch.zeros(nb, bs, Hkv, D, dtype=torch.bfloat16)
+    kc_ref, vc_ref = R.reshape_and_cache_flash(key, val, kc0, kc0.clone(), slots)
+    one = torch.ones(1, device=DEV)
+    for layout in ("NHD", "HND"):
+        if layout == "NHD":
+            kc = kc0.clone().to(DEV); vc = kc0.clone().to(DEV)
+        else:  # [nb, Hkv, bs, D] storage viewed as [nb, bs, Hkv, D]
+            kc = torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=DEV).permute(0, 2, 1, 3)
+            vc = torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=DEV).permute(0, 2, 1, 3)
+        ns.reshape_and_cache_flash(key.to(DEV), val.to(DEV), kc, vc, slots.to(DEV), "auto", one, one)
+        C.assert_equal(bits(kc.contiguous()), bits(kc_ref), layout); C.assert_equal(bits(vc.contiguous()), bits(vc_ref), layout)
+        # the reference's own check: gather back through the slot mapping
+        ok = slots >= 0
+        blk, off = (slots[ok] // bs).to(DEV), (slots[ok] % bs).to(DEV)
+        assert torch.equal(kc[blk, off].cpu(), key[ok])
+    with pytest.raises(RuntimeError):
+        ns.reshape_and_cache_flash(key.to(DEV), val.to(DEV), kc, vc, slots.to(DEV), "fp8", one, one)
+
+
+def test_config4_rope_kv_full_size_properties(op):
+    """Benchmark configuration 4's RoPE stage (32768 tokens, 64/8 heads, positions < 131072): properties over
+    the whole output, the oracle on a sample of tokens."""
+    T, Hq, Hkv, D = 32768, 64, 8, 128
+    d = W.rope_kv_inputs(T, Hq, Hkv, D, 131072, gen_device=DEV)
+    q0, k0 = d["query"].clone(), d["key"].clone()
+    kr = k0.clone()
+    op.vllm_rotary_embedding(d["positions"], q0.clone(), kr, D, d["cos_sin_cache"], True)
+    ks, vs = W.kv_scales(kr, d["value"], Hkv, D)
+    op.rope_kv_store_int8(d["positions"], d["query"], d["key"], d["value"], D, d["cos_sin_cache"], True, d["key_cache"],
+                          d["value_cache"], d["slot_mapping"], ks, vs)
+    assert torch.equal(d["key"], kr), "fused and unfused rotation agree bit for bit"
+    # rotation preserves the norm of every (x, y) pair up to bf16 rounding
+    def pair_norm(t, H):
+        t = t.float().reshape(T, H, 2, D // 2)
+        return (t[:, :, 0] ** 2 + t[:, :, 1] ** 2).sum(-1)
+    assert torch.allclose(pair_norm(d["query"], Hq), pair_norm(q0, Hq), rtol=2e-2)
+    # round trip: cache[slot] * scale reproduces the rotated K / the V to half a code
+    blk, off = d["slot_mapping"] // 16, d["slot_mapping"] % 16
+    kdq = d["key_cache"][blk, off].float() * ks.view(1, Hkv, 1)
+    vdq = d["value_cache"][blk, off].float() * vs.view(1, Hkv, 1)
+    assert float((kdq - d["key"].float().view(T, Hkv, D)).abs().div(ks.view(1, Hkv, 1)).max()) <= 0.5 + 1e-3
+    assert float((vdq - d["value"].float().view(T, Hkv, D)).abs().div(vs.view(1, Hkv, 1)).max()) <= 0.5 + 1e-3
+    assert int(d["key_cache"].abs().max()) == 127 and int(d["value_cache"].abs().max()) == 127
+    # oracle on 128 sampled tokens
+    idx = torch.arange(0, T, T // 128, device=DEV)
+    q_ref, k_ref = R.rotary_embedding(d["positions"][idx].cpu(), q0[idx].cpu(), k0[idx].cpu(), D, d["cos_sin_cache"].cpu(), True)
+    C.assert_equal(bits(d["query"][idx]), bits(q_ref)); C.assert_equal(bits(d["key"][idx]), bits(k_ref))
+
+
+def test_c_abi_rope_called_directly(op):
+    from mcoplib_b200 import cabi
+    from tests.gpu_util import stream_ptr
+    lib = cabi.load()
+    d = W.rope_kv_inputs(64, 8, 2, 128, 512, num_blocks=8)
+    ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
+    g = to_dev(d); ksg, vsg = ks.to(DEV), vs.to(DEV)
+    rc = lib.mcop_rope_kv_store_i8_paged(g["positions"].data_ptr(), g["query"].data_ptr(), g["key"].data_ptr(), g["value"].data_ptr(),
+                                         g["cos_sin_cache"].data_ptr(), cabi.F32_CODE, g["key_cache"].data_ptr(), g["value_cache"].data_ptr(),
+                                         g["slot_mapping"].data_ptr(), ksg.data_ptr(), vsg.data_ptr(), 64, 8, 2, 128, 128, 8 * 128, 2 * 128,
+                                         2 * 128, 16, 8, 1, cabi.BF16_CODE, stream_ptr())
+    cabi.check(rc, lib)
+    torch.cuda.synchronize()
+    C.assert_equal(bits(g["query"]), bits(q_ref)); C.assert_codes(g["key_cache"], kc_ref); C.assert_codes(g["value_cache"], vc_ref)
