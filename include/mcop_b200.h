@@ -37,6 +37,11 @@ enum {
 int mcop_version(void);
 /* Text of the last error on the calling thread ("" if none). */
 const char* mcop_last_error(void);
+/* Device-side status of the current device.  The row-pipeline kernels bound every wait on an asynchronous
+ * copy; a kernel whose wait runs out records a non-zero code, stops and returns instead of hanging.
+ * Returns that code (0 = none) and clears it, or a negative MCOP_ERR_*.  SYNCHRONISES with the device.
+ * No counterpart in the reference (its kernels have no waits). */
+int mcop_device_error(void);
 
 /* ------------------------------------------------------------------------------------------------
  * Part 1 - residual add + RMSNorm (+ per-token int8 quantisation)

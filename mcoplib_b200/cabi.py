@@ -17,6 +17,7 @@ P, I64, I32, F32, SZ = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_size_t
 SIGNATURES = {
     "mcop_version": (I32, []),
     "mcop_last_error": (C.c_char_p, []),
+    "mcop_device_error": (I32, []),
     "mcop_fused_add_rmsnorm": (I32, [P, I64, P, P, I64, I64, F32, I32, P]),
     "mcop_add_rmsnorm_quant_i8": (I32, [P, P, P, I64, P, P, P, I64, I64, F32, I32, P]),
     "mcop_rmsnorm_smooth_quant_i8": (I32, [P, P, P, P, P, P, P, P, I64, I64, F32, I32, I32, P]),

@@ -2,7 +2,10 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "common.cuh"
+#include "tma_pipe.cuh"
 
 namespace mcop {
 namespace {
@@ -17,6 +20,42 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
+// Error word written by pipeline kernels whose bounded wait ran out (one per device that loads the library).
+__device__ int g_pipe_error_word = 0;
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::atomic<int*> g_err_ptr[kMaxDevices];
+std::atomic<int> g_sm_count[kMaxDevices];
+}  // namespace
+
+int* pipe_error_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  int* p = g_err_ptr[dev].load(std::memory_order_acquire);
+  if (p) return p;
+  void* sym = nullptr;
+  if (cudaGetSymbolAddress(&sym, g_pipe_error_word) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  g_err_ptr[dev].store(static_cast<int*>(sym), std::memory_order_release);
+  return static_cast<int*>(sym);
+}
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = g_sm_count[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    return 148;
+  }
+  g_sm_count[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
 int check_launch(const char* what) {
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return MCOP_OK;
@@ -26,3 +65,16 @@ int check_launch(const char* what) {
 
 extern "C" int mcop_version(void) { return 100; }
 extern "C" const char* mcop_last_error(void) { return mcop::g_error; }
+
+extern "C" int mcop_device_error(void) {
+  int* p = mcop::pipe_error_ptr();
+  if (!p) return mcop::set_error(MCOP_ERR_CUDA, "device_error: the error word of the current device is not reachable");
+  int v = 0;
+  cudaError_t e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return mcop::set_error(MCOP_ERR_CUDA, "device_error: %s", cudaGetErrorString(e));
+  if (v != 0) {
+    const int zero = 0;
+    (void)cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return v;
+}

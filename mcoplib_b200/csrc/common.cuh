@@ -166,6 +166,15 @@ __device__ __forceinline__ int q_rn_clamp(float v, int lo, int hi) {
   int q = __float2int_rn(v);  // NaN -> 0
   return max(lo, min(hi, q));
 }
+// Conversion without the (quarter-rate) float-to-int instruction: adding 1.5 * 2^23 makes the fp32 adder round v
+// to the nearest integer, ties to even, and leaves it in the low mantissa bits, so the low byte of the sum is
+// the two's-complement int8 code.  Valid for |v| < 2^22; callers guarantee -128 <= v <= 127 (and no NaN).
+__device__ __forceinline__ uint32_t rn_low_byte(float v) { return __float_as_uint(__fadd_rn(v, 12582912.0f)); }
+// packs the low bytes of four words
+__device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
 __device__ __forceinline__ uint2 pack_i8x8(const int (&q)[8]) {
   uint32_t a = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
   uint32_t b = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);

@@ -1,0 +1,437 @@
+// Part 3c of the hot path: MoE combine (gather).
+//
+// out[t] (+)= sum over the rows r of token t, in ASCENDING r, of [w(r) *] y[r], accumulated in fp32 and rounded
+// once: the result does not depend on scheduling (the reference's bf16 atomics do).
+//
+// Rows of a token are found through an inverse map: tok2row [tokens, topk] as written by the scatter, or a
+// (count, list) table built by a small inversion pre-pass when only the reference's 3-argument signature is
+// available.  The main kernel is persistent: a CTA takes chunks of up to 64 consecutive tokens, sorts each token's row
+// list in shared memory, and then streams the y rows through a ring of shared-memory stages filled by bulk
+// asynchronous copies, so the loads of the rows ahead overlap the adds of the current row.
+#include <atomic>
+
+#include "common.cuh"
+#include "tma_pipe.cuh"
+
+namespace mcop {
+namespace {
+
+struct GatherParams {
+  const __nv_bfloat16* y; const int32_t* row2tok; __nv_bfloat16* out;
+  const int32_t* tok2row; int topk;                      // direct inverse (nullable)
+  const int32_t* cnt; const int32_t* list; int cap;      // inverse built by the pre-pass
+  const int32_t* topk_ids; const float* topk_weights; const int32_t* starts; int experts;  // weighted form
+  int64_t rows; int64_t tokens; int hidden_size; int weighted; int accumulate;
+};
+
+constexpr int kMaxList = 64;    // rows of one token the row-per-CTA kernels handle without the slow scan
+constexpr int kChunkTokens = 64;
+constexpr int kPipeMaxRows = 16;  // rows per token the pipelined kernel keeps in shared memory
+
+// Inversion pre-pass: per token a counter and up to `cap` row ids (unordered; the gather sorts them).
+__global__ void gather_invert_kernel(const int32_t* __restrict__ row2tok, int32_t* cnt, int32_t* list, int64_t rows,
+                                     int64_t tokens, int cap) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int t = row2tok[r];
+  if (t < 0 || t >= tokens) return;
+  const int pos = atomicAdd(&cnt[t], 1);
+  if (pos < cap) list[(int64_t)t * cap + pos] = (int32_t)r;
+}
+
+// Weight of row r of token t: the expert owning r is the first e with starts[e+1] > r; the weight is that of
+// the first slot of t holding e (0 if none).
+__device__ __forceinline__ float row_weight(const GatherParams& p, int64_t t, int64_t r) {
+  int lo = 0, hi = p.experts - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (p.starts[mid + 1] > r) hi = mid; else lo = mid + 1;
+  }
+  for (int j = 0; j < p.topk; ++j)
+    if (p.topk_ids[t * p.topk + j] == lo) return p.topk_weights[t * p.topk + j];
+  return 0.f;
+}
+
+__device__ __forceinline__ void accumulate8(float (&acc)[8], const uint4 raw, bool weighted, float w) {
+  float f[8];
+  unpack_bf16x8(raw, f);
+#pragma unroll
+  for (int q = 0; q < 8; ++q) acc[q] = __fadd_rn(acc[q], weighted ? __fmul_rn(w, f[q]) : f[q]);
+}
+
+// Slow path shared by both vector kernels: the token owns more rows than the inverse holds, so row2tok is
+// scanned in ascending order.  Every thread walks the same rows; no shared memory, no barrier.
+template <int THREADS, int NVEC>
+__device__ void accumulate_by_scan(const GatherParams& p, int64_t t, float (&acc)[NVEC][8]) {
+  const int nv = p.hidden_size >> 3;
+  for (int64_t r = 0; r < p.rows; ++r) {
+    if (__ldg(p.row2tok + r) != (int32_t)t) continue;  // uniform over the CTA
+    const float w = p.weighted ? row_weight(p, t, r) : 1.f;
+    const __nv_bfloat16* src = p.y + r * p.hidden_size;
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      const int v = threadIdx.x + k * THREADS;
+      if (v < nv) accumulate8(acc[k], ld_nc_u4(src + v * 8), p.weighted != 0, w);
+    }
+  }
+}
+
+// Collect the rows of token t in ascending order into s_rows[0..n) (and their weights into s_w).
+// Returns n, or -1 if the token has more rows than the inverse holds.
+__device__ int gather_collect(const GatherParams& p, int64_t t, int32_t* s_rows, float* s_w, int32_t* s_tmp) {
+  __shared__ int s_n;
+  int n = 0;
+  if (p.tok2row) {
+    n = p.topk;
+    if (threadIdx.x < n) s_tmp[threadIdx.x] = p.tok2row[t * p.topk + threadIdx.x];
+  } else {
+    n = p.cnt[t];
+    if (n > p.cap || n > kMaxList) return -1;
+    if (threadIdx.x < n) s_tmp[threadIdx.x] = p.list[t * (int64_t)p.cap + threadIdx.x];
+  }
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  if (threadIdx.x < n) {
+    const int r = s_tmp[threadIdx.x];
+    if (r >= 0 && r < p.rows) {
+      int rank = 0;
+      for (int i = 0; i < n; ++i) {
+        const int o = s_tmp[i];
+        if (o >= 0 && o < p.rows && (o < r || (o == r && i < (int)threadIdx.x))) ++rank;
+      }
+      s_rows[rank] = r;
+      atomicAdd(&s_n, 1);
+    }
+  }
+  __syncthreads();
+  n = s_n;
+  if (p.weighted && threadIdx.x < n) s_w[threadIdx.x] = row_weight(p, t, s_rows[threadIdx.x]);
+  __syncthreads();
+  return n;
+}
+
+// One CTA per token, rows held in registers.  Used for small problems and for shapes the pipelined kernel
+// does not take.
+template <int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS) gather_vec(GatherParams p) {
+  __shared__ int32_t s_rows[kMaxList];
+  __shared__ int32_t s_tmp[kMaxList];
+  __shared__ float s_w[kMaxList];
+  const int64_t t = blockIdx.x;
+  const int nv = p.hidden_size >> 3;
+  __nv_bfloat16* out = p.out + t * (int64_t)p.hidden_size;
+  float acc[NVEC][8];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (p.accumulate && v < nv) {
+      Vec8<__nv_bfloat16>::load(out + v * 8, acc[i]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[i][q] = 0.f;
+    }
+  }
+  const int n = gather_collect(p, t, s_rows, s_w, s_tmp);
+  if (n >= 0) {
+    for (int r0 = 0; r0 < n; r0 += 4) {
+      uint4 raw[4][NVEC];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u < n) {
+          const __nv_bfloat16* src = p.y + (int64_t)s_rows[r0 + u] * p.hidden_size;
+#pragma unroll
+          for (int i = 0; i < NVEC; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (v < nv) raw[u][i] = ld_nc_u4(src + v * 8);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u < n) {
+          const float w = p.weighted ? s_w[r0 + u] : 1.f;
+#pragma unroll
+          for (int i = 0; i < NVEC; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (v < nv) accumulate8(acc[i], raw[u][i], p.weighted != 0, w);
+          }
+        }
+      }
+    }
+  } else {
+    accumulate_by_scan<THREADS, NVEC>(p, t, acc);
+  }
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nv) st_cs_u4(out + v * 8, pack_bf16x8(acc[i]));
+  }
+}
+
+// Persistent pipelined kernel.  Dynamic shared memory: 128 bytes of mbarriers, then `stages` row buffers.
+template <int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe(GatherParams p, int stages, int chunk, int* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int32_t s_rows[kChunkTokens][kPipeMaxRows];
+  __shared__ float s_w[kChunkTokens][kPipeMaxRows];
+  __shared__ int s_cnt[kChunkTokens];   // rows of the token; -1 = more than the table holds (slow scan)
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  unsigned char* buf = smem + 128;
+  const int H = p.hidden_size, nv = H >> 3;
+  const uint32_t row_bytes = (uint32_t)H * 2u;
+  const int64_t nchunks = (p.tokens + chunk - 1) / chunk;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  uint32_t it = 0;        // items consumed so far by this CTA (selects stage and phase)
+  uint32_t issued = 0;    // items issued so far (thread 0 only)
+  bool alive = true;
+  for (int64_t c = blockIdx.x; c < nchunks && alive; c += gridDim.x) {
+    const int64_t t0 = c * chunk;
+    const int ntok = (int)min((int64_t)chunk, p.tokens - t0);
+    // ---- phase A: one thread per token builds the token's ascending row list (and weights)
+    if (threadIdx.x < ntok) {
+      const int64_t t = t0 + threadIdx.x;
+      int rows[kPipeMaxRows];
+      int n = 0;
+      bool overflow = false;
+      if (p.tok2row) {
+        for (int j = 0; j < p.topk; ++j) {
+          const int r = p.tok2row[t * p.topk + j];
+          if (r >= 0 && r < p.rows) rows[n++] = r;
+        }
+      } else {
+        const int c0 = p.cnt[t];
+        if (c0 > p.cap) overflow = true;
+        else
+          for (int j = 0; j < c0; ++j) rows[n++] = p.list[t * (int64_t)p.cap + j];
+      }
+      if (!overflow) {
+        for (int a = 1; a < n; ++a) {  // insertion sort, n <= 16
+          const int key = rows[a];
+          int b = a - 1;
+          while (b >= 0 && rows[b] > key) { rows[b + 1] = rows[b]; --b; }
+          rows[b + 1] = key;
+        }
+        for (int j = 0; j < n; ++j) {
+          s_rows[threadIdx.x][j] = rows[j];
+          if (p.weighted) s_w[threadIdx.x][j] = row_weight(p, t, rows[j]);
+        }
+      }
+      s_cnt[threadIdx.x] = overflow ? -1 : n;
+    }
+    __syncthreads();
+    // ---- phase B: stream the rows of the chunk
+    int ptl = 0, pj = 0;  // producer cursor (thread 0)
+    auto issue_next = [&]() -> bool {  // issues the next row of the chunk, if any
+      while (ptl < ntok && (s_cnt[ptl] < 0 || pj >= s_cnt[ptl])) { ++ptl; pj = 0; }
+      if (ptl >= ntok) return false;
+      const int s = (int)(issued % (uint32_t)stages);
+      mbar_expect_tx(&full[s], row_bytes);
+      bulk_g2s(buf + (size_t)s * row_bytes, p.y + (int64_t)s_rows[ptl][pj] * H, row_bytes, &full[s]);
+      ++issued; ++pj;
+      return true;
+    };
+    if (threadIdx.x == 0)
+      for (int s = 0; s < stages; ++s)
+        if (!issue_next()) break;
+    for (int tl = 0; tl < ntok && alive; ++tl) {
+      const int64_t t = t0 + tl;
+      __nv_bfloat16* out = p.out + t * (int64_t)H;
+      float acc[NVEC][8];
+#pragma unroll
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (p.accumulate && v < nv) {
+          Vec8<__nv_bfloat16>::load(out + v * 8, acc[k]);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[k][q] = 0.f;
+        }
+      }
+      const int n = s_cnt[tl];
+      if (n < 0) {
+        accumulate_by_scan<THREADS, NVEC>(p, t, acc);
+      } else {
+        for (int j = 0; j < n; ++j) {
+          const int s = (int)(it % (uint32_t)stages);
+          const bool ok = mbar_wait_bounded(&full[s], (it / (uint32_t)stages) & 1u, err, 3);
+          if (ok) {
+            const unsigned char* src = buf + (size_t)s * row_bytes;
+            const float w = p.weighted ? s_w[tl][j] : 1.f;
+#pragma unroll
+            for (int k = 0; k < NVEC; ++k) {
+              const int v = threadIdx.x + k * THREADS;
+              if (v < nv) accumulate8(acc[k], lds_u4(src + v * 16), p.weighted != 0, w);
+            }
+          }
+          // one barrier per row: agrees on success and tells that every thread has left the stage buffer
+          if (!__syncthreads_and(ok)) { alive = false; break; }
+          ++it;
+          if (threadIdx.x == 0) {
+            proxy_fence_before_reuse();
+            issue_next();
+          }
+        }
+      }
+      if (alive) {
+#pragma unroll
+        for (int k = 0; k < NVEC; ++k) {
+          const int v = threadIdx.x + k * THREADS;
+          if (v < nv) st_cs_u4(out + v * 8, pack_bf16x8(acc[k]));
+        }
+      }
+    }
+    __syncthreads();  // the row lists are rebuilt for the next chunk
+  }
+  if (!alive && threadIdx.x == 0) {
+    // a wait ran out: drain (bounded) the copies still in flight before the CTA gives its shared memory back
+    for (uint32_t k = it; k < issued; ++k)
+      (void)mbar_wait_bounded(&full[k % (uint32_t)stages], (k / (uint32_t)stages) & 1u, err, 4);
+  }
+}
+
+// Any hidden size / alignment: one thread per element, rows found by the same inverse (or a scan).
+__global__ void __launch_bounds__(256) gather_any(GatherParams p) {
+  __shared__ int32_t s_rows[kMaxList];
+  __shared__ int32_t s_tmp[kMaxList];
+  __shared__ float s_w[kMaxList];
+  const int64_t t = blockIdx.x;
+  const int H = p.hidden_size;
+  __nv_bfloat16* out = p.out + t * (int64_t)H;
+  const int n = gather_collect(p, t, s_rows, s_w, s_tmp);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float acc = p.accumulate ? __bfloat162float(out[i]) : 0.f;
+    if (n >= 0) {
+      for (int u = 0; u < n; ++u) {
+        const float f = __bfloat162float(p.y[(int64_t)s_rows[u] * H + i]);
+        acc = __fadd_rn(acc, p.weighted ? __fmul_rn(s_w[u], f) : f);
+      }
+    } else {
+      for (int64_t r = 0; r < p.rows; ++r) {
+        if (p.row2tok[r] != (int32_t)t) continue;
+        const float w = p.weighted ? row_weight(p, t, r) : 1.f;
+        const float f = __bfloat162float(p.y[r * H + i]);
+        acc = __fadd_rn(acc, p.weighted ? __fmul_rn(w, f) : f);
+      }
+    }
+    out[i] = __float2bfloat16_rn(acc);
+  }
+}
+
+int gather_cap(int64_t tokens, int64_t rows) {
+  if (tokens <= 0) return 1;
+  int64_t c = (rows + tokens - 1) / tokens;
+  if (c < 1) c = 1;
+  if (c > 32) c = 32;
+  return (int)c;
+}
+
+template <int THREADS>
+int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t stream) {
+  const size_t row_bytes = (size_t)p.hidden_size * 2;
+  int stages = (int)((96 * 1024) / row_bytes);
+  stages = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
+  const size_t smem = 128 + (size_t)stages * row_bytes;
+  int per_sm = (int)((227 * 1024) / (smem + 10 * 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 2048 / THREADS ? 2048 / THREADS : per_sm);
+  if (per_sm > 4) per_sm = 4;
+  // chunk of tokens a CTA prepares at once: up to 64, smaller when there are too few tokens to give every CTA
+  // several chunks
+  int64_t grid = (int64_t)sm_count() * per_sm;
+  int chunk = (int)(tokens / (grid * 4));
+  chunk = chunk < 8 ? 8 : (chunk > kChunkTokens ? kChunkTokens : chunk);
+  const int64_t nchunks = (tokens + chunk - 1) / chunk;
+  if (grid > nchunks) grid = nchunks;
+  static std::atomic<int> attr_done{0};
+  if (!attr_done.load(std::memory_order_relaxed)) {
+    cudaError_t e = cudaFuncSetAttribute(gather_pipe<THREADS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_gather: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done.store(1, std::memory_order_relaxed);
+  }
+  gather_pipe<THREADS, 4><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, chunk, pipe_error_ptr());
+  return check_launch("moe_gather (pipelined)");
+}
+
+int launch_gather(GatherParams p, int64_t tokens, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (tokens == 0) return MCOP_OK;
+  MCOP_REQUIRE(tokens <= 0x7fffffffLL && p.rows <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "moe_gather: too many tokens or rows");
+  p.tokens = tokens;
+  if (p.tok2row) {
+    MCOP_REQUIRE(p.topk >= 1 && p.topk <= kMaxList, MCOP_ERR_ARGUMENT, "moe_gather: topk %d out of range with tok2row", p.topk);
+  } else {
+    const size_t need = mcop_moe_gather_workspace_bytes(tokens, p.rows);
+    MCOP_REQUIRE(workspace && workspace_bytes >= need, MCOP_ERR_WORKSPACE, "moe_gather: workspace of %zu bytes needed, %zu given",
+                 need, workspace_bytes);
+    MCOP_REQUIRE(aligned16(workspace), MCOP_ERR_ARGUMENT, "moe_gather: workspace must be 16-byte aligned");
+    int32_t* cnt = reinterpret_cast<int32_t*>(workspace);
+    p.cap = gather_cap(tokens, p.rows);
+    p.cnt = cnt;
+    p.list = cnt + ((tokens + 63) / 64) * 64;
+    cudaError_t e = cudaMemsetAsync(cnt, 0, (size_t)tokens * sizeof(int32_t), stream);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_gather: memset: %s", cudaGetErrorString(e));
+    if (p.rows > 0) {
+      const int64_t blocks = (p.rows + 255) / 256;
+      gather_invert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.row2tok, cnt, const_cast<int32_t*>(p.list), p.rows, tokens, p.cap);
+      const int rc = check_launch("moe_gather (invert)");
+      if (rc) return rc;
+    }
+  }
+  const int nv = p.hidden_size >> 3;
+  const bool vec_ok = p.hidden_size % 8 == 0 && aligned16(p.y) && aligned16(p.out) && nv <= 4096;
+  const unsigned grid = (unsigned)tokens;
+  const int per_token = p.tok2row ? p.topk : p.cap;
+  // the pipelined kernel pays off once there are a few waves of tokens; rows wider than 2048 vectors or more
+  // rows per token than its table holds take the row-per-CTA kernel
+  if (vec_ok && nv > 256 && nv <= 2048 && per_token <= kPipeMaxRows && tokens >= 1024) {
+    if (nv <= 1024) return launch_gather_pipe<256>(p, tokens, stream);
+    return launch_gather_pipe<512>(p, tokens, stream);
+  }
+  if (!vec_ok) gather_any<<<grid, 256, 0, stream>>>(p);
+  else if (nv <= 256) gather_vec<128, 2><<<grid, 128, 0, stream>>>(p);
+  else if (nv <= 1024) gather_vec<256, 4><<<grid, 256, 0, stream>>>(p);
+  else if (nv <= 2048) gather_vec<512, 4><<<grid, 512, 0, stream>>>(p);
+  else gather_vec<1024, 4><<<grid, 1024, 0, stream>>>(p);
+  return check_launch("moe_gather");
+}
+
+}  // namespace
+}  // namespace mcop
+
+using namespace mcop;
+
+extern "C" size_t mcop_moe_gather_workspace_bytes(int64_t tokens, int64_t rows) {
+  if (tokens <= 0 || rows < 0) return 0;
+  const int64_t cnt = ((tokens + 63) / 64) * 64;
+  return (size_t)(cnt + tokens * gather_cap(tokens, rows)) * sizeof(int32_t);
+}
+
+extern "C" int mcop_moe_gather(const void* y, const int32_t* row2tok, void* out, const int32_t* tok2row, int topk,
+                               int64_t tokens, int64_t rows, int64_t hidden_size, void* workspace,
+                               size_t workspace_bytes, mcop_stream_t stream) {
+  MCOP_REQUIRE(y && row2tok && out, MCOP_ERR_ARGUMENT, "moe_gather: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && rows >= 0 && hidden_size > 0 && hidden_size <= 0x7fffffff, MCOP_ERR_ARGUMENT, "moe_gather: bad sizes");
+  GatherParams p{};
+  p.y = reinterpret_cast<const __nv_bfloat16*>(y); p.row2tok = row2tok; p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.tok2row = tok2row; p.topk = topk; p.rows = rows; p.hidden_size = (int)hidden_size; p.weighted = 0; p.accumulate = 1;
+  return launch_gather(p, tokens, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_moe_gather_weighted(const void* y, const int32_t* row2tok, const int32_t* topk_ids,
+                                        const float* topk_weights, const int32_t* starts, void* out,
+                                        const int32_t* tok2row, int accumulate, int64_t tokens, int64_t rows,
+                                        int64_t hidden_size, int topk, int experts, void* workspace,
+                                        size_t workspace_bytes, mcop_stream_t stream) {
+  MCOP_REQUIRE(y && row2tok && topk_ids && topk_weights && starts && out, MCOP_ERR_ARGUMENT, "moe_gather_weighted: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && rows >= 0 && hidden_size > 0 && hidden_size <= 0x7fffffff && topk >= 1 && topk <= kMaxList && experts >= 1,
+               MCOP_ERR_ARGUMENT, "moe_gather_weighted: bad sizes");
+  GatherParams p{};
+  p.y = reinterpret_cast<const __nv_bfloat16*>(y); p.row2tok = row2tok; p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.tok2row = tok2row; p.topk = topk; p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.starts = starts;
+  p.experts = experts; p.rows = rows; p.hidden_size = (int)hidden_size; p.weighted = 1; p.accumulate = accumulate;
+  return launch_gather(p, tokens, workspace, workspace_bytes, (cudaStream_t)stream);
+}

@@ -1,0 +1,491 @@
+// Part 3b of the hot path: MoE dispatch (scatter + per-row int8 quantisation).
+//
+// Scatter is a deterministic counting sort, not a sort:
+//   rank kernel  - one CTA per tile of 512 tokens builds, in shared memory, one bitmap of the tile's tokens per
+//                  expert; popcounts give the tile's per-expert histogram and the rank of every (token, slot)
+//                  among the tile's rows of that expert.  The last CTA to finish (one atomic ticket, nobody
+//                  waits) turns the histograms into per-tile bases, counts and starts.
+//   fill kernel  - one thread per (token, slot): row = starts[e] + tile_base[tile][e] + rank; writes row2tok,
+//                  tok2row and the row's routing weight.  Rows end up ordered by (expert, token).
+//   quant kernel - persistent CTAs take work items (token super-tile, expert, part) in token-major order, so
+//                  the k readers of a token row run close together in time and the row comes from HBM once and
+//                  from L2 afterwards.  An item's rows are contiguous in the output and share the expert, so
+//                  the expert's smooth-scale slice sits in registers for the whole item while the token rows
+//                  stream through a ring of shared-memory stages filled by bulk asynchronous copies.
+// Shapes the quant kernel does not take (row length not a multiple of 8, misaligned buffers, very wide rows)
+// use a row-per-token kernel with the same arithmetic.
+#include <atomic>
+
+#include "common.cuh"
+#include "tma_pipe.cuh"
+
+namespace mcop {
+namespace {
+
+constexpr int kTileTokens = 512;
+constexpr int kTileWords = kTileTokens / 32;
+constexpr int kMaxExperts = 1024;
+constexpr int kBatchRows = 64;   // row indices staged in shared memory at a time by the quant kernel
+
+struct ScatterWs {
+  int32_t* ticket;     // [0] ticket of the rank kernel, [1] work counter of the quant kernel (64 ints reserved)
+  int32_t* tile_hist;  // [tiles, E] histogram, overwritten by the exclusive per-expert prefix over tiles
+  int32_t* rank;       // [T*k] rank of the (token, slot) inside its tile and expert, -1 if dropped
+  float* row_w;        // [T*k] routing weight of every output row
+};
+
+__host__ __device__ inline int64_t scatter_tiles(int64_t tokens) { return (tokens + kTileTokens - 1) / kTileTokens; }
+
+// dynamic shared memory: bitmap [E][kTileWords] u32, then prefix [E][kTileWords] u16
+__global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __restrict__ ids, ScatterWs ws,
+                                                           int32_t* __restrict__ counts, int32_t* __restrict__ starts,
+                                                           int64_t tokens, int topk, int E) {
+  extern __shared__ uint32_t smem_u32[];
+  uint32_t* bitmap = smem_u32;
+  uint16_t* prefix = reinterpret_cast<uint16_t*>(smem_u32 + (size_t)E * kTileWords);
+  __shared__ int is_last;
+  const int64_t tile = blockIdx.x;
+  const int64_t tok0 = tile * kTileTokens;
+  const int ntok = (int)min((int64_t)kTileTokens, tokens - tok0);
+  for (int i = threadIdx.x; i < E * kTileWords; i += blockDim.x) bitmap[i] = 0;
+  __syncthreads();
+  const int32_t* tids = ids + tok0 * topk;
+  const int n = ntok * topk;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = tids[i];
+    if (e >= 0 && e < E) {
+      const int tl = i / topk;
+      atomicOr(&bitmap[e * kTileWords + (tl >> 5)], 1u << (tl & 31));
+    }
+  }
+  __syncthreads();
+  // one half-warp per expert: exclusive prefix of the 16 word popcounts
+  {
+    const int hw = threadIdx.x >> 4, l = threadIdx.x & 15, nhw = blockDim.x >> 4;
+    for (int e0 = 0; e0 < E; e0 += nhw) {  // trip count is uniform over the warp: the shuffles need every lane
+      const int e = e0 + hw;
+      const bool valid = e < E;
+      const int c = valid ? __popc(bitmap[e * kTileWords + l]) : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o, 16);
+        if (l >= o) inc += v;
+      }
+      if (valid) {
+        prefix[e * kTileWords + l] = (uint16_t)(inc - c);
+        if (l == 15) ws.tile_hist[tile * E + e] = inc;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = tids[i];
+    int r = -1;
+    if (e >= 0 && e < E) {
+      const int tl = i / topk, wd = tl >> 5;
+      r = prefix[e * kTileWords + wd] + __popc(bitmap[e * kTileWords + wd] & ((1u << (tl & 31)) - 1u));
+    }
+    ws.rank[tok0 * topk + i] = r;
+  }
+  // ticket: the last CTA to arrive finishes the job; nobody spins
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(ws.ticket, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int ntiles = gridDim.x;
+  int32_t* cnt_s = reinterpret_cast<int32_t*>(smem_u32);  // reuse: E ints
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarp) {
+    int carry = 0;
+    for (int t0 = 0; t0 < ntiles; t0 += 32) {
+      const int t = t0 + lane;
+      const int c = t < ntiles ? __ldcg(&ws.tile_hist[(int64_t)t * E + e]) : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      if (t < ntiles) ws.tile_hist[(int64_t)t * E + e] = carry + inc - c;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) { cnt_s[e] = carry; counts[e] = carry; }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int c = e < E ? cnt_s[e] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      if (e < E) starts[e] = carry + inc - c;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+  }
+}
+
+struct ScatterQuantParams {
+  const __nv_bfloat16* hidden; const int32_t* ids; const float* weights; const float* smooth;
+  int8_t* rows; float* row_scales; int32_t* row2tok; const int32_t* starts; const int32_t* counts; int32_t* tok2row;
+  const int32_t* tile_base; const int32_t* rank; float* row_w; int32_t* work_counter;
+  int64_t tokens; int hidden_size, topk, E;
+  int supertile, parts;   // quant kernel work items: (super-tile of `supertile` tiles, expert, part of `parts`)
+};
+
+__device__ __forceinline__ int scatter_row_of(const ScatterQuantParams& p, int64_t t, int j, int& e, float& w) {
+  e = p.ids[t * p.topk + j];
+  if (e < 0 || e >= p.E) return -1;
+  // weight of the FIRST slot of the token that holds this expert
+  int jf = j;
+  for (int i = 0; i < j; ++i)
+    if (p.ids[t * p.topk + i] == e) { jf = i; break; }
+  w = p.weights[t * p.topk + jf];
+  const int64_t tile = t / kTileTokens;
+  return p.starts[e] + p.tile_base[tile * p.E + e] + p.rank[t * p.topk + j];
+}
+
+__global__ void __launch_bounds__(256) scatter_fill_kernel(ScatterQuantParams p) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= p.tokens * p.topk) return;
+  const int64_t t = i / p.topk;
+  const int j = (int)(i % p.topk);
+  int e; float w = 0.f;
+  const int row = scatter_row_of(p, t, j, e, w);
+  if (p.tok2row) p.tok2row[i] = row;
+  if (row >= 0) {
+    p.row2tok[row] = (int32_t)t;
+    p.row_w[row] = w;
+  }
+}
+
+__device__ __forceinline__ void row_scale_from_amax(float amax, float& scale_out, float& mul) {
+  scale_out = (float)((double)amax * 0.0078740157);
+  mul = 127.0f * (1.0f / amax);   // amax == 0 -> inf -> 0 * inf = NaN -> code 0
+}
+
+
+// Persistent pipelined quant kernel.  Dynamic shared memory: 128 bytes of mbarriers, then `stages` row buffers.
+template <int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) scatter_quant_pipe(ScatterQuantParams p, int stages, int* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ float red[2][33];
+  __shared__ int32_t s_tok[kBatchRows];
+  __shared__ float s_wt[kBatchRows];
+  __shared__ int s_item;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  unsigned char* buf = smem + 128;
+  const int H = p.hidden_size, nv = H >> 3;
+  const uint32_t row_bytes = (uint32_t)H * 2u;
+  const int ntiles = (int)scatter_tiles(p.tokens);
+  const int nsuper = (ntiles + p.supertile - 1) / p.supertile;
+  const int64_t nitems = (int64_t)nsuper * p.E * p.parts;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int NWARP = THREADS / 32;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  uint32_t it = 0, issued = 0, flip = 0;
+  bool alive = true;
+  while (alive) {
+    if (threadIdx.x == 0) s_item = atomicAdd(p.work_counter, 1);
+    __syncthreads();
+    const int64_t item = s_item;
+    __syncthreads();  // s_item may be rewritten only after everybody has read it
+    if (item >= nitems) break;
+    const int part = (int)(item % p.parts);
+    const int e = (int)((item / p.parts) % p.E);
+    const int sup = (int)(item / ((int64_t)p.parts * p.E));
+    const int tile_lo = sup * p.supertile;
+    const int tile_hi = min(tile_lo + p.supertile, ntiles);
+    const int base_e = p.starts[e];
+    const int rb_all = base_e + p.tile_base[(int64_t)tile_lo * p.E + e];
+    const int re_all = tile_hi < ntiles ? base_e + p.tile_base[(int64_t)tile_hi * p.E + e] : base_e + p.counts[e];
+    const int nall = re_all - rb_all;
+    const int rb = rb_all + (int)(((int64_t)nall * part) / p.parts);
+    const int re = rb_all + (int)(((int64_t)nall * (part + 1)) / p.parts);
+    if (re <= rb) continue;  // uniform over the CTA
+    // the expert's smooth-scale slice stays in registers for the whole item
+    float sm[NVEC][8];
+    const float* smp = p.smooth + (int64_t)e * H;
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      const int v = threadIdx.x + k * THREADS;
+      if (v < nv) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(smp + v * 8));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(smp + v * 8) + 1);
+        sm[k][0] = a.x; sm[k][1] = a.y; sm[k][2] = a.z; sm[k][3] = a.w;
+        sm[k][4] = b.x; sm[k][5] = b.y; sm[k][6] = b.z; sm[k][7] = b.w;
+      }
+    }
+    for (int b0 = rb; b0 < re && alive; b0 += kBatchRows) {
+      const int nb = min(kBatchRows, re - b0);
+      if (threadIdx.x < nb) {
+        s_tok[threadIdx.x] = p.row2tok[b0 + threadIdx.x];
+        s_wt[threadIdx.x] = p.row_w[b0 + threadIdx.x];
+      }
+      __syncthreads();
+      int pi = 0;  // producer cursor inside the batch (thread 0)
+      auto issue_next = [&]() {
+        if (pi >= nb) return;
+        const int s = (int)(issued % (uint32_t)stages);
+        mbar_expect_tx(&full[s], row_bytes);
+        bulk_g2s(buf + (size_t)s * row_bytes, p.hidden + (int64_t)s_tok[pi] * H, row_bytes, &full[s]);
+        ++issued; ++pi;
+      };
+      if (threadIdx.x == 0)
+        for (int s = 0; s < stages; ++s) issue_next();
+      for (int i = 0; i < nb; ++i) {
+        const int s = (int)(it % (uint32_t)stages);
+        const bool ok = mbar_wait_bounded(&full[s], (it / (uint32_t)stages) & 1u, err, 5);
+        const float w = s_wt[i];
+        const int row = b0 + i;
+        float vv[NVEC][8];
+        float amax = 0.f;
+        if (ok) {
+          const unsigned char* src = buf + (size_t)s * row_bytes;
+#pragma unroll
+          for (int k = 0; k < NVEC; ++k) {
+            const int v = threadIdx.x + k * THREADS;
+            if (v < nv) {
+              unpack_bf16x8(lds_u4(src + v * 16), vv[k]);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                vv[k][q] = vv[k][q] * w * sm[k][q];
+                amax = fmaxf(amax, fabsf(vv[k][q]));
+              }
+            }
+          }
+        }
+        amax = warp_max(amax);
+        float* rd = red[flip & 1u];
+        if (lane == 0) rd[warp] = amax;
+        // the single barrier of the row: agrees on success, publishes the warp maxima and tells that every thread
+        // has left the stage buffer (the two `red` halves alternate, so no second barrier is needed)
+        if (!__syncthreads_and(ok)) { alive = false; break; }
+        ++it; ++flip;
+        if (threadIdx.x == 0) {
+          proxy_fence_before_reuse();
+          issue_next();
+        }
+        float m = lane < NWARP ? rd[lane] : 0.f;
+        m = warp_max(m);
+        float scale, mul;
+        row_scale_from_amax(m, scale, mul);
+        if (!(m > 0.f)) mul = 0.f;  // all-zero row: codes 0 (keeps NaN out of the bit-level conversion below)
+        if (threadIdx.x == 0) p.row_scales[row] = scale;
+        int8_t* out = p.rows + (int64_t)row * H;
+#pragma unroll
+        for (int k = 0; k < NVEC; ++k) {
+          const int v = threadIdx.x + k * THREADS;
+          if (v < nv) {
+            // |v * mul| <= 127 * (1 + 2^-22): rounds into [-127, 127], no clamp needed
+            uint32_t c[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) c[q] = rn_low_byte(__fmul_rn(vv[k][q], mul));
+            st_cs_u2(out + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
+          }
+        }
+      }
+      __syncthreads();  // s_tok / s_wt are rewritten by the next batch
+    }
+  }
+  if (!alive && threadIdx.x == 0) {
+    for (uint32_t k = it; k < issued; ++k)
+      (void)mbar_wait_bounded(&full[k % (uint32_t)stages], (k / (uint32_t)stages) & 1u, err, 6);
+  }
+}
+
+// Row-per-token kernels (any shape).  They compute the row index themselves (no fill pass needed).
+template <int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS) scatter_quant_vec(ScatterQuantParams p) {
+  __shared__ float red[33];
+  const int64_t t = blockIdx.x;
+  const int nv = p.hidden_size >> 3;
+  const __nv_bfloat16* x = p.hidden + t * (int64_t)p.hidden_size;
+  float xv[NVEC][8];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nv) Vec8<__nv_bfloat16>::load_nc(x + v * 8, xv[i]);
+  }
+  for (int j = 0; j < p.topk; ++j) {
+    int e; float w = 0.f;
+    const int row = scatter_row_of(p, t, j, e, w);
+    if (threadIdx.x == 0 && p.tok2row) p.tok2row[t * p.topk + j] = row;
+    if (row < 0) continue;  // uniform over the CTA
+    const float* sm = p.smooth + (int64_t)e * p.hidden_size;
+    float vv[NVEC][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nv) {
+        const float4 s0 = __ldg(reinterpret_cast<const float4*>(sm + v * 8));
+        const float4 s1 = __ldg(reinterpret_cast<const float4*>(sm + v * 8) + 1);
+        const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          vv[i][q] = xv[i][q] * w * s[q];
+          amax = fmaxf(amax, fabsf(vv[i][q]));
+        }
+      }
+    }
+    amax = block_reduce<true>(amax, red);
+    float scale, mul;
+    row_scale_from_amax(amax, scale, mul);
+    if (threadIdx.x == 0) { p.row_scales[row] = scale; p.row2tok[row] = (int32_t)t; }
+    int8_t* out = p.rows + (int64_t)row * p.hidden_size;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nv) {
+        int c[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) c[q] = q_rn_clamp(vv[i][q] * mul, -127, 127);
+        st_cs_u2(out + v * 8, pack_i8x8(c));
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) scatter_quant_any(ScatterQuantParams p) {
+  __shared__ float red[33];
+  const int64_t t = blockIdx.x;
+  const int H = p.hidden_size;
+  const __nv_bfloat16* x = p.hidden + t * (int64_t)H;
+  for (int j = 0; j < p.topk; ++j) {
+    int e; float w = 0.f;
+    const int row = scatter_row_of(p, t, j, e, w);
+    if (threadIdx.x == 0 && p.tok2row) p.tok2row[t * p.topk + j] = row;
+    if (row < 0) continue;
+    const float* sm = p.smooth + (int64_t)e * H;
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(x[i]) * w * sm[i]));
+    amax = block_reduce<true>(amax, red);
+    float scale, mul;
+    row_scale_from_amax(amax, scale, mul);
+    if (threadIdx.x == 0) { p.row_scales[row] = scale; p.row2tok[row] = (int32_t)t; }
+    int8_t* out = p.rows + (int64_t)row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      out[i] = (int8_t)q_rn_clamp(__bfloat162float(x[i]) * w * sm[i] * mul, -127, 127);
+  }
+}
+
+template <int THREADS>
+int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
+  const size_t row_bytes = (size_t)p.hidden_size * 2;
+  int stages = (int)((80 * 1024) / row_bytes);
+  stages = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
+  const size_t smem = 128 + (size_t)stages * row_bytes;
+  int per_sm = (int)((227 * 1024) / (smem + 2 * 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 2048 / THREADS ? 2048 / THREADS : per_sm);
+  if (per_sm > 2) per_sm = 2;
+  // work items: aim at ~40 rows each so that a few items land on every CTA and the tail stays short
+  const double rows_per_tile_expert = (double)kTileTokens * p.topk / p.E;
+  int supertile = (int)((40.0 + rows_per_tile_expert - 1e-9) / rows_per_tile_expert);
+  if (supertile < 1) supertile = 1;
+  if (supertile > 64) supertile = 64;
+  int parts = (int)(supertile * rows_per_tile_expert / 40.0);
+  if (parts < 1) parts = 1;
+  if (parts > 64) parts = 64;
+  p.supertile = supertile;
+  p.parts = parts;
+  const int64_t ntiles = scatter_tiles(p.tokens);
+  const int64_t nitems = ((ntiles + supertile - 1) / supertile) * p.E * parts;
+  int64_t grid = (int64_t)sm_count() * per_sm;
+  if (grid > nitems) grid = nitems;
+  static std::atomic<int> attr_done{0};
+  if (!attr_done.load(std::memory_order_relaxed)) {
+    cudaError_t e = cudaFuncSetAttribute(scatter_quant_pipe<THREADS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done.store(1, std::memory_order_relaxed);
+  }
+  scatter_quant_pipe<THREADS, 4><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
+  return check_launch("moe_scatter_quant_i8 (quant, pipelined)");
+}
+
+}  // namespace
+}  // namespace mcop
+
+using namespace mcop;
+
+extern "C" size_t mcop_moe_scatter_workspace_bytes(int64_t tokens, int topk, int experts_per_rank) {
+  if (tokens < 0 || topk < 0 || experts_per_rank < 0) return 0;
+  const int64_t tiles = scatter_tiles(tokens);
+  return (size_t)(64 + tiles * experts_per_rank + 2 * tokens * topk) * sizeof(int32_t);
+}
+
+extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids, const float* weights,
+                                         const float* smooth, int8_t* rows, float* row_scales, int32_t* row2tok,
+                                         int32_t* counts, int32_t* starts, int32_t* tok2row, int64_t tokens,
+                                         int64_t hidden_size, int topk, int experts_per_rank, void* workspace,
+                                         size_t workspace_bytes, mcop_stream_t stream) {
+  MCOP_REQUIRE(hidden && ids && weights && smooth && rows && row_scales && row2tok && counts && starts, MCOP_ERR_ARGUMENT,
+               "moe_scatter_quant_i8: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && hidden_size > 0 && hidden_size <= 0x7fffffff && topk >= 1 && topk <= 64 && experts_per_rank >= 1,
+               MCOP_ERR_ARGUMENT, "moe_scatter_quant_i8: bad sizes");
+  MCOP_REQUIRE(experts_per_rank <= kMaxExperts, MCOP_ERR_UNSUPPORTED, "moe_scatter_quant_i8: more than %d experts per rank", kMaxExperts);
+  MCOP_REQUIRE(tokens * topk <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "moe_scatter_quant_i8: tokens*topk exceeds int32 row ids");
+  const size_t need = mcop_moe_scatter_workspace_bytes(tokens, topk, experts_per_rank);
+  MCOP_REQUIRE(workspace && workspace_bytes >= need, MCOP_ERR_WORKSPACE, "moe_scatter_quant_i8: workspace of %zu bytes needed, %zu given",
+               need, workspace_bytes);
+  MCOP_REQUIRE(aligned16(workspace), MCOP_ERR_ARGUMENT, "moe_scatter_quant_i8: workspace must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int E = experts_per_rank;
+  const int64_t tiles = scatter_tiles(tokens);
+  ScatterWs ws;
+  ws.ticket = reinterpret_cast<int32_t*>(workspace);
+  ws.tile_hist = ws.ticket + 64;
+  ws.rank = ws.tile_hist + tiles * E;
+  ws.row_w = reinterpret_cast<float*>(ws.rank + tokens * topk);
+  if (tokens == 0) {
+    cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int32_t) * E, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(starts, 0, sizeof(int32_t) * E, s);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: memset: %s", cudaGetErrorString(e));
+    return MCOP_OK;
+  }
+  cudaError_t e = cudaMemsetAsync(ws.ticket, 0, 2 * sizeof(int32_t), s);
+  MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: memset: %s", cudaGetErrorString(e));
+  const size_t smem = (size_t)E * kTileWords * (sizeof(uint32_t) + sizeof(uint16_t));
+  if (smem > 48 * 1024) {
+    e = cudaFuncSetAttribute(scatter_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  }
+  scatter_rank_kernel<<<(unsigned)tiles, 256, smem, s>>>(ids, ws, counts, starts, tokens, topk, E);
+  int rc = check_launch("moe_scatter_quant_i8 (rank)");
+  if (rc) return rc;
+  ScatterQuantParams p{};
+  p.hidden = reinterpret_cast<const __nv_bfloat16*>(hidden); p.ids = ids; p.weights = weights; p.smooth = smooth;
+  p.rows = rows; p.row_scales = row_scales; p.row2tok = row2tok; p.starts = starts; p.counts = counts; p.tok2row = tok2row;
+  p.tile_base = ws.tile_hist; p.rank = ws.rank; p.row_w = ws.row_w; p.work_counter = ws.ticket + 1;
+  p.tokens = tokens; p.hidden_size = (int)hidden_size; p.topk = topk; p.E = E;
+  const int nv = (int)(hidden_size >> 3);
+  const bool vec_ok = hidden_size % 8 == 0 && aligned16(hidden) && aligned16(smooth) && (reinterpret_cast<uintptr_t>(rows) & 7u) == 0 && nv <= 4096;
+  const unsigned grid = (unsigned)tokens;
+  if (vec_ok && nv > 256 && nv <= 2048 && tokens * topk >= 2048) {
+    const int64_t n = tokens * topk;
+    scatter_fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p);
+    rc = check_launch("moe_scatter_quant_i8 (fill)");
+    if (rc) return rc;
+    if (nv <= 1024) return launch_quant_pipe<256>(p, s);
+    return launch_quant_pipe<512>(p, s);
+  }
+  if (!vec_ok) scatter_quant_any<<<grid, 256, 0, s>>>(p);
+  else if (nv <= 256) scatter_quant_vec<128, 2><<<grid, 128, 0, s>>>(p);
+  else if (nv <= 1024) scatter_quant_vec<256, 4><<<grid, 256, 0, s>>>(p);
+  else if (nv <= 2048) scatter_quant_vec<512, 4><<<grid, 512, 0, s>>>(p);
+  else scatter_quant_vec<1024, 4><<<grid, 1024, 0, s>>>(p);
+  return check_launch("moe_scatter_quant_i8 (quant)");
+}

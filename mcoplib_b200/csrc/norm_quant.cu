@@ -7,9 +7,12 @@
 // multi-pass kernel with the same arithmetic.
 #include <math.h>
 
+#include <atomic>
 #include <initializer_list>
+#include <type_traits>
 
 #include "common.cuh"
+#include "tma_pipe.cuh"
 
 namespace mcop {
 namespace {
@@ -244,12 +247,186 @@ __global__ void __launch_bounds__(256) norm_rows_any(NormParams p) {
   for (int i = threadIdx.x; i < H; i += blockDim.x) q[i] = (int8_t)q_rn_clamp(keep[i] * inv, lo, 127);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Persistent, pipelined form of the bf16 norm + quant kernel (kQuant).
+//
+// A CTA walks the rows blockIdx.x, blockIdx.x + gridDim.x, ...  The x row and the residual row of the rows
+// `stages` ahead are already on their way into shared memory (bulk asynchronous copies completing on an
+// mbarrier), so the memory system stays busy while the CTA reduces and quantises the current row.
+// Arithmetic is the same as norm_rows_vec<bf16, bf16, kQuant>, written with packed bf16x2 instructions:
+// T(s*r) and T(T(s*r)*w) are exactly the roundings cvt.rn.bf16x2 and mul.rn.bf16x2 perform.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_bf16_pipe(NormParams p, int64_t tokens, int stages, int* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ float red[33];
+  __shared__ double red64[33];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // `stages` (<= 8) barriers in the first 128 bytes
+  unsigned char* buf = smem + 128;
+  const int H = p.hidden, nv = H >> 3;
+  const uint32_t row_bytes = (uint32_t)H * 2u;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x);
+  const __nv_bfloat16* rin = reinterpret_cast<const __nv_bfloat16*>(p.residual_in);
+  __nv_bfloat16* rout = reinterpret_cast<__nv_bfloat16*>(p.residual_out);
+  const bool has_res = rin != nullptr;
+  const uint32_t stage_bytes = has_res ? 2u * row_bytes : row_bytes;
+  const int64_t first = blockIdx.x, step = gridDim.x;
+  const int64_t n = first < tokens ? (tokens - first + step - 1) / step : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  auto issue = [&](int s, int64_t row) {
+    unsigned char* dst = buf + (size_t)s * stage_bytes;
+    mbar_expect_tx(&full[s], stage_bytes);
+    bulk_g2s(dst, x + row * p.x_stride, row_bytes, &full[s]);
+    if (has_res) bulk_g2s(dst + row_bytes, rin + row * (int64_t)H, row_bytes, &full[s]);
+  };
+  if (threadIdx.x == 0)
+    for (int s = 0; s < stages && s < n; ++s) issue(s, first + s * step);
+
+  // the norm weight stays in registers, packed as bf16 pairs, for every row this CTA handles
+  uint4 w2[NVEC];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    w2[i] = v < nv ? ld_nc_u4(reinterpret_cast<const __nv_bfloat16*>(p.weight) + v * 8) : make_uint4(0, 0, 0, 0);
+  }
+
+  int64_t i = 0;
+  for (; i < n; ++i) {
+    const int s = (int)(i % stages);
+    const bool ok = mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), err, 1);
+    if (!__syncthreads_and(ok)) break;  // uniform decision: nobody is left behind at a barrier
+    const int64_t row = first + i * step;
+    const unsigned char* xs = buf + (size_t)s * stage_bytes;
+    float sv[NVEC][8];
+    double ss = 0.0;
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      const int v = threadIdx.x + k * THREADS;
+      if (v < nv) {
+        unpack_bf16x8(lds_u4(xs + v * 16), sv[k]);
+        if (has_res) {
+          float r[8];
+          unpack_bf16x8(lds_u4(xs + row_bytes + v * 16), r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sv[k][j] += r[j];
+          st_u4(rout + row * (int64_t)H + v * 8, pack_bf16x8(sv[k]));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fma((double)sv[k][j], (double)sv[k][j], ss);  // the product is exact in double
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sv[k][j] = 0.f;
+      }
+    }
+    ss = block_sum_f64(ss, red64);  // its barrier also tells that every thread has left the stage buffer
+    if (threadIdx.x == 0 && i + stages < n) {
+      proxy_fence_before_reuse();
+      issue(s, first + (i + stages) * step);
+    }
+    const float r = inv_rms(ss, H, p.eps);
+    uint32_t n2[NVEC][4];
+    __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      const uint32_t wv[4] = {w2[k].x, w2[k].y, w2[k].z, w2[k].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t t = bf16x2_from(sv[k][2 * j] * r, sv[k][2 * j + 1] * r);
+        const __nv_bfloat162 nn = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&t), *reinterpret_cast<const __nv_bfloat162*>(&wv[j]));
+        n2[k][j] = *reinterpret_cast<const uint32_t*>(&nn);
+        amax2 = __hmax2(amax2, __habs2(nn));
+      }
+    }
+    float amax = fmaxf(__low2float(amax2), __high2float(amax2));
+    amax = block_reduce<true>(amax, red);
+    const bool clamp = p.scale_ub != nullptr;  // only an upper bound on the scale can push codes out of range
+    if (clamp) amax = fminf(amax, *p.scale_ub);
+    const float scale = fmaxf(amax / 127.0f, FLT_EPSILON);
+    const float inv = 1.0f / scale;
+    if (threadIdx.x == 0) p.scales[row] = scale;
+    int8_t* q = p.q + row * (int64_t)H;
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      const int v = threadIdx.x + k * THREADS;
+      if (v < nv) {
+        uint32_t c[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a = __fmul_rn(__uint_as_float(n2[k][j] << 16), inv);
+          float b = __fmul_rn(__uint_as_float(n2[k][j] & 0xffff0000u), inv);
+          if (clamp) {
+            a = fminf(fmaxf(a, -128.f), 127.f);
+            b = fminf(fmaxf(b, -128.f), 127.f);
+          }
+          c[2 * j] = rn_low_byte(a);      // without a bound |n * inv| <= 127 * (1 + 2^-22): always in range
+          c[2 * j + 1] = rn_low_byte(b);
+        }
+        st_cs_u2(q + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
+      }
+    }
+  }
+  if (i < n && threadIdx.x == 0) {
+    // a wait ran out: drain (bounded) what is still in flight so that no copy lands after the CTA has exited
+    for (int64_t k = i; k < n && k < i + stages; ++k)
+      (void)mbar_wait_bounded(&full[k % stages], (uint32_t)((k / stages) & 1), err, 2);
+  }
+}
+
+
+// Returns MCOP_OK / an error, or 1 when the shape does not fit the pipelined kernel.
+inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t stream) {
+  const int nv = p.hidden >> 3;
+  const size_t row_bytes = (size_t)p.hidden * 2;
+  const size_t stage_bytes = p.residual_in ? 2 * row_bytes : row_bytes;
+  int stages = (int)((110 * 1024) / stage_bytes);
+  stages = stages < 2 ? 2 : (stages > 4 ? 4 : stages);
+  const size_t smem = 128 + (size_t)stages * stage_bytes;
+  if (smem > 220 * 1024) return 1;
+  const int threads = nv <= 1024 ? 256 : 512;
+  int per_sm = (int)((227 * 1024) / (smem + 1024));
+  per_sm = per_sm < 1 ? 1 : per_sm;
+  if (per_sm > 2048 / threads) per_sm = 2048 / threads;
+  if (per_sm > 4) per_sm = 4;
+  int64_t grid = (int64_t)sm_count() * per_sm;
+  if (grid > tokens) grid = tokens;
+  int* err = pipe_error_ptr();
+  static std::atomic<int> attr_done[2];
+  auto launch = [&](auto kernel, int slot) -> int {
+    if (attr_done[slot].load(std::memory_order_relaxed) < (int)smem) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "norm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      attr_done[slot].store(220 * 1024, std::memory_order_relaxed);
+    }
+    kernel<<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, err);
+    return check_launch("norm (pipelined)");
+  };
+  if (threads == 256) return launch(norm_quant_bf16_pipe<256, 4>, 0);
+  return launch(norm_quant_bf16_pipe<512, 4>, 1);
+}
+
 template <typename T, typename WT, int MODE>
 int launch_norm(const NormParams& p, int64_t tokens, bool vec_ok, cudaStream_t stream) {
   if (tokens == 0) return MCOP_OK;
   MCOP_REQUIRE(tokens <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "norm: %lld tokens exceed the grid limit", (long long)tokens);
   const int nv = p.hidden >> 3;
   const dim3 grid((unsigned)tokens);
+  if constexpr (MODE == kQuant && std::is_same<T, __nv_bfloat16>::value) {
+    if (vec_ok && nv <= 2048) {
+      const int rc = launch_norm_pipe(p, tokens, stream);
+      if (rc != 1) return rc;  // 1 = not applicable, fall through to the row-per-CTA kernel
+    }
+  }
   if (vec_ok && nv <= 4096) {
     if (nv <= 256) norm_rows_vec<T, WT, MODE, 128, 2><<<grid, 128, 0, stream>>>(p);
     else if (nv <= 1024) norm_rows_vec<T, WT, MODE, 256, 4><<<grid, 256, 0, stream>>>(p);

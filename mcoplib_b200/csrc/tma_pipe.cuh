@@ -1,0 +1,75 @@
+// Row pipeline primitives for sm_100a: 1-D bulk asynchronous copies (TMA, cp.async.bulk, never multicast)
+// from global into shared memory, completion tracked by an mbarrier per stage.
+//
+// Usage pattern of the row-streaming kernels (one elected thread produces, every thread consumes):
+//   prologue : elected thread arms stage s (expect_tx with the byte count) and issues the copies of row s;
+//   steady   : all threads wait on stage s (bounded spin), move the row to registers, pass a CTA barrier,
+//              then the elected thread re-arms stage s for the row STAGES ahead.
+// Every wait is bounded: when the limit is hit the kernel records an error code in the per-device error word
+// (pipe_error_ptr()), stops issuing new copies, drains the copies already in flight (again bounded) and returns,
+// so a lost completion can never turn into a hang.  The host reads (and clears) the code with mcop_device_error().
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mcop {
+
+// Device address of the error word of the current device (0 = no error); set by a pipeline kernel whose bounded
+// wait ran out.  Resolved once per device with cudaGetSymbolAddress; returns nullptr if that fails.
+int* pipe_error_ptr();
+
+constexpr uint32_t kPipeSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+// makes the barrier initialisation visible to the asynchronous proxy before the first copy uses it
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// orders earlier generic-proxy accesses of shared memory before later asynchronous-proxy writes to it
+__device__ __forceinline__ void proxy_fence_before_reuse() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// global -> shared bulk copy; dst, src 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after recording `code`) if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* err, int code) {
+  for (uint32_t i = 0; i < kPipeSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  if (err) atomicCAS(err, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ uint4 lds_u4(const void* p) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(smem_addr(p)));
+  return r;
+}
+
+// Number of SMs of the current device (cached per device; no allocation, no synchronisation).
+int sm_count();
+
+}  // namespace mcop

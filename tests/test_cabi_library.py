@@ -41,7 +41,7 @@ def test_ctypes_binding_matches_header():
 def test_every_declaration_cites_the_reference():
     hdr = open(HEADER).read()
     for name in _declarations():
-        if name in ("mcop_version", "mcop_last_error", "mcop_moe_scatter_workspace_bytes", "mcop_moe_gather_workspace_bytes"):
+        if name in ("mcop_version", "mcop_last_error", "mcop_device_error", "mcop_moe_scatter_workspace_bytes", "mcop_moe_gather_workspace_bytes"):
             continue
         pos = hdr.index(name + "(")
         comment = hdr[hdr.rfind("/*", 0, pos):pos]
@@ -52,7 +52,7 @@ def test_every_declaration_cites_the_reference():
 def test_version_and_workspace_queries():
     lib = cabi.load()
     assert lib.mcop_version() >= 100
-    assert lib.mcop_moe_scatter_workspace_bytes(8192, 8, 256) == (64 + 16 * 256 + 8192 * 8) * 4
+    assert lib.mcop_moe_scatter_workspace_bytes(8192, 8, 256) == (64 + 16 * 256 + 2 * 8192 * 8) * 4
     assert lib.mcop_moe_gather_workspace_bytes(1000, 2000) == (1024 + 1000 * 2) * 4
     assert lib.mcop_moe_gather_workspace_bytes(0, 0) == 0
 

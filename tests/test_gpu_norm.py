@@ -235,8 +235,8 @@ def test_norm_quant_full_size_properties(op):
     n = ((s * torch.rsqrt((s * s).mean(-1, keepdim=True) + 1e-6)).bfloat16() * w).float()
     assert torch.allclose(sc * 127.0, n.abs().amax(-1, keepdim=True), rtol=1e-2, atol=1e-3)
     # dequantised codes reproduce the normalised row to half a code
-    # (torch's rsqrt may move n by one bf16 ulp, 2^-8 relative, on some elements)
-    assert bool(((codes.float() * sc - n).abs() <= 0.51 * sc + 0.008 * n.abs()).all())
+    # (torch's approximate rsqrt may flip either bf16 rounding of n: up to two bf16 ulps, 2^-6 relative)
+    assert bool(((codes.float() * sc - n).abs() <= 0.51 * sc + 0.02 * n.abs()).all())
     # oracle on 256 sampled rows
     idx = torch.arange(0, T, T // 256, device=DEV)
     q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(x[idx].cpu(), w.cpu(), 1e-6, residual=res0[idx].cpu())
