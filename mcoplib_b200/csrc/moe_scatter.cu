@@ -174,7 +174,7 @@ __device__ __forceinline__ void row_scale_from_amax(float amax, float& scale_out
 
 // Persistent pipelined quant kernel.  Dynamic shared memory: 128 bytes of mbarriers, then `stages` row buffers.
 template <int THREADS, int NVEC>
-__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) scatter_quant_pipe(ScatterQuantParams p, int stages, int* err) {
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_quant_pipe(ScatterQuantParams p, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float red[2][33];
   __shared__ int32_t s_tok[kBatchRows];
@@ -217,7 +217,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) scatter_qua
     const int re = rb_all + (int)(((int64_t)nall * (part + 1)) / p.parts);
     if (re <= rb) continue;  // uniform over the CTA
     // the expert's smooth-scale slice stays in registers for the whole item
-    float sm[NVEC][8];
+    // (kept as pairs: the arithmetic below uses the packed fp32x2 multiply / add of sm_100)
+    float2 sm[NVEC][4];
     const float* smp = p.smooth + (int64_t)e * H;
 #pragma unroll
     for (int k = 0; k < NVEC; ++k) {
@@ -225,8 +226,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) scatter_qua
       if (v < nv) {
         const float4 a = __ldg(reinterpret_cast<const float4*>(smp + v * 8));
         const float4 b = __ldg(reinterpret_cast<const float4*>(smp + v * 8) + 1);
-        sm[k][0] = a.x; sm[k][1] = a.y; sm[k][2] = a.z; sm[k][3] = a.w;
-        sm[k][4] = b.x; sm[k][5] = b.y; sm[k][6] = b.z; sm[k][7] = b.w;
+        sm[k][0] = make_float2(a.x, a.y); sm[k][1] = make_float2(a.z, a.w);
+        sm[k][2] = make_float2(b.x, b.y); sm[k][3] = make_float2(b.z, b.w);
       }
     }
     for (int b0 = rb; b0 < re && alive; b0 += kBatchRows) {
@@ -251,19 +252,22 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) scatter_qua
         const bool ok = mbar_wait_bounded(&full[s], (it / (uint32_t)stages) & 1u, err, 5);
         const float w = s_wt[i];
         const int row = b0 + i;
-        float vv[NVEC][8];
+        float2 vv[NVEC][4];
         float amax = 0.f;
         if (ok) {
           const unsigned char* src = buf + (size_t)s * row_bytes;
+          const float2 w2 = make_float2(w, w);
 #pragma unroll
           for (int k = 0; k < NVEC; ++k) {
             const int v = threadIdx.x + k * THREADS;
             if (v < nv) {
-              unpack_bf16x8(lds_u4(src + v * 16), vv[k]);
+              const uint4 raw = lds_u4(src + v * 16);
+              const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                vv[k][q] = vv[k][q] * w * sm[k][q];
-                amax = fmaxf(amax, fabsf(vv[k][q]));
+              for (int q = 0; q < 4; ++q) {
+                const float2 x2 = make_float2(__uint_as_float(wd[q] << 16), __uint_as_float(wd[q] & 0xffff0000u));
+                vv[k][q] = __fmul2_rn(__fmul2_rn(x2, w2), sm[k][q]);  // (x * w) * smooth, each product rounded
+                amax = fmaxf(amax, fmaxf(fabsf(vv[k][q].x), fabsf(vv[k][q].y)));
               }
             }
           }
@@ -284,6 +288,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) scatter_qua
         float scale, mul;
         row_scale_from_amax(m, scale, mul);
         if (!(m > 0.f)) mul = 0.f;  // all-zero row: codes 0 (keeps NaN out of the bit-level conversion below)
+        const float2 mul2 = make_float2(mul, mul), magic2 = make_float2(12582912.0f, 12582912.0f);
         if (threadIdx.x == 0) p.row_scales[row] = scale;
         int8_t* out = p.rows + (int64_t)row * H;
 #pragma unroll
@@ -293,7 +298,11 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) scatter_qua
             // |v * mul| <= 127 * (1 + 2^-22): rounds into [-127, 127], no clamp needed
             uint32_t c[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) c[q] = rn_low_byte(__fmul_rn(vv[k][q], mul));
+            for (int q = 0; q < 4; ++q) {
+              const float2 r2 = __fadd2_rn(__fmul2_rn(vv[k][q], mul2), magic2);  // see rn_low_byte()
+              c[2 * q] = __float_as_uint(r2.x);
+              c[2 * q + 1] = __float_as_uint(r2.y);
+            }
             st_cs_u2(out + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
           }
         }
@@ -386,12 +395,14 @@ __global__ void __launch_bounds__(256) scatter_quant_any(ScatterQuantParams p) {
 template <int THREADS>
 int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   const size_t row_bytes = (size_t)p.hidden_size * 2;
-  int stages = (int)((80 * 1024) / row_bytes);
-  stages = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
+  // three CTAs per SM when the rows are narrow enough (the kernel is compiled for <= 80 registers at 256 threads):
+  // each gets a third of the shared memory for its ring of row buffers
+  const int want_per_sm = THREADS <= 256 ? 3 : 1;
+  int stages = (int)(((227 * 1024) / want_per_sm - 3 * 1024) / row_bytes);
+  stages = stages < 2 ? 2 : (stages > 6 ? 6 : stages);
   const size_t smem = 128 + (size_t)stages * row_bytes;
   int per_sm = (int)((227 * 1024) / (smem + 2 * 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 2048 / THREADS ? 2048 / THREADS : per_sm);
-  if (per_sm > 2) per_sm = 2;
+  per_sm = per_sm < 1 ? 1 : (per_sm > want_per_sm ? want_per_sm : per_sm);
   // work items: aim at ~40 rows each so that a few items land on every CTA and the tail stays short
   const double rows_per_tile_expert = (double)kTileTokens * p.topk / p.E;
   int supertile = (int)((40.0 + rows_per_tile_expert - 1e-9) / rows_per_tile_expert);
