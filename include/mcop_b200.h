@@ -215,6 +215,29 @@ int mcop_moe_gather_weighted(const void* y, const int32_t* row2tok, const int32_
                              int64_t hidden_size, int topk, int experts, void* workspace,
                              size_t workspace_bytes, mcop_stream_t stream);
 
+/* Size of the built-in scratch area of mcop_moe_gather_noalloc (bytes held by every GPU that loads the library). */
+#define MCOP_GATHER_NOALLOC_SCRATCH_BYTES (4u << 20)
+
+/* mcop_moe_gather for callers that have no way to hand over scratch memory.  No counterpart in the reference.
+ *
+ * Same result as mcop_moe_gather(y, row2tok, out, tok2row = NULL, ...): out[row2tok[r]] += y[r], rows of a token
+ * summed in ascending r in fp32, one bf16 rounding.  The row -> token map is inverted into a scratch table; here
+ * that table lives in a fixed MCOP_GATHER_NOALLOC_SCRATCH_BYTES array inside the library instead of a caller
+ * workspace, so the call performs no device allocation of any kind (no cudaMalloc / cudaFree, no allocating
+ * library routine, no framework allocator).  It is meant for hosts that own nothing but the input and output
+ * buffers they were given - a plugin loaded into a serving engine that has already reserved the device memory
+ * for its own pool, a bare C host without an allocator, a latency-critical loop where the implicit device
+ * synchronisation of an allocation is not acceptable.
+ *
+ * Limit: mcop_moe_gather_workspace_bytes(tokens, rows) must not exceed MCOP_GATHER_NOALLOC_SCRATCH_BYTES
+ * (e.g. 65536 tokens x 8 rows each); larger problems are rejected with MCOP_ERR_WORKSPACE and nothing runs.
+ * The first call on a device resolves the device address of the array (cudaGetSymbolAddress with that device
+ * current); make that first call outside any stream capture.  All calls on a device share the one array and it
+ * keeps the previous call's contents: every call re-zeroes the counters it needs, but two calls whose kernels
+ * overlap on the GPU (different streams, no ordering between them) race on it - serialise them. */
+int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, void* out, int64_t tokens, int64_t rows,
+                            int64_t hidden_size, mcop_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

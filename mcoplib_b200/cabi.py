@@ -37,7 +37,10 @@ SIGNATURES = {
     "mcop_moe_gather_workspace_bytes": (SZ, [I64, I64]),
     "mcop_moe_gather": (I32, [P, P, P, P, I32, I64, I64, I64, P, SZ, P]),
     "mcop_moe_gather_weighted": (I32, [P, P, P, P, P, P, P, I32, I64, I64, I64, I32, I32, P, SZ, P]),
+    "mcop_moe_gather_noalloc": (I32, [P, P, P, I64, I64, I64, P]),
 }
+
+GATHER_NOALLOC_SCRATCH_BYTES = 4 << 20
 
 F32_CODE, BF16_CODE, F16_CODE = 0, 1, 2
 

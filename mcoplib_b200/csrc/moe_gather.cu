@@ -435,3 +435,57 @@ extern "C" int mcop_moe_gather_weighted(const void* y, const int32_t* row2tok, c
   p.experts = experts; p.rows = rows; p.hidden_size = (int)hidden_size; p.weighted = 1; p.accumulate = accumulate;
   return launch_gather(p, tokens, workspace, workspace_bytes, (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the inversion table lives in a fixed array inside the library.
+// ---------------------------------------------------------------------------------------------
+namespace {
+// Scratch of mcop_moe_gather_noalloc: per-token counters followed by the per-token row lists.
+// Every device that loads the library holds these 4 MiB until the process exits.
+static __device__ __align__(256) int32_t g_gather_noalloc_scratch[MCOP_GATHER_NOALLOC_SCRATCH_BYTES / sizeof(int32_t)];
+
+constexpr int kNoallocMaxDevices = 64;
+std::atomic<void*> g_noalloc_ptr[kNoallocMaxDevices];
+
+// Device address of the scratch array on the CURRENT device.  On the host the array's name is only a handle
+// of the symbol, not an address a kernel can use, so the address is asked from the runtime, once per device.
+void* noalloc_scratch_ptr() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) {
+    set_error(MCOP_ERR_CUDA, "moe_gather_noalloc: cannot identify the current device");
+    return nullptr;
+  }
+  void* p = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (p) return p;
+  void* sym = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&sym, g_gather_noalloc_scratch);
+  if (e != cudaSuccess || !sym) {
+    (void)cudaGetLastError();
+    set_error(MCOP_ERR_CUDA, "moe_gather_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+    return nullptr;
+  }
+  g_noalloc_ptr[dev].store(sym, std::memory_order_release);
+  return sym;
+}
+}  // namespace
+
+extern "C" int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, void* out, int64_t tokens, int64_t rows,
+                                       int64_t hidden_size, mcop_stream_t stream) {
+  MCOP_REQUIRE(y && row2tok && out, MCOP_ERR_ARGUMENT, "moe_gather_noalloc: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && rows >= 0 && hidden_size > 0 && hidden_size <= 0x7fffffff, MCOP_ERR_ARGUMENT,
+               "moe_gather_noalloc: bad sizes");
+  const size_t need = mcop_moe_gather_workspace_bytes(tokens, rows);
+  MCOP_REQUIRE(need <= MCOP_GATHER_NOALLOC_SCRATCH_BYTES, MCOP_ERR_WORKSPACE,
+               "moe_gather_noalloc: %lld tokens x %lld rows need %zu bytes of scratch, the built-in area holds %u; "
+               "use mcop_moe_gather with a caller workspace",
+               (long long)tokens, (long long)rows, need, (unsigned)MCOP_GATHER_NOALLOC_SCRATCH_BYTES);
+  if (tokens == 0) return MCOP_OK;
+  void* scratch = noalloc_scratch_ptr();  // first call on this device: resolves the address (not inside a capture)
+  if (!scratch) return MCOP_ERR_CUDA;
+  GatherParams p{};
+  p.y = reinterpret_cast<const __nv_bfloat16*>(y); p.row2tok = row2tok; p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.tok2row = nullptr; p.topk = 0; p.rows = rows; p.hidden_size = (int)hidden_size; p.weighted = 0; p.accumulate = 1;
+  // launch_gather zeroes the counters it reads (cudaMemsetAsync on the stream) before the inversion pass, so
+  // whatever the previous call left in the array is harmless.
+  return launch_gather(p, tokens, scratch, MCOP_GATHER_NOALLOC_SCRATCH_BYTES, (cudaStream_t)stream);
+}

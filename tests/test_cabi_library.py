@@ -46,6 +46,7 @@ def test_every_declaration_cites_the_reference():
         pos = hdr.index(name + "(")
         comment = hdr[hdr.rfind("/*", 0, pos):pos]
         assert re.search(r"\.(cu|cuh|h|cpp)\b.*:\d+", comment, re.S) or "no reference counterpart" in comment.lower() \
+            or "no counterpart in the reference" in comment.lower() \
             or "No single reference operator" in comment, f"{name}: no reference citation"
 
 
