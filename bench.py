@@ -92,7 +92,7 @@ class Chain5:
     """Configuration 5: T tokens x hidden 7168, softmax top-2 of 8 experts."""
     name = "config5 token_sharded_chain_262144: add+rmsnorm+int8 quant -> softmax top2/8 -> scatter+int8 quant -> weighted gather"
     kernels = ["norm_quant", "softmax_topk", "scatter", "gather"]
-    launches_per_step = 5  # norm, softmax, scatter rank + scatter quant, gather (tok2row given: no inversion pass)
+    launches_per_step = 6  # norm, softmax, scatter rank + fill + quant, gather (tok2row given: no inversion pass)
 
     def __init__(self, tokens, hidden=7168, experts=8, topk=2, t0=0, device="cuda", gen_device="cuda", pinned_host=False):
         from mcoplib_b200 import workloads as W
@@ -173,7 +173,7 @@ class Route3:
     """Configuration 3: DeepSeek-V3-shaped gate (256 experts, 8 groups, top-8) + scatter + weighted gather, hidden 7168."""
     name = "config3 deepseek_route_dispatch_8192: grouped sigmoid gate -> scatter+int8 quant -> weighted gather"
     kernels = ["gate", "scatter", "gather"]
-    launches_per_step = 4
+    launches_per_step = 5  # gate, scatter rank + fill + quant, gather
 
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W

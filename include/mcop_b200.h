@@ -92,6 +92,12 @@ int mcop_head_rmsnorm(void* out, const void* x, const void* weight, int64_t toke
 int mcop_scale_dynamic_quant_i8(int8_t* out, float* scales, const void* x, const float* smooth,
                                 int64_t tokens, int64_t hidden, int dtype, mcop_stream_t stream);
 
+/* torch.ops._C.dynamic_scaled_int8_quant (symmetric form, azp = None),
+ * op/vllm/quantization/compressed_tensors/int8_quant_kernels.cu:95-132 (schema op/vllm/torch_bindings.cpp:375-379):
+ * scales = max|x| / 127; out = int8(rne(x * (127 / max|x|))), all-zero rows give codes 0. */
+int mcop_dynamic_scaled_int8_quant(int8_t* out, float* scales, const void* x, int64_t tokens, int64_t hidden,
+                                   int dtype, mcop_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Part 2 - rotary embedding and the int8 KV-cache store
  * ---------------------------------------------------------------------------------------------- */
@@ -214,6 +220,14 @@ int mcop_moe_gather_weighted(const void* y, const int32_t* row2tok, const int32_
                              const int32_t* tok2row, int accumulate, int64_t tokens, int64_t rows,
                              int64_t hidden_size, int topk, int experts, void* workspace,
                              size_t workspace_bytes, mcop_stream_t stream);
+
+/* mcoplib.op.moe_swiglu_dynamic_quantize, op/moe_swiglu_dq.cu:63-292 (include/moe_swiglu_dq.h): the rows produced by
+ * the expert up-projection, x bf16 [rows, 2*hidden] = gate || up, grouped by expert (rows of expert e are
+ * [starts[e], starts[e] + counts[e])): v = up * (gate / (1 + exp(-gate))) * smooth[e]; scales = max|v| * (1/127);
+ * out = int8(rne(v * (127 / max|v|))) clamped to +-127.  Rows owned by no expert are not written. */
+int mcop_moe_swiglu_quant_i8(const void* x, const float* smooth, const int32_t* starts, const int32_t* counts,
+                             int8_t* out, float* scales, int64_t rows, int64_t hidden, int experts,
+                             mcop_stream_t stream);
 
 /* Size of the built-in scratch area of mcop_moe_gather_noalloc (bytes held by every GPU that loads the library). */
 #define MCOP_GATHER_NOALLOC_SCRATCH_BYTES (4u << 20)

@@ -26,7 +26,7 @@ BUILD = os.path.join(HERE, "build")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-CU_SOURCES = ["api_common.cu", "norm_quant.cu", "rope_kv.cu", "moe_route.cu", "moe_scatter.cu", "moe_gather.cu"]
+CU_SOURCES = ["api_common.cu", "norm_quant.cu", "rope_kv.cu", "moe_route.cu", "moe_scatter.cu", "moe_gather.cu", "moe_act_quant.cu"]
 # -fmad=false: products and sums are rounded separately, as the CPU evaluation of the same formulas does.
 # Never --use_fast_math: division, sqrt and expf stay IEEE / full precision.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-fmad=false", "-lineinfo",
@@ -56,7 +56,7 @@ def _run(cmd, verbose):
 
 def build_kernels(force=False, verbose=False, extra_nvcc=()) -> str:
     os.makedirs(BUILD, exist_ok=True)
-    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(INCLUDE, "mcop_b200.h")]
+    headers = [os.path.join(CSRC, h) for h in ("common.cuh", "tma_pipe.cuh", "rope_pipe.inl")] + [os.path.join(INCLUDE, "mcop_b200.h")]
     objs, jobs = [], []
     for src in CU_SOURCES:
         s = os.path.join(CSRC, src)

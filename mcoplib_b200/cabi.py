@@ -24,6 +24,7 @@ SIGNATURES = {
     "mcop_rmsnorm": (I32, [P, P, P, P, P, I64, I64, F32, I32, I32, I32, P]),
     "mcop_head_rmsnorm": (I32, [P, P, P, I64, I64, I64, F32, I32, I32, I32, I32, P]),
     "mcop_scale_dynamic_quant_i8": (I32, [P, P, P, P, I64, I64, I32, P]),
+    "mcop_dynamic_scaled_int8_quant": (I32, [P, P, P, I64, I64, I32, P]),
     "mcop_rope_inplace": (I32, [P, P, P, P, I32, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
     "mcop_rope_packed": (I32, [P, P, P, P, P, P, I32, I64, I32, I32, I32, I32, P]),
     "mcop_fused_rope_fwd": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
@@ -37,6 +38,7 @@ SIGNATURES = {
     "mcop_moe_gather_workspace_bytes": (SZ, [I64, I64]),
     "mcop_moe_gather": (I32, [P, P, P, P, I32, I64, I64, I64, P, SZ, P]),
     "mcop_moe_gather_weighted": (I32, [P, P, P, P, P, P, P, I32, I64, I64, I64, I32, I32, P, SZ, P]),
+    "mcop_moe_swiglu_quant_i8": (I32, [P, P, P, P, P, P, I64, I64, I32, P]),
     "mcop_moe_gather_noalloc": (I32, [P, P, P, I64, I64, I64, P]),
 }
 

@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const float2 x2 = make_float2(__uint_as_float(wd[q] << 16), __uint_as_float(wd[q] & 0xffff0000u));
-                vv[k][q] = __fmul2_rn(__fmul2_rn(x2, w2), sm[k][q]);  // (x * w) * smooth, each product rounded
+                vv[k][q] = mul2_rn(mul2_rn(x2, w2), sm[k][q]);  // (x * w) * smooth, each product rounded
                 amax = fmaxf(amax, fmaxf(fabsf(vv[k][q].x), fabsf(vv[k][q].y)));
               }
             }
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
         float scale, mul;
         row_scale_from_amax(m, scale, mul);
         if (!(m > 0.f)) mul = 0.f;  // all-zero row: codes 0 (keeps NaN out of the bit-level conversion below)
-        const float2 mul2 = make_float2(mul, mul), magic2 = make_float2(12582912.0f, 12582912.0f);
+        const float2 mul2 = make_float2(mul, mul);
         if (threadIdx.x == 0) p.row_scales[row] = scale;
         int8_t* out = p.rows + (int64_t)row * H;
 #pragma unroll
@@ -299,9 +299,10 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
             uint32_t c[8];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const float2 r2 = __fadd2_rn(__fmul2_rn(vv[k][q], mul2), magic2);  // see rn_low_byte()
-              c[2 * q] = __float_as_uint(r2.x);
-              c[2 * q + 1] = __float_as_uint(r2.y);
+              // packed product, scalar rounding adds (a packed add could be fused with the product by the assembler)
+              const float2 pr = mul2_rn(vv[k][q], mul2);
+              c[2 * q] = rn_low_byte(pr.x);
+              c[2 * q + 1] = rn_low_byte(pr.y);
             }
             st_cs_u2(out + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
           }

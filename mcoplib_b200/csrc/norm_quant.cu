@@ -532,10 +532,44 @@ __global__ void __launch_bounds__(256) scale_quant_kernel(int8_t* q, float* scal
     qr[i] = (int8_t)q_rn_clamp(ElemTraits<T>::to_float(xr[i]) * smooth[i] / scale, -128, 127);
 }
 
+// ---------------------------------------------------------------------------------------------
+// dynamic_scaled_int8_quant (symmetric): scale = max|x| / 127; q = rne(x * (127 / max|x|)), 0 for an all-zero row.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) dynamic_int8_quant_kernel(int8_t* q, float* scales, const T* x, int hidden) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * (int64_t)hidden;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) amax = fmaxf(amax, fabsf(ElemTraits<T>::to_float(xr[i])));
+  amax = block_reduce<true>(amax, red);
+  if (threadIdx.x == 0) scales[row] = amax / 127.0f;
+  const float inv = amax == 0.f ? 0.f : 127.0f / amax;
+  int8_t* qr = q + row * (int64_t)hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    qr[i] = (int8_t)q_rn_clamp(ElemTraits<T>::to_float(xr[i]) * inv, -128, 127);
+}
+
 }  // namespace
 }  // namespace mcop
 
 using namespace mcop;
+
+extern "C" int mcop_dynamic_scaled_int8_quant(int8_t* out, float* scales, const void* x, int64_t tokens, int64_t hidden,
+                                              int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(out && scales && x, MCOP_ERR_ARGUMENT, "dynamic_scaled_int8_quant: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && tokens <= 0x7fffffffLL && hidden > 0 && hidden <= 0x7fffffff, MCOP_ERR_ARGUMENT,
+               "dynamic_scaled_int8_quant: bad sizes");
+  if (tokens == 0) return MCOP_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case MCOP_BF16: dynamic_int8_quant_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __nv_bfloat16*)x, (int)hidden); break;
+    case MCOP_F16: dynamic_int8_quant_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __half*)x, (int)hidden); break;
+    case MCOP_F32: dynamic_int8_quant_kernel<float><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const float*)x, (int)hidden); break;
+    default: return set_error(MCOP_ERR_UNSUPPORTED, "dynamic_scaled_int8_quant: unknown dtype code %d", dtype);
+  }
+  return check_launch("dynamic_scaled_int8_quant");
+}
 
 extern "C" int mcop_fused_add_rmsnorm(void* x, int64_t x_row_stride, void* residual, const void* weight,
                                       int64_t tokens, int64_t hidden, float eps, int dtype, mcop_stream_t stream) {

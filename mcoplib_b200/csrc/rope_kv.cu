@@ -6,7 +6,10 @@
 // once per token into registers.  With the fused store, the thread that rotated a K slice also
 // quantises it (the bf16-ROUNDED rotated value) into the paged int8 cache, and V slices are read once
 // and written once as int8: K and V never make a second trip through HBM.
+#include <atomic>
+
 #include "common.cuh"
+#include "tma_pipe.cuh"
 
 namespace mcop {
 namespace {
@@ -57,6 +60,44 @@ __device__ __forceinline__ void rotate8(const float (&x)[8], const float (&y)[8]
   }
 }
 
+// bf16 NeoX rotation of 8 pairs in fp32 with one rounding, on packed data: the products and sums are the packed
+// fp32x2 instructions of sm_100 (each lane rounded exactly like __fmul_rn / __fadd_rn; x*c - y*s is formed as
+// x*c + y*(-s), which is the same value), and the results go straight to bf16 pairs.  Also returns the ROUNDED
+// results widened to fp32 when `need_f32` (the fused store quantises them).
+struct CosSin8 {
+  float2 c[4], s[4], ns[4];
+};
+__device__ __forceinline__ CosSin8 make_cos_sin(const float (&c)[8], const float (&s)[8]) {
+  CosSin8 r;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    r.c[q] = make_float2(c[2 * q], c[2 * q + 1]);
+    r.s[q] = make_float2(s[2 * q], s[2 * q + 1]);
+    r.ns[q] = make_float2(-s[2 * q], -s[2 * q + 1]);
+  }
+  return r;
+}
+__device__ __forceinline__ void rotate_bf16x8_packed(const uint4 xr, const uint4 yr, const CosSin8& cs, uint4& xo, uint4& yo) {
+  const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w}, yw[4] = {yr.x, yr.y, yr.z, yr.w};
+  uint32_t ox[4], oy[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 x2 = make_float2(__uint_as_float(xw[q] << 16), __uint_as_float(xw[q] & 0xffff0000u));
+    const float2 y2 = make_float2(__uint_as_float(yw[q] << 16), __uint_as_float(yw[q] & 0xffff0000u));
+    // products packed, sums scalar: a packed add fed by a single-use packed product is turned into a fused
+    // multiply-add by the assembler (measured), which would drop the intermediate rounding; scalar add.rn is not
+    const float2 xc = mul2_rn(x2, cs.c[q]), ys = mul2_rn(y2, cs.ns[q]);
+    const float2 yc = mul2_rn(y2, cs.c[q]), xs = mul2_rn(x2, cs.s[q]);
+    const float2 a = make_float2(__fadd_rn(xc.x, ys.x), __fadd_rn(xc.y, ys.y));
+    const float2 b = make_float2(__fadd_rn(yc.x, xs.x), __fadd_rn(yc.y, xs.y));
+    __nv_bfloat162 ha = __floats2bfloat162_rn(a.x, a.y), hb = __floats2bfloat162_rn(b.x, b.y);
+    ox[q] = *reinterpret_cast<uint32_t*>(&ha);
+    oy[q] = *reinterpret_cast<uint32_t*>(&hb);
+  }
+  xo = make_uint4(ox[0], ox[1], ox[2], ox[3]);
+  yo = make_uint4(oy[0], oy[1], oy[2], oy[3]);
+}
+
 __device__ __forceinline__ uint2 quant8(const float (&v)[8], float inv) {
   int c[8];
 #pragma unroll
@@ -83,6 +124,7 @@ __global__ void __launch_bounds__(256) rope_neox_vec(RopeParams p) {
   }
   const int heads_per_iter = blockDim.x / hv;
   const int nqk = p.num_heads + p.num_kv_heads;
+  const CosSin8 cs8 = make_cos_sin(c, s);
   for (int h = threadIdx.x / hv; h < nqk; h += heads_per_iter) {
     const bool is_k = h >= p.num_heads;
     const int hh = is_k ? h - p.num_heads : h;
@@ -91,11 +133,22 @@ __global__ void __launch_bounds__(256) rope_neox_vec(RopeParams p) {
     T* dst = (is_k ? reinterpret_cast<T*>(p.k_dst) + t * p.k_stride
                    : reinterpret_cast<T*>(p.q_dst) + t * p.q_stride) + hh * p.head_stride;
     float x[8], y[8], xo[8], yo[8];
-    Vec8<T>::load(src + j * 8, x);
-    Vec8<T>::load(src + half + j * 8, y);
-    rotate8<T, PER_OP>(x, y, c, s, xo, yo);
-    Vec8<T>::store(dst + j * 8, xo);
-    Vec8<T>::store(dst + half + j * 8, yo);
+    if constexpr (ElemTraits<T>::code == MCOP_BF16 && !PER_OP) {
+      uint4 xp, yp;
+      rotate_bf16x8_packed(ld_u4(src + j * 8), ld_u4(src + half + j * 8), cs8, xp, yp);
+      st_u4(dst + j * 8, xp);
+      st_u4(dst + half + j * 8, yp);
+      if (STORE && is_k && slot >= 0) {
+        unpack_bf16x8(xp, xo);
+        unpack_bf16x8(yp, yo);
+      }
+    } else {
+      Vec8<T>::load(src + j * 8, x);
+      Vec8<T>::load(src + half + j * 8, y);
+      rotate8<T, PER_OP>(x, y, c, s, xo, yo);
+      Vec8<T>::store(dst + j * 8, xo);
+      Vec8<T>::store(dst + half + j * 8, yo);
+    }
     if (STORE && is_k && slot >= 0) {
       const float inv = 1.0f / p.k_scale[hh];
       int8_t* kc = p.k_cache + (slot * p.num_kv_heads + hh) * (int64_t)p.head_size;
@@ -173,10 +226,22 @@ __global__ void __launch_bounds__(256) rope_any(RopeParams p, int is_neox) {
 
 inline int esize(int dtype) { return dtype == MCOP_F32 ? 4 : 2; }
 
+#include "rope_pipe.inl"
+
 template <typename T, typename CT, bool PER_OP, bool STORE>
 int launch_rope_t(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok, cudaStream_t stream) {
   if (tokens == 0) return MCOP_OK;
   MCOP_REQUIRE(tokens <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "rope: %lld tokens exceed the grid limit", (long long)tokens);
+  if constexpr (sizeof(T) == 2) {
+    // the pipelined kernel wants explicit positions, heads packed back to back, a key tensor, and cos || sin as
+    // one contiguous table row; it pays off once there are a few waves of tokens
+    const bool one_row = reinterpret_cast<const char*>(p.sin) == reinterpret_cast<const char*>(p.cos) + (size_t)(p.rot_dim / 2) * sizeof(CT);
+    if (vec_ok && tokens >= 16384 && p.positions && p.k_src && p.num_kv_heads > 0 && p.head_stride == p.head_size &&
+        one_row && p.cs_row_stride == p.rot_dim) {
+      const int rc = launch_rope_pipe<T, CT, PER_OP, STORE>(p, tokens, stream);
+      if (rc != 1) return rc;
+    }
+  }
   if (vec_ok) {
     const int hv = p.rot_dim >> 4;
     const int threads = hv * (256 / hv > 0 ? 256 / hv : 1);

@@ -165,6 +165,23 @@ std::tuple<Tensor, Tensor> scale_dynamic_quant(const Tensor& hidden_states, cons
   return {q, s};
 }
 
+// torch.ops._C.dynamic_scaled_int8_quant (op/vllm/quantization/compressed_tensors/int8_quant_kernels.cu:459-526),
+// symmetric form only (azp must be None)
+void dynamic_scaled_int8_quant(Tensor& out, const Tensor& input, Tensor& scales, std::optional<Tensor> azp) {
+  check_cuda(input, "input");
+  TORCH_CHECK(input.is_contiguous());
+  TORCH_CHECK(out.is_contiguous());
+  TORCH_CHECK(scales.is_contiguous());
+  TORCH_CHECK(!azp.has_value(), "asymmetric quantisation (azp) is not built");
+  TORCH_CHECK(out.scalar_type() == at::kChar && scales.scalar_type() == at::kFloat);
+  const int64_t hidden = input.size(-1);
+  const int64_t tokens = hidden ? input.numel() / hidden : 0;
+  TORCH_CHECK(scales.numel() >= tokens && out.numel() == input.numel());
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_dynamic_scaled_int8_quant(out.data_ptr<int8_t>(), scales.data_ptr<float>(), input.data_ptr(), tokens, hidden,
+                                          dtype_code(input, "dynamic_scaled_int8_quant"), cur_stream()));
+}
+
 // ---------------------------------------------------------------- part 2
 
 // torch.ops._C.rotary_embedding (op/vllm/pos_encoding_kernels.cu:135-217); the cos/sin cache may also be fp32
@@ -441,6 +458,28 @@ void moe_gather(Tensor scatter_tokens, Tensor scatter_tokens_offset, Tensor conv
                            tokens, rows, hidden, wsp, ws_bytes, cur_stream()));
 }
 
+// mcoplib.op.moe_swiglu_dynamic_quantize (op/moe_swiglu_dq.cu, include/moe_swiglu_dq.h)
+void moe_swiglu_dynamic_quantize(Tensor scatter_tokens, Tensor smooth_scale, Tensor experts_tokens_start, Tensor experts_tokens_count,
+                                 Tensor& y, Tensor& per_tokens_scale, int total_experts_num) {
+  check_cuda(scatter_tokens, "scatter_tokens");
+  TORCH_CHECK(scatter_tokens.scalar_type() == at::kBFloat16, "Only bfloat16 is supported");
+  TORCH_CHECK(scatter_tokens.is_contiguous() && smooth_scale.is_contiguous() && y.is_contiguous() && per_tokens_scale.is_contiguous());
+  TORCH_CHECK(experts_tokens_start.is_contiguous() && experts_tokens_count.is_contiguous());
+  TORCH_CHECK(smooth_scale.scalar_type() == at::kFloat && y.scalar_type() == at::kChar && per_tokens_scale.scalar_type() == at::kFloat);
+  TORCH_CHECK(experts_tokens_start.scalar_type() == at::kInt && experts_tokens_count.scalar_type() == at::kInt);
+  const int64_t hidden2 = scatter_tokens.size(-1);
+  TORCH_CHECK(hidden2 % 2 == 0, "the last dimension holds gate || up");
+  const int64_t hidden = hidden2 / 2;
+  const int64_t rows = hidden2 ? scatter_tokens.numel() / hidden2 : 0;
+  TORCH_CHECK(y.numel() == rows * hidden && per_tokens_scale.numel() >= rows);
+  TORCH_CHECK(total_experts_num >= 1 && experts_tokens_start.numel() >= total_experts_num && experts_tokens_count.numel() >= total_experts_num);
+  TORCH_CHECK(smooth_scale.numel() >= (int64_t)total_experts_num * hidden);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(scatter_tokens));
+  check_rc(mcop_moe_swiglu_quant_i8(scatter_tokens.data_ptr(), smooth_scale.data_ptr<float>(), experts_tokens_start.data_ptr<int32_t>(),
+                                    experts_tokens_count.data_ptr<int32_t>(), y.data_ptr<int8_t>(), per_tokens_scale.data_ptr<float>(), rows,
+                                    hidden, total_experts_num, cur_stream()));
+}
+
 // Weighted combine (addition of this build)
 void moe_gather_weighted(Tensor y, Tensor row2tok, Tensor topk_ids, Tensor topk_weights, Tensor experts_token_start, Tensor out,
                          bool accumulate, std::optional<Tensor> tok2row) {
@@ -504,6 +543,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("shared_experts_per_rank"), py::arg("shared_tokens_per_sp"), py::arg("tok2row") = py::none());
   m.def("moe_gather", &moe_gather, py::arg("scatter_tokens"), py::arg("scatter_tokens_offset"), py::arg("convergent_tokens"),
         py::arg("tok2row") = py::none());
+  m.def("moe_swiglu_dynamic_quantize", &moe_swiglu_dynamic_quantize);
   // additions of this build (no reference counterpart)
   m.def("rope_kv_store_int8", &rope_kv_store_int8);
   m.def("moe_gather_weighted", &moe_gather_weighted, py::arg("y"), py::arg("row2tok"), py::arg("topk_ids"), py::arg("topk_weights"),
@@ -524,6 +564,8 @@ TORCH_LIBRARY(MCOP_TORCH_NS, ops) {
       "rms_norm_dynamic_per_token_quant(Tensor! result, Tensor input, Tensor weight, Tensor! scale, float epsilon, "
       "Tensor? scale_ub, Tensor!? residual) -> ()");
   ops.impl("rms_norm_dynamic_per_token_quant", torch::kCUDA, &rms_norm_dynamic_per_token_quant_vllm);
+  ops.def("dynamic_scaled_int8_quant(Tensor! result, Tensor input, Tensor! scale, Tensor!? azp) -> ()");
+  ops.impl("dynamic_scaled_int8_quant", torch::kCUDA, &dynamic_scaled_int8_quant);
   ops.def(
       "rotary_embedding(Tensor positions, Tensor! query, Tensor!? key, int head_size, Tensor cos_sin_cache, bool is_neox) -> ()");
   ops.impl("rotary_embedding", torch::kCUDA, &rotary_embedding_vllm);

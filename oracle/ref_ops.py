@@ -175,6 +175,21 @@ def scale_dynamic_quant(hidden: torch.Tensor, smooth: torch.Tensor) -> Tuple[tor
     return q, scale.reshape(-1)
 
 
+def dynamic_scaled_int8_quant(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """torch.ops._C.dynamic_scaled_int8_quant, symmetric form,
+    op/vllm/quantization/compressed_tensors/int8_quant_kernels.cu:95-132: scale = max|x| / 127;
+    q = clamp(rne(float(x) * (127 / max|x|)), -128, 127), inv = 0 for an all-zero row.
+    Pinned by the reference's own check round(x / scale)
+    (benchmark/runners/mcoplib_mxbenchmark_dynamic_scaled_int8_quant_runners.py:42-62), tolerance 1 code.
+    Returns (codes int8, scales fp32 [tokens, 1])."""
+    f = x.float()
+    a = f.abs().amax(dim=-1, keepdim=True)
+    # tensor / tensor: a correctly rounded division (scalar / tensor is evaluated by torch as reciprocal * scalar)
+    inv = torch.where(a == 0, torch.zeros_like(a), torch.full_like(a, 127.0) / a)
+    q = torch.round(f * inv).clamp(-128, 127).to(torch.int8)
+    return q, (a / 127.0).reshape(-1, 1)
+
+
 # --------------------------------------------------------------------------------------
 # Part 2: RoPE and the int8 KV store
 # --------------------------------------------------------------------------------------
@@ -518,6 +533,35 @@ def moe_scatter_dynamic_quant(hidden: torch.Tensor, ids: torch.Tensor, weights: 
         sc = 127.0 * (1.0 / a)
         rows[sl] = float_to_int8_sym(v * sc.unsqueeze(1))
     return rows, scales, row2tok, counts, starts, tok2row
+
+
+def moe_swiglu_dynamic_quantize(x: torch.Tensor, smooth: torch.Tensor, starts: torch.Tensor, counts: torch.Tensor,
+                                experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """mcoplib.op.moe_swiglu_dynamic_quantize, op/moe_swiglu_dq.cu:63-118; the reference's own torch reference is
+    moe_swiglu_dynamic_quant_run (unit_test/test_moe_swiglu_dq.py:16-44, silu(x1) * x2 then
+    smooth_per_token_dynamic_quant per expert), which pins this function (codes atol 1).
+
+    x [rows, 2H] = gate || up; rows of expert e are [starts[e], starts[e]+counts[e]);
+    v = up * (gate * (1 / (1 + exp(-gate)))) * smooth[e] (fp32, left to right); a = max|v|;
+    scale = float(double(a) * 0.0078740157); q = clamp(rne(v * (127 * (1/a))), -127, 127); a == 0 -> codes 0.
+    Rows owned by no expert stay 0.  Returns (codes int8 [rows, H], scales fp32 [rows])."""
+    rows, h2 = x.shape
+    H = h2 // 2
+    q = torch.zeros(rows, H, dtype=torch.int8)
+    sc = torch.zeros(rows, dtype=torch.float32)
+    for e in range(experts):
+        a0, n = int(starts[e]), int(counts[e])
+        if n <= 0:
+            continue
+        g = x[a0:a0 + n, :H].float()
+        u = x[a0:a0 + n, H:].float()
+        sig = g * (1.0 / (1.0 + torch.exp(-g)))
+        v = u * sig * smooth[e].float().unsqueeze(0)
+        a = v.abs().amax(dim=1)
+        sc[a0:a0 + n] = (a.double() * 0.0078740157).float()
+        mul = torch.where(a > 0, 127.0 * (1.0 / a), torch.zeros_like(a))
+        q[a0:a0 + n] = float_to_int8_sym(v * mul.unsqueeze(1))
+    return q, sc
 
 
 def moe_gather(y: torch.Tensor, row2tok: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

@@ -132,6 +132,25 @@ def main():
     q, s = fn(hs, sm)
     put(store, "ref:unit_test/test_moe_swiglu_dq.py:smooth_per_token_dynamic_quant/0", hidden=hs, smooth=sm, codes=q, scales=s)
 
+    # ---------------------------------------------------------------- moe_swiglu_dynamic_quantize ("next" row)
+    # unit_test/test_moe_swiglu_dq.py:16-44 moe_swiglu_dynamic_quant_run (calls smooth_per_token_dynamic_quant).
+    run = load_function(ref, "unit_test/test_moe_swiglu_dq.py", "moe_swiglu_dynamic_quant_run",
+                        extra_globals={"smooth_per_token_dynamic_quant": fn})
+    g = torch.Generator().manual_seed(6)
+    E, H = 4, 256
+    counts = torch.tensor([5, 0, 9, 6], dtype=torch.int32)
+    starts = (torch.cumsum(counts, 0) - counts).to(torch.int32)
+    rows = int(counts.sum())
+    xs = torch.randn(rows, 2 * H, generator=g).bfloat16()
+    sm = 0.5 + torch.rand(E, H, generator=g)
+    qt = torch.zeros(rows, H, dtype=torch.int8)
+    st = torch.zeros(rows)
+    # the reference function multiplies in bf16 (its inputs are bf16 tensors); feed fp32 views so that it follows
+    # the kernel's fp32 arithmetic
+    run(xs.float(), sm, counts, starts, qt, st, E)
+    put(store, "ref:unit_test/test_moe_swiglu_dq.py:moe_swiglu_dynamic_quant_run/0", x=xs, smooth=sm, counts=counts,
+        starts=starts, codes=qt, scales=st)
+
     # ---------------------------------------------------------------- a8: store_kv_cache
     # unit_test/test_store_kv.py:91-128 TestKVCacheStorage.run_reference_impl (fp16, seed 42 layout,
     # 8 Q heads / 1 KV head, D 128; token count reduced from 4096 to 48 and two sequences).

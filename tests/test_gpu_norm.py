@@ -266,3 +266,19 @@ def test_c_abi_called_directly(op):
     cabi.check(rc, lib)
     torch.cuda.synchronize()
     C.assert_codes(out, q_ref); C.assert_equal(bits(res), bits(r_ref))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_dynamic_scaled_int8_quant(op, dtype):
+    ns = getattr(torch.ops, op.torch_namespace)
+    x = W.per_token("randn", 60, 0, 130, 4100, dtype)
+    x[7] = 0
+    q_ref, s_ref = R.dynamic_scaled_int8_quant(x)
+    out = Canary((130, 4100), torch.int8); sc = Canary((130, 1), torch.float32)
+    ns.dynamic_scaled_int8_quant(out.t, x.to(DEV), sc.t, None)
+    torch.cuda.synchronize()
+    out.check(); sc.check()
+    C.assert_codes(out.t, q_ref); C.assert_close(sc.t, s_ref, abs_=1e-7)
+    assert int(out.t[7].abs().max()) == 0
+    with pytest.raises(RuntimeError):
+        ns.dynamic_scaled_int8_quant(out.t, x.to(DEV), sc.t, torch.zeros(130, 1, dtype=torch.int32, device=DEV))

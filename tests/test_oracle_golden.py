@@ -154,3 +154,17 @@ def test_softmax_topk(golden):
         w, ids = R.moe_softmax_topk(r["gating"], r["k"])
         assert_equal(ids, r["ids"], key)
         assert torch.allclose(w, r["weights"], rtol=1e-5, atol=1e-6), key
+
+
+def test_dynamic_scaled_int8_quant_against_the_runner_formula():
+    # benchmark/runners/mcoplib_mxbenchmark_dynamic_scaled_int8_quant_runners.py:42-62: round(x / scale) clamped
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(64, 777, generator=g).bfloat16()
+    x[5] = 0
+    q, s = R.dynamic_scaled_int8_quant(x)
+    safe = s.clone()
+    safe[safe == 0] = 1.0
+    ref = torch.clamp(torch.round(x.float() / safe), -128, 127).to(torch.int8)
+    assert code_stats(q, ref)["max_abs"] <= 1
+    assert code_stats(q, ref)["frac_diff"] < 1e-3
+    assert int(q[5].abs().max()) == 0 and float(s[5]) == 0.0
