@@ -15,6 +15,13 @@ __device__ __forceinline__ bool better(float v, int i, float ov, int oi) {
   return ov > v || (ov == v && oi < i);
 }
 
+// Order-preserving map from float to unsigned (a < b  <=>  key(a) < key(b) for non-NaN values), so that warp-wide
+// integer max (redux.sync) can stand in for a float max.
+__device__ __forceinline__ unsigned ordered_key(float v) {
+  const unsigned b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
 // ---------------------------------------------------------------------------------------------
 // softmax + top-k.  A row is spread over TPR lanes (a power of two), VPT contiguous experts per lane.
 // ---------------------------------------------------------------------------------------------
@@ -152,16 +159,14 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
     const float gscore = round_code(m1 + m2, p.ts);
     const int gid = lane / lpg;
     sel = 0;
+    // One warp-wide integer max (redux.sync) on an order-preserving key finds the best remaining group score; the
+    // lowest lane holding it belongs to the lowest group index (lanes are ordered by group).
     for (int r = 0; r < p.topk_group; ++r) {
-      float bv = ((sel >> gid) & 1u) ? -INFINITY : gscore;
-      int bi = ((sel >> gid) & 1u) ? 0x7fffffff : gid;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (better(bv, bi, ov, oi)) { bv = ov; bi = oi; }
-      }
-      if (bi < 32) sel |= 1u << bi;
+      const unsigned key = ((sel >> gid) & 1u) ? 0u : ordered_key(gscore);
+      const unsigned best = __reduce_max_sync(0xffffffffu, key);
+      const unsigned who = __ballot_sync(0xffffffffu, key == best);
+      const int win = (__ffs(who) - 1) / lpg;
+      sel |= 1u << win;
     }
     if (!((sel >> gid) & 1u)) {
 #pragma unroll
@@ -175,23 +180,23 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
   float my_w = 0.f;
   int my_id = 0;
   for (int kk = 0; kk < p.topk; ++kk) {
-    float bv = biased[0];
-    int bi = first;
+    // local arg-max (lowest index wins inside the lane), then one redux.sync on the order-preserving key and a
+    // ballot: the lowest lane holding the warp maximum owns the lowest expert index among equals
+    float bv = biased[0], bs = score[0];
+    int bl = 0;
 #pragma unroll
     for (int i = 1; i < V; ++i)
-      if (biased[i] > bv) { bv = biased[i]; bi = first + i; }
+      if (biased[i] > bv) { bv = biased[i]; bs = score[i]; bl = i; }
+    const unsigned key = ordered_key(bv);
+    const unsigned best = __reduce_max_sync(0xffffffffu, key);
+    const int src = __ffs(__ballot_sync(0xffffffffu, key == best)) - 1;
+    const int bi = __shfl_sync(0xffffffffu, first + bl, src);
+    const float sc = __shfl_sync(0xffffffffu, bs, src);
+    if (lane == src) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (better(bv, bi, ov, oi)) { bv = ov; bi = oi; }
+      for (int i = 0; i < V; ++i)
+        if (i == bl) biased[i] = -INFINITY;
     }
-    float sc = 0.f;
-    const bool mine = (bi / V == lane);
-#pragma unroll
-    for (int i = 0; i < V; ++i)
-      if (mine && i == bi % V) { sc = score[i]; biased[i] = -INFINITY; }
-    sc = __shfl_sync(0xffffffffu, sc, bi / V);
     if (lane == kk) { my_w = sc; my_id = bi; }
   }
   if (p.renormalize) {

@@ -98,8 +98,24 @@ __global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __rest
   const int ntiles = gridDim.x;
   int32_t* cnt_s = reinterpret_cast<int32_t*>(smem_u32);  // reuse: E ints
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  if (ntiles <= 64) {
+    // few tiles: one thread per expert walks the tiles; the loads are coalesced over experts and independent of
+    // each other, so they overlap instead of paying one memory latency per expert
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      int run = 0;
+#pragma unroll 8
+      for (int t = 0; t < ntiles; ++t) {
+        const int c = __ldcg(&ws.tile_hist[(int64_t)t * E + e]);
+        ws.tile_hist[(int64_t)t * E + e] = run;
+        run += c;
+      }
+      cnt_s[e] = run;
+      counts[e] = run;
+    }
+  } else
   for (int e = warp; e < E; e += nwarp) {
     int carry = 0;
+#pragma unroll 4
     for (int t0 = 0; t0 < ntiles; t0 += 32) {
       const int t = t0 + lane;
       const int c = t < ntiles ? __ldcg(&ws.tile_hist[(int64_t)t * E + e]) : 0;
