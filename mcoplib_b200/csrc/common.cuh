@@ -166,31 +166,12 @@ __device__ __forceinline__ int q_rn_clamp(float v, int lo, int hi) {
   int q = __float2int_rn(v);  // NaN -> 0
   return max(lo, min(hi, q));
 }
-// Packed fp32x2 arithmetic of sm_100 with an explicit rounding mode: every lane of mul2_rn is rounded exactly
-// like __fmul_rn (measured: bit-identical on 4M random pairs).  CAUTION for add2_rn: when its operand is a packed
-// product with no other use, the assembler merges the two into one packed fused multiply-add in spite of the
-// `.rn` qualifiers (measured: 26 % of results change in the last bit).  Where the intermediate rounding matters,
-// add the lanes with scalar __fadd_rn instead.
-__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "mul.rn.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "add.rn.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
+// Packed fp32x2 multiply of sm_100: both lanes rounded exactly like __fmul_rn (measured bit-identical on 4M random
+// pairs).  There is deliberately no packed add here: a packed add whose operand is a single-use packed product
+// is merged by the assembler into one packed fused multiply-add, even with `.rn` on both (measured: 26 % of the
+// results change in the last bit), which would drop an intermediate rounding the arithmetic contracts rely on.
+// Sums that follow a packed product are therefore formed lane by lane with the scalar __fadd_rn.
+__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) { return __fmul2_rn(a, b); }
 
 // Conversion without the (quarter-rate) float-to-int instruction: adding 1.5 * 2^23 makes the fp32 adder round v
 // to the nearest integer, ties to even, and leaves it in the low mantissa bits, so the low byte of the sum is

@@ -175,28 +175,35 @@ int launch_rope_pipe(const RopeParams& p, int64_t tokens, cudaStream_t stream) {
   int threads = hpi * hv;
   if (threads < 64) threads = 64 / hv * hv;  // chunk staging needs >= 64 threads
   if (threads > 256 || threads % hv != 0) return 1;
-  // up to three CTAs per SM, each with its share of shared memory for the ring
-  const int want = 3;
-  int stages = (int)(((227 * 1024) / want - 4 * 1024) / stage_bytes);
-  if (stages < 2) stages = (int)(((227 * 1024) / 2 - 4 * 1024) / stage_bytes);
-  if (stages < 2) return 1;
-  if (stages > 6) stages = 6;
-  const size_t smem = 128 + (size_t)stages * stage_bytes;
-  int per_sm = (int)((227 * 1024) / (smem + 3 * 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > want ? want : per_sm);
-  if (per_sm * threads * 112 > 65536) per_sm = 65536 / (threads * 112);  // register file (the kernel uses <= 112)
-  if (per_sm < 1) per_sm = 1;
-  int64_t grid = (int64_t)sm_count() * per_sm;
-  int chunk = (int)(tokens / (grid * 4));
-  chunk = chunk < 8 ? 8 : (chunk > kRopeChunk ? kRopeChunk : chunk);
-  const int64_t nchunks = (tokens + chunk - 1) / chunk;
-  if (grid > nchunks) grid = nchunks;
   static std::atomic<int> attr_done{0};
   if (!attr_done.load(std::memory_order_relaxed)) {
     cudaError_t e = cudaFuncSetAttribute(rope_neox_pipe<T, CT, PER_OP, STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "rope: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done.store(1, std::memory_order_relaxed);
   }
+  // CTAs per SM: try three, then two, then one; each gets its share of shared memory for the ring.  The register
+  // file is split over the four schedulers, so the runtime is asked how many CTAs really fit: a grid larger than
+  // what is resident would run as one and a half waves.
+  int stages = 0, per_sm = 0;
+  size_t smem = 0;
+  for (int want = 3; want >= 1 && per_sm == 0; --want) {
+    int st = (int)(((227 * 1024) / want - 4 * 1024) / stage_bytes);
+    if (st < 2) continue;
+    if (st > 6) st = 6;
+    const size_t sm_bytes = 128 + (size_t)st * stage_bytes;
+    int fit = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, rope_neox_pipe<T, CT, PER_OP, STORE>, threads, sm_bytes) != cudaSuccess) {
+      (void)cudaGetLastError();
+      fit = 0;
+    }
+    if (fit >= want) { stages = st; smem = sm_bytes; per_sm = want; }
+  }
+  if (per_sm == 0) return 1;
+  int64_t grid = (int64_t)sm_count() * per_sm;
+  int chunk = (int)(tokens / (grid * 4));
+  chunk = chunk < 8 ? 8 : (chunk > kRopeChunk ? kRopeChunk : chunk);
+  const int64_t nchunks = (tokens + chunk - 1) / chunk;
+  if (grid > nchunks) grid = nchunks;
   rope_neox_pipe<T, CT, PER_OP, STORE><<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, chunk, pipe_error_ptr());
   return check_launch("rope (pipelined)");
 }
