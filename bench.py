@@ -30,8 +30,9 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "fused_chain_tokens_per_s"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per token of the norm+quant kernel at hidden 7168,
-# from the ncu capture summarised in profiles/norm_quant_7168.md; None until such a capture exists.
-NORM_QUANT_DRAM_BYTES_PER_TOKEN = None
+# from the ncu capture summarised in profiles/norm_quant_bf16_pipe_chain5_32768x7168.md (939.6 MB read + 649.0 MB
+# written for 32,768 tokens); traffic grows in proportion to the tokens (every row is touched exactly once).
+NORM_QUANT_DRAM_BYTES_PER_TOKEN = (939_579_648 + 649_004_032) / 32768
 
 
 def measured_peak():
