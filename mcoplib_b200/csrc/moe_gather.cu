@@ -179,7 +179,6 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
   unsigned char* buf = smem + 128;
   const int H = p.hidden_size, nv = H >> 3;
   const uint32_t row_bytes = (uint32_t)H * 2u;
-  const int64_t nchunks = (p.tokens + chunk - 1) / chunk;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
@@ -190,9 +189,12 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
   uint32_t it = 0;        // items consumed so far by this CTA (selects stage and phase)
   uint32_t issued = 0;    // items issued so far (thread 0 only)
   bool alive = true;
-  for (int64_t c = blockIdx.x; c < nchunks && alive; c += gridDim.x) {
-    const int64_t t0 = c * chunk;
-    const int ntok = (int)min((int64_t)chunk, p.tokens - t0);
+  // every CTA owns one contiguous share of the tokens (equal to within one token, whatever the chunk size) and
+  // walks it in chunks
+  const int64_t tok_begin = (p.tokens * (int64_t)blockIdx.x) / gridDim.x;
+  const int64_t tok_end = (p.tokens * ((int64_t)blockIdx.x + 1)) / gridDim.x;
+  for (int64_t t0 = tok_begin; t0 < tok_end && alive; t0 += chunk) {
+    const int ntok = (int)min((int64_t)chunk, tok_end - t0);
     // ---- phase A: one thread per token builds the token's ascending row list (and weights)
     if (threadIdx.x < ntok) {
       const int64_t t = t0 + threadIdx.x;
@@ -340,13 +342,10 @@ int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t strea
   int per_sm = (int)((227 * 1024) / (smem + 10 * 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 2048 / THREADS ? 2048 / THREADS : per_sm);
   if (per_sm > 4) per_sm = 4;
-  // chunk of tokens a CTA prepares at once: up to 64, smaller when there are too few tokens to give every CTA
-  // several chunks
+  // every CTA gets an equal contiguous share of the tokens and prepares it in chunks of up to 64 tokens
   int64_t grid = (int64_t)sm_count() * per_sm;
-  int chunk = (int)(tokens / (grid * 4));
-  chunk = chunk < 8 ? 8 : (chunk > kChunkTokens ? kChunkTokens : chunk);
-  const int64_t nchunks = (tokens + chunk - 1) / chunk;
-  if (grid > nchunks) grid = nchunks;
+  if (grid > (tokens + 7) / 8) grid = (tokens + 7) / 8;
+  const int chunk = kChunkTokens;
   static std::atomic<int> attr_done{0};
   if (!attr_done.load(std::memory_order_relaxed)) {
     cudaError_t e = cudaFuncSetAttribute(gather_pipe<THREADS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);

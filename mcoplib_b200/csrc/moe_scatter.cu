@@ -420,12 +420,16 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   const size_t smem = 128 + (size_t)stages * row_bytes;
   int per_sm = (int)((227 * 1024) / (smem + 2 * 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > want_per_sm ? want_per_sm : per_sm);
-  // work items: aim at ~40 rows each so that a few items land on every CTA and the tail stays short
+  // work items: ~40 rows each amortise the per-item set-up; with few rows in total they shrink (down to 16) so that
+  // every CTA still gets half a dozen items from the counter and the tail of the last wave stays short
+  const double total_rows = (double)p.tokens * p.topk;
+  double target = total_rows / ((double)sm_count() * per_sm * 6.0);
+  target = target < 16.0 ? 16.0 : (target > 40.0 ? 40.0 : target);
   const double rows_per_tile_expert = (double)kTileTokens * p.topk / p.E;
-  int supertile = (int)((40.0 + rows_per_tile_expert - 1e-9) / rows_per_tile_expert);
+  int supertile = (int)((target + rows_per_tile_expert - 1e-9) / rows_per_tile_expert);
   if (supertile < 1) supertile = 1;
   if (supertile > 64) supertile = 64;
-  int parts = (int)(supertile * rows_per_tile_expert / 40.0);
+  int parts = (int)(supertile * rows_per_tile_expert / target);
   if (parts < 1) parts = 1;
   if (parts > 64) parts = 64;
   p.supertile = supertile;

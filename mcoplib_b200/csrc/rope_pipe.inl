@@ -23,8 +23,7 @@ __global__ void __launch_bounds__(256, 2) rope_neox_pipe(RopeParams p, int64_t t
   const uint32_t v_bytes = STORE ? k_bytes : 0u;
   const uint32_t cs_bytes = (uint32_t)(p.rot_dim * sizeof(CT));
   const uint32_t stage_bytes = q_bytes + k_bytes + v_bytes + cs_bytes;
-  const int64_t nchunks = (tokens + chunk - 1) / chunk;
-  const int j = threadIdx.x % hv;            // slice of the head this thread owns (blockDim % hv == 0)
+  const int j = threadIdx.x % hv;           // slice of the head this thread owns (blockDim % hv == 0)
   const int heads_per_iter = blockDim.x / hv;
   const int nqk = p.num_heads + p.num_kv_heads;
 
@@ -36,9 +35,11 @@ __global__ void __launch_bounds__(256, 2) rope_neox_pipe(RopeParams p, int64_t t
 
   uint32_t it = 0, issued = 0;
   bool alive = true;
-  for (int64_t c = blockIdx.x; c < nchunks && alive; c += gridDim.x) {
-    const int64_t t0 = c * chunk;
-    const int ntok = (int)min((int64_t)chunk, tokens - t0);
+  // every CTA owns one contiguous share of the tokens (equal to within one token) and walks it in chunks
+  const int64_t tok_begin = (tokens * (int64_t)blockIdx.x) / gridDim.x;
+  const int64_t tok_end = (tokens * ((int64_t)blockIdx.x + 1)) / gridDim.x;
+  for (int64_t t0 = tok_begin; t0 < tok_end && alive; t0 += chunk) {
+    const int ntok = (int)min((int64_t)chunk, tok_end - t0);
     if (threadIdx.x < ntok) {
       s_pos[threadIdx.x] = p.positions[t0 + threadIdx.x];
       if (STORE) {
@@ -200,10 +201,8 @@ int launch_rope_pipe(const RopeParams& p, int64_t tokens, cudaStream_t stream) {
   }
   if (per_sm == 0) return 1;
   int64_t grid = (int64_t)sm_count() * per_sm;
-  int chunk = (int)(tokens / (grid * 4));
-  chunk = chunk < 8 ? 8 : (chunk > kRopeChunk ? kRopeChunk : chunk);
-  const int64_t nchunks = (tokens + chunk - 1) / chunk;
-  if (grid > nchunks) grid = nchunks;
+  if (grid > (tokens + 7) / 8) grid = (tokens + 7) / 8;
+  const int chunk = kRopeChunk;
   rope_neox_pipe<T, CT, PER_OP, STORE><<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, chunk, pipe_error_ptr());
   return check_launch("rope (pipelined)");
 }
