@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
   }
   __syncthreads();
 
-  uint32_t it = 0;        // items consumed so far by this CTA (selects stage and phase)
+  uint32_t it = 0;        // items consumed so far by this CTA
+  RingPos cons, prod;     // ring positions of the consumer (all threads) and of the producer (thread 0)
   uint32_t issued = 0;    // items issued so far (thread 0 only)
   bool alive = true;
   // every CTA owns one contiguous share of the tokens (equal to within one token, whatever the chunk size) and
@@ -232,10 +233,11 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
     auto issue_next = [&]() -> bool {  // issues the next row of the chunk, if any
       while (ptl < ntok && (s_cnt[ptl] < 0 || pj >= s_cnt[ptl])) { ++ptl; pj = 0; }
       if (ptl >= ntok) return false;
-      const int s = (int)(issued % (uint32_t)stages);
+      const int s = prod.s;
       mbar_expect_tx(&full[s], row_bytes);
       bulk_g2s(buf + (size_t)s * row_bytes, p.y + (int64_t)s_rows[ptl][pj] * H, row_bytes, &full[s]);
       ++issued; ++pj;
+      prod.advance(stages);
       return true;
     };
     if (threadIdx.x == 0)
@@ -260,8 +262,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
         accumulate_by_scan<THREADS, NVEC>(p, t, acc);
       } else {
         for (int j = 0; j < n; ++j) {
-          const int s = (int)(it % (uint32_t)stages);
-          const bool ok = mbar_wait_bounded(&full[s], (it / (uint32_t)stages) & 1u, err, 3);
+          const int s = cons.s;
+          const bool ok = mbar_wait_bounded(&full[s], cons.phase, err, 3);
           if (ok) {
             const unsigned char* src = buf + (size_t)s * row_bytes;
             const float w = p.weighted ? s_w[tl][j] : 1.f;
@@ -274,6 +276,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
           // one barrier per row: agrees on success and tells that every thread has left the stage buffer
           if (!__syncthreads_and(ok)) { alive = false; break; }
           ++it;
+          cons.advance(stages);
           if (threadIdx.x == 0) {
             proxy_fence_before_reuse();
             issue_next();
@@ -292,8 +295,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
   }
   if (!alive && threadIdx.x == 0) {
     // a wait ran out: drain (bounded) the copies still in flight before the CTA gives its shared memory back
-    for (uint32_t k = it; k < issued; ++k)
-      (void)mbar_wait_bounded(&full[k % (uint32_t)stages], (k / (uint32_t)stages) & 1u, err, 4);
+    for (uint32_t k = it; k < issued; ++k, cons.advance(stages))
+      (void)mbar_wait_bounded(&full[cons.s], cons.phase, err, 4);
   }
 }
 

@@ -213,6 +213,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
   __syncthreads();
 
   uint32_t it = 0, issued = 0, flip = 0;
+  RingPos cons, prod;  // ring positions of the consumer (all threads) and of the producer (thread 0)
   bool alive = true;
   while (alive) {
     if (threadIdx.x == 0) s_item = atomicAdd(p.work_counter, 1);
@@ -256,16 +257,17 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
       int pi = 0;  // producer cursor inside the batch (thread 0)
       auto issue_next = [&]() {
         if (pi >= nb) return;
-        const int s = (int)(issued % (uint32_t)stages);
+        const int s = prod.s;
         mbar_expect_tx(&full[s], row_bytes);
         bulk_g2s(buf + (size_t)s * row_bytes, p.hidden + (int64_t)s_tok[pi] * H, row_bytes, &full[s]);
         ++issued; ++pi;
+        prod.advance(stages);
       };
       if (threadIdx.x == 0)
         for (int s = 0; s < stages; ++s) issue_next();
       for (int i = 0; i < nb; ++i) {
-        const int s = (int)(it % (uint32_t)stages);
-        const bool ok = mbar_wait_bounded(&full[s], (it / (uint32_t)stages) & 1u, err, 5);
+        const int s = cons.s;
+        const bool ok = mbar_wait_bounded(&full[s], cons.phase, err, 5);
         const float w = s_wt[i];
         const int row = b0 + i;
         float2 vv[NVEC][4];
@@ -295,6 +297,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
         // has left the stage buffer (the two `red` halves alternate, so no second barrier is needed)
         if (!__syncthreads_and(ok)) { alive = false; break; }
         ++it; ++flip;
+        cons.advance(stages);
         if (threadIdx.x == 0) {
           proxy_fence_before_reuse();
           issue_next();
@@ -328,8 +331,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
     }
   }
   if (!alive && threadIdx.x == 0) {
-    for (uint32_t k = it; k < issued; ++k)
-      (void)mbar_wait_bounded(&full[k % (uint32_t)stages], (k / (uint32_t)stages) & 1u, err, 6);
+    for (uint32_t k = it; k < issued; ++k, cons.advance(stages))
+      (void)mbar_wait_bounded(&full[cons.s], cons.phase, err, 6);
   }
 }
 

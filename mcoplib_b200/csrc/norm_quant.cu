@@ -302,9 +302,10 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
   }
 
   int64_t i = 0;
-  for (; i < n; ++i) {
-    const int s = (int)(i % stages);
-    const bool ok = mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), err, 1);
+  RingPos pos;
+  for (; i < n; ++i, pos.advance(stages)) {
+    const int s = pos.s;
+    const bool ok = mbar_wait_bounded(&full[s], pos.phase, err, 1);
     if (!__syncthreads_and(ok)) break;  // uniform decision: nobody is left behind at a barrier
     const int64_t row = first + i * step;
     const unsigned char* xs = buf + (size_t)s * stage_bytes;
@@ -378,8 +379,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
   }
   if (i < n && threadIdx.x == 0) {
     // a wait ran out: drain (bounded) what is still in flight so that no copy lands after the CTA has exited
-    for (int64_t k = i; k < n && k < i + stages; ++k)
-      (void)mbar_wait_bounded(&full[k % stages], (uint32_t)((k / stages) & 1), err, 2);
+    for (int64_t k = i; k < n && k < i + stages; ++k, pos.advance(stages))
+      (void)mbar_wait_bounded(&full[pos.s], pos.phase, err, 2);
   }
 }
 

@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(256, 2) rope_neox_pipe(RopeParams p, int64_t t
   __syncthreads();
 
   uint32_t it = 0, issued = 0;
+  RingPos cons, prod;  // ring positions of the consumer (all threads) and of the producer (thread 0)
   bool alive = true;
   // every CTA owns one contiguous share of the tokens (equal to within one token) and walks it in chunks
   const int64_t tok_begin = (tokens * (int64_t)blockIdx.x) / gridDim.x;
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(256, 2) rope_neox_pipe(RopeParams p, int64_t t
     int pi = 0;  // producer cursor (thread 0)
     auto issue_next = [&]() {
       if (pi >= ntok) return;
-      const int s = (int)(issued % (uint32_t)stages);
+      const int s = prod.s;
       unsigned char* dst = buf + (size_t)s * stage_bytes;
       const int64_t t = t0 + pi;
       mbar_expect_tx(&full[s], stage_bytes);
@@ -61,12 +62,13 @@ __global__ void __launch_bounds__(256, 2) rope_neox_pipe(RopeParams p, int64_t t
       if (STORE) bulk_g2s(dst + q_bytes + k_bytes, reinterpret_cast<const T*>(p.v_src) + t * p.v_stride, v_bytes, &full[s]);
       bulk_g2s(dst + q_bytes + k_bytes + v_bytes, reinterpret_cast<const CT*>(p.cos) + s_pos[pi] * p.cs_row_stride, cs_bytes, &full[s]);
       ++issued; ++pi;
+      prod.advance(stages);
     };
     if (threadIdx.x == 0)
       for (int s = 0; s < stages; ++s) issue_next();
     for (int tl = 0; tl < ntok; ++tl) {
-      const int s = (int)(it % (uint32_t)stages);
-      const bool ok = mbar_wait_bounded(&full[s], (it / (uint32_t)stages) & 1u, err, 7);
+      const int s = cons.s;
+      const bool ok = mbar_wait_bounded(&full[s], cons.phase, err, 7);
       if (ok) {
         const int64_t t = t0 + tl;
         const unsigned char* st = buf + (size_t)s * stage_bytes;
@@ -148,6 +150,7 @@ __global__ void __launch_bounds__(256, 2) rope_neox_pipe(RopeParams p, int64_t t
       // one barrier per token: agrees on success and tells that every thread has left the stage buffer
       if (!__syncthreads_and(ok)) { alive = false; break; }
       ++it;
+      cons.advance(stages);
       if (threadIdx.x == 0) {
         proxy_fence_before_reuse();
         issue_next();
@@ -156,8 +159,8 @@ __global__ void __launch_bounds__(256, 2) rope_neox_pipe(RopeParams p, int64_t t
     __syncthreads();  // s_pos / s_slot are rewritten by the next chunk
   }
   if (!alive && threadIdx.x == 0) {
-    for (uint32_t k = it; k < issued; ++k)
-      (void)mbar_wait_bounded(&full[k % (uint32_t)stages], (k / (uint32_t)stages) & 1u, err, 8);
+    for (uint32_t k = it; k < issued; ++k, cons.advance(stages))
+      (void)mbar_wait_bounded(&full[cons.s], cons.phase, err, 8);
   }
 }
 

@@ -63,6 +63,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// Position in a ring of `stages` buffers: stage index and phase parity of its mbarrier, advanced without the
+// integer division a running counter would need on every row.
+struct RingPos {
+  int s = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int stages) {
+    if (++s == stages) { s = 0; phase ^= 1u; }
+  }
+};
+
 __device__ __forceinline__ uint4 lds_u4(const void* p) {
   uint4 r;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(smem_addr(p)));
