@@ -302,13 +302,14 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
           proxy_fence_before_reuse();
           issue_next();
         }
-        float m = lane < NWARP ? rd[lane] : 0.f;
-        m = warp_max(m);
-        float scale, mul;
-        row_scale_from_amax(m, scale, mul);
-        if (!(m > 0.f)) mul = 0.f;  // all-zero row: codes 0 (keeps NaN out of the bit-level conversion below)
+        // max over the NWARP (a power of two <= 32) warp maxima: every lane reads one of them, log2(NWARP) steps
+        float m = rd[lane & (NWARP - 1)];
+#pragma unroll
+        for (int o = NWARP / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        // all-zero row: codes 0 (keeps NaN out of the bit-level conversion below)
+        const float mul = m > 0.f ? 127.0f * (1.0f / m) : 0.f;
         const float2 mul2 = make_float2(mul, mul);
-        if (threadIdx.x == 0) p.row_scales[row] = scale;
+        if (threadIdx.x == 0) p.row_scales[row] = (float)((double)m * 0.0078740157);
         int8_t* out = p.rows + (int64_t)row * H;
 #pragma unroll
         for (int k = 0; k < NVEC; ++k) {
