@@ -203,6 +203,18 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Warp maximum of values that are >= 0 and not NaN: for those the order of the floats is the order of their bit
+// patterns as unsigned integers, so one redux.sync replaces the five shuffle + max steps.
+__device__ __forceinline__ float warp_max_nonneg(float v) {
+  return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
+}
+// max(|a|, |b|, |c|) in one instruction (three-input maximum of sm_100); a NaN operand is ignored like in fmaxf.
+__device__ __forceinline__ float max3_abs(float a, float b, float c) {
+  float d;
+  asm("max.abs.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool IS_MAX> __device__ __forceinline__ float block_reduce(float v, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
   v = IS_MAX ? warp_max(v) : warp_sum(v);

@@ -189,7 +189,7 @@ __device__ __forceinline__ void row_scale_from_amax(float amax, float& scale_out
 
 
 // Persistent pipelined quant kernel.  Dynamic shared memory: 128 bytes of mbarriers, then `stages` row buffers.
-template <int THREADS, int NVEC>
+template <int THREADS, int NVEC, bool FULL>  // FULL: the row is exactly THREADS * NVEC vectors of 8, no lane is ever idle
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_quant_pipe(ScatterQuantParams p, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float red[2][33];
@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
 #pragma unroll
     for (int k = 0; k < NVEC; ++k) {
       const int v = threadIdx.x + k * THREADS;
-      if (v < nv) {
+      if (FULL || v < nv) {
         const float4 a = __ldg(reinterpret_cast<const float4*>(smp + v * 8));
         const float4 b = __ldg(reinterpret_cast<const float4*>(smp + v * 8) + 1);
         sm[k][0] = make_float2(a.x, a.y); sm[k][1] = make_float2(a.z, a.w);
@@ -278,19 +278,19 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
 #pragma unroll
           for (int k = 0; k < NVEC; ++k) {
             const int v = threadIdx.x + k * THREADS;
-            if (v < nv) {
+            if (FULL || v < nv) {
               const uint4 raw = lds_u4(src + v * 16);
               const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const float2 x2 = make_float2(__uint_as_float(wd[q] << 16), __uint_as_float(wd[q] & 0xffff0000u));
                 vv[k][q] = mul2_rn(mul2_rn(x2, w2), sm[k][q]);  // (x * w) * smooth, each product rounded
-                amax = fmaxf(amax, fmaxf(fabsf(vv[k][q].x), fabsf(vv[k][q].y)));
+                amax = max3_abs(amax, vv[k][q].x, vv[k][q].y);
               }
             }
           }
         }
-        amax = warp_max(amax);
+        amax = warp_max_nonneg(amax);
         float* rd = red[flip & 1u];
         if (lane == 0) rd[warp] = amax;
         // the single barrier of the row: agrees on success, publishes the warp maxima and tells that every thread
@@ -302,10 +302,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
           proxy_fence_before_reuse();
           issue_next();
         }
-        // max over the NWARP (a power of two <= 32) warp maxima: every lane reads one of them, log2(NWARP) steps
-        float m = rd[lane & (NWARP - 1)];
-#pragma unroll
-        for (int o = NWARP / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        // max over the NWARP warp maxima: the first NWARP lanes read one each, one warp reduction
+        const float m = warp_max_nonneg(lane < NWARP ? rd[lane] : 0.f);
         // all-zero row: codes 0 (keeps NaN out of the bit-level conversion below)
         const float mul = m > 0.f ? 127.0f * (1.0f / m) : 0.f;
         const float2 mul2 = make_float2(mul, mul);
@@ -314,7 +312,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_qua
 #pragma unroll
         for (int k = 0; k < NVEC; ++k) {
           const int v = threadIdx.x + k * THREADS;
-          if (v < nv) {
+          if (FULL || v < nv) {
             // |v * mul| <= 127 * (1 + 2^-22): rounds into [-127, 127], no clamp needed
             uint32_t c[8];
 #pragma unroll
@@ -444,11 +442,16 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   if (grid > nitems) grid = nitems;
   static std::atomic<int> attr_done{0};
   if (!attr_done.load(std::memory_order_relaxed)) {
-    cudaError_t e = cudaFuncSetAttribute(scatter_quant_pipe<THREADS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(scatter_quant_pipe<THREADS, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(scatter_quant_pipe<THREADS, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done.store(1, std::memory_order_relaxed);
   }
-  scatter_quant_pipe<THREADS, 4><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
+  if ((p.hidden_size >> 3) == THREADS * 4)
+    scatter_quant_pipe<THREADS, 4, true><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
+  else
+    scatter_quant_pipe<THREADS, 4, false><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
   return check_launch("moe_scatter_quant_i8 (quant, pipelined)");
 }
 
@@ -515,6 +518,8 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
     scatter_fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p);
     rc = check_launch("moe_scatter_quant_i8 (fill)");
     if (rc) return rc;
+    // 7 warps when they tile the row exactly (hidden 7168 = 4 x 224 vectors of 8): no idle lanes in the last pass
+    if (nv <= 896 && nv % 224 == 0) return launch_quant_pipe<224>(p, s);
     if (nv <= 1024) return launch_quant_pipe<256>(p, s);
     return launch_quant_pipe<512>(p, s);
   }
