@@ -262,11 +262,20 @@ __device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int THREADS, int NVEC>
+// FULL: the row is exactly THREADS * NVEC vectors of 8, so no lane is ever idle and no pass needs a bounds test.
+// LOCKSTEP selects how the warps of the CTA are kept together (both forms compute the same values):
+//   false - two CTA barriers per row: the per-warp partial results of the two reductions go to shared-memory slots
+//           that alternate between consecutive rows, so neither reduction needs a trailing barrier;
+//   true  - a barrier before the stage is read and the classic two-barrier block reductions (five per row).
+// Measured on B200: with 7 warps (hidden 7168) the loose form is 6 % faster (6.36 vs 5.97 TB/s); with 8 warps
+// (hidden 8192) the lock-step form is 14 % faster (6.26 vs 5.50 TB/s), so the launcher picks per CTA size.
+template <int THREADS, int NVEC, bool FULL, bool LOCKSTEP>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_bf16_pipe(NormParams p, int64_t tokens, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ float red[33];
-  __shared__ double red64[33];
+  __shared__ float red[2][32];
+  __shared__ __align__(16) double red64[2][32];
+  constexpr int NWARP = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // `stages` (<= 8) barriers in the first 128 bytes
   unsigned char* buf = smem + 128;
   const int H = p.hidden, nv = H >> 3;
@@ -298,23 +307,27 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * THREADS;
-    w2[i] = v < nv ? ld_nc_u4(reinterpret_cast<const __nv_bfloat16*>(p.weight) + v * 8) : make_uint4(0, 0, 0, 0);
+    w2[i] = (FULL || v < nv) ? ld_nc_u4(reinterpret_cast<const __nv_bfloat16*>(p.weight) + v * 8) : make_uint4(0, 0, 0, 0);
   }
 
   int64_t i = 0;
   RingPos pos;
-  for (; i < n; ++i, pos.advance(stages)) {
+  uint32_t flip = 0;
+  for (; i < n; ++i, pos.advance(stages), flip ^= 1u) {
     const int s = pos.s;
     const bool ok = mbar_wait_bounded(&full[s], pos.phase, err, 1);
-    if (!__syncthreads_and(ok)) break;  // uniform decision: nobody is left behind at a barrier
+    if constexpr (LOCKSTEP) {
+      if (!__syncthreads_and(ok)) break;  // uniform decision: nobody is left behind at a barrier
+    }
     const int64_t row = first + i * step;
     const unsigned char* xs = buf + (size_t)s * stage_bytes;
     float sv[NVEC][8];
     double ss = 0.0;
+    if (ok)  // when the wait ran out the stage is not read; the next barrier then ends the loop for everybody
 #pragma unroll
     for (int k = 0; k < NVEC; ++k) {
       const int v = threadIdx.x + k * THREADS;
-      if (v < nv) {
+      if (FULL || v < nv) {
         unpack_bf16x8(lds_u4(xs + v * 16), sv[k]);
         if (has_res) {
           float r[8];
@@ -330,10 +343,24 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
         for (int j = 0; j < 8; ++j) sv[k][j] = 0.f;
       }
     }
-    ss = block_sum_f64(ss, red64);  // its barrier also tells that every thread has left the stage buffer
+    if constexpr (LOCKSTEP) {
+      ss = block_sum_f64(ss, &red64[0][0]);  // its barrier also tells that every thread has left the stage buffer
+    } else {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) red64[flip][warp] = ss;
+      // first barrier of the row: agrees on success, publishes the warps' partial sums and tells that every thread
+      // has left the stage buffer
+      if (!__syncthreads_and(ok)) break;
+    }
     if (threadIdx.x == 0 && i + stages < n) {
       proxy_fence_before_reuse();
       issue(s, first + (i + stages) * step);
+    }
+    if constexpr (!LOCKSTEP) {
+      ss = lane < NWARP ? red64[flip][lane] : 0.0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     }
     const float r = inv_rms(ss, H, p.eps);
     uint32_t n2[NVEC][4];
@@ -349,8 +376,15 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
         amax2 = __hmax2(amax2, __habs2(nn));
       }
     }
-    float amax = fmaxf(__low2float(amax2), __high2float(amax2));
-    amax = block_reduce<true>(amax, red);
+    float amax = fmaxf(__low2float(amax2), __high2float(amax2));  // never negative, never NaN
+    if constexpr (LOCKSTEP) {
+      amax = block_reduce<true>(amax, &red[0][0]);
+    } else {
+      amax = warp_max_nonneg(amax);
+      if (lane == 0) red[flip][warp] = amax;
+      __syncthreads();  // second barrier of the row
+      amax = warp_max_nonneg(lane < NWARP ? red[flip][lane] : 0.f);
+    }
     const bool clamp = p.scale_ub != nullptr;  // only an upper bound on the scale can push codes out of range
     if (clamp) amax = fminf(amax, *p.scale_ub);
     const float scale = fmaxf(amax / 127.0f, FLT_EPSILON);
@@ -360,7 +394,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
 #pragma unroll
     for (int k = 0; k < NVEC; ++k) {
       const int v = threadIdx.x + k * THREADS;
-      if (v < nv) {
+      if (FULL || v < nv) {
         uint32_t c[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -394,7 +428,9 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   stages = stages < 2 ? 2 : (stages > 4 ? 4 : stages);
   const size_t smem = 128 + (size_t)stages * stage_bytes;
   if (smem > 220 * 1024) return 1;
-  const int threads = nv <= 1024 ? 256 : 512;
+  // 7 warps when they tile the row exactly (hidden 7168 = 4 x 224 vectors of 8), else 8 or 16
+  const int threads = (nv <= 896 && nv % 224 == 0) ? 224 : (nv <= 1024 ? 256 : 512);
+  const bool full = nv == threads * 4;
   int per_sm = (int)((227 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : per_sm;
   if (per_sm > 2048 / threads) per_sm = 2048 / threads;
@@ -402,7 +438,7 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > tokens) grid = tokens;
   int* err = pipe_error_ptr();
-  static std::atomic<int> attr_done[2];
+  static std::atomic<int> attr_done[4];
   auto launch = [&](auto kernel, int slot) -> int {
     if (attr_done[slot].load(std::memory_order_relaxed) < (int)smem) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
@@ -412,8 +448,10 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
     kernel<<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, err);
     return check_launch("norm (pipelined)");
   };
-  if (threads == 256) return launch(norm_quant_bf16_pipe<256, 4>, 0);
-  return launch(norm_quant_bf16_pipe<512, 4>, 1);
+  if (threads == 224)
+    return full ? launch(norm_quant_bf16_pipe<224, 4, true, false>, 0) : launch(norm_quant_bf16_pipe<224, 4, false, false>, 1);
+  if (threads == 256) return launch(norm_quant_bf16_pipe<256, 4, false, true>, 2);
+  return launch(norm_quant_bf16_pipe<512, 4, false, true>, 3);
 }
 
 template <typename T, typename WT, int MODE>
