@@ -9,6 +9,7 @@
 // multiple of 16 bytes.
 
 constexpr int kRopeChunk = 64;
+constexpr int kRopeMaxKvHeads = 128;  // more KV heads than this use the token-per-CTA kernel
 
 // 80 registers per thread (no spills in any instantiation): four CTAs of six warps then fit the register file of an
 // SM, which is split over its four schedulers (24 warps = 6 per scheduler x 32 lanes x 80 registers).
@@ -17,6 +18,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int64_t s_pos[kRopeChunk];
   __shared__ int64_t s_slot[kRopeChunk];
+  __shared__ float s_kinv[kRopeMaxKvHeads], s_vinv[kRopeMaxKvHeads];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   unsigned char* buf = smem + 128;
   const int D = p.head_size, half = D >> 1, hv = half >> 3;
@@ -32,6 +34,13 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
+  }
+  if (STORE) {
+    // reciprocal scales once per CTA: the token loop then reads them from shared memory, not from global memory
+    for (int h = threadIdx.x; h < p.num_kv_heads; h += blockDim.x) {
+      s_kinv[h] = 1.0f / p.k_scale[h];
+      s_vinv[h] = 1.0f / p.v_scale[h];
+    }
   }
   __syncthreads();
 
@@ -123,7 +132,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
             Vec8<T>::store(dst + half + j * 8, yo);
           }
           if (STORE && is_k && slot >= 0) {
-            const float inv = 1.0f / p.k_scale[hh];
+            const float inv = s_kinv[hh];
             int8_t* kc = p.k_cache + (slot * p.num_kv_heads + hh) * (int64_t)D;
             st_cs_u2(kc + j * 8, quant8(xo, inv));
             st_cs_u2(kc + half + j * 8, quant8(yo, inv));
@@ -143,7 +152,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
               unpack_f16x8(lds_u4(vs + hh * D + e), a);
               unpack_f16x8(lds_u4(vs + hh * D + e + 8), b);
             }
-            const float inv = 1.0f / p.v_scale[hh];
+            const float inv = s_vinv[hh];
             const uint2 qa = quant8(a, inv), qb = quant8(b, inv);
             st_cs_u4(p.v_cache + (slot * p.num_kv_heads + hh) * (int64_t)D + e, make_uint4(qa.x, qa.y, qb.x, qb.y));
           }
@@ -170,7 +179,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
 template <typename T, typename CT, bool PER_OP, bool STORE>
 int launch_rope_pipe(const RopeParams& p, int64_t tokens, cudaStream_t stream) {
   const int D = p.head_size, hv = D >> 4;
-  if (hv < 1 || 256 % hv != 0) return 1;
+  if (hv < 1 || 256 % hv != 0 || p.num_kv_heads > kRopeMaxKvHeads) return 1;
   const size_t stage_bytes = (size_t)(p.num_heads + p.num_kv_heads * (STORE ? 2 : 1)) * D * sizeof(T) + (size_t)p.rot_dim * sizeof(CT);
   // block size: the (Hq + Hkv) heads are walked in `iters` rounds of `hpi` heads, chosen so that every round is
   // full (72 heads -> 3 rounds of 24 heads = 192 threads at D = 128) instead of leaving a ragged last round
