@@ -229,6 +229,25 @@ int mcop_moe_swiglu_quant_i8(const void* x, const float* smooth, const int32_t* 
                              int8_t* out, float* scales, int64_t rows, int64_t hidden, int experts,
                              mcop_stream_t stream);
 
+/* mcoplib.op.fused_silu_mul_dq_reorder_quant, op/int8_quant_kernels.cu:1355-1417,1893-1940 (include/int8_quant_kernel.h:7-14),
+ * and with row_ids == NULL the unmasked form fused_silu_mul_dq_quant_interface (:1877-1891):
+ * x [rows, 2n] = gate || up in dtype (MCOP_BF16 / MCOP_F16); row r is processed iff id_lo <= row_ids[r] <= id_hi
+ * (ids int32, or int64 when ids_are_i64), other rows are not written.  v = up * (gate * (1 / (1 + exp(-gate)))) in
+ * fp32; scales[r] = max|v| * (1/127); out[r, :] = int8(rne(v * (127 / max|v|))).  The reference accepts a w2_scale
+ * tensor and never applies it (both instantiations pass HAS_SCALE = false), so there is no such argument here. */
+int mcop_silu_mul_quant_i8(const void* x, int dtype, const void* row_ids, int ids_are_i64, int64_t id_lo,
+                           int64_t id_hi, int8_t* out, float* scales, int64_t rows, int64_t n,
+                           mcop_stream_t stream);
+
+/* mcoplib.op.fused_silu_mul_dq_mask_quant, op/int8_quant_kernels.cu:881-955,1844-1875 (include/int8_quant_kernel.h:2-5):
+ * x [groups, rows_per_group, 2n]; group_counts[g] (int32 / int64) = number of valid rows of group g.  Every valid row
+ * becomes one byte record of out_stride_elems * 2 bytes in out_packed [groups, rows_per_group, out_stride_elems]
+ * (16-bit elements): bytes [0, n) the int8 codes, bytes [n, n+4) the fp32 scale; other rows and bytes are not
+ * written.  Same arithmetic as mcop_silu_mul_quant_i8.  n must be a multiple of 4 (the reference needs 8). */
+int mcop_silu_mul_quant_i8_masked_pack(const void* x, int dtype, const void* group_counts, int counts_are_i64,
+                                       void* out_packed, int64_t groups, int64_t rows_per_group, int64_t n,
+                                       int64_t out_stride_elems, mcop_stream_t stream);
+
 /* Size of the built-in scratch area of mcop_moe_gather_noalloc (bytes held by every GPU that loads the library). */
 #define MCOP_GATHER_NOALLOC_SCRATCH_BYTES (4u << 20)
 

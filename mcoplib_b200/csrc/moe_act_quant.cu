@@ -124,3 +124,168 @@ extern "C" int mcop_moe_swiglu_quant_i8(const void* x, const float* smooth, cons
   else swiglu_quant_vec<1024, 4><<<grid, 1024, 0, s>>>(p);
   return check_launch("moe_swiglu_quant_i8");
 }
+
+// ---------------------------------------------------------------------------------------------
+// SiLU(gate) * up + per-row int8 quantisation without a smooth scale, in the two addressings of
+// mcoplib.op.fused_silu_mul_dq_reorder_quant and mcoplib.op.fused_silu_mul_dq_mask_quant
+// (op/int8_quant_kernels.cu:881-955, 1355-1417).  One CTA per processed row; the activated values stay in
+// registers across the abs-max reduction.
+// ---------------------------------------------------------------------------------------------
+namespace mcop {
+namespace {
+
+struct SiluMulParams {
+  const void* x;                 // [rows, 2n]: gate || up
+  int64_t rows; int n;
+  const void* ids; int ids_i64; int64_t id_lo, id_hi;   // reorder form: row processed iff id in [lo, hi]; null = all
+  const void* mask; int mask_i64; int64_t per_group;    // mask form: rows = groups * per_group, row (g, m) iff m < mask[g]
+  int8_t* out; int64_t out_row_bytes;                    // codes of row r at out + r * out_row_bytes
+  float* scales;                                         // null: the scale is packed into the row at byte n
+};
+
+__device__ __forceinline__ int64_t load_index(const void* p, int is_i64, int64_t i) {
+  return is_i64 ? reinterpret_cast<const int64_t*>(p)[i] : (int64_t)reinterpret_cast<const int32_t*>(p)[i];
+}
+
+__device__ __forceinline__ float silu_mul_value(float gate, float up) {
+  return up * (gate * (1.0f / (1.0f + expf(-gate))));
+}
+
+__device__ __forceinline__ void silu_mul_store_scale(const SiluMulParams& p, int64_t row, float amax) {
+  const float sc = (float)((double)amax * 0.0078740157);
+  if (p.scales) p.scales[row] = sc;
+  else *reinterpret_cast<float*>(p.out + row * p.out_row_bytes + p.n) = sc;
+}
+
+template <typename T, int THREADS, int NVEC>
+__device__ __forceinline__ void silu_mul_row_vec(const SiluMulParams& p, int64_t row, float* red) {
+  const int n = p.n, nv = n >> 3;
+  const T* g = reinterpret_cast<const T*>(p.x) + row * 2 * (int64_t)n;
+  const T* u = g + n;
+  float v[NVEC][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int k = threadIdx.x + i * THREADS;
+    if (k < nv) {
+      float a[8], b[8];
+      Vec8<T>::load_nc(g + k * 8, a);
+      Vec8<T>::load_nc(u + k * 8, b);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        v[i][q] = silu_mul_value(a[q], b[q]);
+        amax = fmaxf(amax, fabsf(v[i][q]));
+      }
+    }
+  }
+  amax = block_reduce<true>(amax, red);
+  if (threadIdx.x == 0) silu_mul_store_scale(p, row, amax);
+  const float mul = amax > 0.f ? 127.0f * (1.0f / amax) : 0.f;
+  int8_t* out = p.out + row * p.out_row_bytes;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int k = threadIdx.x + i * THREADS;
+    if (k < nv) {
+      int c[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) c[q] = q_rn_clamp(v[i][q] * mul, -128, 127);
+      st_cs_u2(out + k * 8, pack_i8x8(c));
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void silu_mul_row_any(const SiluMulParams& p, int64_t row, float* red) {
+  const int n = p.n;
+  const T* g = reinterpret_cast<const T*>(p.x) + row * 2 * (int64_t)n;
+  const T* u = g + n;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    amax = fmaxf(amax, fabsf(silu_mul_value(ElemTraits<T>::to_float(g[i]), ElemTraits<T>::to_float(u[i]))));
+  amax = block_reduce<true>(amax, red);
+  if (threadIdx.x == 0) silu_mul_store_scale(p, row, amax);
+  const float mul = amax > 0.f ? 127.0f * (1.0f / amax) : 0.f;
+  int8_t* out = p.out + row * p.out_row_bytes;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    out[i] = (int8_t)q_rn_clamp(silu_mul_value(ElemTraits<T>::to_float(g[i]), ElemTraits<T>::to_float(u[i])) * mul, -128, 127);
+}
+
+// grid.x walks rows (reorder form) or the rows of group blockIdx.y (mask form)
+template <typename T, int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(SiluMulParams p) {
+  __shared__ float red[33];
+  if (p.mask) {
+    const int64_t g = blockIdx.y;
+    int64_t cnt = load_index(p.mask, p.mask_i64, g);
+    cnt = cnt < 0 ? 0 : (cnt > p.per_group ? p.per_group : cnt);
+    for (int64_t m = blockIdx.x; m < cnt; m += gridDim.x) {  // uniform over the CTA
+      if constexpr (NVEC > 0) silu_mul_row_vec<T, THREADS, (NVEC > 0 ? NVEC : 1)>(p, g * p.per_group + m, red);
+      else silu_mul_row_any<T>(p, g * p.per_group + m, red);
+    }
+    return;
+  }
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    if (p.ids) {
+      const int64_t id = load_index(p.ids, p.ids_i64, row);
+      if (id < p.id_lo || id > p.id_hi) continue;  // uniform over the CTA
+    }
+    if constexpr (NVEC > 0) silu_mul_row_vec<T, THREADS, (NVEC > 0 ? NVEC : 1)>(p, row, red);
+    else silu_mul_row_any<T>(p, row, red);
+  }
+}
+
+template <typename T>
+int launch_silu_mul(const SiluMulParams& p, dim3 grid, bool vec_ok, cudaStream_t s, const char* what) {
+  const int nv = p.n >> 3;
+  if (!vec_ok) silu_mul_quant_kernel<T, 256, 0><<<grid, 256, 0, s>>>(p);
+  else if (nv <= 256) silu_mul_quant_kernel<T, 128, 2><<<grid, 128, 0, s>>>(p);
+  else if (nv <= 1024) silu_mul_quant_kernel<T, 256, 4><<<grid, 256, 0, s>>>(p);
+  else if (nv <= 2048) silu_mul_quant_kernel<T, 512, 4><<<grid, 512, 0, s>>>(p);
+  else silu_mul_quant_kernel<T, 1024, 4><<<grid, 1024, 0, s>>>(p);
+  return check_launch(what);
+}
+
+int dispatch_silu_mul(const SiluMulParams& p, dim3 grid, int dtype, cudaStream_t s, const char* what) {
+  const bool vec_ok = p.n % 8 == 0 && aligned16(p.x) && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0 &&
+                      p.out_row_bytes % 8 == 0 && (p.n >> 3) <= 4096;
+  switch (dtype) {
+    case MCOP_BF16: return launch_silu_mul<__nv_bfloat16>(p, grid, vec_ok, s, what);
+    case MCOP_F16: return launch_silu_mul<__half>(p, grid, vec_ok, s, what);
+  }
+  return set_error(MCOP_ERR_UNSUPPORTED, "%s: activation dtype %d (bf16 or f16 expected)", what, dtype);
+}
+
+}  // namespace
+}  // namespace mcop
+
+extern "C" int mcop_silu_mul_quant_i8(const void* x, int dtype, const void* row_ids, int ids_are_i64, int64_t id_lo,
+                                      int64_t id_hi, int8_t* out, float* scales, int64_t rows, int64_t n,
+                                      mcop_stream_t stream) {
+  MCOP_REQUIRE(x && out && scales, MCOP_ERR_ARGUMENT, "silu_mul_quant_i8: null pointer");
+  MCOP_REQUIRE(rows >= 0 && n > 0 && n <= 0x3fffffff, MCOP_ERR_ARGUMENT, "silu_mul_quant_i8: bad sizes");
+  if (rows == 0) return MCOP_OK;
+  SiluMulParams p{};
+  p.x = x; p.rows = rows; p.n = (int)n;
+  p.ids = row_ids; p.ids_i64 = ids_are_i64; p.id_lo = id_lo; p.id_hi = id_hi;
+  p.out = out; p.out_row_bytes = n; p.scales = scales;
+  const int64_t gx = rows < 0x7fffffffLL ? rows : 0x7fffffffLL;
+  return dispatch_silu_mul(p, dim3((unsigned)gx), dtype, (cudaStream_t)stream, "silu_mul_quant_i8");
+}
+
+extern "C" int mcop_silu_mul_quant_i8_masked_pack(const void* x, int dtype, const void* group_counts, int counts_are_i64,
+                                                  void* out_packed, int64_t groups, int64_t rows_per_group, int64_t n,
+                                                  int64_t out_stride_elems, mcop_stream_t stream) {
+  MCOP_REQUIRE(x && group_counts && out_packed, MCOP_ERR_ARGUMENT, "silu_mul_quant_i8_masked_pack: null pointer");
+  MCOP_REQUIRE(groups >= 0 && groups <= 65535 && rows_per_group >= 0 && n > 0 && n <= 0x3fffffff && n % 4 == 0, MCOP_ERR_ARGUMENT,
+               "silu_mul_quant_i8_masked_pack: bad sizes (at most 65535 groups, n a multiple of 4)");
+  MCOP_REQUIRE(out_stride_elems * 2 >= n + 4, MCOP_ERR_ARGUMENT,
+               "silu_mul_quant_i8_masked_pack: a row of %lld elements cannot hold %lld codes and the scale",
+               (long long)out_stride_elems, (long long)n);
+  if (groups == 0 || rows_per_group == 0) return MCOP_OK;
+  SiluMulParams p{};
+  p.x = x; p.rows = groups * rows_per_group; p.n = (int)n;
+  p.mask = group_counts; p.mask_i64 = counts_are_i64; p.per_group = rows_per_group;
+  p.out = reinterpret_cast<int8_t*>(out_packed); p.out_row_bytes = out_stride_elems * 2; p.scales = nullptr;
+  const int64_t gx = rows_per_group < 4096 ? rows_per_group : 4096;
+  return dispatch_silu_mul(p, dim3((unsigned)gx, (unsigned)groups), dtype, (cudaStream_t)stream, "silu_mul_quant_i8_masked_pack");
+}

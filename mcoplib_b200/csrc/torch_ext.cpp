@@ -480,6 +480,66 @@ void moe_swiglu_dynamic_quantize(Tensor scatter_tokens, Tensor smooth_scale, Ten
                                     hidden, total_experts_num, cur_stream()));
 }
 
+// mcoplib.op.fused_silu_mul_dq_reorder_quant (op/int8_quant_kernels.cu:1893-1940, include/int8_quant_kernel.h:7-14).
+// w2_scale is accepted and, as in the reference (HAS_SCALE = false in every instantiation), not applied.
+void fused_silu_mul_dq_reorder_quant(Tensor& out, Tensor& scale, const Tensor& input, const Tensor& reorder_topk_ids,
+                                     const Tensor& w2_scale, int64_t start_expert_id, int64_t end_expert_id) {
+  check_cuda(input, "input");
+  TORCH_CHECK(input.is_contiguous());
+  TORCH_CHECK(scale.is_contiguous());
+  TORCH_CHECK(out.is_contiguous());
+  TORCH_CHECK(reorder_topk_ids.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == at::kChar && scale.scalar_type() == at::kFloat);
+  TORCH_CHECK(reorder_topk_ids.scalar_type() == at::kInt || reorder_topk_ids.scalar_type() == at::kLong,
+              "reorder_topk_ids must be int32 or int64");
+  (void)w2_scale;
+  const int64_t hidden2 = input.size(-1);
+  TORCH_CHECK(hidden2 > 0 && hidden2 % 2 == 0, "the last dimension holds gate || up");
+  const int64_t rows = input.numel() / hidden2;
+  TORCH_CHECK(out.numel() == rows * (hidden2 / 2) && scale.numel() >= rows && reorder_topk_ids.numel() >= rows);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_silu_mul_quant_i8(input.data_ptr(), dtype_code(input, "fused_silu_mul_dq_reorder_quant"), reorder_topk_ids.data_ptr(),
+                                  reorder_topk_ids.scalar_type() == at::kLong ? 1 : 0, start_expert_id, end_expert_id,
+                                  out.data_ptr<int8_t>(), scale.data_ptr<float>(), rows, hidden2 / 2, cur_stream()));
+}
+
+// sglang's fused_silu_mul_dq_quant_interface (op/int8_quant_kernels.cu:1877-1891): every row is processed
+void fused_silu_mul_dq_quant(Tensor& out, Tensor& scale, const Tensor& input) {
+  check_cuda(input, "input");
+  TORCH_CHECK(input.is_contiguous());
+  TORCH_CHECK(scale.is_contiguous());
+  TORCH_CHECK(out.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == at::kChar && scale.scalar_type() == at::kFloat);
+  const int64_t hidden2 = input.size(-1);
+  TORCH_CHECK(hidden2 > 0 && hidden2 % 2 == 0, "the last dimension holds gate || up");
+  const int64_t rows = input.numel() / hidden2;
+  TORCH_CHECK(out.numel() == rows * (hidden2 / 2) && scale.numel() >= rows);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_silu_mul_quant_i8(input.data_ptr(), dtype_code(input, "fused_silu_mul_dq_quant"), nullptr, 0, 0, 0, out.data_ptr<int8_t>(),
+                                  scale.data_ptr<float>(), rows, hidden2 / 2, cur_stream()));
+}
+
+// mcoplib.op.fused_silu_mul_dq_mask_quant (op/int8_quant_kernels.cu:1844-1875, include/int8_quant_kernel.h:2-5)
+void fused_silu_mul_dq_mask_quant(Tensor& out, const Tensor& input, const Tensor& mask) {
+  check_cuda(input, "input");
+  TORCH_CHECK(input.is_contiguous());
+  TORCH_CHECK(out.is_contiguous());
+  TORCH_CHECK(mask.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == input.scalar_type(), "out is a byte record per row, declared in the activation dtype");
+  TORCH_CHECK(mask.scalar_type() == at::kInt || mask.scalar_type() == at::kLong, "mask must be int32 or int64");
+  const int64_t hidden2 = input.size(-1);
+  TORCH_CHECK(hidden2 > 0 && hidden2 % 2 == 0, "the last dimension holds gate || up");
+  const int64_t rows = input.numel() / hidden2;
+  const int64_t groups = mask.numel();
+  TORCH_CHECK(groups >= 1 && groups <= 1024 && rows % groups == 0);
+  const int64_t out_stride = ((hidden2 / 4 + 2) + 255) / 256 * 256;
+  TORCH_CHECK(out.numel() >= rows * out_stride && out.size(-1) == out_stride, "out must be [groups, rows, ", out_stride, "]");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_silu_mul_quant_i8_masked_pack(input.data_ptr(), dtype_code(input, "fused_silu_mul_dq_mask_quant"), mask.data_ptr(),
+                                              mask.scalar_type() == at::kLong ? 1 : 0, out.data_ptr(), groups, rows / groups, hidden2 / 2,
+                                              out_stride, cur_stream()));
+}
+
 // Weighted combine (addition of this build)
 void moe_gather_weighted(Tensor y, Tensor row2tok, Tensor topk_ids, Tensor topk_weights, Tensor experts_token_start, Tensor out,
                          bool accumulate, std::optional<Tensor> tok2row) {
@@ -544,6 +604,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_gather", &moe_gather, py::arg("scatter_tokens"), py::arg("scatter_tokens_offset"), py::arg("convergent_tokens"),
         py::arg("tok2row") = py::none());
   m.def("moe_swiglu_dynamic_quantize", &moe_swiglu_dynamic_quantize);
+  m.def("fused_silu_mul_dq_mask_quant", &fused_silu_mul_dq_mask_quant);
+  m.def("fused_silu_mul_dq_reorder_quant", &fused_silu_mul_dq_reorder_quant);
+  m.def("fused_silu_mul_dq_quant", &fused_silu_mul_dq_quant);
   // additions of this build (no reference counterpart)
   m.def("rope_kv_store_int8", &rope_kv_store_int8);
   m.def("moe_gather_weighted", &moe_gather_weighted, py::arg("y"), py::arg("row2tok"), py::arg("topk_ids"), py::arg("topk_weights"),

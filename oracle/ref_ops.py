@@ -564,6 +564,70 @@ def moe_swiglu_dynamic_quantize(x: torch.Tensor, smooth: torch.Tensor, starts: t
     return q, sc
 
 
+def absmax_row_quant(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row int8 quantisation shared by the silu_and_mul_*quant kernels of op/int8_quant_kernels.cu
+    (:934-953, :1398-1417): a = max|v|; scale = float(double(a) * 0.0078740157); q = rne(v * (127 * (1/a)))
+    saturated to int8 (|v * 127/a| <= 127 up to rounding, so the clamp never acts); a == 0 -> codes 0, scale 0.
+    Pinned (codes atol 1, scales allclose) by the reference tests' ref_dynamic_per_token_quant
+    (unit_test/test_silu_mul_dq_reorder_mask.py:12-45)."""
+    a = v.abs().amax(dim=-1)
+    sc = (a.double() * 0.0078740157).float()
+    mul = torch.where(a > 0, 127.0 * (1.0 / a), torch.zeros_like(a))
+    return float_to_int8_sym(v * mul.unsqueeze(-1)), sc
+
+
+def silu_mul(x: torch.Tensor) -> torch.Tensor:
+    """x [..., 2N] = gate || up in bf16/f16 -> fp32 up * (gate * (1 / (1 + exp(-gate)))), the expression of
+    op/int8_quant_kernels.cu:1383-1386 (no rounding to the activation type before the quantisation)."""
+    n = x.shape[-1] // 2
+    g = x[..., :n].float()
+    u = x[..., n:].float()
+    return u * (g * (1.0 / (1.0 + torch.exp(-g))))
+
+
+def fused_silu_mul_dq_reorder_quant(x: torch.Tensor, reorder_topk_ids: Optional[torch.Tensor], start_expert_id: int,
+                                    end_expert_id: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """mcoplib.op.fused_silu_mul_dq_reorder_quant, op/int8_quant_kernels.cu:1355-1417,1893-1940.
+    x [R, 2N]; row r is processed iff start <= reorder_topk_ids[r] <= end (all rows when ids is None: the form of
+    fused_silu_mul_dq_quant_interface, :1877-1891).  The w2_scale argument of the reference is never applied:
+    both branches of the interface instantiate the kernel with HAS_SCALE = false (:1908-1935).
+    Returns (codes int8 [R, N], scales fp32 [R], active bool [R]); inactive rows are 0 here, untouched on the GPU.
+    PARITY UNPINNED beyond absmax_row_quant: the reference test only prints error figures."""
+    R, n2 = x.shape
+    active = torch.ones(R, dtype=torch.bool) if reorder_topk_ids is None else \
+        (reorder_topk_ids.long() >= start_expert_id) & (reorder_topk_ids.long() <= end_expert_id)
+    q, sc = absmax_row_quant(silu_mul(x))
+    q = torch.where(active.unsqueeze(1), q, torch.zeros_like(q))
+    sc = torch.where(active, sc, torch.zeros_like(sc))
+    return q, sc, active
+
+
+def silu_mul_pack_stride(two_n: int) -> int:
+    """Row stride, in activation elements, of the packed output of fused_silu_mul_dq_mask_quant
+    (op/int8_quant_kernels.cu:1861): N code bytes + 4 scale bytes, rounded up to 256 elements."""
+    return ((two_n // 4 + 2) + 255) // 256 * 256
+
+
+def fused_silu_mul_dq_mask_quant(x: torch.Tensor, mask: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """mcoplib.op.fused_silu_mul_dq_mask_quant, op/int8_quant_kernels.cu:881-955,1844-1875.
+    x [G, M, 2N]; mask [G] = valid rows per group.  Output rows are byte records of out_stride * 2 bytes:
+    bytes [0, N) int8 codes, bytes [N, N+4) the fp32 scale; only rows m < mask[g] are written.
+    Returns (packed uint8 [G, M, stride_bytes] with unwritten bytes 0, written bool [G, M]).
+    The reference test checks the packed scale only (unit_test/test_silu_mul_dq_mask.py:223-236, rtol 1e-4,
+    atol 1e-3 against a bf16-rounded Triton product); codes are pinned through absmax_row_quant."""
+    G, M, n2 = x.shape
+    n = n2 // 2
+    stride_bytes = silu_mul_pack_stride(n2) * x.element_size()
+    q, sc = absmax_row_quant(silu_mul(x))
+    m_idx = torch.arange(M).unsqueeze(0)
+    written = m_idx < mask.long().clamp(0, M).unsqueeze(1)
+    packed = torch.zeros(G, M, stride_bytes, dtype=torch.uint8)
+    packed[:, :, :n] = q.view(torch.uint8)
+    packed[:, :, n:n + 4] = sc.contiguous().view(torch.uint8).reshape(G, M, 4)
+    packed = torch.where(written.unsqueeze(-1), packed, torch.zeros_like(packed))
+    return packed, written
+
+
 def moe_gather(y: torch.Tensor, row2tok: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """mcoplib.op.moe_gather, op/moe_gather.cu:30-62,137-150: out[row2tok[r]] += y[r].
     PARITY UNPINNED.  The reference accumulates with bf16 atomics in an unspecified order; this

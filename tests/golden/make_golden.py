@@ -151,6 +151,24 @@ def main():
     put(store, "ref:unit_test/test_moe_swiglu_dq.py:moe_swiglu_dynamic_quant_run/0", x=xs, smooth=sm, counts=counts,
         starts=starts, codes=qt, scales=st)
 
+    # ---------------------------------------------------------------- row quant of fused_silu_mul_dq_* ("next" row)
+    # unit_test/test_silu_mul_dq_reorder_mask.py:9-45 as_float32_tensor + ref_dynamic_per_token_quant (the torch part
+    # of that test; its SiLU*up product comes from a Triton kernel and cannot run here).  Fed with the fp32 product
+    # of the kernel's expression so that it follows the kernel's arithmetic.
+    import typing
+    tnames = {"Optional": typing.Optional, "Tuple": typing.Tuple, "Union": typing.Union}
+    as32 = load_function(ref, "unit_test/test_silu_mul_dq_reorder_mask.py", "as_float32_tensor",
+                         extra_globals=tnames, patch=[("device='cuda'", "device='cpu'")])
+    fn = load_function(ref, "unit_test/test_silu_mul_dq_reorder_mask.py", "ref_dynamic_per_token_quant",
+                       extra_globals=dict(tnames, as_float32_tensor=as32))
+    g = torch.Generator().manual_seed(8)
+    gu = torch.randn(24, 2 * 320, generator=g).bfloat16()
+    gate, up = gu[:, :320].float(), gu[:, 320:].float()
+    v = up * (gate * (1.0 / (1.0 + torch.exp(-gate))))
+    q, s = fn(v, torch.int8)
+    put(store, "ref:unit_test/test_silu_mul_dq_reorder_mask.py:ref_dynamic_per_token_quant/0", gate_up=gu, product=v,
+        codes=q, scales=s.reshape(-1))
+
     # ---------------------------------------------------------------- a8: store_kv_cache
     # unit_test/test_store_kv.py:91-128 TestKVCacheStorage.run_reference_impl (fp16, seed 42 layout,
     # 8 Q heads / 1 KV head, D 128; token count reduced from 4096 to 48 and two sequences).
