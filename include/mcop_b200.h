@@ -229,7 +229,20 @@ int mcop_moe_swiglu_quant_i8(const void* x, const float* smooth, const int32_t* 
                              int8_t* out, float* scales, int64_t rows, int64_t hidden, int experts,
                              mcop_stream_t stream);
 
-/* mcoplib.op.fused_silu_mul_dq_reorder_quant, op/int8_quant_kernels.cu:1355-1417,1893-1940 (include/int8_quant_kernel.h:7-14),
+/* mcoplib.op.fused_add_rms_norm_dynamic_per_token_quant_padding_output,
+ * op/fused_add_layernorm_per_token_quant_padding_output.cu:397-416 (include/fused_add_layernorm_per_token_quant_padding_output.h:3-11;
+ * wrapper mcoplib/custom_ops.py:7-27): residual add + RMSNorm + per-token int8 quantisation whose primary output is one
+ * byte record per token of pad_size_elems 16-bit elements: bytes [0, hidden) the codes, bytes [hidden, hidden+4) the
+ * fp32 scale, the rest not written.  residual is updated in place to T(x + residual).  out_norm (T [tokens, hidden]),
+ * out_codes (int8 [tokens, hidden]) and out_scales (fp32 [tokens]) are optional (NULL = not wanted).
+ * form: 0 = the reference's choice (1 iff hidden == 7168), 1 = its fp32 form (kernel :182-283), 2 = its rounded form
+ * (kernel :287-340); the two differ in where values are rounded to T, see the kernel file.  hidden % 4 == 0. */
+int mcop_add_rmsnorm_quant_i8_padded(const void* x, void* residual, const void* weight, void* out_packed,
+                                     void* out_norm, int8_t* out_codes, float* out_scales, int64_t tokens,
+                                     int64_t hidden, int64_t pad_size_elems, float eps, int form, int dtype,
+                                     mcop_stream_t stream);
+
+/* mcoplib.op.fused_silu_mul_dq_reorder_quant,op/int8_quant_kernels.cu:1355-1417,1893-1940 (include/int8_quant_kernel.h:7-14),
  * and with row_ids == NULL the unmasked form fused_silu_mul_dq_quant_interface (:1877-1891):
  * x [rows, 2n] = gate || up in dtype (MCOP_BF16 / MCOP_F16); row r is processed iff id_lo <= row_ids[r] <= id_hi
  * (ids int32, or int64 when ids_are_i64), other rows are not written.  v = up * (gate * (1 / (1 + exp(-gate)))) in

@@ -23,9 +23,16 @@ def _missing(name):
         "(needs nvcc with sm_100a support); there is no fallback implementation.")
 
 
-try:
-    from . import op  # noqa: F401  (pybind11 + torch-library shims)
-except ImportError as _e:  # pragma: no cover - exercised only on a broken install
-    if not _os.path.exists(LIBRARY_PATH):
-        _missing("libmcop_b200.so")
-    raise
+_OP_NAME = "op" + (__import__("sysconfig").get_config_var("EXT_SUFFIX") or ".so")
+_built = _os.path.exists(LIBRARY_PATH) and _os.path.exists(_os.path.join(PACKAGE_DIR, _OP_NAME))
+
+if _built:
+    from . import op  # noqa: F401  (pybind11 + torch-library shims; registers torch.ops.<namespace>.*)
+
+
+def __getattr__(name):
+    # Reached only when the native components are not built: the package itself stays importable so that
+    # `python -m mcoplib_b200.build` can run, but any use of the operators raises.
+    if name == "op":
+        _missing("libmcop_b200.so" if not _os.path.exists(LIBRARY_PATH) else _OP_NAME)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

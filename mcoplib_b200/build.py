@@ -26,7 +26,7 @@ BUILD = os.path.join(HERE, "build")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-CU_SOURCES = ["api_common.cu", "norm_quant.cu", "rope_kv.cu", "moe_route.cu", "moe_scatter.cu", "moe_gather.cu", "moe_act_quant.cu"]
+CU_SOURCES = ["api_common.cu", "norm_quant.cu", "norm_pad_quant.cu", "rope_kv.cu", "moe_route.cu", "moe_scatter.cu", "moe_gather.cu", "moe_act_quant.cu"]
 # -fmad=false: products and sums are rounded separately, as the CPU evaluation of the same formulas does.
 # Never --use_fast_math: division, sqrt and expf stay IEEE / full precision.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-fmad=false", "-lineinfo",

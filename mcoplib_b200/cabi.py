@@ -39,6 +39,7 @@ SIGNATURES = {
     "mcop_moe_gather": (I32, [P, P, P, P, I32, I64, I64, I64, P, SZ, P]),
     "mcop_moe_gather_weighted": (I32, [P, P, P, P, P, P, P, I32, I64, I64, I64, I32, I32, P, SZ, P]),
     "mcop_moe_swiglu_quant_i8": (I32, [P, P, P, P, P, P, I64, I64, I32, P]),
+    "mcop_add_rmsnorm_quant_i8_padded": (I32, [P, P, P, P, P, P, P, I64, I64, I64, F32, I32, I32, P]),
     "mcop_silu_mul_quant_i8": (I32, [P, I32, P, I32, I64, I64, P, P, I64, I64, P]),
     "mcop_silu_mul_quant_i8_masked_pack": (I32, [P, I32, P, I32, P, I64, I64, I64, I64, P]),
     "mcop_moe_gather_noalloc": (I32, [P, P, P, I64, I64, I64, P]),

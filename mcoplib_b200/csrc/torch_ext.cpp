@@ -480,6 +480,35 @@ void moe_swiglu_dynamic_quantize(Tensor scatter_tokens, Tensor smooth_scale, Ten
                                     hidden, total_experts_num, cur_stream()));
 }
 
+// mcoplib.op.fused_add_rms_norm_dynamic_per_token_quant_padding_output
+// (op/fused_add_layernorm_per_token_quant_padding_output.cu:397-416): `output` is the int8 view of a
+// [tokens, pad_size] 16-bit tensor, i.e. int8 [tokens, 2 * pad_size]
+void fused_add_rms_norm_dynamic_per_token_quant_padding_output(Tensor& output, Tensor& output_rms, Tensor& output_quant_int8,
+                                                               Tensor& out_scales, const Tensor& input, Tensor& residual,
+                                                               const Tensor& weight, int64_t pad_size, double epsilon) {
+  check_cuda(input, "input");
+  TORCH_CHECK(output.dtype() == torch::kInt8);
+  TORCH_CHECK(input.dtype() == at::ScalarType::BFloat16);
+  TORCH_CHECK(output.is_contiguous() && input.is_contiguous());
+  TORCH_CHECK(residual.is_contiguous() && weight.is_contiguous() && output_rms.is_contiguous() && output_quant_int8.is_contiguous() &&
+              out_scales.is_contiguous());
+  TORCH_CHECK(residual.scalar_type() == input.scalar_type() && weight.scalar_type() == input.scalar_type() &&
+              output_rms.scalar_type() == input.scalar_type());
+  TORCH_CHECK(output_quant_int8.scalar_type() == at::kChar && out_scales.scalar_type() == at::kFloat);
+  const int64_t hidden = input.size(-1);
+  TORCH_CHECK(hidden > 0 && hidden % 4 == 0, "hidden size must be a multiple of 4");
+  const int64_t tokens = input.numel() / hidden;
+  TORCH_CHECK(residual.numel() == input.numel() && weight.numel() == hidden && output_rms.numel() == input.numel() &&
+              output_quant_int8.numel() == input.numel() && out_scales.numel() >= tokens);
+  TORCH_CHECK(pad_size * 2 >= hidden + 4 && output.numel() == tokens * pad_size * 2,
+              "output must be the int8 view of [tokens, pad_size] 16-bit elements and hold the codes and the scale");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_add_rmsnorm_quant_i8_padded(input.data_ptr(), residual.data_ptr(), weight.data_ptr(), output.data_ptr(),
+                                            output_rms.data_ptr(), output_quant_int8.data_ptr<int8_t>(), out_scales.data_ptr<float>(),
+                                            tokens, hidden, pad_size, (float)epsilon, 0,
+                                            dtype_code(input, "fused_add_rms_norm_dynamic_per_token_quant_padding_output"), cur_stream()));
+}
+
 // mcoplib.op.fused_silu_mul_dq_reorder_quant (op/int8_quant_kernels.cu:1893-1940, include/int8_quant_kernel.h:7-14).
 // w2_scale is accepted and, as in the reference (HAS_SCALE = false in every instantiation), not applied.
 void fused_silu_mul_dq_reorder_quant(Tensor& out, Tensor& scale, const Tensor& input, const Tensor& reorder_topk_ids,
@@ -604,6 +633,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_gather", &moe_gather, py::arg("scatter_tokens"), py::arg("scatter_tokens_offset"), py::arg("convergent_tokens"),
         py::arg("tok2row") = py::none());
   m.def("moe_swiglu_dynamic_quantize", &moe_swiglu_dynamic_quantize);
+  m.def("fused_add_rms_norm_dynamic_per_token_quant_padding_output", &fused_add_rms_norm_dynamic_per_token_quant_padding_output);
   m.def("fused_silu_mul_dq_mask_quant", &fused_silu_mul_dq_mask_quant);
   m.def("fused_silu_mul_dq_reorder_quant", &fused_silu_mul_dq_reorder_quant);
   m.def("fused_silu_mul_dq_quant", &fused_silu_mul_dq_quant);

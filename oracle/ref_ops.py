@@ -98,6 +98,45 @@ def rms_norm_dynamic_per_token_quant(
     return q, scale.reshape(-1, 1), new_res
 
 
+def fused_add_rms_norm_dynamic_per_token_quant_padding_output(
+        x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, pad_size: int, eps: float, form: int = 0):
+    """mcoplib.op.fused_add_rms_norm_dynamic_per_token_quant_padding_output (wrapper mcoplib/custom_ops.py:7-27),
+    op/fused_add_layernorm_per_token_quant_padding_output.cu.  PARITY UNPINNED: the reference test
+    (unit_test/test_fused_add_rms_norm_custom.py:41-46) evaluates allclose without asserting it.
+
+    The reference picks one of two arithmetic forms by the row length (:371-394); form 0 = its choice.
+      form 1 (hidden == 7168, kernel :182-283): s = float(x) + float(res); res := T(s); v = s * float(w);
+        a = max|v|; r = rsqrt(mean(s^2) + eps); scale = max(a * r / 127, FLT_EPSILON); y = v * r; norm = T(y);
+        code = clamp(rne(y * (1/scale)), -128, 127).
+      form 2 (other lengths, kernel :287-340): a = max|T(T(s) * w)|; r from the unrounded s; scale as above;
+        n = T(T(float(T(s)) * r) * w); code = clamp(rne(float(n) * (1/scale)), -128, 127); norm = n.
+    Record of a token: pad_size elements of T = bytes [0, H) codes, [H, H+4) the fp32 scale, rest not written.
+    Returns (packed uint8 [T, 2*pad_size] with unwritten bytes 0, new_residual T, norm T, codes int8, scales fp32 [T,1])."""
+    T = x.dtype
+    Tn, H = x.shape
+    if form == 0:
+        form = 1 if H == 7168 else 2
+    s = x.float() + residual.float()
+    new_res = s.to(T)
+    inv = _rsqrt(_mean_sq(s) + eps)
+    w = weight.float()
+    if form == 1:
+        v = s * w
+        a = v.abs().amax(dim=-1, keepdim=True)
+        y = v * inv
+        norm = y.to(T)
+    else:
+        a = rt(rt(s, T) * w, T).abs().amax(dim=-1, keepdim=True)
+        y = rt(rt(rt(s, T) * inv, T) * w, T)
+        norm = y.to(T)
+    scale = torch.clamp((a * inv) / 127.0, min=FLT_EPSILON)
+    q = torch.round(y * (1.0 / scale)).clamp(-128, 127).to(torch.int8)
+    packed = torch.zeros(Tn, 2 * pad_size, dtype=torch.uint8)
+    packed[:, :H] = q.view(torch.uint8)
+    packed[:, H:H + 4] = scale.reshape(-1).contiguous().view(torch.uint8).reshape(Tn, 4)
+    return packed, new_res, norm, q, scale.reshape(-1, 1)
+
+
 def fused_rms_norm_dq(
         x: torch.Tensor, weight: torch.Tensor, smooth: torch.Tensor, eps: float,
         residual: Optional[torch.Tensor] = None,
