@@ -172,6 +172,13 @@ int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query, void* key
 int mcop_moe_softmax_topk(float* topk_weights, int32_t* topk_ids, const float* logits, int64_t tokens,
                           int experts, int k, mcop_stream_t stream);
 
+/* torch.ops._moe_C.topk_softmax, op/vllm/moe/topk_softmax_kernels.cu:884-918 (schema op/vllm/moe/torch_bindings.cpp:6-9):
+ * logits [tokens, experts] in fp32 / bf16 / f16 -> fp32 softmax -> top-k (ties to the lowest index, descending order);
+ * the weights are the softmax probabilities, divided by their sum only when renormalize != 0.
+ * token_expert_indices (nullable) int32 [tokens, k] receives j * tokens + t.  experts <= 1024, k <= min(experts, 32). */
+int mcop_topk_softmax(float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices, const void* logits,
+                      int64_t tokens, int experts, int k, int renormalize, int logits_dtype, mcop_stream_t stream);
+
 /* mcoplib.op.fused_moe_gate_deepseek (moegate_type 0), op/fused_moe_gate_deepseek.cu:63-138
  * (include/fused_moe_gate_deepseek.h:6-18).  Sigmoid scores + bias, group score = two best biased scores,
  * keep topk_group groups, top-k experts of the kept groups (ties to the lower index, descending biased
@@ -183,6 +190,17 @@ int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bias, float* t
                                   int groups, int topk_group, int topk, int renormalize,
                                   float routed_scaling, int logits_dtype, int bias_dtype,
                                   mcop_stream_t stream);
+
+/* mcoplib.op.fused_moe_gate_opt, op/moe_fused_gate_opt.cu:9-92 (kernels kernel/fused_moe_gate.cuh:137-251,346-463):
+ * the same selection as mcop_moe_gate_grouped_sigmoid with logits and bias of one dtype, and sglang's weights:
+ * routed weight = T(score / T(fp32 sum of the selected scores)) when renormalize, else the score; never scaled.
+ * With num_shared_experts == 1 the last of the topk slots is the fused shared expert: id = experts, weight =
+ * (sum of the routed weights) / routed_scaling when renormalize, else 0; topk - 1 routed experts are selected.
+ * num_shared_experts > 1 is rejected (the reference fills those ids from rand()). */
+int mcop_moe_gate_grouped_sigmoid_shared(const void* logits, const void* bias, float* topk_weights,
+                                         int32_t* topk_ids, int64_t tokens, int experts, int groups,
+                                         int topk_group, int topk, int renormalize, int num_shared_experts,
+                                         double routed_scaling, int dtype, mcop_stream_t stream);
 
 /* Bytes of scratch mcop_moe_scatter_quant_i8 needs (contents need no initialisation). */
 size_t mcop_moe_scatter_workspace_bytes(int64_t tokens, int topk, int experts_per_rank);
@@ -228,6 +246,14 @@ int mcop_moe_gather_weighted(const void* y, const int32_t* row2tok, const int32_
 int mcop_moe_swiglu_quant_i8(const void* x, const float* smooth, const int32_t* starts, const int32_t* counts,
                              int8_t* out, float* scales, int64_t rows, int64_t hidden, int experts,
                              mcop_stream_t stream);
+
+/* sglang flavour of the same operator with one more output, rms_norm_dynamic_per_token_quant_custom(out, out_bf16, input,
+ * weight, scales, eps, scale_ub, residual): op/sglang/include/sgl_kernel_ops.h:138-145, op/sglang/csrc/common_extension.cc:84-86,
+ * op/sglang/csrc/elementwise/fused_layernorm_dynamic_per_token_quant_custom.cu:434-460.  Identical to
+ * mcop_add_rmsnorm_quant_i8, and out_norm [tokens, hidden] in T receives n (the normalised row before quantisation). */
+int mcop_add_rmsnorm_quant_i8_norm_out(int8_t* out, void* out_norm, float* scales, const void* x, int64_t x_row_stride,
+                                       const void* weight, void* residual, const float* scale_ub, int64_t tokens,
+                                       int64_t hidden, float eps, int dtype, mcop_stream_t stream);
 
 /* mcoplib.op.fused_add_rms_norm_dynamic_per_token_quant_padding_output,
  * op/fused_add_layernorm_per_token_quant_padding_output.cu:397-416 (include/fused_add_layernorm_per_token_quant_padding_output.h:3-11;

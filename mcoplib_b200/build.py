@@ -72,6 +72,11 @@ def build_kernels(force=False, verbose=False, extra_nvcc=()) -> str:
     return lib
 
 
+def moe_namespace(namespace: str) -> str:
+    """torch.ops namespace of the MoE routing operators: `_moe_C` beside `_C`, `mcop_moe_C` beside `mcop_C`."""
+    return namespace[:-1] + "moe_C" if namespace.endswith("_C") else namespace + "_moe"
+
+
 def build_torch_ext(force=False, verbose=False, namespace="mcop_C") -> str:
     import torch
     from torch.utils import cpp_extension as ce
@@ -86,7 +91,8 @@ def build_torch_ext(force=False, verbose=False, namespace="mcop_C") -> str:
     torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=op", "-DTORCH_API_INCLUDE_EXTENSION_H",
-           f"-D_GLIBCXX_USE_CXX11_ABI={abi}", f"-DMCOP_TORCH_NS={namespace}", "-Wno-attributes"] + inc + [src, "-o", out,
+           f"-D_GLIBCXX_USE_CXX11_ABI={abi}", f"-DMCOP_TORCH_NS={namespace}", f"-DMCOP_TORCH_NS_MOE={moe_namespace(namespace)}",
+           "-Wno-attributes"] + inc + [src, "-o", out,
            "-L" + HERE, "-lmcop_b200", "-L" + torch_lib, "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
            "-ltorch_python", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
     _run(cmd, verbose)

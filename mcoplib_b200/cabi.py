@@ -32,13 +32,16 @@ SIGNATURES = {
     "mcop_reshape_and_cache_flash": (I32, [P, P, I64, I64, P, P, I64, I64, I64, P, I64, I32, I32, I32, I32, P]),
     "mcop_rope_kv_store_i8_paged": (I32, [P, P, P, P, P, I32, P, P, P, P, P, I64, I32, I32, I32, I32, I64, I64, I64, I32, I64, I32, I32, P]),
     "mcop_moe_softmax_topk": (I32, [P, P, P, I64, I32, I32, P]),
+    "mcop_topk_softmax": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
     "mcop_moe_gate_grouped_sigmoid": (I32, [P, P, P, P, P, I64, I32, I32, I32, I32, I32, F32, I32, I32, P]),
+    "mcop_moe_gate_grouped_sigmoid_shared": (I32, [P, P, P, P, I64, I32, I32, I32, I32, I32, I32, C.c_double, I32, P]),
     "mcop_moe_scatter_workspace_bytes": (SZ, [I64, I32, I32]),
     "mcop_moe_scatter_quant_i8": (I32, [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, P, SZ, P]),
     "mcop_moe_gather_workspace_bytes": (SZ, [I64, I64]),
     "mcop_moe_gather": (I32, [P, P, P, P, I32, I64, I64, I64, P, SZ, P]),
     "mcop_moe_gather_weighted": (I32, [P, P, P, P, P, P, P, I32, I64, I64, I64, I32, I32, P, SZ, P]),
     "mcop_moe_swiglu_quant_i8": (I32, [P, P, P, P, P, P, I64, I64, I32, P]),
+    "mcop_add_rmsnorm_quant_i8_norm_out": (I32, [P, P, P, P, I64, P, P, P, I64, I64, F32, I32, P]),
     "mcop_add_rmsnorm_quant_i8_padded": (I32, [P, P, P, P, P, P, P, I64, I64, I64, F32, I32, I32, P]),
     "mcop_silu_mul_quant_i8": (I32, [P, I32, P, I32, I64, I64, P, P, I64, I64, P]),
     "mcop_silu_mul_quant_i8_masked_pack": (I32, [P, I32, P, I32, P, I64, I64, I64, I64, P]),

@@ -25,10 +25,12 @@ __device__ __forceinline__ unsigned ordered_key(float v) {
 // ---------------------------------------------------------------------------------------------
 // softmax + top-k.  A row is spread over TPR lanes (a power of two), VPT contiguous experts per lane.
 // ---------------------------------------------------------------------------------------------
-template <int VPT, int TPR>
+// LT: logits type.  renorm: divide the k weights by their sum.  src_rows (nullable): vLLM's token_expert_indices,
+// src_rows[t, j] = j * tokens + t.
+template <typename LT, int VPT, int TPR>
 __global__ void __launch_bounds__(128) softmax_topk_kernel(float* __restrict__ weights, int32_t* __restrict__ ids,
-                                                           const float* __restrict__ logits, int64_t tokens,
-                                                           int experts, int k, bool vec_ok) {
+                                                           int32_t* __restrict__ src_rows, const LT* __restrict__ logits,
+                                                           int64_t tokens, int experts, int k, bool vec_ok, bool renorm) {
   constexpr int ROWS_PER_WARP = 32 / TPR;
   const int lane = threadIdx.x & 31;
   const int g = lane % TPR;
@@ -36,7 +38,7 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(float* __restrict__ w
   const bool active = row < tokens;
   const int first = g * VPT;
   float p[VPT];
-  if (active && vec_ok) {
+  if (sizeof(LT) == 4 && active && vec_ok) {
     const float4* src = reinterpret_cast<const float4*>(logits + row * experts + first);
 #pragma unroll
     for (int i = 0; i < VPT / 4; ++i) {
@@ -46,7 +48,7 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(float* __restrict__ w
   } else {
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
-      p[i] = (active && first + i < experts) ? __ldg(logits + row * experts + first + i) : -INFINITY;
+      p[i] = (active && first + i < experts) ? ElemTraits<LT>::to_float(logits[row * experts + first + i]) : -INFINITY;
   }
   float m = p[0];
 #pragma unroll
@@ -81,6 +83,7 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(float* __restrict__ w
     if (active && g == 0) {
       weights[row * k + kk] = bv;
       ids[row * k + kk] = bi;
+      if (src_rows) src_rows[row * k + kk] = (int32_t)(kk * tokens + row);
       tot += bv;
     }
     if (bi / VPT == g) {
@@ -89,19 +92,35 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(float* __restrict__ w
         if (i == bi % VPT) p[i] = -1.0f;  // probabilities are >= 0
     }
   }
-  if (active && g == 0)
-    for (int kk = 0; kk < k; ++kk) weights[row * k + kk] = weights[row * k + kk] / tot;
+  if (renorm && active && g == 0) {
+    const float denom = tot > 0.f ? tot : 1.f;
+    for (int kk = 0; kk < k; ++kk) weights[row * k + kk] = weights[row * k + kk] / denom;
+  }
 }
 
-template <int VPT, int TPR>
-int launch_softmax(float* w, int32_t* ids, const float* logits, int64_t tokens, int experts, int k, cudaStream_t s) {
+template <typename LT, int VPT, int TPR>
+int launch_softmax(float* w, int32_t* ids, int32_t* src_rows, const LT* logits, int64_t tokens, int experts, int k, bool renorm,
+                   cudaStream_t s) {
   constexpr int WARPS = 4;
   const int64_t rows_per_block = WARPS * (32 / TPR);
   const int64_t blocks = (tokens + rows_per_block - 1) / rows_per_block;
   MCOP_REQUIRE(blocks <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "moe_softmax_topk: too many tokens");
   const bool vec_ok = experts == VPT * TPR && aligned16(logits);
-  softmax_topk_kernel<VPT, TPR><<<(unsigned)blocks, WARPS * 32, 0, s>>>(w, ids, logits, tokens, experts, k, vec_ok);
+  softmax_topk_kernel<LT, VPT, TPR><<<(unsigned)blocks, WARPS * 32, 0, s>>>(w, ids, src_rows, logits, tokens, experts, k, vec_ok, renorm);
   return check_launch("moe_softmax_topk");
+}
+
+template <typename LT>
+int dispatch_softmax(float* w, int32_t* ids, int32_t* src_rows, const LT* logits, int64_t tokens, int experts, int k, bool renorm,
+                     cudaStream_t s) {
+  if (experts <= 8) return launch_softmax<LT, 8, 1>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
+  if (experts <= 16) return launch_softmax<LT, 8, 2>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
+  if (experts <= 32) return launch_softmax<LT, 8, 4>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
+  if (experts <= 64) return launch_softmax<LT, 8, 8>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
+  if (experts <= 128) return launch_softmax<LT, 8, 16>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
+  if (experts <= 256) return launch_softmax<LT, 8, 32>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
+  if (experts <= 512) return launch_softmax<LT, 16, 32>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
+  return launch_softmax<LT, 32, 32>(w, ids, src_rows, logits, tokens, experts, k, renorm, s);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -112,6 +131,11 @@ struct GateParams {
   const void* logits; const void* bias; float* weights; int32_t* ids; int32_t* group_mask;
   int64_t tokens; int experts, groups, topk_group, topk, renormalize; float scaling;
   int t1, ts;  // dtype codes: logits type, and the wider of logits/bias types
+  // style 0: mcoplib.op.fused_moe_gate_deepseek weights.  style 1: mcoplib.op.fused_moe_gate_opt weights
+  // (kernel/fused_moe_gate.cuh:346-420): the last `shared` of the topk slots name the fused shared expert
+  // (id = experts) instead of a routed expert; routed weights are not scaled.
+  int style, shared;
+  double shared_mul;  // style 1: weight of the shared slot = sum of the routed weights * shared_mul
 };
 
 template <typename T1, typename T2, int V>
@@ -179,7 +203,8 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
 
   float my_w = 0.f;
   int my_id = 0;
-  for (int kk = 0; kk < p.topk; ++kk) {
+  const int routed = p.topk - p.shared;
+  for (int kk = 0; kk < routed; ++kk) {
     // local arg-max (lowest index wins inside the lane), then one redux.sync on the order-preserving key and a
     // ballot: the lowest lane holding the warp maximum owns the lowest expert index among equals
     float bv = biased[0], bs = score[0];
@@ -198,6 +223,30 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
         if (i == bl) biased[i] = -INFINITY;
     }
     if (lane == kk) { my_w = sc; my_id = bi; }
+  }
+  if (p.style == 1) {
+    // fp32 sum over a 16-lane xor-butterfly (offsets 8, 4, 2, 1) of the routed scores, one rounding of the sum and
+    // one of the quotient to the logits type (kernel/fused_moe_gate.cuh:361-385); lanes >= routed contribute 0
+    auto sum16 = [&](float v) {
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      return v;
+    };
+    const float tot = sum16(lane < routed ? my_w : 0.f);
+    if (p.renormalize) my_w = round_code(my_w / round_code(tot, p.t1), p.t1);
+    if (p.shared) {
+      // the shared slot: id = experts, weight = (sum of the final routed weights) * shared_mul, only when renormalising
+      const float tot2 = sum16(lane < routed ? my_w : 0.f);
+      if (lane >= routed) {
+        my_id = p.experts;
+        my_w = p.renormalize ? (float)((double)tot2 * p.shared_mul) : 0.f;
+      }
+    }
+    if (lane < p.topk) {
+      p.weights[row * p.topk + lane] = my_w;
+      p.ids[row * p.topk + lane] = my_id;
+    }
+    return;
   }
   if (p.renormalize) {
     float tot;
@@ -226,7 +275,7 @@ int launch_gate_v(const GateParams& p, cudaStream_t s) {
   const unsigned gb = (unsigned)blocks;
   switch (p.experts / 32) {
 #define MCOP_GATE_CASE(V) case V: gate_kernel<T1, T2, V><<<gb, WARPS * 32, 0, s>>>(p); break;
-    MCOP_GATE_CASE(1) MCOP_GATE_CASE(2) MCOP_GATE_CASE(4) MCOP_GATE_CASE(6) MCOP_GATE_CASE(8)
+    MCOP_GATE_CASE(1) MCOP_GATE_CASE(2) MCOP_GATE_CASE(3) MCOP_GATE_CASE(4) MCOP_GATE_CASE(5) MCOP_GATE_CASE(6) MCOP_GATE_CASE(8)
     MCOP_GATE_CASE(10) MCOP_GATE_CASE(12) MCOP_GATE_CASE(14) MCOP_GATE_CASE(16)
 #undef MCOP_GATE_CASE
     default: return set_error(MCOP_ERR_UNSUPPORTED, "moe_gate: %d experts not supported", p.experts);
@@ -253,24 +302,37 @@ extern "C" int mcop_moe_softmax_topk(float* topk_weights, int32_t* topk_ids, con
                "moe_softmax_topk: bad sizes tokens=%lld experts=%d k=%d", (long long)tokens, experts, k);
   MCOP_REQUIRE(experts <= 1024, MCOP_ERR_UNSUPPORTED, "moe_softmax_topk: more than 1024 experts");
   if (tokens == 0) return MCOP_OK;
-  cudaStream_t s = (cudaStream_t)stream;
-  if (experts <= 8) return launch_softmax<8, 1>(topk_weights, topk_ids, logits, tokens, experts, k, s);
-  if (experts <= 16) return launch_softmax<8, 2>(topk_weights, topk_ids, logits, tokens, experts, k, s);
-  if (experts <= 32) return launch_softmax<8, 4>(topk_weights, topk_ids, logits, tokens, experts, k, s);
-  if (experts <= 64) return launch_softmax<8, 8>(topk_weights, topk_ids, logits, tokens, experts, k, s);
-  if (experts <= 128) return launch_softmax<8, 16>(topk_weights, topk_ids, logits, tokens, experts, k, s);
-  if (experts <= 256) return launch_softmax<8, 32>(topk_weights, topk_ids, logits, tokens, experts, k, s);
-  if (experts <= 512) return launch_softmax<16, 32>(topk_weights, topk_ids, logits, tokens, experts, k, s);
-  return launch_softmax<32, 32>(topk_weights, topk_ids, logits, tokens, experts, k, s);
+  return dispatch_softmax<float>(topk_weights, topk_ids, nullptr, logits, tokens, experts, k, true, (cudaStream_t)stream);
 }
 
-extern "C" int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bias, float* topk_weights,
-                                             int32_t* topk_ids, int32_t* group_mask, int64_t tokens, int experts,
-                                             int groups, int topk_group, int topk, int renormalize,
-                                             float routed_scaling, int logits_dtype, int bias_dtype,
-                                             mcop_stream_t stream) {
+extern "C" int mcop_topk_softmax(float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices, const void* logits,
+                                 int64_t tokens, int experts, int k, int renormalize, int logits_dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(topk_weights && topk_ids && logits, MCOP_ERR_ARGUMENT, "topk_softmax: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && experts >= 1 && k >= 1 && k <= experts && k <= 32, MCOP_ERR_ARGUMENT,
+               "topk_softmax: bad sizes tokens=%lld experts=%d k=%d", (long long)tokens, experts, k);
+  MCOP_REQUIRE(experts <= 1024, MCOP_ERR_UNSUPPORTED, "topk_softmax: more than 1024 experts");
+  MCOP_REQUIRE(!token_expert_indices || tokens * k <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "topk_softmax: tokens*k exceeds int32");
+  if (tokens == 0) return MCOP_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool rn = renormalize != 0;
+  switch (logits_dtype) {
+    case MCOP_F32: return dispatch_softmax<float>(topk_weights, topk_ids, token_expert_indices, reinterpret_cast<const float*>(logits), tokens, experts, k, rn, s);
+    case MCOP_BF16: return dispatch_softmax<__nv_bfloat16>(topk_weights, topk_ids, token_expert_indices, reinterpret_cast<const __nv_bfloat16*>(logits), tokens, experts, k, rn, s);
+    case MCOP_F16: return dispatch_softmax<__half>(topk_weights, topk_ids, token_expert_indices, reinterpret_cast<const __half*>(logits), tokens, experts, k, rn, s);
+  }
+  return set_error(MCOP_ERR_UNSUPPORTED, "topk_softmax: unknown logits dtype %d", logits_dtype);
+}
+
+static int gate_entry(const void* logits, const void* bias, float* topk_weights, int32_t* topk_ids, int32_t* group_mask,
+                      int64_t tokens, int experts, int groups, int topk_group, int topk_total, int renormalize,
+                      float routed_scaling, int logits_dtype, int bias_dtype, int style, int shared, double shared_mul,
+                      mcop_stream_t stream) {
   MCOP_REQUIRE(logits && bias && topk_weights && topk_ids, MCOP_ERR_ARGUMENT, "moe_gate: null pointer");
-  MCOP_REQUIRE(tokens >= 0 && experts > 0 && topk >= 1 && topk <= 32, MCOP_ERR_ARGUMENT, "moe_gate: bad sizes");
+  MCOP_REQUIRE(shared >= 0 && shared <= 1 && topk_total - shared >= 1, MCOP_ERR_UNSUPPORTED,
+               "moe_gate: %d fused shared experts (0 or 1 supported: the reference draws the ids of more from rand())", shared);
+  MCOP_REQUIRE(style == 0 || topk_total <= 16, MCOP_ERR_UNSUPPORTED, "moe_gate: at most 16 slots in this form");
+  const int topk = topk_total - shared;  // routed experts to select
+  MCOP_REQUIRE(tokens >= 0 && experts > 0 && topk >= 1 && topk_total <= 32, MCOP_ERR_ARGUMENT, "moe_gate: bad sizes");
   MCOP_REQUIRE(experts % 32 == 0 && experts <= 512, MCOP_ERR_UNSUPPORTED,
                "moe_gate: experts must be a multiple of 32 and at most 512 (got %d)", experts);
   if (groups < 1) groups = 1;
@@ -286,8 +348,8 @@ extern "C" int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bia
     MCOP_REQUIRE(topk <= experts, MCOP_ERR_ARGUMENT, "moe_gate: topk > experts");
   }
   if (tokens == 0) return MCOP_OK;
-  GateParams p{logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk,
-               renormalize, routed_scaling, logits_dtype, 0};
+  GateParams p{logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk_total,
+               renormalize, routed_scaling, logits_dtype, 0, style, shared, shared_mul};
   const int s1 = logits_dtype == MCOP_F32 ? 4 : 2, s2 = bias_dtype == MCOP_F32 ? 4 : 2;
   p.ts = s1 >= s2 ? logits_dtype : bias_dtype;
   cudaStream_t s = (cudaStream_t)stream;
@@ -297,4 +359,22 @@ extern "C" int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bia
     case MCOP_F16: return launch_gate_bias<__half>(p, bias_dtype, s);
   }
   return set_error(MCOP_ERR_UNSUPPORTED, "moe_gate: unknown logits dtype %d", logits_dtype);
+}
+
+extern "C" int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bias, float* topk_weights,
+                                             int32_t* topk_ids, int32_t* group_mask, int64_t tokens, int experts,
+                                             int groups, int topk_group, int topk, int renormalize,
+                                             float routed_scaling, int logits_dtype, int bias_dtype,
+                                             mcop_stream_t stream) {
+  return gate_entry(logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk, renormalize,
+                    routed_scaling, logits_dtype, bias_dtype, 0, 0, 0.0, stream);
+}
+
+extern "C" int mcop_moe_gate_grouped_sigmoid_shared(const void* logits, const void* bias, float* topk_weights,
+                                                    int32_t* topk_ids, int64_t tokens, int experts, int groups,
+                                                    int topk_group, int topk, int renormalize, int num_shared_experts,
+                                                    double routed_scaling, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(routed_scaling != 0.0, MCOP_ERR_ARGUMENT, "moe_gate: routed_scaling must not be 0");
+  return gate_entry(logits, bias, topk_weights, topk_ids, nullptr, tokens, experts, groups, topk_group, topk, renormalize, 1.0f,
+                    dtype, dtype, 1, num_shared_experts, 1.0 / routed_scaling, stream);
 }

@@ -149,7 +149,8 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
           s[i][j] = round_to<T>(round_to<T>(s[i][j] * r) * wv[j]);
           amax = fmaxf(amax, fabsf(s[i][j]));
         }
-        if (MODE == kFusedAdd) Vec8<T>::store(reinterpret_cast<T*>(p.out) + row * p.out_stride + v * 8, s[i]);
+        // kQuant: the normalised row is an optional extra output (sglang's out_bf16)
+        if (MODE == kFusedAdd || (MODE == kQuant && p.out)) Vec8<T>::store(reinterpret_cast<T*>(p.out) + row * p.out_stride + v * 8, s[i]);
       }
     }
   }
@@ -224,7 +225,7 @@ __global__ void __launch_bounds__(256) norm_rows_any(NormParams p) {
       v = nw * ElemTraits<WT>::to_float(sm[i]);
     } else {
       v = round_to<T>(round_to<T>(keep[i] * r) * ElemTraits<WT>::to_float(w[i]));
-      if (MODE == kFusedAdd) out[i] = ElemTraits<T>::from_float(v);
+      if (MODE == kFusedAdd || (MODE == kQuant && out)) out[i] = ElemTraits<T>::from_float(v);
     }
     keep[i] = v;
     amax = fmaxf(amax, fabsf(v));
@@ -408,6 +409,12 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
           c[2 * j + 1] = rn_low_byte(b);
         }
         st_cs_u2(q + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
+#if MCOP_VAR != 1
+        if (p.out)  // optional extra output: the normalised bf16 row
+#else
+        if (false)
+#endif
+          st_u4(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.out_stride + v * 8, make_uint4(n2[k][0], n2[k][1], n2[k][2], n2[k][3]));
       }
     }
   }
@@ -632,6 +639,21 @@ extern "C" int mcop_add_rmsnorm_quant_i8(int8_t* out, float* scales, const void*
   p.x = x; p.x_stride = x_row_stride; p.weight = weight; p.residual_in = residual; p.residual_out = residual;
   p.q = out; p.scales = scales; p.scale_ub = scale_ub; p.hidden = (int)hidden; p.eps = eps;
   const bool vec = rows_vectorisable(hidden, dtype, dtype, x, x_row_stride, {residual}, {weight}, out);
+  return dispatch_norm<kQuant>(p, tokens, vec, dtype, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_add_rmsnorm_quant_i8_norm_out(int8_t* out, void* out_norm, float* scales, const void* x, int64_t x_row_stride,
+                                                  const void* weight, void* residual, const float* scale_ub, int64_t tokens,
+                                                  int64_t hidden, float eps, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(out && out_norm && scales && x && weight, MCOP_ERR_ARGUMENT, "add_rmsnorm_quant_i8_norm_out: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && hidden > 0 && hidden <= 0x7fffffff && x_row_stride >= hidden, MCOP_ERR_ARGUMENT,
+               "add_rmsnorm_quant_i8_norm_out: bad sizes tokens=%lld hidden=%lld stride=%lld", (long long)tokens, (long long)hidden,
+               (long long)x_row_stride);
+  NormParams p{};
+  p.x = x; p.x_stride = x_row_stride; p.weight = weight; p.residual_in = residual; p.residual_out = residual;
+  p.out = out_norm; p.out_stride = hidden;
+  p.q = out; p.scales = scales; p.scale_ub = scale_ub; p.hidden = (int)hidden; p.eps = eps;
+  const bool vec = rows_vectorisable(hidden, dtype, dtype, x, x_row_stride, {residual, out_norm}, {weight}, out);
   return dispatch_norm<kQuant>(p, tokens, vec, dtype, dtype, (cudaStream_t)stream);
 }
 

@@ -25,6 +25,11 @@
 #define MCOP_CAT_(a, b) a##b
 #define MCOP_CAT(a, b) MCOP_CAT_(a, b)
 #define MCOP_TORCH_NS_CACHE MCOP_CAT(MCOP_TORCH_NS, _cache_ops)
+// the MoE routing operators of vLLM live in their own library: _moe_C beside _C, mcop_moe_C beside mcop_C
+// (the build passes -DMCOP_TORCH_NS_MOE next to -DMCOP_TORCH_NS)
+#ifndef MCOP_TORCH_NS_MOE
+#define MCOP_TORCH_NS_MOE mcop_moe_C
+#endif
 
 namespace {
 
@@ -94,6 +99,28 @@ void rms_norm_dynamic_per_token_quant_vllm(Tensor& out, const Tensor& input, con
                                      weight.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr,
                                      scale_ub.has_value() ? scale_ub->data_ptr<float>() : nullptr, tokens, hidden,
                                      (float)var_epsilon, dtype_code(input, "rms_norm_dynamic_per_token_quant"), cur_stream()));
+}
+
+// sglang's rms_norm_dynamic_per_token_quant_custom with the extra normalised output
+// (op/sglang/include/sgl_kernel_ops.h:138-145, op/sglang/csrc/elementwise/fused_layernorm_dynamic_per_token_quant_custom.cu:434-460)
+void rms_norm_dynamic_per_token_quant_sgl(Tensor& out, Tensor& out_bf16, const Tensor& input, const Tensor& weight, Tensor& scales,
+                                          double var_epsilon, std::optional<Tensor> scale_ub, std::optional<Tensor> residual) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == at::kChar, "only int8 output is built");
+  TORCH_CHECK(out.is_contiguous() && input.is_contiguous());
+  TORCH_CHECK(!scale_ub.has_value(), "scale_ub goes with the fp8 output only");  // the reference's rule (:451-453)
+  TORCH_CHECK(scales.dtype() == torch::kFloat32);
+  TORCH_CHECK(weight.scalar_type() == input.scalar_type() && out_bf16.scalar_type() == input.scalar_type() && out_bf16.is_contiguous() &&
+              out_bf16.numel() == input.numel());
+  if (residual.has_value()) TORCH_CHECK(residual->scalar_type() == input.scalar_type() && residual->is_contiguous());
+  const int64_t hidden = input.size(-1);
+  const int64_t tokens = hidden ? input.numel() / hidden : 0;
+  TORCH_CHECK(scales.numel() >= tokens && scales.is_contiguous(), "scales must hold one fp32 per token");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_rc(mcop_add_rmsnorm_quant_i8_norm_out(out.data_ptr<int8_t>(), out_bf16.data_ptr(), scales.data_ptr<float>(), input.data_ptr(), hidden,
+                                              weight.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr, nullptr, tokens,
+                                              hidden, (float)var_epsilon, dtype_code(input, "rms_norm_dynamic_per_token_quant_custom"),
+                                              cur_stream()));
 }
 
 // mcoplib.op.rms_norm_dynamic_per_token_quant, 9 arguments (op/fused_rms_norm_dq.cu:646-667)
@@ -359,6 +386,26 @@ void moe_softmax_topk(Tensor topk_weights, Tensor topk_indices, Tensor gating_ou
                                  experts, k, cur_stream()));
 }
 
+// torch.ops._moe_C.topk_softmax (op/vllm/moe/topk_softmax_kernels.cu:884-918, schema op/vllm/moe/torch_bindings.cpp:6-9)
+void topk_softmax(Tensor& topk_weights, Tensor& topk_indices, Tensor& token_expert_indices, Tensor& gating_output, bool renormalize) {
+  check_cuda(gating_output, "gating_output");
+  TORCH_CHECK(gating_output.scalar_type() == at::kFloat || gating_output.scalar_type() == at::kHalf ||
+                  gating_output.scalar_type() == at::kBFloat16,
+              "Unsupported gating_output data type: ", gating_output.scalar_type());
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat && topk_indices.scalar_type() == at::kInt &&
+              token_expert_indices.scalar_type() == at::kInt);
+  TORCH_CHECK(gating_output.is_contiguous() && topk_weights.is_contiguous() && topk_indices.is_contiguous() &&
+              token_expert_indices.is_contiguous());
+  const int experts = (int)gating_output.size(-1);
+  const int64_t tokens = experts ? gating_output.numel() / experts : 0;
+  const int k = (int)topk_weights.size(-1);
+  TORCH_CHECK(topk_weights.numel() == tokens * k && topk_indices.numel() == tokens * k && token_expert_indices.numel() == tokens * k);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(gating_output));
+  check_rc(mcop_topk_softmax(topk_weights.data_ptr<float>(), topk_indices.data_ptr<int32_t>(), token_expert_indices.data_ptr<int32_t>(),
+                             gating_output.data_ptr(), tokens, experts, k, renormalize ? 1 : 0, dtype_code(gating_output, "topk_softmax"),
+                             cur_stream()));
+}
+
 // mcoplib.op.fused_moe_gate_deepseek (op/fused_moe_gate_deepseek.cu:63-138)
 int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Tensor& out_routing_weights, Tensor& out_selected_experts,
                             int topk, bool renormalize, int num_expert_group, int topk_group,
@@ -384,6 +431,37 @@ int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Ten
                                          out_selected_experts.data_ptr<int32_t>(), gm, tokens, experts, num_expert_group, topk_group, topk,
                                          renormalize ? 1 : 0, routed_scaling_factor.value_or(1.0f), dtype_code(gating_outputs, "gating_outputs"),
                                          dtype_code(correction_bias, "correction_bias"), cur_stream()));
+  return 0;
+}
+
+// mcoplib.op.fused_moe_gate_opt (op/moe_fused_gate_opt.cu:9-92): the reference's argument checks, in its order
+int64_t fused_moe_gate_opt(Tensor& gating_outputs, Tensor& correction_bias, Tensor& out_routing_weights, Tensor& out_selected_experts,
+                           int64_t topk, bool renormalize, int64_t num_expert_group, int64_t topk_group,
+                           std::optional<int64_t> num_fused_shared_experts, std::optional<double> routed_scaling_factor) {
+  check_cuda(gating_outputs, "gating_outputs");
+  TORCH_CHECK(((topk == 8) || (topk == 9)), "Expected topk = 8, but get topk = ", topk);
+  const int64_t num_shared = num_fused_shared_experts.value_or(0);
+  if (num_shared > 0) TORCH_CHECK(topk >= 9, "Expected topk >= 9 when fused_num_shared_experts > 0, but get topk = ", topk);
+  if (num_shared == 0) TORCH_CHECK(topk == 8, "Expected topk == 8 when fused_num_shared_experts = 0 or None, but get topk = ", topk);
+  TORCH_CHECK(num_shared <= 1, "more than one fused shared expert is not built (the reference draws their ids from rand())");
+  TORCH_CHECK(gating_outputs.dim() == 2 && gating_outputs.is_contiguous() && correction_bias.is_contiguous());
+  TORCH_CHECK(correction_bias.scalar_type() == gating_outputs.scalar_type(), "bias and logits must have one dtype");
+  TORCH_CHECK(out_routing_weights.scalar_type() == at::kFloat && out_routing_weights.is_contiguous());
+  TORCH_CHECK(out_selected_experts.scalar_type() == at::kInt && out_selected_experts.is_contiguous(), "selected experts must be int32");
+  const int64_t tokens = gating_outputs.size(0);
+  const int64_t experts = gating_outputs.size(1);
+  const bool known = (num_expert_group == 8 && topk_group == 4 && experts == 256) ||
+                     (num_expert_group == 1 && topk_group == 1 && (experts == 160 || experts == 320 || experts == 384 || experts == 448));
+  TORCH_CHECK(known, "Invalid arguments with TOPK = ", topk, ", NUM_EXPERT_GROUP = ", num_expert_group, ", TOPK_GROUP = ", topk_group,
+              ", NUM_EXPERTS = ", experts);
+  TORCH_CHECK(correction_bias.numel() == experts);
+  TORCH_CHECK(out_routing_weights.numel() == tokens * topk && out_selected_experts.numel() == tokens * topk);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(gating_outputs));
+  check_rc(mcop_moe_gate_grouped_sigmoid_shared(gating_outputs.data_ptr(), correction_bias.data_ptr(), out_routing_weights.data_ptr<float>(),
+                                                out_selected_experts.data_ptr<int32_t>(), tokens, (int)experts, (int)num_expert_group,
+                                                (int)topk_group, (int)topk, renormalize ? 1 : 0, (int)num_shared,
+                                                routed_scaling_factor.value_or(1.0), dtype_code(gating_outputs, "gating_outputs"),
+                                                cur_stream()));
   return 0;
 }
 
@@ -611,6 +689,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mcoplib.op operator surface of the per-token inference hot path, B200 (sm_100a) kernels";
   m.def("rms_norm_dynamic_per_token_quant", &rms_norm_dynamic_per_token_quant_9);
   m.def("rms_norm_dynamic_per_token_quant_custom", &rms_norm_dynamic_per_token_quant_vllm);
+  m.def("sgl_rms_norm_dynamic_per_token_quant_custom", &rms_norm_dynamic_per_token_quant_sgl);
   m.def("rms_norm", &rms_norm);
   m.def("head_rms_norm", &head_rms_norm);
   m.def("scale_dynamic_quant", &scale_dynamic_quant, py::arg("hidden_states"), py::arg("smooth_scales"),
@@ -626,6 +705,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out_routing_weights"), py::arg("out_selected_experts"), py::arg("topk"), py::arg("renormalize"),
         py::arg("num_expert_group"), py::arg("topk_group"), py::arg("num_fused_shared_experts") = py::none(),
         py::arg("routed_scaling_factor") = py::none(), py::arg("moegate_type") = py::none(), py::arg("debug_group_mask") = py::none());
+  m.def("fused_moe_gate_opt", &fused_moe_gate_opt, py::arg("gating_outputs"), py::arg("correction_bias"), py::arg("out_routing_weights"),
+        py::arg("out_selected_experts"), py::arg("topk"), py::arg("renormalize"), py::arg("num_expert_group"), py::arg("topk_group"),
+        py::arg("num_fused_shared_experts") = py::none(), py::arg("routed_scaling_factor") = py::none());
   m.def("moe_scatter_dynamic_quant", &moe_scatter_dynamic_quant, py::arg("hidden_status"), py::arg("selected_experts"),
         py::arg("moe_weights"), py::arg("smooth_scale"), py::arg("scatter_tokens"), py::arg("scatter_per_token_scale"),
         py::arg("scatter_tokens_offset"), py::arg("experts_token_count"), py::arg("experts_token_start"), py::arg("experts_per_rank"),
@@ -645,9 +727,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fused_add_rms_norm", &fused_add_rms_norm);
   m.def("vllm_rotary_embedding", &rotary_embedding_vllm);
   m.def("reshape_and_cache_flash", &reshape_and_cache_flash);
+  m.def("topk_softmax", &topk_softmax);
 #define MCOP_STR_(x) #x
 #define MCOP_STR(x) MCOP_STR_(x)
   m.attr("torch_namespace") = MCOP_STR(MCOP_TORCH_NS);
+  m.attr("torch_moe_namespace") = MCOP_STR(MCOP_TORCH_NS_MOE);
 }
 
 TORCH_LIBRARY(MCOP_TORCH_NS, ops) {
@@ -666,6 +750,13 @@ TORCH_LIBRARY(MCOP_TORCH_NS, ops) {
       "rope_kv_store_int8(Tensor positions, Tensor! query, Tensor! key, Tensor value, int head_size, Tensor cos_sin_cache, "
       "bool is_neox, Tensor! key_cache, Tensor! value_cache, Tensor slot_mapping, Tensor k_scale, Tensor v_scale) -> ()");
   ops.impl("rope_kv_store_int8", torch::kCUDA, &rope_kv_store_int8);
+}
+
+TORCH_LIBRARY(MCOP_TORCH_NS_MOE, moe_ops) {
+  moe_ops.def(
+      "topk_softmax(Tensor! topk_weights, Tensor! topk_indices, Tensor! token_expert_indices, Tensor gating_output, "
+      "bool renormalize) -> ()");
+  moe_ops.impl("topk_softmax", torch::kCUDA, &topk_softmax);
 }
 
 TORCH_LIBRARY(MCOP_TORCH_NS_CACHE, cache_ops) {

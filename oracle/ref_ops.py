@@ -71,7 +71,8 @@ def rms_norm_dynamic_per_token_quant(
         x: torch.Tensor, weight: torch.Tensor, eps: float,
         residual: Optional[torch.Tensor] = None,
         scale_ub: Optional[torch.Tensor] = None,
-) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+        return_norm: bool = False,
+):
     """op/vllm/quantization/fused_kernels/fused_layernorm_dynamic_per_token_quant.cu:14-90 with
     layernorm_utils.cuh:17-45 (rms), :145-177 (scale) and :180-217 (norm + quant);
     same contract as mcoplib.op.rms_norm_dynamic_per_token_quant_custom
@@ -80,7 +81,9 @@ def rms_norm_dynamic_per_token_quant(
     s = float(x) + float(res); res := T(s); var = mean(s^2) on the unrounded s;
     n = T(T(s * rsqrt(var+eps)) * w); a = max|n| (clamped by scale_ub if given);
     scale = max(a / 127, FLT_EPSILON); q = clamp(rne(n * (1/scale)), -128, 127).
-    Returns (codes int8 [T,H], scales fp32 [T,1], new_residual or None)."""
+    Returns (codes int8 [T,H], scales fp32 [T,1], new_residual or None); with return_norm also n in T, the extra
+    out_bf16 output of sglang's flavour (op/sglang/csrc/elementwise/fused_layernorm_dynamic_per_token_quant_custom.cu:434-460,
+    norm_and_quant in op/sglang/include/layernorm_utils.cuh)."""
     T = x.dtype
     s = x.float()
     new_res = None
@@ -95,6 +98,8 @@ def rms_norm_dynamic_per_token_quant(
         a = torch.minimum(a, scale_ub.float().reshape(()))
     scale = torch.clamp(a / 127.0, min=FLT_EPSILON)
     q = torch.round(n * (1.0 / scale)).clamp(-128, 127).to(torch.int8)
+    if return_norm:
+        return q, scale.reshape(-1, 1), new_res, n.to(T)
     return q, scale.reshape(-1, 1), new_res
 
 
@@ -426,6 +431,28 @@ def moe_softmax_topk(gating: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.
     return vals / tot.unsqueeze(-1), ids.to(torch.int32)
 
 
+def topk_softmax(gating: torch.Tensor, k: int, renormalize: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """torch.ops._moe_C.topk_softmax, op/vllm/moe/topk_softmax_kernels.cu:396-545 (topkGatingSoftmax) and :884-918.
+    Pinned by the check of benchmark/runners/mcoplib_mxbenchmark_topk_softmax_runners.py:38-49 (topk of the logits,
+    softmax over the selected = the renormalised form; ids exact).
+
+    Logits of any float type are widened to fp32; p = exp(x - max) * (1 / sum); k rounds of arg-max, ties to the
+    lowest index; weights = p_sel, divided by their sum (accumulated in selection order, 1 if it is 0) only when
+    renormalize.  Returns (weights fp32 [T,k], ids int32 [T,k], token_expert_indices int32 [T,k] = j*T + t)."""
+    x = gating.float()
+    e = torch.exp(x - x.amax(dim=-1, keepdim=True))
+    p = e * (1.0 / e.sum(dim=-1, keepdim=True))
+    vals, ids = stable_topk(p, k)
+    if renormalize:
+        tot = torch.zeros(vals.shape[:-1], dtype=torch.float32)
+        for j in range(k):
+            tot = tot + vals[..., j]
+        vals = vals / torch.where(tot > 0, tot, torch.ones_like(tot)).unsqueeze(-1)
+    n = x.shape[0]
+    src = (torch.arange(k).unsqueeze(0) * n + torch.arange(n).unsqueeze(1)).to(torch.int32)
+    return vals, ids.to(torch.int32), src
+
+
 def softmax_topk_margin(gating: torch.Tensor, k: int) -> torch.Tensor:
     """float64 decision margins of the softmax top-k: gaps between consecutive sorted logits at
     ranks 0..k (k gaps per row).  A CUDA/CPU id mismatch is excusable only where a gap is within a
@@ -497,6 +524,43 @@ def fused_moe_gate_deepseek(gating: torch.Tensor, bias: torch.Tensor, topk: int,
     w = w * routed_scaling
     bits = (gmask.to(torch.int64) << torch.arange(gmask.shape[1]).unsqueeze(0)).sum(dim=1)
     return w.float(), ids.to(torch.int32), bits.to(torch.int32)
+
+
+def fused_moe_gate_opt(gating: torch.Tensor, bias: torch.Tensor, topk: int, renormalize: bool, num_expert_group: int,
+                       topk_group: int, num_fused_shared_experts: int = 0,
+                       routed_scaling_factor: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """mcoplib.op.fused_moe_gate_opt, op/moe_fused_gate_opt.cu:9-92; selection kernel/fused_moe_gate.cuh:137-251
+    (grouped) and :253-343 (one group), weights :346-420.  Pinned by biased_grouped_topk of
+    unit_test/test_fused_moe_gate_opt.py:78-135 (row-sorted ids exact, row-sorted weights to 1e-3).
+
+    Selection as fused_moe_gate_deepseek with logits and bias of one dtype T.  Weights: s = T(sigmoid) of the
+    selected experts; tot = fp32 sum in xor-butterfly order; w = float(T(s / T(tot))) when renormalize, else s;
+    no scaling.  One fused shared expert: topk - 1 routed experts, last slot id = E and weight =
+    float(double(fp32 butterfly sum of the routed w) * (1 / routed_scaling_factor)) when renormalize, else 0.
+    Returns (weights fp32 [T, topk], ids int32 [T, topk])."""
+    n, E = gating.shape
+    shared = int(num_fused_shared_experts or 0)
+    assert shared in (0, 1)
+    routed = topk - shared
+    assert routed <= 8
+    _, ids, _ = fused_moe_gate_deepseek(gating, bias.to(gating.dtype), routed, False, num_expert_group, topk_group, 1.0)
+    T = gating.dtype
+    score = _gate_scores(gating, bias.to(gating.dtype))[0]
+    w = torch.gather(score, 1, ids.long())
+
+    def bsum(v):  # 16-lane butterfly with zeros beyond `routed`, fp32
+        p = torch.zeros(n, 8)
+        p[:, :routed] = v
+        return _butterfly_sum8(p, torch.float32)
+
+    if renormalize:
+        w = rt(w / rt(bsum(w), T).unsqueeze(-1), T)
+    if shared:
+        mul = 1.0 / float(routed_scaling_factor if routed_scaling_factor is not None else 1.0)
+        ws = (bsum(w).double() * mul).float() if renormalize else torch.zeros(n)
+        w = torch.cat([w, ws.unsqueeze(-1)], dim=1)
+        ids = torch.cat([ids, torch.full((n, 1), E, dtype=torch.int32)], dim=1)
+    return w.float(), ids.to(torch.int32)
 
 
 def gate_margins(gating: torch.Tensor, bias: torch.Tensor, topk: int, num_expert_group: int,

@@ -22,6 +22,7 @@ import ast
 import os
 import textwrap
 import types
+import typing
 
 import numpy as np
 import torch
@@ -87,6 +88,24 @@ def main():
         w, ids = fn(gating, gating, bias, 8, True, 8, 4, scaling)
         put(store, f"ref:unit_test/test_fused_moe_gate_deepseek.py:biased_grouped_topk/{i}",
             gating=gating, bias=bias, weights=w, ids=ids, scaling=scaling)
+
+    # ---------------------------------------------------------------- fused_moe_gate_opt ("next" row)
+    # unit_test/test_fused_moe_gate_opt.py:78-135 biased_grouped_topk (the -inf masking variant, with the fused
+    # shared expert), inputs as moe_gate_func (:152-153: torch.rand logits and bias), TestMoeGate's three cases in
+    # bf16 plus fp32 cases (no ties).  With one shared expert the function overwrites the LAST of nine unsorted
+    # picks; on the CPU torch.topk returns them in descending order, so the last is the ninth best - checked here.
+    fn = load_function(ref, "unit_test/test_fused_moe_gate_opt.py", "biased_grouped_topk", extra_globals={"Optional": typing.Optional})
+    cases = [(torch.bfloat16, 256, 8, 4, 8, 0, 1.0), (torch.bfloat16, 160, 1, 1, 8, 0, 1.0), (torch.bfloat16, 160, 1, 1, 9, 1, 1.0),
+             (torch.float32, 256, 8, 4, 8, 0, 1.0), (torch.float32, 384, 1, 1, 9, 1, 2.5), (torch.float32, 448, 1, 1, 8, 0, 1.0)]
+    for i, (dtype, E, G, TG, k, shared, scaling) in enumerate(cases):
+        g = torch.Generator().manual_seed(200 + i)
+        gating = torch.rand(16, E, generator=g, dtype=torch.float32).to(dtype)
+        bias = torch.rand(E, generator=g, dtype=torch.float32).to(dtype)
+        w, ids = fn(gating, gating, bias, k, True, G, TG, shared, scaling)
+        if shared:
+            assert bool((ids[:, -1] == E).all())
+        put(store, f"ref:unit_test/test_fused_moe_gate_opt.py:biased_grouped_topk/{i}", gating=gating, bias=bias, weights=w, ids=ids,
+            scaling=scaling, groups=G, topk_group=TG, topk=k, shared=shared)
 
     # ---------------------------------------------------------------- a4: rms_norm (rms_div form)
     # unit_test/test_rms_norm.py:4-38 rms_norm_ref: after_res / rsqrt(mean+eps) * weight.
@@ -155,8 +174,7 @@ def main():
     # unit_test/test_silu_mul_dq_reorder_mask.py:9-45 as_float32_tensor + ref_dynamic_per_token_quant (the torch part
     # of that test; its SiLU*up product comes from a Triton kernel and cannot run here).  Fed with the fp32 product
     # of the kernel's expression so that it follows the kernel's arithmetic.
-    import typing
-    tnames = {"Optional": typing.Optional, "Tuple": typing.Tuple, "Union": typing.Union}
+    tnames ={"Optional": typing.Optional, "Tuple": typing.Tuple, "Union": typing.Union}
     as32 = load_function(ref, "unit_test/test_silu_mul_dq_reorder_mask.py", "as_float32_tensor",
                          extra_globals=tnames, patch=[("device='cuda'", "device='cpu'")])
     fn = load_function(ref, "unit_test/test_silu_mul_dq_reorder_mask.py", "ref_dynamic_per_token_quant",

@@ -85,6 +85,40 @@ def test_c_abi_with_an_explicit_form_leaves_the_padding_alone(H, form, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("T,H,dtype,with_res", [(300, 7168, torch.bfloat16, True), (64, 8192, torch.bfloat16, True),
+                                                (40, 4096, torch.bfloat16, False), (17, 1000, torch.float16, True),
+                                                (5, 36, torch.bfloat16, True), (20000, 7168, torch.bfloat16, True)])
+def test_sglang_flavour_also_returns_the_normalised_row(T, H, dtype, with_res):
+    """rms_norm_dynamic_per_token_quant_custom(out, out_bf16, ...) of sglang: same codes / scales / residual as the
+    7-argument operator, bit for bit, plus n (every size class: pipelined, row-per-CTA, unaligned)."""
+    from mcoplib_b200 import op
+    from tests.gpu_util import DEV, Canary, bits
+    x, res, w = _inputs(T, H, dtype, seed=4)
+    xd, wd = x.to(DEV), w.to(DEV)
+    r1 = res.to(DEV) if with_res else None
+    r2 = res.to(DEV) if with_res else None
+    q1 = torch.empty(T, H, dtype=torch.int8, device=DEV); s1 = torch.empty(T, 1, device=DEV)
+    op.rms_norm_dynamic_per_token_quant_custom(q1, xd, wd, s1, 1e-6, None, r1)
+    q2 = Canary((T, H), torch.int8); n2 = Canary((T, H), dtype); s2 = torch.empty(T, 1, device=DEV)
+    op.sgl_rms_norm_dynamic_per_token_quant_custom(q2.t, n2.t, xd, wd, s2, 1e-6, None, r2)
+    torch.cuda.synchronize()
+    q2.check(); n2.check()
+    assert torch.equal(q1, q2.t) and torch.equal(s1, s2)
+    if with_res:
+        assert torch.equal(bits(r1), bits(r2))
+    if T <= 1000:
+        q_ref, s_ref, _, n_ref = R.rms_norm_dynamic_per_token_quant(x, w, 1e-6, residual=res if with_res else None, return_norm=True)
+        C.assert_codes(q2.t, q_ref)
+        assert float((n2.t.cpu().float() != n_ref.float()).float().mean()) < 1e-4
+        C.assert_close(n2.t.float(), n_ref.float(), "norm output", rel=2 ** -6, abs_=1e-6)
+    else:   # size-independent property: the codes are the quantised normalised row
+        back = torch.round(n2.t.cpu().float() * (1.0 / s2.cpu())).clamp(-128, 127).to(torch.int8)
+        assert torch.equal(back, q2.t.cpu())
+    with pytest.raises(RuntimeError):
+        op.sgl_rms_norm_dynamic_per_token_quant_custom(q2.t, n2.t, xd, wd, s2, 1e-6, torch.ones(1, device=DEV), r2)
+
+
+@pytest.mark.gpu
 def test_rejects_a_record_too_small_and_wrong_dtypes():
     from mcoplib_b200 import op
     from tests.gpu_util import DEV
