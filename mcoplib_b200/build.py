@@ -84,7 +84,7 @@ def build_torch_ext(force=False, verbose=False, namespace="mcop_C") -> str:
     src = os.path.join(CSRC, "torch_ext.cpp")
     out = os.path.join(HERE, OP_NAME)
     lib = os.path.join(HERE, LIB_NAME)
-    if not force and _newer(out, [src, lib, os.path.join(INCLUDE, "mcop_b200.h")]):
+    if not force and _newer(out, [src, lib, os.path.join(INCLUDE, "mcop_b200.h"), os.path.join(CSRC, "debug_trace.hpp")]):
         return out
     inc = ["-I" + p for p in ce.include_paths()] + ["-I" + sysconfig.get_paths()["include"], "-I" + INCLUDE,
                                                     "-I" + os.path.join(CUDA_HOME, "include")]

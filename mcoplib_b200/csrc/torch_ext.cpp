@@ -18,6 +18,7 @@
 #include <tuple>
 
 #include "mcop_b200.h"
+#include "debug_trace.hpp"
 
 #ifndef MCOP_TORCH_NS
 #define MCOP_TORCH_NS mcop_C
@@ -58,6 +59,7 @@ Tensor scratch_bytes(size_t bytes, const Tensor& like) {
 
 // torch.ops._C.fused_add_rms_norm (op/vllm/layernorm_kernels.cu:243-292)
 void fused_add_rms_norm(Tensor& input, Tensor& residual, Tensor& weight, double epsilon) {
+  MCOP_DEBUG_CALL("fused_add_rms_norm", input, residual, weight, epsilon);
   check_cuda(input, "input");
   TORCH_CHECK(weight.scalar_type() == input.scalar_type());
   TORCH_CHECK(input.scalar_type() == residual.scalar_type());
@@ -84,6 +86,7 @@ void fused_add_rms_norm(Tensor& input, Tensor& residual, Tensor& weight, double 
 void rms_norm_dynamic_per_token_quant_vllm(Tensor& out, const Tensor& input, const Tensor& weight, Tensor& scales,
                                            double var_epsilon, std::optional<Tensor> scale_ub,
                                            std::optional<Tensor> residual) {
+  MCOP_DEBUG_CALL("rms_norm_dynamic_per_token_quant_custom", out, input, weight, scales, var_epsilon, scale_ub, residual);
   check_cuda(input, "input");
   TORCH_CHECK(out.scalar_type() == at::kChar, "only int8 output is built");
   TORCH_CHECK(out.is_contiguous() && input.is_contiguous());
@@ -105,6 +108,7 @@ void rms_norm_dynamic_per_token_quant_vllm(Tensor& out, const Tensor& input, con
 // (op/sglang/include/sgl_kernel_ops.h:138-145, op/sglang/csrc/elementwise/fused_layernorm_dynamic_per_token_quant_custom.cu:434-460)
 void rms_norm_dynamic_per_token_quant_sgl(Tensor& out, Tensor& out_bf16, const Tensor& input, const Tensor& weight, Tensor& scales,
                                           double var_epsilon, std::optional<Tensor> scale_ub, std::optional<Tensor> residual) {
+  MCOP_DEBUG_CALL("rms_norm_dynamic_per_token_quant_custom", out, out_bf16, input, weight, scales, var_epsilon, scale_ub, residual);
   check_cuda(input, "input");
   TORCH_CHECK(out.scalar_type() == at::kChar, "only int8 output is built");
   TORCH_CHECK(out.is_contiguous() && input.is_contiguous());
@@ -127,6 +131,7 @@ void rms_norm_dynamic_per_token_quant_sgl(Tensor& out, Tensor& out_bf16, const T
 void rms_norm_dynamic_per_token_quant_9(Tensor& out, const Tensor& input, const Tensor& weight, const Tensor& smooth_scale,
                                         Tensor& scales, double var_epsilon, Tensor& after_res, Tensor& after_norm,
                                         std::optional<Tensor> residual) {
+  MCOP_DEBUG_CALL("rms_norm_dynamic_per_token_quant", out, input, weight, smooth_scale, scales, var_epsilon, after_res, after_norm, residual);
   check_cuda(input, "input");
   TORCH_CHECK(out.scalar_type() == at::kChar);
   TORCH_CHECK(out.is_contiguous() && input.is_contiguous());
@@ -149,6 +154,7 @@ void rms_norm_dynamic_per_token_quant_9(Tensor& out, const Tensor& input, const 
 // mcoplib.op.rms_norm (op/fused_rms_norm_dq.cu:980-999)
 void rms_norm(Tensor& out, const Tensor& input, const Tensor& weight, double var_epsilon, std::optional<Tensor> after_res,
               std::optional<Tensor> residual, bool rms_div) {
+  MCOP_DEBUG_CALL("rms_norm", out, input, weight, var_epsilon, after_res, residual, rms_div);
   check_cuda(input, "input");
   TORCH_CHECK(out.is_contiguous() && input.is_contiguous() && weight.is_contiguous());
   TORCH_CHECK(out.scalar_type() == input.scalar_type());
@@ -166,6 +172,7 @@ void rms_norm(Tensor& out, const Tensor& input, const Tensor& weight, double var
 
 // mcoplib.op.head_rms_norm (op/fused_rms_norm_dq.cu:804-812)
 void head_rms_norm(Tensor& out, const Tensor& hidden_states, const Tensor& weight, double var_epsilon, int head_offset, int head_norm) {
+  MCOP_DEBUG_CALL("head_rms_norm", out, hidden_states, weight, var_epsilon, head_offset, head_norm);
   check_cuda(hidden_states, "hidden_states");
   TORCH_CHECK(hidden_states.dim() == 3, "hidden_states must be [tokens, heads, head_dim]");
   TORCH_CHECK(out.is_contiguous() && hidden_states.is_contiguous() && weight.is_contiguous());
@@ -178,6 +185,7 @@ void head_rms_norm(Tensor& out, const Tensor& hidden_states, const Tensor& weigh
 
 // mcoplib.op.scale_dynamic_quant (op/scale_dynamic_quant.cu:127-153): allocates and returns (codes, scales)
 std::tuple<Tensor, Tensor> scale_dynamic_quant(const Tensor& hidden_states, const Tensor& smooth_scales, at::ScalarType dst) {
+  MCOP_DEBUG_CALL("scale_dynamic_quant", hidden_states, smooth_scales, dst);
   check_cuda(hidden_states, "hidden_states");
   TORCH_CHECK(dst == at::kChar, "only int8 output is built");
   TORCH_CHECK(hidden_states.is_contiguous() && smooth_scales.is_contiguous());
@@ -195,6 +203,7 @@ std::tuple<Tensor, Tensor> scale_dynamic_quant(const Tensor& hidden_states, cons
 // torch.ops._C.dynamic_scaled_int8_quant (op/vllm/quantization/compressed_tensors/int8_quant_kernels.cu:459-526),
 // symmetric form only (azp must be None)
 void dynamic_scaled_int8_quant(Tensor& out, const Tensor& input, Tensor& scales, std::optional<Tensor> azp) {
+  MCOP_DEBUG_CALL("dynamic_scaled_int8_quant", out, input, scales, azp);
   check_cuda(input, "input");
   TORCH_CHECK(input.is_contiguous());
   TORCH_CHECK(out.is_contiguous());
@@ -214,6 +223,7 @@ void dynamic_scaled_int8_quant(Tensor& out, const Tensor& input, Tensor& scales,
 // torch.ops._C.rotary_embedding (op/vllm/pos_encoding_kernels.cu:135-217); the cos/sin cache may also be fp32
 void rotary_embedding_vllm(Tensor& positions, Tensor& query, std::optional<Tensor> key, int64_t head_size, Tensor& cos_sin_cache,
                            bool is_neox) {
+  MCOP_DEBUG_CALL("rotary_embedding", positions, query, key, head_size, cos_sin_cache, is_neox);
   check_cuda(query, "query");
   TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous());
   const int64_t num_tokens = positions.numel();
@@ -254,6 +264,7 @@ void rotary_embedding_vllm(Tensor& positions, Tensor& query, std::optional<Tenso
 // mcoplib.op.rotary_embedding (op/rotary_embedding.cu:99-121)
 void rotary_embedding_packed(Tensor packed_qkv, Tensor q_len, Tensor accum_q_lens, Tensor cache_lens, Tensor cos, Tensor sin,
                              Tensor output, int q_head_num, int kv_head_num, int rope_offset) {
+  MCOP_DEBUG_CALL("rotary_embedding", packed_qkv, q_len, accum_q_lens, cache_lens, cos, sin, output, q_head_num, kv_head_num, rope_offset);
   (void)rope_offset;  // accepted and unused, as in the reference (op/rotary_embedding.cu:68-70)
   (void)q_len;
   check_cuda(packed_qkv, "packed_qkv");
@@ -276,6 +287,7 @@ void rotary_embedding_packed(Tensor packed_qkv, Tensor q_len, Tensor accum_q_len
 
 // mcoplib.op.fused_rope_fwd (op/fused_rope.cu:13-74)
 Tensor fused_rope_fwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> indexes, bool force_bf16_attn) {
+  MCOP_DEBUG_CALL("fused_rope_fwd", qkv, cos, sin, indexes, force_bf16_attn);
   check_cuda(qkv, "qkv"); check_cuda(cos, "cos"); check_cuda(sin, "sin");
   TORCH_CHECK(qkv.is_contiguous() && cos.is_contiguous() && sin.is_contiguous());
   if (indexes.has_value()) {
@@ -297,6 +309,7 @@ Tensor fused_rope_fwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> 
 void store_kv_cache_cuda_interface(Tensor packed_qkv, Tensor q_lens, Tensor accum_q_lens, Tensor cache_lens, Tensor cache_slot_ids,
                                    Tensor& k_cache, Tensor& v_cache, Tensor k_scale, Tensor v_scale, int batch_size, int q_head_num,
                                    int kv_head_num) {
+  MCOP_DEBUG_CALL("store_kv_cache_cuda_interface", packed_qkv, q_lens, accum_q_lens, cache_lens, cache_slot_ids, k_cache, v_cache, k_scale, v_scale, batch_size, q_head_num, kv_head_num);
   check_cuda(packed_qkv, "packed_qkv"); check_cuda(q_lens, "q_lens"); check_cuda(accum_q_lens, "accum_q_lens");
   check_cuda(cache_lens, "cache_lens"); check_cuda(cache_slot_ids, "cache_slot_ids"); check_cuda(k_cache, "k_cache");
   check_cuda(v_cache, "v_cache"); check_cuda(k_scale, "k_scale"); check_cuda(v_scale, "v_scale");
@@ -321,6 +334,7 @@ void store_kv_cache_cuda_interface(Tensor packed_qkv, Tensor q_lens, Tensor accu
 // torch.ops._C_cache_ops.reshape_and_cache_flash (op/vllm/cache_kernels.cu:610-650): only kv_cache_dtype "auto"
 void reshape_and_cache_flash(Tensor& key, Tensor& value, Tensor& key_cache, Tensor& value_cache, Tensor& slot_mapping,
                              const std::string& kv_cache_dtype, Tensor& k_scale, Tensor& v_scale) {
+  MCOP_DEBUG_CALL("reshape_and_cache_flash", key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale, v_scale);
   (void)k_scale; (void)v_scale;
   check_cuda(key, "key");
   TORCH_CHECK(kv_cache_dtype == "auto", "only kv_cache_dtype \"auto\" is built (as in the reference)");
@@ -342,6 +356,7 @@ void reshape_and_cache_flash(Tensor& key, Tensor& value, Tensor& key_cache, Tens
 // Fused RoPE + int8 paged store (addition of this build, composition of the three ops above)
 void rope_kv_store_int8(Tensor& positions, Tensor& query, Tensor& key, Tensor& value, int64_t head_size, Tensor& cos_sin_cache,
                         bool is_neox, Tensor& key_cache, Tensor& value_cache, Tensor& slot_mapping, Tensor& k_scale, Tensor& v_scale) {
+  MCOP_DEBUG_CALL("rope_kv_store_int8", positions, query, key, value, head_size, cos_sin_cache, is_neox, key_cache, value_cache, slot_mapping, k_scale, v_scale);
   check_cuda(query, "query");
   TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.dim() == 1);
   TORCH_CHECK(slot_mapping.scalar_type() == at::kLong && slot_mapping.is_contiguous());
@@ -372,6 +387,7 @@ void rope_kv_store_int8(Tensor& positions, Tensor& query, Tensor& key, Tensor& v
 
 // mcoplib.op.moe_softmax_topk (op/moe_softmax_topk.cu:216-235)
 void moe_softmax_topk(Tensor topk_weights, Tensor topk_indices, Tensor gating_output, bool pre_softmax) {
+  MCOP_DEBUG_CALL("moe_softmax_topk", topk_weights, topk_indices, gating_output, pre_softmax);
   (void)pre_softmax;  // unused on this path in the reference as well: the weights are always renormalised
   check_cuda(gating_output, "gating_output");
   TORCH_CHECK(gating_output.scalar_type() == at::kFloat, "gating_output must be float32");
@@ -388,6 +404,7 @@ void moe_softmax_topk(Tensor topk_weights, Tensor topk_indices, Tensor gating_ou
 
 // torch.ops._moe_C.topk_softmax (op/vllm/moe/topk_softmax_kernels.cu:884-918, schema op/vllm/moe/torch_bindings.cpp:6-9)
 void topk_softmax(Tensor& topk_weights, Tensor& topk_indices, Tensor& token_expert_indices, Tensor& gating_output, bool renormalize) {
+  MCOP_DEBUG_CALL("topk_softmax", topk_weights, topk_indices, token_expert_indices, gating_output, renormalize);
   check_cuda(gating_output, "gating_output");
   TORCH_CHECK(gating_output.scalar_type() == at::kFloat || gating_output.scalar_type() == at::kHalf ||
                   gating_output.scalar_type() == at::kBFloat16,
@@ -411,6 +428,7 @@ int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Ten
                             int topk, bool renormalize, int num_expert_group, int topk_group,
                             std::optional<int> num_fused_shared_experts, std::optional<float> routed_scaling_factor,
                             std::optional<int> moegate_type, std::optional<Tensor> debug_group_mask) {
+  MCOP_DEBUG_CALL("fused_moe_gate_deepseek", gating_outputs, correction_bias, out_routing_weights, out_selected_experts, topk, renormalize, num_expert_group, topk_group, num_fused_shared_experts, routed_scaling_factor, moegate_type, debug_group_mask);
   check_cuda(gating_outputs, "gating_outputs");
   TORCH_CHECK(gating_outputs.dim() == 2 && gating_outputs.is_contiguous() && correction_bias.is_contiguous());
   TORCH_CHECK(out_routing_weights.scalar_type() == at::kFloat && out_routing_weights.is_contiguous());
@@ -438,6 +456,7 @@ int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Ten
 int64_t fused_moe_gate_opt(Tensor& gating_outputs, Tensor& correction_bias, Tensor& out_routing_weights, Tensor& out_selected_experts,
                            int64_t topk, bool renormalize, int64_t num_expert_group, int64_t topk_group,
                            std::optional<int64_t> num_fused_shared_experts, std::optional<double> routed_scaling_factor) {
+  MCOP_DEBUG_CALL("fused_moe_gate_opt", gating_outputs, correction_bias, out_routing_weights, out_selected_experts, topk, renormalize, num_expert_group, topk_group, num_fused_shared_experts, routed_scaling_factor);
   check_cuda(gating_outputs, "gating_outputs");
   TORCH_CHECK(((topk == 8) || (topk == 9)), "Expected topk = 8, but get topk = ", topk);
   const int64_t num_shared = num_fused_shared_experts.value_or(0);
@@ -470,6 +489,7 @@ void moe_scatter_dynamic_quant(Tensor hidden_status, Tensor selected_experts, Te
                                Tensor scatter_per_token_scale, Tensor scatter_tokens_offset, Tensor experts_token_count,
                                Tensor experts_token_start, int experts_per_rank, int shared_experts_per_rank, int shared_tokens_per_sp,
                                std::optional<Tensor> tok2row) {
+  MCOP_DEBUG_CALL("moe_scatter_dynamic_quant", hidden_status, selected_experts, moe_weights, smooth_scale, scatter_tokens, scatter_per_token_scale, scatter_tokens_offset, experts_token_count, experts_token_start, experts_per_rank, shared_experts_per_rank, shared_tokens_per_sp, tok2row);
   check_cuda(hidden_status, "hidden_status"); check_cuda(selected_experts, "selected_experts"); check_cuda(smooth_scale, "smooth_scale");
   TORCH_CHECK(hidden_status.is_contiguous() && selected_experts.is_contiguous() && smooth_scale.is_contiguous());
   TORCH_CHECK(hidden_status.scalar_type() == at::kBFloat16, "Only float16, bfloat16 are supported");
@@ -506,6 +526,7 @@ void moe_scatter_dynamic_quant(Tensor hidden_status, Tensor selected_experts, Te
 
 // mcoplib.op.moe_gather (op/moe_gather.cu:137-150)
 void moe_gather(Tensor scatter_tokens, Tensor scatter_tokens_offset, Tensor convergent_tokens, std::optional<Tensor> tok2row) {
+  MCOP_DEBUG_CALL("moe_gather", scatter_tokens, scatter_tokens_offset, convergent_tokens, tok2row);
   check_cuda(scatter_tokens, "scatter_tokens");
   TORCH_CHECK(scatter_tokens.scalar_type() == at::kBFloat16 && convergent_tokens.scalar_type() == at::kBFloat16,
               "Only float16, bfloat16 are supported");
@@ -539,6 +560,7 @@ void moe_gather(Tensor scatter_tokens, Tensor scatter_tokens_offset, Tensor conv
 // mcoplib.op.moe_swiglu_dynamic_quantize (op/moe_swiglu_dq.cu, include/moe_swiglu_dq.h)
 void moe_swiglu_dynamic_quantize(Tensor scatter_tokens, Tensor smooth_scale, Tensor experts_tokens_start, Tensor experts_tokens_count,
                                  Tensor& y, Tensor& per_tokens_scale, int total_experts_num) {
+  MCOP_DEBUG_CALL("moe_swiglu_dynamic_quantize", scatter_tokens, smooth_scale, experts_tokens_start, experts_tokens_count, y, per_tokens_scale, total_experts_num);
   check_cuda(scatter_tokens, "scatter_tokens");
   TORCH_CHECK(scatter_tokens.scalar_type() == at::kBFloat16, "Only bfloat16 is supported");
   TORCH_CHECK(scatter_tokens.is_contiguous() && smooth_scale.is_contiguous() && y.is_contiguous() && per_tokens_scale.is_contiguous());
@@ -564,6 +586,7 @@ void moe_swiglu_dynamic_quantize(Tensor scatter_tokens, Tensor smooth_scale, Ten
 void fused_add_rms_norm_dynamic_per_token_quant_padding_output(Tensor& output, Tensor& output_rms, Tensor& output_quant_int8,
                                                                Tensor& out_scales, const Tensor& input, Tensor& residual,
                                                                const Tensor& weight, int64_t pad_size, double epsilon) {
+  MCOP_DEBUG_CALL("add_rms_norm_dynamic_per_token_quant_padding_output", output, output_rms, output_quant_int8, out_scales, input, residual, weight, pad_size, epsilon);
   check_cuda(input, "input");
   TORCH_CHECK(output.dtype() == torch::kInt8);
   TORCH_CHECK(input.dtype() == at::ScalarType::BFloat16);
@@ -591,6 +614,7 @@ void fused_add_rms_norm_dynamic_per_token_quant_padding_output(Tensor& output, T
 // w2_scale is accepted and, as in the reference (HAS_SCALE = false in every instantiation), not applied.
 void fused_silu_mul_dq_reorder_quant(Tensor& out, Tensor& scale, const Tensor& input, const Tensor& reorder_topk_ids,
                                      const Tensor& w2_scale, int64_t start_expert_id, int64_t end_expert_id) {
+  MCOP_DEBUG_CALL("fused_silu_mul_dq_quant_reordered_topk_interface", out, scale, input, reorder_topk_ids, w2_scale, start_expert_id, end_expert_id);
   check_cuda(input, "input");
   TORCH_CHECK(input.is_contiguous());
   TORCH_CHECK(scale.is_contiguous());
@@ -612,6 +636,7 @@ void fused_silu_mul_dq_reorder_quant(Tensor& out, Tensor& scale, const Tensor& i
 
 // sglang's fused_silu_mul_dq_quant_interface (op/int8_quant_kernels.cu:1877-1891): every row is processed
 void fused_silu_mul_dq_quant(Tensor& out, Tensor& scale, const Tensor& input) {
+  MCOP_DEBUG_CALL("fused_silu_mul_dq_quant_interface", out, scale, input);
   check_cuda(input, "input");
   TORCH_CHECK(input.is_contiguous());
   TORCH_CHECK(scale.is_contiguous());
@@ -628,6 +653,7 @@ void fused_silu_mul_dq_quant(Tensor& out, Tensor& scale, const Tensor& input) {
 
 // mcoplib.op.fused_silu_mul_dq_mask_quant (op/int8_quant_kernels.cu:1844-1875, include/int8_quant_kernel.h:2-5)
 void fused_silu_mul_dq_mask_quant(Tensor& out, const Tensor& input, const Tensor& mask) {
+  MCOP_DEBUG_CALL("fused_silu_mul_dq_mask_quant_pack", out, input, mask);
   check_cuda(input, "input");
   TORCH_CHECK(input.is_contiguous());
   TORCH_CHECK(out.is_contiguous());
@@ -650,6 +676,7 @@ void fused_silu_mul_dq_mask_quant(Tensor& out, const Tensor& input, const Tensor
 // Weighted combine (addition of this build)
 void moe_gather_weighted(Tensor y, Tensor row2tok, Tensor topk_ids, Tensor topk_weights, Tensor experts_token_start, Tensor out,
                          bool accumulate, std::optional<Tensor> tok2row) {
+  MCOP_DEBUG_CALL("moe_gather_weighted", y, row2tok, topk_ids, topk_weights, experts_token_start, out, accumulate, tok2row);
   check_cuda(y, "y");
   TORCH_CHECK(y.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "Only bfloat16 is supported");
   TORCH_CHECK(y.is_contiguous() && row2tok.is_contiguous() && topk_ids.is_contiguous() && topk_weights.is_contiguous() &&
