@@ -30,9 +30,9 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "fused_chain_tokens_per_s"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per token of the norm+quant kernel at hidden 7168,
-# from the ncu capture summarised in profiles/norm_quant_bf16_pipe_chain5_32768x7168.md (939.6 MB read + 649.0 MB
+# from the ncu capture summarised in profiles/norm_quant_bf16_pipe_chain5_32768x7168.md (939.8 MB read + 651.5 MB
 # written for 32,768 tokens); traffic grows in proportion to the tokens (every row is touched exactly once).
-NORM_QUANT_DRAM_BYTES_PER_TOKEN = (939_579_648 + 649_004_032) / 32768
+NORM_QUANT_DRAM_BYTES_PER_TOKEN = (939_755_520 + 651_474_432) / 32768
 
 
 def measured_peak():
@@ -234,7 +234,65 @@ class Rope2:
                                                r["key_cache"], r["value_cache"], r["slot_mapping"], self.ks, self.vs)]
 
 
-WORKLOADS = {"chain5": (Chain5, 262144), "chain4": (Chain4, 32768), "route3": (Route3, 8192), "rope2": (Rope2, 4096)}
+class Next6:
+    """The operators either side of the path (alternate output formats of part 1, the activation-quant steps after the
+    expert up-projection, vLLM's softmax router), each timed on its own: hidden 7168, expert intermediate size 2048."""
+    name = "next rows: padded-record norm+quant, norm+quant with norm output, per-token int8 quant, swiglu+quant, silu_mul+quant, topk_softmax"
+    kernels = ["norm_quant_padded", "norm_quant_norm_out", "dynamic_int8_quant", "swiglu_quant", "silu_mul_quant", "topk_softmax"]
+    launches_per_step = 6
+
+    def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
+        from mcoplib_b200 import workloads as W
+        self.T, self.H, self.I, self.E, self.W = tokens, 7168, 2048, 8, W
+        d = W.norm_quant_inputs(tokens, 7168, t0, 0, gen_device, device)
+        self.x, self.res, self.w = d["x"], d["residual"], d["weight"]
+        o = dict(device=device)
+        self.pad = 3840
+        self.packed = torch.empty(tokens, 2 * self.pad, dtype=torch.int8, **o)
+        self.norm = torch.empty(tokens, 7168, dtype=torch.bfloat16, **o)
+        self.codes = torch.empty(tokens, 7168, dtype=torch.int8, **o)
+        self.scales = torch.empty(tokens, 1, dtype=torch.float32, **o)
+        R = 2 * tokens                                   # rows after a top-2 dispatch
+        self.R = R
+        self.gu = W.per_token("randn", 80, 2 * t0, 2 * t0 + R, 2 * self.I, torch.bfloat16, 0, gen_device, device)
+        self.smooth = torch.ones(self.E, self.I, dtype=torch.float32, **o)
+        per = R // self.E
+        self.counts = torch.full((self.E,), per, dtype=torch.int32, **o)
+        self.counts[-1] += R - per * self.E
+        self.starts = (torch.cumsum(self.counts, 0) - self.counts).to(torch.int32)
+        self.act = torch.empty(R, self.I, dtype=torch.int8, **o)
+        self.act_scale = torch.empty(R, dtype=torch.float32, **o)
+        self.row_ids = (torch.arange(R, device=device, dtype=torch.int64) % self.E)
+        self.logits = W.router_inputs(tokens, 8, t0, 0, gen_device, device)["logits"]
+        self.tw = torch.empty(tokens, 2, dtype=torch.float32, **o)
+        self.ti = torch.empty(tokens, 2, dtype=torch.int32, **o)
+        self.tsrc = torch.empty(tokens, 2, dtype=torch.int32, **o)
+        self.none = torch.empty(0)
+
+    def bytes_per_kernel(self):
+        T, H, R, I = self.T, self.H, self.R, self.I
+        nq = self.W.norm_quant_bytes(T, H)
+        return {"norm_quant_padded": nq + T * H * (2 + 1) + 4 * T,        # + norm output, plain codes and the packed scale
+                "norm_quant_norm_out": nq + T * H * 2,
+                "dynamic_int8_quant": T * H * (2 + 1) + 4 * T,
+                "swiglu_quant": R * I * (4 + 1) + 4 * R + self.E * I * 4,
+                "silu_mul_quant": R * I * (4 + 1) + 4 * R + 8 * R,
+                "topk_softmax": self.W.gate_bytes(T, 8, 2) - 8 * 4 + 8 * T}
+
+    def stages(self, ops):
+        return [
+            lambda: ops.fused_add_rms_norm_dynamic_per_token_quant_padding_output(self.packed, self.norm, self.codes, self.scales, self.x,
+                                                                                  self.res, self.w, self.pad, 1e-6),
+            lambda: ops.sgl_rms_norm_dynamic_per_token_quant_custom(self.codes, self.norm, self.x, self.w, self.scales, 1e-6, None, self.res),
+            lambda: ops.dynamic_scaled_int8_quant(self.codes, self.x, self.scales, None),
+            lambda: ops.moe_swiglu_dynamic_quantize(self.gu, self.smooth, self.starts, self.counts, self.act, self.act_scale, self.E),
+            lambda: ops.fused_silu_mul_dq_reorder_quant(self.act, self.act_scale, self.gu, self.row_ids, self.none, 0, self.E - 1),
+            lambda: ops.topk_softmax(self.tw, self.ti, self.tsrc, self.logits, True),
+        ]
+
+
+WORKLOADS = {"chain5": (Chain5, 262144), "chain4": (Chain4, 32768), "route3": (Route3, 8192), "rope2": (Rope2, 4096),
+             "next6": (Next6, 65536)}
 
 
 # ------------------------------------------------------------------------------------------------

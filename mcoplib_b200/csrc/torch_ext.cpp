@@ -755,6 +755,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("vllm_rotary_embedding", &rotary_embedding_vllm);
   m.def("reshape_and_cache_flash", &reshape_and_cache_flash);
   m.def("topk_softmax", &topk_softmax);
+  m.def("dynamic_scaled_int8_quant", &dynamic_scaled_int8_quant);
 #define MCOP_STR_(x) #x
 #define MCOP_STR(x) MCOP_STR_(x)
   m.attr("torch_namespace") = MCOP_STR(MCOP_TORCH_NS);
