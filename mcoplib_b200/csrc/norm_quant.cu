@@ -270,7 +270,7 @@ __device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
 //   true  - a barrier before the stage is read and the classic two-barrier block reductions (five per row).
 // Measured on B200: with 7 warps (hidden 7168) the loose form is 6 % faster (6.36 vs 5.97 TB/s); with 8 warps
 // (hidden 8192) the lock-step form is 14 % faster (6.26 vs 5.50 TB/s), so the launcher picks per CTA size.
-template <int THREADS, int NVEC, bool FULL, bool LOCKSTEP>
+template <int THREADS, int NVEC, bool FULL, bool LOCKSTEP, bool NORM_OUT>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_bf16_pipe(NormParams p, int64_t tokens, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float red[2][32];
@@ -409,11 +409,9 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
           c[2 * j + 1] = rn_low_byte(b);
         }
         st_cs_u2(q + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
-#if MCOP_VAR != 1
-        if (p.out)  // optional extra output: the normalised bf16 row
-#else
-        if (false)
-#endif
+        // optional extra output, the normalised bf16 row: a compile-time variant because a run-time test of p.out here
+        // costs the plain form 3-4 % (6.13 against 6.38 TB/s at hidden 7168, measured on one box)
+        if constexpr (NORM_OUT)
           st_u4(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.out_stride + v * 8, make_uint4(n2[k][0], n2[k][1], n2[k][2], n2[k][3]));
       }
     }
@@ -445,7 +443,8 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > tokens) grid = tokens;
   int* err = pipe_error_ptr();
-  static std::atomic<int> attr_done[4];
+  static std::atomic<int> attr_done[8];
+  const bool no = p.out != nullptr;  // also write the normalised row
   auto launch = [&](auto kernel, int slot) -> int {
     if (attr_done[slot].load(std::memory_order_relaxed) < (int)smem) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
@@ -455,10 +454,13 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
     kernel<<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, err);
     return check_launch("norm (pipelined)");
   };
-  if (threads == 224)
-    return full ? launch(norm_quant_bf16_pipe<224, 4, true, false>, 0) : launch(norm_quant_bf16_pipe<224, 4, false, false>, 1);
-  if (threads == 256) return launch(norm_quant_bf16_pipe<256, 4, false, true>, 2);
-  return launch(norm_quant_bf16_pipe<512, 4, false, true>, 3);
+  if (threads == 224) {
+    if (full) return no ? launch(norm_quant_bf16_pipe<224, 4, true, false, true>, 0) : launch(norm_quant_bf16_pipe<224, 4, true, false, false>, 1);
+    return no ? launch(norm_quant_bf16_pipe<224, 4, false, false, true>, 2) : launch(norm_quant_bf16_pipe<224, 4, false, false, false>, 3);
+  }
+  if (threads == 256)
+    return no ? launch(norm_quant_bf16_pipe<256, 4, false, true, true>, 4) : launch(norm_quant_bf16_pipe<256, 4, false, true, false>, 5);
+  return no ? launch(norm_quant_bf16_pipe<512, 4, false, true, true>, 6) : launch(norm_quant_bf16_pipe<512, 4, false, true, false>, 7);
 }
 
 template <typename T, typename WT, int MODE>
@@ -596,6 +598,53 @@ __global__ void __launch_bounds__(256) dynamic_int8_quant_kernel(int8_t* q, floa
     qr[i] = (int8_t)q_rn_clamp(ElemTraits<T>::to_float(xr[i]) * inv, -128, 127);
 }
 
+// the same with the row held in registers: one 16-byte (fp32: two) load per 8 elements, one 8-byte store
+template <typename T, int THREADS, int NVEC>
+__global__ void __launch_bounds__(THREADS) dynamic_int8_quant_vec(int8_t* q, float* scales, const T* x, int hidden) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const int nv = hidden >> 3;
+  const T* xr = x + row * (int64_t)hidden;
+  float v[NVEC][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int k = threadIdx.x + i * THREADS;
+    if (k < nv) {
+      Vec8<T>::load_nc(xr + k * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    }
+  }
+  amax = block_reduce<true>(amax, red);
+  if (threadIdx.x == 0) scales[row] = amax / 127.0f;
+  const float inv = amax == 0.f ? 0.f : 127.0f / amax;
+  int8_t* qr = q + row * (int64_t)hidden;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int k = threadIdx.x + i * THREADS;
+    if (k < nv) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(v[i][j] * inv, -128, 127);
+      st_cs_u2(qr + k * 8, pack_i8x8(c));
+    }
+  }
+}
+
+template <typename T>
+int launch_dynamic_int8_quant(int8_t* out, float* scales, const T* x, int64_t tokens, int hidden, cudaStream_t s) {
+  const int nv = hidden >> 3;
+  const unsigned grid = (unsigned)tokens;
+  const bool vec_ok = hidden % 8 == 0 && nv <= 4096 && aligned16(x) && (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
+  if (!vec_ok) dynamic_int8_quant_kernel<T><<<grid, 256, 0, s>>>(out, scales, x, hidden);
+  else if (nv <= 256) dynamic_int8_quant_vec<T, 128, 2><<<grid, 128, 0, s>>>(out, scales, x, hidden);
+  else if (nv <= 1024) dynamic_int8_quant_vec<T, 256, 4><<<grid, 256, 0, s>>>(out, scales, x, hidden);
+  else if (nv <= 2048) dynamic_int8_quant_vec<T, 512, 4><<<grid, 512, 0, s>>>(out, scales, x, hidden);
+  else dynamic_int8_quant_vec<T, 1024, 4><<<grid, 1024, 0, s>>>(out, scales, x, hidden);
+  return check_launch("dynamic_scaled_int8_quant");
+}
+
 }  // namespace
 }  // namespace mcop
 
@@ -609,12 +658,11 @@ extern "C" int mcop_dynamic_scaled_int8_quant(int8_t* out, float* scales, const 
   if (tokens == 0) return MCOP_OK;
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
-    case MCOP_BF16: dynamic_int8_quant_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __nv_bfloat16*)x, (int)hidden); break;
-    case MCOP_F16: dynamic_int8_quant_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __half*)x, (int)hidden); break;
-    case MCOP_F32: dynamic_int8_quant_kernel<float><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const float*)x, (int)hidden); break;
-    default: return set_error(MCOP_ERR_UNSUPPORTED, "dynamic_scaled_int8_quant: unknown dtype code %d", dtype);
+    case MCOP_BF16: return launch_dynamic_int8_quant(out, scales, (const __nv_bfloat16*)x, tokens, (int)hidden, s);
+    case MCOP_F16: return launch_dynamic_int8_quant(out, scales, (const __half*)x, tokens, (int)hidden, s);
+    case MCOP_F32: return launch_dynamic_int8_quant(out, scales, (const float*)x, tokens, (int)hidden, s);
   }
-  return check_launch("dynamic_scaled_int8_quant");
+  return set_error(MCOP_ERR_UNSUPPORTED, "dynamic_scaled_int8_quant: unknown dtype code %d", dtype);
 }
 
 extern "C" int mcop_fused_add_rmsnorm(void* x, int64_t x_row_stride, void* residual, const void* weight,
