@@ -182,6 +182,16 @@ __device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
+// Eight codes rne(v[j] * mul) packed into 8 bytes without a float-to-int conversion (those run at a quarter of the
+// rate of an add).  Requires |v[j] * mul| <= 127.5 after rounding, which abs-max scaling guarantees
+// (|v * (127 / max|v|)| <= 127 * (1 + 2^-22)); finite inputs only.
+__device__ __forceinline__ uint2 quant8_rn_unclamped(const float (&v)[8], float mul) {
+  uint32_t c[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) c[j] = rn_low_byte(__fmul_rn(v[j], mul));
+  return make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7]));
+}
+
 __device__ __forceinline__ uint2 pack_i8x8(const int (&q)[8]) {
   uint32_t a = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
   uint32_t b = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);

@@ -72,10 +72,7 @@ __global__ void __launch_bounds__(THREADS) swiglu_quant_vec(SwigluParams p) {
   for (int i = 0; i < NVEC; ++i) {
     const int k = threadIdx.x + i * THREADS;
     if (k < nv) {
-      int c[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) c[q] = q_rn_clamp(v[i][q] * mul, -127, 127);
-      st_cs_u2(out + k * 8, pack_i8x8(c));
+      st_cs_u2(out + k * 8, quant8_rn_unclamped(v[i], mul));
     }
   }
 }
@@ -186,10 +183,7 @@ __device__ __forceinline__ void silu_mul_row_vec(const SiluMulParams& p, int64_t
   for (int i = 0; i < NVEC; ++i) {
     const int k = threadIdx.x + i * THREADS;
     if (k < nv) {
-      int c[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) c[q] = q_rn_clamp(v[i][q] * mul, -128, 127);
-      st_cs_u2(out + k * 8, pack_i8x8(c));
+      st_cs_u2(out + k * 8, quant8_rn_unclamped(v[i], mul));
     }
   }
 }

@@ -624,10 +624,7 @@ __global__ void __launch_bounds__(THREADS) dynamic_int8_quant_vec(int8_t* q, flo
   for (int i = 0; i < NVEC; ++i) {
     const int k = threadIdx.x + i * THREADS;
     if (k < nv) {
-      int c[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(v[i][j] * inv, -128, 127);
-      st_cs_u2(qr + k * 8, pack_i8x8(c));
+      st_cs_u2(qr + k * 8, quant8_rn_unclamped(v[i], inv));
     }
   }
 }
