@@ -6,6 +6,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "tma_pipe.cuh"  // sm_count()
 
 namespace mcop {
 namespace {
@@ -262,7 +263,9 @@ extern "C" int mcop_silu_mul_quant_i8(const void* x, int dtype, const void* row_
   p.x = x; p.rows = rows; p.n = (int)n;
   p.ids = row_ids; p.ids_i64 = ids_are_i64; p.id_lo = id_lo; p.id_hi = id_hi;
   p.out = out; p.out_row_bytes = n; p.scales = scales;
-  const int64_t gx = rows < 0x7fffffffLL ? rows : 0x7fffffffLL;
+  // grid-stride over the rows with at most 16 CTAs per SM: fewer, longer-lived CTAs than one per row
+  const int64_t cap = (int64_t)sm_count() * 16;
+  const int64_t gx = rows < cap ? rows : cap;
   return dispatch_silu_mul(p, dim3((unsigned)gx), dtype, (cudaStream_t)stream, "silu_mul_quant_i8");
 }
 
