@@ -202,6 +202,17 @@ int mcop_moe_gate_grouped_sigmoid_shared(const void* logits, const void* bias, f
                                          int topk_group, int topk, int renormalize, int num_shared_experts,
                                          double routed_scaling, int dtype, mcop_stream_t stream);
 
+/* torch.ops._moe_C.grouped_topk, op/vllm/moe/grouped_topk_kernels.cu:962-1060 (kernels :560-870; schema
+ * op/vllm/moe/torch_bindings.cpp:86-91): score = x (scoring_func 0) or T(0.5 * tanh(0.5 x) + 0.5) (scoring_func 1);
+ * biased = T(score + bias); group score = T(best + second best biased score of the group); keep topk_group groups, then
+ * the top-k experts of the kept groups (ties to the lower index, descending biased score);
+ * value = score * (routed_scaling / (1e-20 + sum of the selected scores)) when renormalize, else score * routed_scaling.
+ * A token whose topk_group-th group score is -inf or not finite gets ids 0..k-1 and values 1/k, as in the reference.
+ * Same shape limits as mcop_moe_gate_grouped_sigmoid; bias dtype = scores dtype or fp32. */
+int mcop_grouped_topk(const void* scores, const void* bias, float* topk_values, int32_t* topk_ids, int64_t tokens,
+                      int experts, int n_group, int topk_group, int topk, int renormalize, double routed_scaling,
+                      int scoring_func, int scores_dtype, int bias_dtype, mcop_stream_t stream);
+
 /* Bytes of scratch mcop_moe_scatter_quant_i8 needs (contents need no initialisation). */
 size_t mcop_moe_scatter_workspace_bytes(int64_t tokens, int topk, int experts_per_rank);
 

@@ -32,6 +32,7 @@ SIGNATURES = {
     "mcop_reshape_and_cache_flash": (I32, [P, P, I64, I64, P, P, I64, I64, I64, P, I64, I32, I32, I32, I32, P]),
     "mcop_rope_kv_store_i8_paged": (I32, [P, P, P, P, P, I32, P, P, P, P, P, I64, I32, I32, I32, I32, I64, I64, I64, I32, I64, I32, I32, P]),
     "mcop_moe_softmax_topk": (I32, [P, P, P, I64, I32, I32, P]),
+    "mcop_grouped_topk": (I32, [P, P, P, P, I64, I32, I32, I32, I32, I32, C.c_double, I32, I32, I32, P]),
     "mcop_topk_softmax": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
     "mcop_moe_gate_grouped_sigmoid": (I32, [P, P, P, P, P, I64, I32, I32, I32, I32, I32, F32, I32, I32, P]),
     "mcop_moe_gate_grouped_sigmoid_shared": (I32, [P, P, P, P, I64, I32, I32, I32, I32, I32, I32, C.c_double, I32, P]),

@@ -134,8 +134,13 @@ struct GateParams {
   // style 0: mcoplib.op.fused_moe_gate_deepseek weights.  style 1: mcoplib.op.fused_moe_gate_opt weights
   // (kernel/fused_moe_gate.cuh:346-420): the last `shared` of the topk slots name the fused shared expert
   // (id = experts) instead of a routed expert; routed weights are not scaled.
+  // style 2: torch.ops._moe_C.grouped_topk (op/vllm/moe/grouped_topk_kernels.cu:560-870): score = x (scoring 0) or
+  // T(0.5 * tanh(0.5 x) + 0.5) (scoring 1); biased = T(score + float(bias)); non-finite logits never win an expert slot,
+  // non-finite group scores count as -inf, and a token whose topk_group-th group score is -inf gets ids 0..k-1 with
+  // weights 1/k; weight = score * (scaling / (1e-20 + fp32 butterfly sum of the selected scores)) when renormalize.
   int style, shared;
   double shared_mul;  // style 1: weight of the shared slot = sum of the routed weights * shared_mul
+  int scoring;        // style 2 only
 };
 
 template <typename T1, typename T2, int V>
@@ -158,13 +163,20 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
 #pragma unroll
     for (int i = 0; i < V; ++i) xin[i] = ElemTraits<T1>::to_float(x[i]);
   }
+  const bool vllm_form = p.style == 2;
 #pragma unroll
   for (int i = 0; i < V; ++i) {
-    score[i] = round_code(1.0f / (1.0f + expf(-xin[i])), p.t1);
-    biased[i] = round_code(score[i] + round_code(ElemTraits<T2>::to_float(b[i]), p.ts), p.ts);
+    if (vllm_form) {
+      score[i] = p.scoring == 0 ? xin[i] : round_code(0.5f * tanhf(0.5f * xin[i]) + 0.5f, p.t1);
+      biased[i] = round_code(score[i] + ElemTraits<T2>::to_float(b[i]), p.t1);
+    } else {
+      score[i] = round_code(1.0f / (1.0f + expf(-xin[i])), p.t1);
+      biased[i] = round_code(score[i] + round_code(ElemTraits<T2>::to_float(b[i]), p.ts), p.ts);
+    }
   }
 
   unsigned sel = 0xffffffffu;
+  bool fallback = false;  // style 2: no valid group choice, uniform default routing
   if (p.groups > 1) {
     const int lpg = (p.experts / p.groups) / V;  // lanes per group, a power of two
     float m1 = -INFINITY, m2 = -INFINITY;
@@ -180,18 +192,21 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
       const float n2 = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
       m1 = n1; m2 = n2;
     }
-    const float gscore = round_code(m1 + m2, p.ts);
+    float gscore = round_code(m1 + m2, p.ts);
+    if (vllm_form && !isfinite(gscore)) gscore = -INFINITY;
     const int gid = lane / lpg;
     sel = 0;
     // One warp-wide integer max (redux.sync) on an order-preserving key finds the best remaining group score; the
     // lowest lane holding it belongs to the lowest group index (lanes are ordered by group).
+    unsigned best = 0;
     for (int r = 0; r < p.topk_group; ++r) {
       const unsigned key = ((sel >> gid) & 1u) ? 0u : ordered_key(gscore);
-      const unsigned best = __reduce_max_sync(0xffffffffu, key);
+      best = __reduce_max_sync(0xffffffffu, key);
       const unsigned who = __ballot_sync(0xffffffffu, key == best);
       const int win = (__ffs(who) - 1) / lpg;
       sel |= 1u << win;
     }
+    fallback = vllm_form && best <= ordered_key(-INFINITY);
     if (!((sel >> gid) & 1u)) {
 #pragma unroll
       for (int i = 0; i < V; ++i) biased[i] = -INFINITY;
@@ -199,6 +214,12 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
     if (p.group_mask && lane == 0) p.group_mask[row] = (int32_t)sel;
   } else if (p.group_mask && lane == 0) {
     p.group_mask[row] = 1;
+  }
+
+  if (vllm_form) {
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+      if (!isfinite(xin[i])) biased[i] = -INFINITY;
   }
 
   float my_w = 0.f;
@@ -223,6 +244,25 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
         if (i == bl) biased[i] = -INFINITY;
     }
     if (lane == kk) { my_w = sc; my_id = bi; }
+  }
+  if (vllm_form) {
+    float w;
+    if (fallback) {
+      my_id = lane;
+      w = 1.0f / (float)p.topk;
+    } else {
+      float sum = lane < p.topk ? my_w : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      float scale = p.scaling;
+      if (p.renormalize) scale /= 1e-20f + sum;
+      w = my_w * scale;
+    }
+    if (lane < p.topk) {
+      p.weights[row * p.topk + lane] = w;
+      p.ids[row * p.topk + lane] = my_id;
+    }
+    return;
   }
   if (p.style == 1) {
     // fp32 sum over a 16-lane xor-butterfly (offsets 8, 4, 2, 1) of the routed scores, one rounding of the sum and
@@ -326,11 +366,11 @@ extern "C" int mcop_topk_softmax(float* topk_weights, int32_t* topk_ids, int32_t
 static int gate_entry(const void* logits, const void* bias, float* topk_weights, int32_t* topk_ids, int32_t* group_mask,
                       int64_t tokens, int experts, int groups, int topk_group, int topk_total, int renormalize,
                       float routed_scaling, int logits_dtype, int bias_dtype, int style, int shared, double shared_mul,
-                      mcop_stream_t stream) {
+                      int scoring, mcop_stream_t stream) {
   MCOP_REQUIRE(logits && bias && topk_weights && topk_ids, MCOP_ERR_ARGUMENT, "moe_gate: null pointer");
   MCOP_REQUIRE(shared >= 0 && shared <= 1 && topk_total - shared >= 1, MCOP_ERR_UNSUPPORTED,
                "moe_gate: %d fused shared experts (0 or 1 supported: the reference draws the ids of more from rand())", shared);
-  MCOP_REQUIRE(style == 0 || topk_total <= 16, MCOP_ERR_UNSUPPORTED, "moe_gate: at most 16 slots in this form");
+  MCOP_REQUIRE(style != 1 || topk_total <= 16, MCOP_ERR_UNSUPPORTED, "moe_gate: at most 16 slots in this form");
   const int topk = topk_total - shared;  // routed experts to select
   MCOP_REQUIRE(tokens >= 0 && experts > 0 && topk >= 1 && topk_total <= 32, MCOP_ERR_ARGUMENT, "moe_gate: bad sizes");
   MCOP_REQUIRE(experts % 32 == 0 && experts <= 512, MCOP_ERR_UNSUPPORTED,
@@ -349,7 +389,7 @@ static int gate_entry(const void* logits, const void* bias, float* topk_weights,
   }
   if (tokens == 0) return MCOP_OK;
   GateParams p{logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk_total,
-               renormalize, routed_scaling, logits_dtype, 0, style, shared, shared_mul};
+               renormalize, routed_scaling, logits_dtype, 0, style, shared, shared_mul, scoring};
   const int s1 = logits_dtype == MCOP_F32 ? 4 : 2, s2 = bias_dtype == MCOP_F32 ? 4 : 2;
   p.ts = s1 >= s2 ? logits_dtype : bias_dtype;
   cudaStream_t s = (cudaStream_t)stream;
@@ -367,7 +407,7 @@ extern "C" int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bia
                                              float routed_scaling, int logits_dtype, int bias_dtype,
                                              mcop_stream_t stream) {
   return gate_entry(logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk, renormalize,
-                    routed_scaling, logits_dtype, bias_dtype, 0, 0, 0.0, stream);
+                    routed_scaling, logits_dtype, bias_dtype, 0, 0, 0.0, 0, stream);
 }
 
 extern "C" int mcop_moe_gate_grouped_sigmoid_shared(const void* logits, const void* bias, float* topk_weights,
@@ -376,5 +416,13 @@ extern "C" int mcop_moe_gate_grouped_sigmoid_shared(const void* logits, const vo
                                                     double routed_scaling, int dtype, mcop_stream_t stream) {
   MCOP_REQUIRE(routed_scaling != 0.0, MCOP_ERR_ARGUMENT, "moe_gate: routed_scaling must not be 0");
   return gate_entry(logits, bias, topk_weights, topk_ids, nullptr, tokens, experts, groups, topk_group, topk, renormalize, 1.0f,
-                    dtype, dtype, 1, num_shared_experts, 1.0 / routed_scaling, stream);
+                    dtype, dtype, 1, num_shared_experts, 1.0 / routed_scaling, 0, stream);
+}
+
+extern "C" int mcop_grouped_topk(const void* scores, const void* bias, float* topk_values, int32_t* topk_ids, int64_t tokens,
+                                 int experts, int n_group, int topk_group, int topk, int renormalize, double routed_scaling,
+                                 int scoring_func, int scores_dtype, int bias_dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(scoring_func == 0 || scoring_func == 1, MCOP_ERR_ARGUMENT, "grouped_topk: scoring_func must be 0 (none) or 1 (sigmoid)");
+  return gate_entry(scores, bias, topk_values, topk_ids, nullptr, tokens, experts, n_group, topk_group, topk, renormalize,
+                    (float)routed_scaling, scores_dtype, bias_dtype, 2, 0, 0.0, scoring_func, stream);
 }

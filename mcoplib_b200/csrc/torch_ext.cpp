@@ -423,6 +423,27 @@ void topk_softmax(Tensor& topk_weights, Tensor& topk_indices, Tensor& token_expe
                              cur_stream()));
 }
 
+// torch.ops._moe_C.grouped_topk (op/vllm/moe/grouped_topk_kernels.cu:962-1060): allocates and returns (values, indices)
+std::tuple<Tensor, Tensor> grouped_topk(const Tensor& scores, int64_t n_group, int64_t topk_group, int64_t topk, bool renormalize,
+                                        double routed_scaling_factor, const Tensor& bias, int64_t scoring_func) {
+  MCOP_DEBUG_CALL("grouped_topk", scores, n_group, topk_group, topk, renormalize, routed_scaling_factor, bias, scoring_func);
+  check_cuda(scores, "scores");
+  TORCH_CHECK(scores.dim() == 2, "scores must be a 2D Tensor");
+  const int64_t tokens = scores.size(0), experts = scores.size(1);
+  TORCH_CHECK(n_group >= 1 && experts % n_group == 0, "num_experts should be divisible by n_group");
+  TORCH_CHECK(n_group <= 32, "n_group should be smaller than or equal to 32 for now");
+  TORCH_CHECK(topk <= 32, "topk should be smaller than or equal to 32 for now");
+  TORCH_CHECK(scoring_func == 0 || scoring_func == 1, "scoring_func must be SCORING_NONE (0) or SCORING_SIGMOID (1)");
+  TORCH_CHECK(scores.is_contiguous() && bias.is_contiguous() && bias.numel() == experts);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(scores));
+  Tensor values = at::empty({tokens, topk}, scores.options().dtype(at::kFloat));
+  Tensor indices = at::empty({tokens, topk}, scores.options().dtype(at::kInt));
+  check_rc(mcop_grouped_topk(scores.data_ptr(), bias.data_ptr(), values.data_ptr<float>(), indices.data_ptr<int32_t>(), tokens, (int)experts,
+                             (int)n_group, (int)topk_group, (int)topk, renormalize ? 1 : 0, routed_scaling_factor, (int)scoring_func,
+                             dtype_code(scores, "scores"), dtype_code(bias, "bias"), cur_stream()));
+  return {values, indices};
+}
+
 // mcoplib.op.fused_moe_gate_deepseek (op/fused_moe_gate_deepseek.cu:63-138)
 int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Tensor& out_routing_weights, Tensor& out_selected_experts,
                             int topk, bool renormalize, int num_expert_group, int topk_group,
@@ -755,6 +776,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("vllm_rotary_embedding", &rotary_embedding_vllm);
   m.def("reshape_and_cache_flash", &reshape_and_cache_flash);
   m.def("topk_softmax", &topk_softmax);
+  m.def("grouped_topk", &grouped_topk, py::arg("scores"), py::arg("n_group"), py::arg("topk_group"), py::arg("topk"),
+        py::arg("renormalize"), py::arg("routed_scaling_factor"), py::arg("bias"), py::arg("scoring_func") = 0);
   m.def("dynamic_scaled_int8_quant", &dynamic_scaled_int8_quant);
 #define MCOP_STR_(x) #x
 #define MCOP_STR(x) MCOP_STR_(x)
@@ -785,6 +808,10 @@ TORCH_LIBRARY(MCOP_TORCH_NS_MOE, moe_ops) {
       "topk_softmax(Tensor! topk_weights, Tensor! topk_indices, Tensor! token_expert_indices, Tensor gating_output, "
       "bool renormalize) -> ()");
   moe_ops.impl("topk_softmax", torch::kCUDA, &topk_softmax);
+  moe_ops.def(
+      "grouped_topk(Tensor scores, int n_group, int topk_group, int topk, bool renormalize, float routed_scaling_factor, "
+      "Tensor bias, int scoring_func) -> (Tensor, Tensor)");
+  moe_ops.impl("grouped_topk", torch::kCUDA, &grouped_topk);
 }
 
 TORCH_LIBRARY(MCOP_TORCH_NS_CACHE, cache_ops) {

@@ -563,6 +563,56 @@ def fused_moe_gate_opt(gating: torch.Tensor, bias: torch.Tensor, topk: int, reno
     return w.float(), ids.to(torch.int32)
 
 
+def grouped_topk(scores: torch.Tensor, n_group: int, topk_group: int, topk: int, renormalize: bool,
+                 routed_scaling_factor: float, bias: torch.Tensor, scoring_func: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """torch.ops._moe_C.grouped_topk, op/vllm/moe/grouped_topk_kernels.cu: scoring :560-583, group scores :585-628,
+    group and expert choice :700-775, weights :783-820.  Pinned (sigmoid scoring, fp32) by biased_grouped_topk of
+    unit_test/test_fused_moe_gate_deepseek.py:15-70, the same routing rule (row-sorted ids exact, weights to 1e-3).
+
+    score = x (scoring_func 0) or T(0.5 * tanh(0.5 * float(x)) + 0.5) (1); biased = T(score + float(bias));
+    group score = T(best + second best biased score), not finite -> -inf; the topk_group best groups (ties to the
+    lower group); the top-k biased scores of the kept groups whose logit is finite (ties to the lower expert id,
+    descending order); value = float(score) * (float(scaling) / (1e-20 + fp32 butterfly sum of the selected
+    scores)) when renormalize, else float(score) * float(scaling).  A token whose topk_group-th group score is -inf
+    gets ids 0..k-1 and values 1/k.  Returns (values fp32 [T,k], ids int32 [T,k])."""
+    n, E = scores.shape
+    T = scores.dtype
+    x = scores.float()
+    score = x if scoring_func == 0 else rt(0.5 * torch.tanh(0.5 * x) + 0.5, T)
+    biased = rt(score + bias.float().unsqueeze(0), T)
+    G = max(int(n_group), 1)
+    fallback = torch.zeros(n, dtype=torch.bool)
+    if G > 1:
+        grp = biased.reshape(n, G, E // G)
+        top2 = torch.sort(grp, dim=-1, descending=True).values[..., :2]
+        gscore = rt(top2[..., 0] + top2[..., 1], T)
+        gscore = torch.where(torch.isfinite(gscore), gscore, torch.full_like(gscore, -float("inf")))
+        gval, gidx = stable_topk(gscore, topk_group)
+        fallback = gval[:, -1] == -float("inf")
+        gmask = torch.zeros(n, G, dtype=torch.bool)
+        gmask.scatter_(1, gidx, True)
+        emask = gmask.unsqueeze(-1).expand(n, G, E // G).reshape(n, E)
+        masked = torch.where(emask, biased, torch.full_like(biased, -float("inf")))
+    else:
+        masked = biased
+    masked = torch.where(torch.isfinite(x), masked, torch.full_like(masked, -float("inf")))
+    _, ids = stable_topk(masked, topk)
+    w = torch.gather(score, 1, ids)
+    scale = torch.full((n,), float(torch.tensor(routed_scaling_factor, dtype=torch.float32)))
+    if renormalize:
+        p = torch.zeros(n, 32)
+        p[:, :topk] = w
+        s = p
+        for o in (16, 8, 4, 2, 1):  # xor butterfly over 32 lanes: lane i adds lane i ^ o
+            s = s + s[:, torch.arange(32) ^ o]
+        scale = scale / (torch.tensor(1e-20, dtype=torch.float32) + s[:, 0])
+    w = w * scale.unsqueeze(-1)
+    if bool(fallback.any()):
+        w[fallback] = 1.0 / topk
+        ids[fallback] = torch.arange(topk)
+    return w.float(), ids.to(torch.int32)
+
+
 def gate_margins(gating: torch.Tensor, bias: torch.Tensor, topk: int, num_expert_group: int,
                  topk_group: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """float64 margins of the grouped gate: (min gap between consecutive group scores around the
