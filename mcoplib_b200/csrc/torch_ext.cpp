@@ -423,6 +423,88 @@ void topk_softmax(Tensor& topk_weights, Tensor& topk_indices, Tensor& token_expe
                              cur_stream()));
 }
 
+// sglang's store_kv_cache (op/sglang/csrc/memory/store.cu:72-150): k_cache[out_loc[i], :] = k[i, :], same for v; rows are
+// the flattened trailing dimensions, a multiple of 128 bytes as in the reference
+void store_kv_cache(Tensor k_cache, Tensor v_cache, Tensor out_loc, Tensor k, Tensor v) {
+  MCOP_DEBUG_CALL("store_kv_cache", k_cache, v_cache, out_loc, k, v);
+  const int64_t max_tokens = k_cache.size(0);
+  const int64_t num_tokens = out_loc.size(0);
+  k_cache = k_cache.view({max_tokens, -1});
+  v_cache = v_cache.view({max_tokens, -1});
+  k = k.view({num_tokens, -1});
+  v = v.view({num_tokens, -1});
+  TORCH_CHECK(k_cache.is_cuda() && v_cache.is_cuda() && out_loc.is_cuda() && k.is_cuda() && v.is_cuda(), "All tensors must be CUDA tensors");
+  TORCH_CHECK(k_cache.sizes() == v_cache.sizes(), "k_cache and v_cache must have the same size");
+  TORCH_CHECK(k_cache.strides() == v_cache.strides(), "k_cache and v_cache must have the same strides");
+  TORCH_CHECK(k.sizes() == v.sizes(), "k and v must have the same size");
+  TORCH_CHECK(k.strides() == v.strides(), "k and v must have the same strides");
+  TORCH_CHECK(k.stride(-1) == 1 && k_cache.stride(-1) == 1, "k and k_cache must be contiguous in head.");
+  TORCH_CHECK(k.size(-1) == k_cache.size(-1), "k and k_cache must have the same head size");
+  TORCH_CHECK(out_loc.dim() == 1 && out_loc.is_contiguous(), "out_loc must be a 1D contiguous tensor");
+  TORCH_CHECK(out_loc.scalar_type() == at::kInt || out_loc.scalar_type() == at::kLong, "out_loc must be of type int32 or int64, got: ",
+              out_loc.scalar_type());
+  TORCH_CHECK(k.scalar_type() == k_cache.scalar_type() && v.scalar_type() == v_cache.scalar_type());
+  const int64_t size_bytes = k.element_size() * k.size(-1);
+  TORCH_CHECK(size_bytes % 128 == 0, "The last dimension size bytes of k and v must be divisible by 128 at least, got: ", size_bytes);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(k));
+  const Tensor loc = out_loc.scalar_type() == at::kLong ? out_loc : out_loc.to(at::kLong);
+  check_rc(mcop_reshape_and_cache_flash(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                                        k_cache.stride(0), 0, 0, loc.data_ptr<int64_t>(), num_tokens, 1, (int)k.size(-1), 1,
+                                        (int)k.element_size(), cur_stream()));
+}
+
+// sglang's apply_rope_pos_ids_cos_sin_cache (op/sglang/csrc/elementwise/rope.cu:28-171): RoPE from an fp32 cos||sin cache at
+// explicit positions, written to q_rope / k_rope (which may be q / k), optionally followed by
+// k_buffer[kv_cache_loc[i]] = k_rope[i], v_buffer[kv_cache_loc[i]] = v[i].  fp32 products and sum, one rounding.
+void apply_rope_pos_ids_cos_sin_cache(Tensor q, Tensor k, Tensor q_rope, Tensor k_rope, Tensor cos_sin_cache, Tensor pos_ids, bool interleave,
+                                      bool enable_pdl, const std::optional<Tensor>& v, const std::optional<Tensor>& k_buffer,
+                                      const std::optional<Tensor>& v_buffer, const std::optional<Tensor>& kv_cache_loc) {
+  MCOP_DEBUG_CALL("apply_rope_pos_ids_cos_sin_cache", q, k, q_rope, k_rope, cos_sin_cache, pos_ids, interleave, enable_pdl, v, k_buffer,
+                  v_buffer, kv_cache_loc);
+  check_cuda(q, "q");
+  const bool save_kv_cache = v.has_value();
+  if (save_kv_cache) {
+    TORCH_CHECK(k_buffer.has_value());
+    TORCH_CHECK(v_buffer.has_value());
+    TORCH_CHECK(kv_cache_loc.has_value());
+    TORCH_CHECK(v->stride(-1) == 1 && k_buffer->stride(-1) == 1 && v_buffer->stride(-1) == 1);
+    TORCH_CHECK(k_buffer->dim() == 3 && v_buffer->dim() == 3 && v->dim() == 3 && kv_cache_loc->dim() == 1);
+    TORCH_CHECK(kv_cache_loc->is_cuda() && kv_cache_loc->is_contiguous() && kv_cache_loc->scalar_type() == at::kLong);
+  } else {
+    TORCH_CHECK(!enable_pdl);
+  }
+  TORCH_CHECK(q.stride(-1) == 1 && k.stride(-1) == 1 && q_rope.stride(-1) == 1 && k_rope.stride(-1) == 1);
+  TORCH_CHECK(cos_sin_cache.is_cuda() && cos_sin_cache.is_contiguous() && pos_ids.is_cuda() && pos_ids.is_contiguous());
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && cos_sin_cache.dim() == 2);
+  TORCH_CHECK(q.size(0) == k.size(0) && q.size(2) == k.size(2));
+  TORCH_CHECK(cos_sin_cache.scalar_type() == at::kFloat && pos_ids.scalar_type() == at::kLong);
+  TORCH_CHECK(q.scalar_type() == at::kHalf || q.scalar_type() == at::kBFloat16, "q must be fp16 or bf16");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && q_rope.scalar_type() == q.scalar_type() && k_rope.scalar_type() == q.scalar_type());
+  TORCH_CHECK(q_rope.sizes() == q.sizes() && k_rope.sizes() == k.sizes());
+  const int64_t nnz = q.size(0);
+  const int heads = (int)q.size(1), kv_heads = (int)k.size(1), head_dim = (int)q.size(2), rot = (int)cos_sin_cache.size(1);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(q));
+  // the rotation kernels work in place: a separate destination first receives a copy (this also carries the
+  // non-rotated tail of every head when rotary_dim < head_dim)
+  if (q_rope.data_ptr() != q.data_ptr()) q_rope.copy_(q);
+  if (k_rope.data_ptr() != k.data_ptr()) k_rope.copy_(k);
+  TORCH_CHECK(q_rope.stride(1) == k_rope.stride(1), "q_rope and k_rope must have one head stride");
+  check_rc(mcop_rope_inplace(pos_ids.data_ptr<int64_t>(), q_rope.data_ptr(), k_rope.data_ptr(), cos_sin_cache.data_ptr(), MCOP_F32, nnz, heads,
+                             kv_heads, head_dim, rot, q_rope.stride(0), k_rope.stride(0), q_rope.stride(1), interleave ? 0 : 1,
+                             dtype_code(q, "apply_rope_pos_ids_cos_sin_cache"), cur_stream()));
+  if (save_kv_cache) {
+    TORCH_CHECK(v->scalar_type() == q.scalar_type() && k_buffer->scalar_type() == q.scalar_type() && v_buffer->scalar_type() == q.scalar_type());
+    TORCH_CHECK(v->size(0) == nnz && v->size(1) == kv_heads && v->size(2) == head_dim && kv_cache_loc->numel() == nnz);
+    TORCH_CHECK(k_rope.stride(1) == head_dim && v->stride(1) == head_dim, "heads of k_rope and v must be contiguous for the buffer save");
+    TORCH_CHECK(k_buffer->strides() == v_buffer->strides() && k_buffer->size(1) == kv_heads && k_buffer->size(2) == head_dim,
+                "k_buffer and v_buffer must share one [*, kv_heads, head_dim] layout");
+    check_rc(mcop_reshape_and_cache_flash(k_rope.data_ptr(), v->data_ptr(), k_rope.stride(0), v->stride(0), k_buffer->data_ptr(),
+                                          v_buffer->data_ptr(), k_buffer->stride(0), 0, k_buffer->stride(1),
+                                          kv_cache_loc->data_ptr<int64_t>(), nnz, kv_heads, head_dim, 1, (int)q.element_size(),
+                                          cur_stream()));
+  }
+}
+
 // torch.ops._moe_C.grouped_topk (op/vllm/moe/grouped_topk_kernels.cu:962-1060): allocates and returns (values, indices)
 std::tuple<Tensor, Tensor> grouped_topk(const Tensor& scores, int64_t n_group, int64_t topk_group, int64_t topk, bool renormalize,
                                         double routed_scaling_factor, const Tensor& bias, int64_t scoring_func) {
@@ -775,6 +857,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fused_add_rms_norm", &fused_add_rms_norm);
   m.def("vllm_rotary_embedding", &rotary_embedding_vllm);
   m.def("reshape_and_cache_flash", &reshape_and_cache_flash);
+  m.def("store_kv_cache", &store_kv_cache);
+  m.def("apply_rope_pos_ids_cos_sin_cache", &apply_rope_pos_ids_cos_sin_cache, py::arg("q"), py::arg("k"), py::arg("q_rope"),
+        py::arg("k_rope"), py::arg("cos_sin_cache"), py::arg("pos_ids"), py::arg("interleave"), py::arg("enable_pdl") = false,
+        py::arg("v") = py::none(), py::arg("k_buffer") = py::none(), py::arg("v_buffer") = py::none(), py::arg("kv_cache_loc") = py::none());
   m.def("topk_softmax", &topk_softmax);
   m.def("grouped_topk", &grouped_topk, py::arg("scores"), py::arg("n_group"), py::arg("topk_group"), py::arg("topk"),
         py::arg("renormalize"), py::arg("routed_scaling_factor"), py::arg("bias"), py::arg("scoring_func") = 0);
