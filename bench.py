@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the per-token hot path (default: benchmark configuration 5, the token-sharded chain).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload chain5|chain4|route3|rope2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload chain5|chain4|route3|rope2|next6]
+                    [--graph]
 
 A step is one pass of the chain over the rank's token shard:
     chain5 : add+RMSNorm+int8 quant -> softmax top-2 of 8 -> scatter with per-row int8 quant -> weighted gather
@@ -403,6 +404,36 @@ def e2e_chain5(ops, tokens_rank, chunk, steps, warmup, device):
     return secs, h2d, d2h
 
 
+_ORIG_AFFINITY = []  # the CPU set of the process before bind_near_gpu narrowed it
+
+
+def bind_near_gpu(local: int):
+    """Runs this process (and therefore the first touch of its pinned host buffers) on the CPUs that share a NUMA node
+    with GPU `local`, as listed by sysfs for the GPU's PCI function.  Only the end-to-end leg depends on it: host
+    memory on the far socket costs PCIe copy bandwidth.  Returns the CPU list used, or None when sysfs has no answer."""
+    try:
+        p = torch.cuda.get_device_properties(local)
+        bdf = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as fh:
+            text = fh.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        orig = os.sched_getaffinity(0)
+        cpus &= orig
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        _ORIG_AFFINITY.append(orig)
+        return text
+    except Exception:  # no sysfs entry, no permission, unknown attribute: run unbound
+        return None
+
+
 def run_ours(args):
     import torch.distributed as dist
     from mcoplib_b200 import op as ops  # raises if the extension is not built: there is no fallback
@@ -414,6 +445,7 @@ def run_ours(args):
         raise RuntimeError("bench.py --impl ours needs a CUDA device (the kernels have no CPU fallback)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa = None if args.no_numa_bind else bind_near_gpu(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     n = max(world, 1)
@@ -516,7 +548,7 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             secs = float(t[0])
         e2e = {"value": tokens_total / secs, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": secs * 1e3,
+               "ms_per_step": secs * 1e3, "host_cpus": numa or "unbound",
                "how": f"host pinned buffers -> H2D -> operators -> D2H of every output, streamed in {min(args.e2e_chunk, tokens_rank)}-token "
                       "chunks on two streams per rank"}
     if world > 1:
@@ -557,6 +589,8 @@ def run_ours(args):
             graph["algorithmic_gb_per_s"] = sum(bpk.values()) / (graph["ms_per_step"] * 1e-3) / 1e9
             line["graph_replay"] = graph
         if n == 1 and args.workload == "chain5" and not args.no_cpu_baseline:
+            if _ORIG_AFFINITY:
+                os.sched_setaffinity(0, _ORIG_AFFINITY[0])  # the CPU baseline uses every host core again
             r = cpu_chain5(args.cpu_sample, reps=args.cpu_reps)
             total = sum(r["seconds"])
             v = r["tokens"] * len(r["seconds"]) / total
@@ -583,6 +617,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens per CPU sample (default 16384 for the cpu_baseline of the GPU arm, 8192 per step of --impl reference)")
     ap.add_argument("--cpu-reps", type=int, default=8, help="passes over the CPU sample for the cpu_baseline of the GPU arm")
+    ap.add_argument("--no-numa-bind", action="store_true", help="do not bind the process to the CPUs local to its GPU")
     ap.add_argument("--graph", action="store_true", help="also time the step as CUDA-graph replays (key graph_replay)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
