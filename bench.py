@@ -583,6 +583,14 @@ def run_ours(args):
             "clocks": clocks,
             "impl": "ours",
         }
+        if args.csv:
+            # performance history in the manner of the reference's benchmark driver (benchmark/README.md:84-103); the report
+            # goes to stderr, stdout stays one JSON line
+            from mcoplib_b200 import perf_csv
+            mode = "generate" if args.generate else ("update" if args.update else "compare")
+            recs = [perf_csv.make_record(torch.cuda.get_device_name(local), f"{args.workload}/{k}", "bf16", f"tokens={tokens_rank}",
+                                         args.steps, v["ms"] * 1e3, v["gb_per_s"], peak) for k, v in kernels.items()]
+            print(perf_csv.format_report(perf_csv.apply(args.csv, recs, mode)), file=sys.stderr, flush=True)
         if e2e is not None:
             line["e2e"] = e2e
         if graph is not None:
@@ -617,6 +625,10 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens per CPU sample (default 16384 for the cpu_baseline of the GPU arm, 8192 per step of --impl reference)")
     ap.add_argument("--cpu-reps", type=int, default=8, help="passes over the CPU sample for the cpu_baseline of the GPU arm")
+    ap.add_argument("--csv", default="", help="performance history file; with --generate, --update or --compare (default)")
+    ap.add_argument("--generate", action="store_true", help="add records that the history does not hold yet")
+    ap.add_argument("--update", action="store_true", help="replace stored records that the run beats by more than 5 %%")
+    ap.add_argument("--compare", action="store_true", help="report the run against the stored records")
     ap.add_argument("--no-numa-bind", action="store_true", help="do not bind the process to the CPUs local to its GPU")
     ap.add_argument("--graph", action="store_true", help="also time the step as CUDA-graph replays (key graph_replay)")
     ap.add_argument("--no-e2e", action="store_true")
