@@ -460,12 +460,13 @@ def run_ours(args):
         tokens_rank = tokens_global // n
         t0 = rank * tokens_rank
         tokens_total = tokens_rank * n
-    wl = cls(tokens_rank, t0=t0, device=device, gen_device=device)
+    kw = {"hidden": args.hidden} if (args.hidden and args.workload == "chain5") else {}
+    wl = cls(tokens_rank, t0=t0, device=device, gen_device=device, **kw)
     # a workload whose traffic per step is below twice the L2 size would be served from L2 when repeated: rotate
     # through enough identical buffer sets that a set has left L2 before its turn comes again
     footprint = sum(wl.bytes_per_kernel().values())
     nsets = 1 if footprint >= 2 * L2_BYTES else int(min(8, -(-2 * L2_BYTES // footprint)))
-    sets = [wl] + [cls(tokens_rank, t0=t0, device=device, gen_device=device) for _ in range(nsets - 1)]
+    sets = [wl] + [cls(tokens_rank, t0=t0, device=device, gen_device=device, **kw) for _ in range(nsets - 1)]
     stage_sets = [w.stages(ops) for w in sets]
     nst = len(stage_sets[0])
     turn = [0]
@@ -571,7 +572,7 @@ def run_ours(args):
             "metric": METRIC, "value": tokens_total / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl.name, "tokens_global": tokens_total, "tokens_per_gpu": tokens_rank,
+            "config": {"workload": wl.name, "hidden": getattr(wl, "H", None), "tokens_global": tokens_total, "tokens_per_gpu": tokens_rank,
                        "parallelism": f"token-sharded x{n}, no collective on the data path",
                        "l2": ("per-step traffic (%.2f GB) exceeds twice the 126 MB L2; no explicit flush" % (footprint / 1e9)) if nsets == 1
                        else ("per-step traffic %.0f MB: steps rotate through %d identical buffer sets so that no step finds its data in L2"
@@ -625,6 +626,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens per CPU sample (default 16384 for the cpu_baseline of the GPU arm, 8192 per step of --impl reference)")
     ap.add_argument("--cpu-reps", type=int, default=8, help="passes over the CPU sample for the cpu_baseline of the GPU arm")
+    ap.add_argument("--hidden", type=int, default=0, help="chain5 only: another row length than 7168 (per-kernel study)")
     ap.add_argument("--csv", default="", help="performance history file; with --generate, --update or --compare (default)")
     ap.add_argument("--generate", action="store_true", help="add records that the history does not hold yet")
     ap.add_argument("--update", action="store_true", help="replace stored records that the run beats by more than 5 %%")

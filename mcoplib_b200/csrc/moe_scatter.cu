@@ -188,9 +188,12 @@ __device__ __forceinline__ void row_scale_from_amax(float amax, float& scale_out
 }
 
 
+// resident CTAs per SM the quant kernel is built for: 3 CTAs of 7-8 warps, 4 of 5-6 warps, 5 of 4 warps, 1 of 16
+constexpr int scatter_ctas_per_sm(int threads) { return threads > 256 ? 1 : (threads >= 192 ? 3 : (threads >= 160 ? 4 : 5)); }
+
 // Persistent pipelined quant kernel.  Dynamic shared memory: 128 bytes of mbarriers, then `stages` row buffers.
 template <int THREADS, int NVEC, bool FULL>  // FULL: the row is exactly THREADS * NVEC vectors of 8, no lane is ever idle
-__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : 1)) scatter_quant_pipe(ScatterQuantParams p, int stages, int* err) {
+__global__ void __launch_bounds__(THREADS, scatter_ctas_per_sm(THREADS)) scatter_quant_pipe(ScatterQuantParams p, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float red[2][33];
   __shared__ int32_t s_tok[kBatchRows];
@@ -414,9 +417,9 @@ __global__ void __launch_bounds__(256) scatter_quant_any(ScatterQuantParams p) {
 template <int THREADS>
 int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   const size_t row_bytes = (size_t)p.hidden_size * 2;
-  // three CTAs per SM when the rows are narrow enough (the kernel is compiled for <= 80 registers at 256 threads):
-  // each gets a third of the shared memory for its ring of row buffers
-  const int want_per_sm = THREADS <= 256 ? 3 : 1;
+  // about 21-24 warps per SM (the kernel is compiled for <= 80 registers): three CTAs of 7-8 warps, more of the
+  // smaller ones; each CTA gets its share of the shared memory for its ring of row buffers
+  const int want_per_sm = scatter_ctas_per_sm(THREADS);
   int stages = (int)(((227 * 1024) / want_per_sm - 3 * 1024) / row_bytes);
   stages = stages < 2 ? 2 : (stages > 6 ? 6 : stages);
   const size_t smem = 128 + (size_t)stages * row_bytes;
@@ -518,7 +521,14 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
     scatter_fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p);
     rc = check_launch("moe_scatter_quant_i8 (fill)");
     if (rc) return rc;
-    // 7 warps when they tile the row exactly (hidden 7168 = 4 x 224 vectors of 8): no idle lanes in the last pass
+    // a CTA of nv / 4 threads tiles the row exactly (hidden 4096, 5120, 6144, 7168, 8192 = 4 x 128 ... 256 vectors of 8):
+    // no idle lanes and no bounds tests in the passes, worth 25 % at hidden 7168
+    switch (nv) {
+      case 512: return launch_quant_pipe<128>(p, s);
+      case 640: return launch_quant_pipe<160>(p, s);
+      case 768: return launch_quant_pipe<192>(p, s);
+      case 896: return launch_quant_pipe<224>(p, s);
+    }
     if (nv <= 896 && nv % 224 == 0) return launch_quant_pipe<224>(p, s);
     if (nv <= 1024) return launch_quant_pipe<256>(p, s);
     return launch_quant_pipe<512>(p, s);

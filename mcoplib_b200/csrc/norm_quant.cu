@@ -433,8 +433,9 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   stages = stages < 2 ? 2 : (stages > 4 ? 4 : stages);
   const size_t smem = 128 + (size_t)stages * stage_bytes;
   if (smem > 220 * 1024) return 1;
-  // 7 warps when they tile the row exactly (hidden 7168 = 4 x 224 vectors of 8), else 8 or 16
-  const int threads = (nv <= 896 && nv % 224 == 0) ? 224 : (nv <= 1024 ? 256 : 512);
+  // 4 to 7 warps when they tile the row exactly (hidden 4096 ... 7168 = 4 x 128 ... 224 vectors of 8), else 8 or 16
+  const bool tiles = nv == 512 || nv == 640 || nv == 768 || nv == 896;
+  const int threads = tiles ? nv / 4 : ((nv <= 896 && nv % 224 == 0) ? 224 : (nv <= 1024 ? 256 : 512));
   const bool full = nv == threads * 4;
   int per_sm = (int)((227 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : per_sm;
@@ -443,7 +444,7 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > tokens) grid = tokens;
   int* err = pipe_error_ptr();
-  static std::atomic<int> attr_done[8];
+  static std::atomic<int> attr_done[14];
   const bool no = p.out != nullptr;  // also write the normalised row
   auto launch = [&](auto kernel, int slot) -> int {
     if (attr_done[slot].load(std::memory_order_relaxed) < (int)smem) {
@@ -454,6 +455,13 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
     kernel<<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, err);
     return check_launch("norm (pipelined)");
   };
+#define MCOP_NORM_TILED(T, SLOT)                                                                        \
+  if (threads == T && full && T != 224)                                                                 \
+    return no ? launch(norm_quant_bf16_pipe<T, 4, true, false, true>, SLOT) : launch(norm_quant_bf16_pipe<T, 4, true, false, false>, SLOT + 1);
+  MCOP_NORM_TILED(128, 8)
+  MCOP_NORM_TILED(160, 10)
+  MCOP_NORM_TILED(192, 12)
+#undef MCOP_NORM_TILED
   if (threads == 224) {
     if (full) return no ? launch(norm_quant_bf16_pipe<224, 4, true, false, true>, 0) : launch(norm_quant_bf16_pipe<224, 4, true, false, false>, 1);
     return no ? launch(norm_quant_bf16_pipe<224, 4, false, false, true>, 2) : launch(norm_quant_bf16_pipe<224, 4, false, false, false>, 3);

@@ -40,7 +40,7 @@ def _run_a2(op, x, w, res, scale_ub=None):
 # shapes of the reference test (unit_test/test_fused_rms_norm_dq.py:17-22, token counts trimmed) + the benchmark shapes
 SHAPES = [(1, 1), (1, 64), (1, 1024), (1, 1025), (1, 1026), (1, 1027), (1, 1028), (1, 1029), (1, 5120), (1, 5137),
           (83, 1), (83, 1033), (83, 2048), (83, 5120), (300, 64), (129, 5137), (256, 4096), (64, 7168), (48, 8192),
-          (3, 16384), (2, 32768), (2, 40000)]
+          (3, 16384), (2, 32768), (2, 40000), (40, 6144), (700, 4096), (333, 5120)]
 
 
 @pytest.mark.parametrize("T,H", SHAPES)
