@@ -3,6 +3,7 @@
 #include <stdio.h>
 
 #include <atomic>
+#include <mutex>
 
 #include "common.cuh"
 #include "tma_pipe.cuh"
@@ -54,6 +55,35 @@ int sm_count() {
   }
   g_sm_count[dev].store(n, std::memory_order_relaxed);
   return n;
+}
+
+// The dynamic shared memory a kernel may use above 48 KB is a property of the kernel ON ONE DEVICE, so the sizes
+// already granted are remembered per (device, kernel); a process that drives several GPUs sets it on each.
+// (A fixed table, no heap: the library's entry points never allocate.  When the table is full the attribute is simply
+// set again on every call, which is correct, only slower.)
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  struct Granted { int dev; const void* kernel; size_t bytes; };
+  constexpr int kSlots = 1024;
+  static std::mutex mu;
+  static Granted table[kSlots];
+  static int used = 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  Granted* slot = nullptr;
+  for (int i = 0; i < used; ++i)
+    if (table[i].dev == dev && table[i].kernel == kernel) { slot = &table[i]; break; }
+  if (slot && slot->bytes >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) return e;
+  if (!slot && used < kSlots) {
+    slot = &table[used++];
+    slot->dev = dev;
+    slot->kernel = kernel;
+  }
+  if (slot) slot->bytes = bytes;
+  return cudaSuccess;
 }
 
 int check_launch(const char* what) {

@@ -349,12 +349,8 @@ int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t strea
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > (tokens + 7) / 8) grid = (tokens + 7) / 8;
   const int chunk = kChunkTokens;
-  static std::atomic<int> attr_done{0};
-  if (!attr_done.load(std::memory_order_relaxed)) {
-    cudaError_t e = cudaFuncSetAttribute(gather_pipe<THREADS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_gather: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_done.store(1, std::memory_order_relaxed);
-  }
+  const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&gather_pipe<THREADS, 4>), 200 * 1024);
+  MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_gather: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   gather_pipe<THREADS, 4><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, chunk, pipe_error_ptr());
   return check_launch("moe_gather (pipelined)");
 }

@@ -443,15 +443,11 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   const int64_t nitems = ((ntiles + supertile - 1) / supertile) * p.E * parts;
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > nitems) grid = nitems;
-  static std::atomic<int> attr_done{0};
-  if (!attr_done.load(std::memory_order_relaxed)) {
-    cudaError_t e = cudaFuncSetAttribute(scatter_quant_pipe<THREADS, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(scatter_quant_pipe<THREADS, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_done.store(1, std::memory_order_relaxed);
-  }
-  if ((p.hidden_size >> 3) == THREADS * 4)
+  const bool full = (p.hidden_size >> 3) == THREADS * 4;
+  const cudaError_t e = ensure_dynamic_smem(full ? reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, true>)
+                                                 : reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, false>), 200 * 1024);
+  MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  if (full)
     scatter_quant_pipe<THREADS, 4, true><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
   else
     scatter_quant_pipe<THREADS, 4, false><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
@@ -502,7 +498,7 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
   MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: memset: %s", cudaGetErrorString(e));
   const size_t smem = (size_t)E * kTileWords * (sizeof(uint32_t) + sizeof(uint16_t));
   if (smem > 48 * 1024) {
-    e = cudaFuncSetAttribute(scatter_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(&scatter_rank_kernel), smem);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   }
   scatter_rank_kernel<<<(unsigned)tiles, 256, smem, s>>>(ids, ws, counts, starts, tokens, topk, E);

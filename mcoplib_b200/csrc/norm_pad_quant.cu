@@ -16,6 +16,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "tma_pipe.cuh"  // ensure_dynamic_smem()
 
 namespace mcop {
 namespace {
@@ -166,7 +167,7 @@ int launch_pad_quant(const PadQuantParams& p, int64_t tokens, cudaStream_t s) {
     const size_t smem = (size_t)H * sizeof(float);
     MCOP_REQUIRE(smem <= 200 * 1024, MCOP_ERR_UNSUPPORTED, "add_rmsnorm_quant_i8_padded: hidden %d too large for the unaligned path", H);
     if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(pad_quant_any<T, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&pad_quant_any<T, FORM>), smem);
       MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "add_rmsnorm_quant_i8_padded: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     }
     pad_quant_any<T, FORM><<<grid, 256, smem, s>>>(p);

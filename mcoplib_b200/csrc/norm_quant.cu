@@ -444,14 +444,10 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > tokens) grid = tokens;
   int* err = pipe_error_ptr();
-  static std::atomic<int> attr_done[14];
   const bool no = p.out != nullptr;  // also write the normalised row
-  auto launch = [&](auto kernel, int slot) -> int {
-    if (attr_done[slot].load(std::memory_order_relaxed) < (int)smem) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-      MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "norm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-      attr_done[slot].store(220 * 1024, std::memory_order_relaxed);
-    }
+  auto launch = [&](auto kernel, int) -> int {
+    const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 220 * 1024);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "norm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     kernel<<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, err);
     return check_launch("norm (pipelined)");
   };
@@ -492,7 +488,7 @@ int launch_norm(const NormParams& p, int64_t tokens, bool vec_ok, cudaStream_t s
     const size_t smem = (size_t)p.hidden * sizeof(float);
     MCOP_REQUIRE(smem <= 200 * 1024, MCOP_ERR_UNSUPPORTED, "norm: hidden %d too large for the unaligned path", p.hidden);
     if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(norm_rows_any<T, WT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&norm_rows_any<T, WT, MODE>), smem);
       MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "norm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     }
     norm_rows_any<T, WT, MODE><<<grid, 256, smem, stream>>>(p);

@@ -190,11 +190,9 @@ int launch_rope_pipe(const RopeParams& p, int64_t tokens, cudaStream_t stream) {
   int threads = hpi * hv;
   if (threads < 64) threads = 64 / hv * hv;  // chunk staging needs >= 64 threads
   if (threads > 256 || threads % hv != 0) return 1;
-  static std::atomic<int> attr_done{0};
-  if (!attr_done.load(std::memory_order_relaxed)) {
-    cudaError_t e = cudaFuncSetAttribute(rope_neox_pipe<T, CT, PER_OP, STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  {
+    const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&rope_neox_pipe<T, CT, PER_OP, STORE>), 200 * 1024);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "rope: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_done.store(1, std::memory_order_relaxed);
   }
   // CTAs per SM: try four, then fewer; each gets its share of shared memory for the ring (at least two stages).
   // The runtime is asked how many CTAs really fit: a grid larger than what is resident would run in uneven waves.

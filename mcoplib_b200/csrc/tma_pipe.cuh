@@ -82,4 +82,8 @@ __device__ __forceinline__ uint4 lds_u4(const void* p) {
 // Number of SMs of the current device (cached per device; no allocation, no synchronisation).
 int sm_count();
 
+// Makes sure `kernel` may use `bytes` of dynamic shared memory on the CURRENT device (the attribute is per device;
+// what has been granted is remembered per device and kernel).  Thread-safe.
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 }  // namespace mcop
