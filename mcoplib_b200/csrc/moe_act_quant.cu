@@ -8,6 +8,13 @@
 #include "common.cuh"
 #include "tma_pipe.cuh"  // sm_count()
 
+// Sigmoid as the reference kernels compute it, with the fast exponential and the approximate reciprocal
+// (op/int8_quant_kernels.cu:1385: val0 * __builtin_mxc_rcpf(1.0f + __builtin_expf(-val0))).  Measured against the IEEE
+// expf + division form on 16.8 M elements: codes differ from the CPU restatement on 4.2e-7 of the elements instead of
+// 2.4e-7 (tolerance 1e-4), scales to 2.2e-7 either way; the kernels run 20-37 % faster (they are bound by instruction
+// issue: exponential, reciprocal and about two dozen other instructions per element).
+#define MCOP_SIGMOID(g) __fdividef(1.0f, 1.0f + __expf(-(g)))
+
 namespace mcop {
 namespace {
 
@@ -32,7 +39,7 @@ __device__ __forceinline__ int expert_of_row(const SwigluParams& p, int64_t r) {
 }
 
 __device__ __forceinline__ float swiglu_value(float gate, float up, float sm) {
-  const float sig = gate * (1.0f / (1.0f + expf(-gate)));
+  const float sig = gate * MCOP_SIGMOID(gate);
   return up * sig * sm;
 }
 
@@ -146,7 +153,7 @@ __device__ __forceinline__ int64_t load_index(const void* p, int is_i64, int64_t
 }
 
 __device__ __forceinline__ float silu_mul_value(float gate, float up) {
-  return up * (gate * (1.0f / (1.0f + expf(-gate))));
+  return up * (gate * MCOP_SIGMOID(gate));
 }
 
 __device__ __forceinline__ void silu_mul_store_scale(const SiluMulParams& p, int64_t row, float amax) {
