@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
       } else {
         for (int j = 0; j < n; ++j) {
           const int s = cons.s;
-          const bool ok = mbar_wait_bounded(&full[s], cons.phase, err, 3);
+          const bool ok = mbar_wait_bounded_sleepy(&full[s], cons.phase, err, 3);
           if (ok) {
             const unsigned char* src = buf + (size_t)s * row_bytes;
             const float w = p.weighted ? s_w[tl][j] : 1.f;

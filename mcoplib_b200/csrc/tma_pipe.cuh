@@ -63,6 +63,29 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// The same with a suspend-time hint: a thread whose phase is not complete yet may stay suspended in hardware for up to
+// kPipeSleepNs before the instruction returns, instead of coming back at once and polling again.  For kernels whose
+// warps mostly wait for data (the gather) this leaves the issue slots to the warps that have work: measured +3 % there,
+// -1 % in the norm and scatter kernels, whose waits are short - so only the gather uses it.  Bounded like the plain
+// form: kPipeSleepLimit tries of at most kPipeSleepNs each (about 1.3 s).
+constexpr uint32_t kPipeSleepNs = 20000u;
+constexpr uint32_t kPipeSleepLimit = 1u << 16;
+__device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint64_t* bar, uint32_t parity, int* err, int code) {
+  for (uint32_t i = 0; i < kPipeSleepLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(kPipeSleepNs)
+        : "memory");
+    if (ok) return true;
+  }
+  if (err) atomicCAS(err, 0, code);
+  return false;
+}
+
 // Position in a ring of `stages` buffers: stage index and phase parity of its mbarrier, advanced without the
 // integer division a running counter would need on every row.
 struct RingPos {
