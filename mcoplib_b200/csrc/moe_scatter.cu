@@ -445,8 +445,9 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > nitems) grid = nitems;
   const bool full = (p.hidden_size >> 3) == THREADS * 4;
-  const cudaError_t e = ensure_dynamic_smem(full ? reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, true>)
-                                                 : reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, false>), 200 * 1024);
+  const void* fn = full ? reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, true>)
+                        : reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, false>);
+  const cudaError_t e = ensure_dynamic_smem(fn, 200 * 1024);
   MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   if (full)
     scatter_quant_pipe<THREADS, 4, true><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
