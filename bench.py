@@ -238,10 +238,13 @@ class Rope2:
 
 class Next6:
     """The operators either side of the path (alternate output formats of part 1, the activation-quant steps after the
-    expert up-projection, vLLM's softmax router), each timed on its own: hidden 7168, expert intermediate size 2048."""
-    name = "next rows: padded-record norm+quant, norm+quant with norm output, per-token int8 quant, swiglu+quant, silu_mul+quant, topk_softmax"
-    kernels = ["norm_quant_padded", "norm_quant_norm_out", "dynamic_int8_quant", "swiglu_quant", "silu_mul_quant", "topk_softmax"]
-    launches_per_step = 6
+    expert up-projection, vLLM's softmax router, its token-major combine and its block-aligned index preparation), each
+    timed on its own: hidden 7168, expert intermediate size 2048."""
+    name = ("next rows: padded-record norm+quant, norm+quant with norm output, per-token int8 quant, swiglu+quant, "
+            "silu_mul+quant, topk_softmax, moe_sum, moe_align_block_size")
+    kernels = ["norm_quant_padded", "norm_quant_norm_out", "dynamic_int8_quant", "swiglu_quant", "silu_mul_quant", "topk_softmax",
+               "moe_sum", "moe_align_block_size"]
+    launches_per_step = 9   # one kernel each, two for moe_align_block_size
 
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W
@@ -270,6 +273,16 @@ class Next6:
         self.ti = torch.empty(tokens, 2, dtype=torch.int32, **o)
         self.tsrc = torch.empty(tokens, 2, dtype=torch.int32, **o)
         self.none = torch.empty(0)
+        # token-major expert outputs [T, 2, H] (the same bytes as the gather input of configuration 5) and their sum
+        self.y3 = W.per_token("randn", 81, 2 * t0, 2 * t0 + R, 7168, torch.bfloat16, 1, gen_device, device).view(tokens, 2, 7168)
+        self.ysum = torch.empty(tokens, 7168, dtype=torch.bfloat16, **o)
+        # block-aligned index preparation of a DeepSeek-V3-shaped routing: top-8 of 256, blocks of 64
+        g = torch.Generator(device="cpu").manual_seed(5)
+        self.align_ids = torch.rand(tokens, 256, generator=g).topk(8, dim=-1).indices.to(torch.int32).to(device)
+        cap = tokens * 8 + 256 * 64
+        self.sorted_ids = torch.empty(cap, dtype=torch.int32, **o)
+        self.block_experts = torch.empty(cap // 64, dtype=torch.int32, **o)
+        self.post_pad = torch.empty(1, dtype=torch.int32, **o)
 
     def bytes_per_kernel(self):
         T, H, R, I = self.T, self.H, self.R, self.I
@@ -279,7 +292,10 @@ class Next6:
                 "dynamic_int8_quant": T * H * (2 + 1) + 4 * T,
                 "swiglu_quant": R * I * (4 + 1) + 4 * R + self.E * I * 4,
                 "silu_mul_quant": R * I * (4 + 1) + 4 * R + 8 * R,
-                "topk_softmax": self.W.gate_bytes(T, 8, 2) - 8 * 4 + 8 * T}
+                "topk_softmax": self.W.gate_bytes(T, 8, 2) - 8 * 4 + 8 * T,
+                "moe_sum": T * H * 2 * (2 + 1),
+                # ids read, sorted positions and block experts written (the byte count of the reference's own runner)
+                "moe_align_block_size": T * 8 * 4 + self.sorted_ids.numel() * 4 + self.block_experts.numel() * 4 + 4}
 
     def stages(self, ops):
         return [
@@ -290,6 +306,8 @@ class Next6:
             lambda: ops.moe_swiglu_dynamic_quantize(self.gu, self.smooth, self.starts, self.counts, self.act, self.act_scale, self.E),
             lambda: ops.fused_silu_mul_dq_reorder_quant(self.act, self.act_scale, self.gu, self.row_ids, self.none, 0, self.E - 1),
             lambda: ops.topk_softmax(self.tw, self.ti, self.tsrc, self.logits, True),
+            lambda: ops.moe_sum(self.y3, self.ysum),
+            lambda: ops.moe_align_block_size(self.align_ids, 256, 64, self.sorted_ids, self.block_experts, self.post_pad, None),
         ]
 
 

@@ -125,6 +125,12 @@ int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, con
 int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
                         int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
 
+/* mcoplib.op.fused_rope_bwd, op/fused_rope.cu:77-138 (kernel/fused_rope_kernel.h:101-191).
+ * The transposed rotation (gradient of fused_rope_fwd), same layout and arguments:
+ * x' = x*c + y*s, y' = y*c - x*s in fp32, one rounding. */
+int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
+                        int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
+
 /* mcoplib.op.store_kv_cache_cuda_interface, op/store_kv.cu:220-350 (include/store_kv.h:2-15).
  * code = clamp(rne(x * scale[h, d]), -127, 127) for the K and V heads of packed_qkv
  * (strides qkv_stride_token / qkv_stride_head, elements) written to cache[slot_ids[b], h, cache_lens[b] + i, :]
@@ -320,6 +326,31 @@ int mcop_silu_mul_quant_i8_masked_pack(const void* x, int dtype, const void* gro
  * overlap on the GPU (different streams, no ordering between them) race on it - serialise them. */
 int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, void* out, int64_t tokens, int64_t rows,
                             int64_t hidden_size, mcop_stream_t stream);
+
+/* torch.ops._moe_C.moe_sum, op/vllm/moe/moe_align_sum_kernels.cu:352-367,770-815 (schema op/vllm/moe/torch_bindings.cpp:13):
+ * output[t, :] = sum_k input[t, k, :], input [tokens, topk, hidden] contiguous, output [tokens, hidden], bf16 / f16 / f32.
+ * topk 2, 3, 4: the running sum is kept in the element type (slots in order, every partial sum rounded), as the
+ * reference's kernels do; any other topk: fp32 accumulation in slot order, one rounding (the reference calls the
+ * framework's reduction there). */
+int mcop_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size, int dtype,
+                 mcop_stream_t stream);
+
+/* torch.ops._moe_C.moe_align_block_size, op/vllm/moe/moe_align_sum_kernels.cu:86-180,612-735
+ * (schema op/vllm/moe/torch_bindings.cpp:18-24).  Index preparation of a block-sparse expert GEMM:
+ *   sorted_token_ids [max_num_tokens_padded]: for every expert e in ascending order, the flat indices i = t*topk + j
+ *     of the routing entries with (mapped) expert e, then the mark `numel` up to a multiple of block_size; every
+ *     position after the last expert's range also holds `numel`;
+ *   expert_ids [max_num_blocks]: the expert of every block of block_size positions; blocks after the padded total: 0;
+ *   num_tokens_post_pad [1]: the padded total.
+ * Entries with id outside [0, num_experts) are dropped; with expert_map (int32 [num_experts], NULL = identity) the id
+ * is mapped first and entries mapped to -1 are dropped.  Inside an expert's range the reference's order depends on
+ * its atomics; here it is ascending flat index (one of the orders the reference can produce; its own check sorts the
+ * ranges before comparing).  num_experts < 1024.  Scratch: mcop_moe_align_block_size_workspace_bytes(). */
+size_t mcop_moe_align_block_size_workspace_bytes(int64_t numel, int num_experts);
+int mcop_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block_size,
+                              int32_t* sorted_token_ids, int64_t max_num_tokens_padded, int32_t* expert_ids,
+                              int64_t max_num_blocks, int32_t* num_tokens_post_pad, const int32_t* expert_map,
+                              void* workspace, size_t workspace_bytes, mcop_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -28,6 +28,7 @@ SIGNATURES = {
     "mcop_rope_inplace": (I32, [P, P, P, P, I32, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
     "mcop_rope_packed": (I32, [P, P, P, P, P, P, I32, I64, I32, I32, I32, I32, P]),
     "mcop_fused_rope_fwd": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
+    "mcop_fused_rope_bwd": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
     "mcop_kv_store_i8": (I32, [P, I64, I64, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, P, P, I32, I64, I32, I32, I32, I32, P]),
     "mcop_reshape_and_cache_flash": (I32, [P, P, I64, I64, P, P, I64, I64, I64, P, I64, I32, I32, I32, I32, P]),
     "mcop_rope_kv_store_i8_paged": (I32, [P, P, P, P, P, I32, P, P, P, P, P, I64, I32, I32, I32, I32, I64, I64, I64, I32, I64, I32, I32, P]),
@@ -39,6 +40,9 @@ SIGNATURES = {
     "mcop_moe_scatter_workspace_bytes": (SZ, [I64, I32, I32]),
     "mcop_moe_scatter_quant_i8": (I32, [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, P, SZ, P]),
     "mcop_moe_gather_workspace_bytes": (SZ, [I64, I64]),
+    "mcop_moe_sum": (I32, [P, P, I64, I32, I64, I32, P]),
+    "mcop_moe_align_block_size_workspace_bytes": (SZ, [I64, I32]),
+    "mcop_moe_align_block_size": (I32, [P, I64, I32, I32, P, I64, P, I64, P, P, P, SZ, P]),
     "mcop_moe_gather": (I32, [P, P, P, P, I32, I64, I64, I64, P, SZ, P]),
     "mcop_moe_gather_weighted": (I32, [P, P, P, P, P, P, P, I32, I64, I64, I64, I32, I32, P, SZ, P]),
     "mcop_moe_swiglu_quant_i8": (I32, [P, P, P, P, P, P, I64, I64, I32, P]),

@@ -487,3 +487,95 @@ extern "C" int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, vo
   // whatever the previous call left in the array is harmless.
   return launch_gather(p, tokens, scratch, MCOP_GATHER_NOALLOC_SCRATCH_BYTES, (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// moe_sum: out[t, :] = sum over the k expert outputs in[t, 0..k-1, :] - the combine step of engines that keep the
+// expert outputs token-major ([T, k, H]) instead of scattering them by expert.
+// K = 2, 3, 4: running sum kept in T (every partial sum rounded to T, slots in order), as the reference's
+// dedicated kernels do; any other k (K = 0): fp32 accumulation in slot order and one rounding, the contract of the
+// library reduction the reference falls back to.
+// ---------------------------------------------------------------------------------------------
+namespace mcop {
+namespace {
+template <typename T, int K>
+__global__ void __launch_bounds__(256) moe_sum_vec(const T* __restrict__ in, T* __restrict__ out, int64_t tokens, int topk, int hidden) {
+  const int nv = hidden >> 3;
+  const int64_t total = tokens * nv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / nv;
+    const int v = (int)(i - t * nv);
+    const T* src = in + (t * topk) * (int64_t)hidden + v * 8;
+    float acc[8];
+    if constexpr (K > 0) {
+      float x[K][8];
+#pragma unroll
+      for (int k = 0; k < K; ++k) Vec8<T>::load_nc(src + (int64_t)k * hidden, x[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = x[0][j];
+#pragma unroll
+      for (int k = 1; k < K; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = round_to<T>(__fadd_rn(acc[j], x[k][j]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 4
+      for (int k = 0; k < topk; ++k) {
+        float x[8];
+        Vec8<T>::load_nc(src + (int64_t)k * hidden, x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], x[j]);
+      }
+    }
+    Vec8<T>::store(out + t * (int64_t)hidden + v * 8, acc);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_sum_any(const T* __restrict__ in, T* __restrict__ out, int64_t tokens, int topk, int hidden) {
+  const int64_t total = tokens * hidden;
+  const bool per_add = topk >= 2 && topk <= 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / hidden;
+    const int c = (int)(i - t * hidden);
+    const T* src = in + (t * topk) * (int64_t)hidden + c;
+    float acc = per_add ? ElemTraits<T>::to_float(src[0]) : 0.f;
+    for (int k = per_add ? 1 : 0; k < topk; ++k) {
+      acc = __fadd_rn(acc, ElemTraits<T>::to_float(src[(int64_t)k * hidden]));
+      if (per_add) acc = round_to<T>(acc);
+    }
+    out[i] = ElemTraits<T>::from_float(acc);
+  }
+}
+
+template <typename T>
+int launch_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden, cudaStream_t stream) {
+  const T* in = reinterpret_cast<const T*>(input);
+  T* out = reinterpret_cast<T*>(output);
+  const bool vec_ok = hidden % 8 == 0 && aligned16(input) && aligned16(output);
+  const int64_t work = vec_ok ? tokens * (hidden >> 3) : tokens * hidden;
+  int64_t grid = (work + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;  // grid-stride beyond a few waves of resident CTAs
+  if (grid > cap) grid = cap;
+  const int H = (int)hidden;
+  if (!vec_ok) moe_sum_any<T><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
+  else if (topk == 2) moe_sum_vec<T, 2><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
+  else if (topk == 3) moe_sum_vec<T, 3><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
+  else if (topk == 4) moe_sum_vec<T, 4><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
+  else moe_sum_vec<T, 0><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
+  return check_launch("moe_sum");
+}
+}  // namespace
+}  // namespace mcop
+
+extern "C" int mcop_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size, int dtype,
+                            mcop_stream_t stream) {
+  MCOP_REQUIRE(input && output, MCOP_ERR_ARGUMENT, "moe_sum: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && topk >= 1 && hidden_size > 0 && hidden_size <= 0x7fffffff, MCOP_ERR_ARGUMENT, "moe_sum: bad sizes");
+  if (tokens == 0) return MCOP_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == MCOP_BF16) return launch_moe_sum<__nv_bfloat16>(input, output, tokens, topk, hidden_size, s);
+  if (dtype == MCOP_F16) return launch_moe_sum<__half>(input, output, tokens, topk, hidden_size, s);
+  if (dtype == MCOP_F32) return launch_moe_sum<float>(input, output, tokens, topk, hidden_size, s);
+  return set_error(MCOP_ERR_UNSUPPORTED, "moe_sum: dtype %d", dtype);
+}

@@ -32,7 +32,26 @@ struct ScatterWs {
   int32_t* tile_hist;  // [tiles, E] histogram, overwritten by the exclusive per-expert prefix over tiles
   int32_t* rank;       // [T*k] rank of the (token, slot) inside its tile and expert, -1 if dropped
   float* row_w;        // [T*k] routing weight of every output row
+  // Only for moe_align_block_size (all zero / null for the scatter):
+  const int32_t* expert_map;  // [E] global -> local expert id, -1 = not on this rank; null = identity
+  int32_t block_size;         // > 0: starts are padded to multiples of block_size, expert_ids / total are written
+  int32_t* expert_ids;        // [max_blocks] expert of every block of block_size sorted positions
+  int64_t max_blocks;
+  int32_t* total;             // [1] number of sorted positions after padding
+  int32_t* prefill;           // [prefill_n] filled with prefill_value by the rank kernel (the "no token" mark)
+  int64_t prefill_n;
+  int32_t prefill_value;
 };
+
+// expert of one routing entry after the optional map; -1 = dropped (out of range, or mapped to -1)
+__device__ __forceinline__ int mapped_expert(int e, int E, const int32_t* __restrict__ map) {
+  if (e < 0 || e >= E) return -1;
+  if (map) {
+    e = map[e];
+    if (e < 0 || e >= E) return -1;
+  }
+  return e;
+}
 
 __host__ __device__ inline int64_t scatter_tiles(int64_t tokens) { return (tokens + kTileTokens - 1) / kTileTokens; }
 
@@ -48,12 +67,17 @@ __global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __rest
   const int64_t tok0 = tile * kTileTokens;
   const int ntok = (int)min((int64_t)kTileTokens, tokens - tok0);
   for (int i = threadIdx.x; i < E * kTileWords; i += blockDim.x) bitmap[i] = 0;
+  if (ws.prefill) {
+    const int64_t per = (ws.prefill_n + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = per * blockIdx.x, hi = min(lo + per, ws.prefill_n);
+    for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) ws.prefill[i] = ws.prefill_value;
+  }
   __syncthreads();
   const int32_t* tids = ids + tok0 * topk;
   const int n = ntok * topk;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = tids[i];
-    if (e >= 0 && e < E) {
+    const int e = mapped_expert(tids[i], E, ws.expert_map);
+    if (e >= 0) {
       const int tl = i / topk;
       atomicOr(&bitmap[e * kTileWords + (tl >> 5)], 1u << (tl & 31));
     }
@@ -80,9 +104,9 @@ __global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __rest
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = tids[i];
+    const int e = mapped_expert(tids[i], E, ws.expert_map);
     int r = -1;
-    if (e >= 0 && e < E) {
+    if (e >= 0) {
       const int tl = i / topk, wd = tl >> 5;
       r = prefix[e * kTileWords + wd] + __popc(bitmap[e * kTileWords + wd] & ((1u << (tl & 31)) - 1u));
     }
@@ -131,21 +155,50 @@ __global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __rest
     if (lane == 0) { cnt_s[e] = carry; counts[e] = carry; }
   }
   __syncthreads();
+  const int bs = ws.block_size;
+  int32_t* pst_s = cnt_s + E;      // padded start and padded count of every expert (align form only)
+  int32_t* pcn_s = cnt_s + 2 * E;  // (the bitmap area is 16 E words, so 3 E + 1 ints fit)
   if (warp == 0) {
     int carry = 0;
     for (int e0 = 0; e0 < E; e0 += 32) {
       const int e = e0 + lane;
-      const int c = e < E ? cnt_s[e] : 0;
+      int c = e < E ? cnt_s[e] : 0;
+      if (bs > 0) c = (c + bs - 1) / bs * bs;
       int inc = c;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, inc, o);
         if (lane >= o) inc += v;
       }
-      if (e < E) starts[e] = carry + inc - c;
+      if (e < E) {
+        starts[e] = carry + inc - c;
+        if (bs > 0) { pst_s[e] = carry + inc - c; pcn_s[e] = c; }
+      }
       carry += __shfl_sync(0xffffffffu, inc, 31);
     }
+    if (bs > 0 && lane == 0) { *ws.total = carry; cnt_s[3 * E] = carry; }
   }
+  if (bs > 0) {  // uniform over the CTA
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+      for (int i = pst_s[e]; i < pst_s[e] + pcn_s[e]; i += bs)
+        if (i / bs < ws.max_blocks) ws.expert_ids[i / bs] = e;
+    // blocks past the padded total belong to no expert: 0, as the reference fills them
+    for (int64_t i = cnt_s[3 * E] / bs + threadIdx.x; i < ws.max_blocks; i += blockDim.x) ws.expert_ids[i] = 0;
+  }
+}
+
+// moe_align_block_size, second step: one thread per routing entry writes its flat index to its sorted position.
+__global__ void __launch_bounds__(256) align_fill_kernel(const int32_t* __restrict__ ids, ScatterWs ws,
+                                                         const int32_t* __restrict__ starts, int32_t* __restrict__ sorted,
+                                                         int64_t numel, int E, int64_t cap) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= numel) return;
+  const int r = ws.rank[i];
+  if (r < 0) return;
+  const int e = mapped_expert(ids[i], E, ws.expert_map);
+  const int64_t pos = (int64_t)starts[e] + ws.tile_hist[(i / kTileTokens) * E + e] + r;
+  if (pos < cap) sorted[pos] = (int32_t)i;
 }
 
 struct ScatterQuantParams {
@@ -485,7 +538,7 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
   cudaStream_t s = (cudaStream_t)stream;
   const int E = experts_per_rank;
   const int64_t tiles = scatter_tiles(tokens);
-  ScatterWs ws;
+  ScatterWs ws{};
   ws.ticket = reinterpret_cast<int32_t*>(workspace);
   ws.tile_hist = ws.ticket + 64;
   ws.rank = ws.tile_hist + tiles * E;
@@ -537,4 +590,68 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
   else if (nv <= 2048) scatter_quant_vec<512, 4><<<grid, 512, 0, s>>>(p);
   else scatter_quant_vec<1024, 4><<<grid, 1024, 0, s>>>(p);
   return check_launch("moe_scatter_quant_i8 (quant)");
+}
+
+// ---------------------------------------------------------------------------------------------
+// moe_align_block_size: the index preparation of the block-sparse expert GEMM.  The same counting sort as the
+// scatter, run over the flat routing entries (a "token" of the rank kernel is one entry, so an expert that a token
+// names twice gets two positions), with every expert's range padded to a multiple of block_size.
+// ---------------------------------------------------------------------------------------------
+extern "C" size_t mcop_moe_align_block_size_workspace_bytes(int64_t numel, int num_experts) {
+  if (numel < 0 || num_experts < 0) return 0;
+  const int64_t tiles = scatter_tiles(numel);
+  return (size_t)(64 + tiles * num_experts + numel + 2 * (int64_t)num_experts) * sizeof(int32_t);
+}
+
+extern "C" int mcop_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block_size,
+                                         int32_t* sorted_token_ids, int64_t max_num_tokens_padded, int32_t* expert_ids,
+                                         int64_t max_num_blocks, int32_t* num_tokens_post_pad, const int32_t* expert_map,
+                                         void* workspace, size_t workspace_bytes, mcop_stream_t stream) {
+  MCOP_REQUIRE(sorted_token_ids && expert_ids && num_tokens_post_pad && (topk_ids || numel == 0), MCOP_ERR_ARGUMENT,
+               "moe_align_block_size: null pointer");
+  MCOP_REQUIRE(numel >= 0 && num_experts >= 1 && max_num_tokens_padded >= 0 && max_num_blocks >= 0, MCOP_ERR_ARGUMENT,
+               "moe_align_block_size: bad sizes");
+  MCOP_REQUIRE(block_size > 0, MCOP_ERR_ARGUMENT, "moe_align_block_size: block_size should be greater than 0");
+  MCOP_REQUIRE(num_experts < kMaxExperts, MCOP_ERR_UNSUPPORTED, "moe_align_block_size: num_experts must be less than %d", kMaxExperts);
+  MCOP_REQUIRE(numel + (int64_t)num_experts * block_size <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED,
+               "moe_align_block_size: padded positions exceed int32");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (numel == 0) {  // nothing routed: every position holds the mark numel = 0, no block belongs to an expert
+    cudaError_t e = cudaMemsetAsync(sorted_token_ids, 0, sizeof(int32_t) * max_num_tokens_padded, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(expert_ids, 0, sizeof(int32_t) * max_num_blocks, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(num_tokens_post_pad, 0, sizeof(int32_t), s);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_align_block_size: memset: %s", cudaGetErrorString(e));
+    return MCOP_OK;
+  }
+  const size_t need = mcop_moe_align_block_size_workspace_bytes(numel, num_experts);
+  MCOP_REQUIRE(workspace && workspace_bytes >= need, MCOP_ERR_WORKSPACE, "moe_align_block_size: workspace of %zu bytes needed, %zu given",
+               need, workspace_bytes);
+  const int E = num_experts;
+  const int64_t tiles = scatter_tiles(numel);
+  ScatterWs ws{};
+  ws.ticket = reinterpret_cast<int32_t*>(workspace);
+  ws.tile_hist = ws.ticket + 64;
+  ws.rank = ws.tile_hist + tiles * E;
+  int32_t* counts = ws.rank + numel;
+  int32_t* starts = counts + E;
+  ws.expert_map = expert_map;
+  ws.block_size = block_size;
+  ws.expert_ids = expert_ids;
+  ws.max_blocks = max_num_blocks;
+  ws.total = num_tokens_post_pad;
+  ws.prefill = sorted_token_ids;
+  ws.prefill_n = max_num_tokens_padded;
+  ws.prefill_value = (int32_t)numel;
+  cudaError_t e = cudaMemsetAsync(ws.ticket, 0, 2 * sizeof(int32_t), s);
+  MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_align_block_size: memset: %s", cudaGetErrorString(e));
+  const size_t smem = (size_t)E * kTileWords * (sizeof(uint32_t) + sizeof(uint16_t));
+  if (smem > 48 * 1024) {
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(&scatter_rank_kernel), smem);
+    MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_align_block_size: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  }
+  scatter_rank_kernel<<<(unsigned)tiles, 256, smem, s>>>(topk_ids, ws, counts, starts, numel, 1, E);
+  int rc = check_launch("moe_align_block_size (rank)");
+  if (rc) return rc;
+  align_fill_kernel<<<(unsigned)((numel + 255) / 256), 256, 0, s>>>(topk_ids, ws, starts, sorted_token_ids, numel, E, max_num_tokens_padded);
+  return check_launch("moe_align_block_size (fill)");
 }

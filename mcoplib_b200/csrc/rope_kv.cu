@@ -27,6 +27,7 @@ struct RopeParams {
   int num_heads, num_kv_heads, head_size, rot_dim;
   // cos / sin rows
   const void* cos; const void* sin; int64_t cs_row_stride;  // elements of the table type
+  uint32_t sin_flip;   // 0, or 0x80000000 to rotate by the negated angle (the transposed rotation of the backward pass)
   // positions: explicit, or derived from packed sequence bounds
   const int64_t* positions;
   const int32_t* accum_q_lens; const int32_t* cache_lens; int batch;
@@ -121,6 +122,10 @@ __global__ void __launch_bounds__(256) rope_neox_vec(RopeParams p) {
   float c[8], s[8];
   Vec8<CT>::load_nc(reinterpret_cast<const CT*>(p.cos) + pos * p.cs_row_stride + j * 8, c);
   Vec8<CT>::load_nc(reinterpret_cast<const CT*>(p.sin) + pos * p.cs_row_stride + j * 8, s);
+  if (p.sin_flip) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) s[q] = __uint_as_float(__float_as_uint(s[q]) ^ p.sin_flip);
+  }
 
   int64_t slot = -1;
   if (STORE) {
@@ -202,7 +207,8 @@ __global__ void __launch_bounds__(256) rope_any(RopeParams p, int is_neox) {
                    : reinterpret_cast<T*>(p.q_dst) + t * p.q_stride) + hh * p.head_stride;
     const int xi = is_neox ? r : 2 * r, yi = is_neox ? half + r : 2 * r + 1;
     const float x = ElemTraits<T>::to_float(src[xi]), y = ElemTraits<T>::to_float(src[yi]);
-    const float c = ElemTraits<CT>::to_float(cr[r]), s = ElemTraits<CT>::to_float(sr[r]);
+    const float c = ElemTraits<CT>::to_float(cr[r]);
+    const float s = __uint_as_float(__float_as_uint(ElemTraits<CT>::to_float(sr[r])) ^ p.sin_flip);
     float xo, yo;
     if (PER_OP) {
       xo = round_to<T>(__fsub_rn(round_to<T>(__fmul_rn(x, c)), round_to<T>(__fmul_rn(y, s))));
@@ -241,7 +247,7 @@ int launch_rope_t(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok,
     // the pipelined kernel wants explicit positions, heads packed back to back, a key tensor, and cos || sin as
     // one contiguous table row; it pays off once there are a few waves of tokens
     const bool one_row = reinterpret_cast<const char*>(p.sin) == reinterpret_cast<const char*>(p.cos) + (size_t)(p.rot_dim / 2) * sizeof(CT);
-    if (vec_ok && tokens >= MCOP_ROPE_PIPE_MIN && p.positions && p.k_src && p.num_kv_heads > 0 && p.head_stride == p.head_size &&
+    if (vec_ok && !p.sin_flip && tokens >= MCOP_ROPE_PIPE_MIN && p.positions && p.k_src && p.num_kv_heads > 0 && p.head_stride == p.head_size &&
         one_row && p.cs_row_stride == p.rot_dim) {
       const int rc = launch_rope_pipe<T, CT, PER_OP, STORE>(p, tokens, stream);
       if (rc != 1) return rc;
@@ -391,11 +397,11 @@ extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const floa
   return launch_rope<false>(p, tokens, 1, dtype, MCOP_F32, true, (cudaStream_t)stream);
 }
 
-extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
-                                   int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
-  MCOP_REQUIRE(qkv && cos && sin, MCOP_ERR_ARGUMENT, "fused_rope_fwd: null pointer");
-  MCOP_REQUIRE(seq >= 0 && planes >= 2 && heads > 0 && head_dim > 0 && head_dim % 2 == 0, MCOP_ERR_ARGUMENT, "fused_rope_fwd: bad sizes");
-  MCOP_REQUIRE(dtype == MCOP_BF16 || dtype == MCOP_F16, MCOP_ERR_UNSUPPORTED, "fused_rope_fwd: only f16 and bf16");
+static int fused_rope_planes(const char* name, void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
+                             int planes, int heads, int head_dim, int dtype, uint32_t sin_flip, mcop_stream_t stream) {
+  MCOP_REQUIRE(qkv && cos && sin, MCOP_ERR_ARGUMENT, "%s: null pointer", name);
+  MCOP_REQUIRE(seq >= 0 && planes >= 2 && heads > 0 && head_dim > 0 && head_dim % 2 == 0, MCOP_ERR_ARGUMENT, "%s: bad sizes", name);
+  MCOP_REQUIRE(dtype == MCOP_BF16 || dtype == MCOP_F16, MCOP_ERR_UNSUPPORTED, "%s: only f16 and bf16", name);
   const int64_t tok_stride = (int64_t)planes * heads * head_dim;
   RopeParams p{};
   p.q_src = qkv; p.q_dst = qkv; p.q_stride = tok_stride;
@@ -404,7 +410,20 @@ extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, 
   p.k_stride = tok_stride; p.head_stride = head_dim;
   p.num_heads = heads; p.num_kv_heads = heads; p.head_size = head_dim; p.rot_dim = head_dim;
   p.cos = cos; p.sin = sin; p.cs_row_stride = head_dim / 2; p.positions = indexes;
+  p.sin_flip = sin_flip;
   return launch_rope<false>(p, seq, 1, dtype, dtype, true, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
+                                   int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
+  return fused_rope_planes("fused_rope_fwd", qkv, cos, sin, indexes, seq, planes, heads, head_dim, dtype, 0u, stream);
+}
+
+// x' = x*c + y*s, y' = y*c - x*s: the forward rotation with the sine negated (negation is exact, so every product
+// and sum rounds as in the forward form).
+extern "C" int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
+                                   int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
+  return fused_rope_planes("fused_rope_bwd", qkv, cos, sin, indexes, seq, planes, heads, head_dim, dtype, 0x80000000u, stream);
 }
 
 extern "C" int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query, void* key, const void* value,

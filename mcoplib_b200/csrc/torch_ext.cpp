@@ -285,9 +285,10 @@ void rotary_embedding_packed(Tensor packed_qkv, Tensor q_len, Tensor accum_q_len
                             head_dim, MCOP_BF16, cur_stream()));
 }
 
-// mcoplib.op.fused_rope_fwd (op/fused_rope.cu:13-74)
-Tensor fused_rope_fwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> indexes, bool force_bf16_attn) {
-  MCOP_DEBUG_CALL("fused_rope_fwd", qkv, cos, sin, indexes, force_bf16_attn);
+// mcoplib.op.fused_rope_fwd / fused_rope_bwd (op/fused_rope.cu:13-74, 77-138): same checks, the rotation or its transpose
+using FusedRopeFn = int (*)(void*, const void*, const void*, const int64_t*, int64_t, int, int, int, int, mcop_stream_t);
+static Tensor fused_rope_planes(const char* name, FusedRopeFn fn, Tensor qkv, const Tensor& cos, const Tensor& sin,
+                                const std::optional<Tensor>& indexes, bool force_bf16_attn) {
   check_cuda(qkv, "qkv"); check_cuda(cos, "cos"); check_cuda(sin, "sin");
   TORCH_CHECK(qkv.is_contiguous() && cos.is_contiguous() && sin.is_contiguous());
   if (indexes.has_value()) {
@@ -300,9 +301,17 @@ Tensor fused_rope_fwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> 
   TORCH_CHECK(cos.scalar_type() == qkv.scalar_type() && sin.scalar_type() == qkv.scalar_type());
   TORCH_CHECK(cos.size(-1) * 2 == qkv.size(3));
   const c10::cuda::OptionalCUDAGuard guard(device_of(qkv));
-  check_rc(mcop_fused_rope_fwd(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), indexes.has_value() ? indexes->data_ptr<int64_t>() : nullptr,
-                               qkv.size(0), (int)qkv.size(1), (int)qkv.size(2), (int)qkv.size(3), dtype_code(qkv, "fused_rope_fwd"), cur_stream()));
+  check_rc(fn(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), indexes.has_value() ? indexes->data_ptr<int64_t>() : nullptr,
+              qkv.size(0), (int)qkv.size(1), (int)qkv.size(2), (int)qkv.size(3), dtype_code(qkv, name), cur_stream()));
   return qkv;
+}
+Tensor fused_rope_fwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> indexes, bool force_bf16_attn) {
+  MCOP_DEBUG_CALL("fused_rope_fwd", qkv, cos, sin, indexes, force_bf16_attn);
+  return fused_rope_planes("fused_rope_fwd", &mcop_fused_rope_fwd, qkv, cos, sin, indexes, force_bf16_attn);
+}
+Tensor fused_rope_bwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> indexes, bool force_bf16_attn) {
+  MCOP_DEBUG_CALL("fused_rope_bwd", qkv, cos, sin, indexes, force_bf16_attn);
+  return fused_rope_planes("fused_rope_bwd", &mcop_fused_rope_bwd, qkv, cos, sin, indexes, force_bf16_attn);
 }
 
 // mcoplib.op.store_kv_cache_cuda_interface (op/store_kv.cu:220-350)
@@ -421,6 +430,56 @@ void topk_softmax(Tensor& topk_weights, Tensor& topk_indices, Tensor& token_expe
   check_rc(mcop_topk_softmax(topk_weights.data_ptr<float>(), topk_indices.data_ptr<int32_t>(), token_expert_indices.data_ptr<int32_t>(),
                              gating_output.data_ptr(), tokens, experts, k, renormalize ? 1 : 0, dtype_code(gating_output, "topk_softmax"),
                              cur_stream()));
+}
+
+// torch.ops._moe_C.moe_sum (op/vllm/moe/moe_align_sum_kernels.cu:770-815): output [tokens, hidden] = sum over dim 1 of
+// input [tokens, topk, hidden]
+void moe_sum(Tensor& input, Tensor& output) {
+  MCOP_DEBUG_CALL("moe_sum", input, output);
+  check_cuda(input, "input"); check_cuda(output, "output");
+  TORCH_CHECK(input.dim() == 3, "moe_sum: input must be [num_tokens, topk, hidden_size]");
+  TORCH_CHECK(input.is_contiguous() && output.is_contiguous(), "moe_sum: tensors must be contiguous");
+  TORCH_CHECK(input.scalar_type() == output.scalar_type(), "moe_sum: input and output dtypes differ");
+  const int64_t hidden = input.size(-1);
+  const int64_t tokens = hidden ? output.numel() / hidden : 0;
+  TORCH_CHECK(tokens == input.size(0) && output.numel() == tokens * hidden, "moe_sum: output must be [num_tokens, hidden_size]");
+  if (tokens == 0 || hidden == 0) return;
+  const c10::cuda::OptionalCUDAGuard guard(device_of(output));
+  check_rc(mcop_moe_sum(input.data_ptr(), output.data_ptr(), tokens, (int)input.size(1), hidden, dtype_code(input, "moe_sum"), cur_stream()));
+}
+
+// torch.ops._moe_C.moe_align_block_size (op/vllm/moe/moe_align_sum_kernels.cu:612-735)
+void moe_align_block_size(Tensor topk_ids, int64_t num_experts, int64_t block_size, Tensor sorted_token_ids, Tensor experts_ids,
+                          Tensor num_tokens_post_pad, std::optional<Tensor> maybe_expert_map) {
+  MCOP_DEBUG_CALL("moe_align_block_size", topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad,
+                  maybe_expert_map);
+  check_cuda(topk_ids, "topk_ids"); check_cuda(sorted_token_ids, "sorted_token_ids"); check_cuda(experts_ids, "experts_ids");
+  check_cuda(num_tokens_post_pad, "num_tokens_post_pad");
+  TORCH_CHECK(block_size > 0, "block_size should be greater than 0. ");
+  TORCH_CHECK(num_experts > 0 && num_experts < 1024, "padded_num_experts must be less than 1024");
+  TORCH_CHECK(c10::isIntegralType(topk_ids.scalar_type(), false), "moe_align_block_size: topk_ids must be an integer tensor");
+  TORCH_CHECK(sorted_token_ids.scalar_type() == at::kInt && experts_ids.scalar_type() == at::kInt &&
+              num_tokens_post_pad.scalar_type() == at::kInt, "moe_align_block_size: outputs must be int32");
+  TORCH_CHECK(sorted_token_ids.is_contiguous() && experts_ids.is_contiguous() && num_tokens_post_pad.numel() >= 1);
+  const c10::cuda::OptionalCUDAGuard guard(device_of(topk_ids));
+  // the kernels read int32 ids; other integer types (the reference dispatches over all of them) are converted first
+  const Tensor ids = topk_ids.scalar_type() == at::kInt && topk_ids.is_contiguous() ? topk_ids : topk_ids.to(at::kInt).contiguous();
+  Tensor map;
+  if (maybe_expert_map.has_value()) {
+    check_cuda(*maybe_expert_map, "expert_map");
+    TORCH_CHECK(maybe_expert_map->numel() >= num_experts, "moe_align_block_size: expert_map shorter than num_experts");
+    map = maybe_expert_map->scalar_type() == at::kInt && maybe_expert_map->is_contiguous() ? *maybe_expert_map
+                                                                                           : maybe_expert_map->to(at::kInt).contiguous();
+  }
+  const int64_t numel = ids.numel();
+  const int64_t cap = sorted_token_ids.size(0);
+  const int64_t blocks = std::min<int64_t>((cap + block_size - 1) / block_size, experts_ids.numel());
+  const size_t ws_bytes = mcop_moe_align_block_size_workspace_bytes(numel, (int)num_experts);
+  Tensor ws = scratch_bytes(ws_bytes, sorted_token_ids);
+  check_rc(mcop_moe_align_block_size(numel ? ids.data_ptr<int32_t>() : nullptr, numel, (int)num_experts, (int)block_size,
+                                     sorted_token_ids.data_ptr<int32_t>(), cap, experts_ids.data_ptr<int32_t>(), blocks,
+                                     num_tokens_post_pad.data_ptr<int32_t>(), map.defined() ? map.data_ptr<int32_t>() : nullptr,
+                                     ws.data_ptr(), ws_bytes, cur_stream()));
 }
 
 // sglang's store_kv_cache (op/sglang/csrc/memory/store.cu:72-150): k_cache[out_loc[i], :] = k[i, :], same for v; rows are
@@ -829,7 +888,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("rope_offset") = 0);
   m.def("fused_rope_fwd", &fused_rope_fwd, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("indexes"),
         py::arg("force_bf16_attn") = false);
+  m.def("fused_rope_bwd", &fused_rope_bwd, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("indexes"),
+        py::arg("force_bf16_attn") = false);
   m.def("store_kv_cache_cuda_interface", &store_kv_cache_cuda_interface);
+  m.def("moe_sum", &moe_sum, py::arg("input"), py::arg("output"));
+  m.def("moe_align_block_size", &moe_align_block_size, py::arg("topk_ids"), py::arg("num_experts"), py::arg("block_size"),
+        py::arg("sorted_token_ids"), py::arg("experts_ids"), py::arg("num_tokens_post_pad"), py::arg("maybe_expert_map") = py::none());
   m.def("moe_softmax_topk", &moe_softmax_topk);
   m.def("fused_moe_gate_deepseek", &fused_moe_gate_deepseek, py::arg("gating_outputs"), py::arg("correction_bias"),
         py::arg("out_routing_weights"), py::arg("out_selected_experts"), py::arg("topk"), py::arg("renormalize"),
@@ -898,6 +962,12 @@ TORCH_LIBRARY(MCOP_TORCH_NS_MOE, moe_ops) {
       "grouped_topk(Tensor scores, int n_group, int topk_group, int topk, bool renormalize, float routed_scaling_factor, "
       "Tensor bias, int scoring_func) -> (Tensor, Tensor)");
   moe_ops.impl("grouped_topk", torch::kCUDA, &grouped_topk);
+  moe_ops.def("moe_sum(Tensor input, Tensor! output) -> ()");
+  moe_ops.impl("moe_sum", torch::kCUDA, &moe_sum);
+  moe_ops.def(
+      "moe_align_block_size(Tensor topk_ids, int num_experts, int block_size, Tensor! sorted_token_ids, Tensor! experts_ids, "
+      "Tensor! num_tokens_post_pad, Tensor? maybe_expert_map) -> ()");
+  moe_ops.impl("moe_align_block_size", torch::kCUDA, &moe_align_block_size);
 }
 
 TORCH_LIBRARY(MCOP_TORCH_NS_CACHE, cache_ops) {

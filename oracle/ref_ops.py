@@ -342,6 +342,14 @@ def fused_rope_fwd(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
     return out
 
 
+def fused_rope_bwd(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                   indexes: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """mcoplib.op.fused_rope_bwd, kernel/fused_rope_kernel.h:101-191: the transposed rotation,
+    x' = x*c + y*s, y' = -x*s + y*c (lines 172-176), fp32 math, one rounding.  Negating the sine is
+    exact, so this is the forward formula evaluated with -sin."""
+    return fused_rope_fwd(qkv, cos, -sin, indexes)
+
+
 def float_to_int8_sym(v: torch.Tensor) -> torch.Tensor:
     """kernel/utils.h:219-226: round-half-even, clamp to [-127, 127]; NaN converts to 0."""
     return torch.nan_to_num(torch.round(v), nan=0.0).clamp(-127, 127).to(torch.int8)
@@ -842,3 +850,58 @@ def moe_gather_weighted(y: torch.Tensor, row2tok: torch.Tensor, topk_ids: torch.
         m = occ == j
         acc[toks[m]] = acc[toks[m]] + w[m].unsqueeze(1) * y[rows[m]].float()
     return acc.to(out.dtype)
+
+
+def moe_sum(inp: torch.Tensor) -> torch.Tensor:
+    """torch.ops._moe_C.moe_sum, op/vllm/moe/moe_align_sum_kernels.cu:352-367 (kernel) and :770-815 (dispatch).
+
+    inp [T, k, H] -> [T, H].  k in {2, 3, 4}: `scalar_t x = 0; x += in[k]` - the running sum lives in the
+    element type, so every partial sum is rounded to it (0 + in[0] is exact).  Any other k: the reference calls
+    at::sum_out, i.e. fp32 accumulation and one rounding; the order of that reduction is the framework's, the
+    restatement adds the slots in order."""
+    T, k, H = inp.shape
+    if 2 <= k <= 4:
+        acc = inp[:, 0].clone()
+        for j in range(1, k):
+            acc = (acc.float() + inp[:, j].float()).to(inp.dtype)
+        return acc
+    acc = torch.zeros(T, H, dtype=torch.float32)
+    for j in range(k):
+        acc = acc + inp[:, j].float()
+    return acc.to(inp.dtype)
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: int, max_num_tokens_padded: int,
+                         expert_map: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """torch.ops._moe_C.moe_align_block_size, op/vllm/moe/moe_align_sum_kernels.cu:86-180 (counting, padded prefix,
+    expert_ids, tail fill with 0) and :306-337 (placement).  Pinned by the bincount construction of
+    benchmark/runners/mcoplib_mxbenchmark_moe_align_block_size_runners.py:62-80, which sorts every expert's range
+    before comparing because the reference's placement order depends on its atomics; this restatement emits the
+    ascending order directly.  (That runner pre-fills its expected expert_ids with -1; the kernel writes 0 to the
+    blocks after the padded total, lines 174-179, and so does this function.)
+
+    Returns (sorted_token_ids int32 [max_num_tokens_padded], expert_ids int32 [ceil(max/block)], total int32 [1])."""
+    flat = topk_ids.reshape(-1).long()
+    numel = flat.numel()
+    e = flat.clone()
+    valid = (e >= 0) & (e < num_experts)
+    if expert_map is not None:
+        m = expert_map.long()
+        e = torch.where(valid, m[e.clamp(0, num_experts - 1)], torch.full_like(e, -1))
+        valid = valid & (e >= 0) & (e < num_experts)
+    sorted_ids = torch.full((max_num_tokens_padded,), numel, dtype=torch.int32)
+    nblocks = (max_num_tokens_padded + block_size - 1) // block_size
+    expert_ids = torch.zeros(nblocks, dtype=torch.int32)
+    off = 0
+    for ex in range(num_experts):
+        idx = torch.nonzero(valid & (e == ex), as_tuple=True)[0]
+        cnt = idx.numel()
+        padded = (cnt + block_size - 1) // block_size * block_size
+        hi = min(off + cnt, max_num_tokens_padded)
+        if hi > off:
+            sorted_ids[off:hi] = idx[:hi - off].to(torch.int32)
+        b0, b1 = off // block_size, min((off + padded) // block_size, nblocks)
+        if b1 > b0:
+            expert_ids[b0:b1] = ex
+        off += padded
+    return sorted_ids, expert_ids, torch.tensor([off], dtype=torch.int32)

@@ -155,6 +155,43 @@ def test_fused_rope_fwd(op):
         op.fused_rope_fwd(qkv.float().to(DEV), cos.to(DEV), sin.to(DEV), None, False)
 
 
+def _fused_rope_bwd_literal(qkv, cos, sin, indexes):
+    """kernel/fused_rope_kernel.h:172-176 written out: x' = x*c + y*s, y' = -x*s + y*c in fp32, one rounding."""
+    S, _, H, D = qkv.shape
+    idx = torch.arange(S) if indexes is None else indexes.long()
+    c = cos[idx].float()[:, None, None, :]
+    s = sin[idx].float()[:, None, None, :]
+    out = qkv.clone()
+    x, y = qkv[:, :2, :, :D // 2].float(), qkv[:, :2, :, D // 2:].float()
+    out[:, :2, :, :D // 2] = (x * c + y * s).to(qkv.dtype)
+    out[:, :2, :, D // 2:] = (-(x * s) + y * c).to(qkv.dtype)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("S,H,D", [(70, 8, 128), (3000, 4, 64), (5, 3, 80)])
+def test_fused_rope_bwd(op, dtype, S, H, D):
+    qkv = W.per_token("randn", 37, 0, S, 3 * H * D, dtype).reshape(S, 3, H, D)
+    cs = W.cos_sin_cache(4096, D, 10000.0)
+    cos, sin = cs[:, :D // 2].to(dtype).contiguous(), cs[:, D // 2:].to(dtype).contiguous()
+    idx = torch.randint(0, 4096, (S,), generator=torch.Generator().manual_seed(2))
+    for indexes in (None, idx):
+        ref = R.fused_rope_bwd(qkv, cos, sin, indexes)
+        C.assert_equal(bits(ref), bits(_fused_rope_bwd_literal(qkv, cos, sin, indexes)))
+        g = qkv.to(DEV)
+        ret = op.fused_rope_bwd(g, cos.to(DEV), sin.to(DEV), indexes.to(DEV) if indexes is not None else None, False)
+        assert ret.data_ptr() == g.data_ptr()
+        C.assert_equal(bits(g), bits(ref))
+        C.assert_equal(bits(g[:, 2]), bits(qkv[:, 2]))  # the V plane is not touched
+        # the transposed rotation undoes the forward one up to the two roundings
+        back = op.fused_rope_bwd(op.fused_rope_fwd(qkv.to(DEV), cos.to(DEV), sin.to(DEV), indexes.to(DEV) if indexes is not None else None, False),
+                                 cos.to(DEV), sin.to(DEV), indexes.to(DEV) if indexes is not None else None, False)
+        tol = 2.0 ** -6 if dtype == torch.bfloat16 else 2.0 ** -9
+        assert torch.allclose(back.float().cpu(), qkv.float(), rtol=0, atol=tol * 8)
+    with pytest.raises(RuntimeError):
+        op.fused_rope_bwd(qkv.float().to(DEV), cos.to(DEV), sin.to(DEV), None, False)
+
+
 def test_store_kv_cache_against_golden(op, golden):
     for key, g in records(golden, "ref:unit_test/test_store_kv.py:run_reference_impl"):
         kc = torch.zeros_like(g["k_cache"]).to(DEV); vc = torch.zeros_like(kc)
