@@ -3,8 +3,9 @@
 // Scatter is a deterministic counting sort, not a sort:
 //   rank kernel  - one CTA per tile of 512 tokens builds, in shared memory, one bitmap of the tile's tokens per
 //                  expert; popcounts give the tile's per-expert histogram and the rank of every (token, slot)
-//                  among the tile's rows of that expert.  The last CTA to finish (one atomic ticket, nobody
-//                  waits) turns the histograms into per-tile bases, counts and starts.
+//                  among the tile's rows of that expert.  With few tiles the last CTA to finish (one atomic ticket,
+//                  nobody waits) turns the histograms into per-tile bases, counts and starts; with many tiles a scan
+//                  kernel with one CTA per expert does (its last CTA derives the starts).
 //   fill kernel  - one thread per (token, slot): row = starts[e] + tile_base[tile][e] + rank; writes row2tok,
 //                  tok2row and the row's routing weight.  Rows end up ordered by (expert, token).
 //   quant kernel - persistent CTAs take work items (token super-tile, expert, part) in token-major order, so
@@ -26,12 +27,14 @@ constexpr int kTileTokens = 512;
 constexpr int kTileWords = kTileTokens / 32;
 constexpr int kMaxExperts = 1024;
 constexpr int kBatchRows = 64;   // row indices staged in shared memory at a time by the quant kernel
+constexpr int kInKernelScanTiles = 64;  // up to this many tiles the rank kernel's last CTA scans them itself
 
 struct ScatterWs {
   int32_t* ticket;     // [0] ticket of the rank kernel, [1] work counter of the quant kernel (64 ints reserved)
   int32_t* tile_hist;  // [tiles, E] histogram, overwritten by the exclusive per-expert prefix over tiles
   int32_t* rank;       // [T*k] rank of the (token, slot) inside its tile and expert, -1 if dropped
   float* row_w;        // [T*k] routing weight of every output row
+  int32_t separate_scan;  // more than kInKernelScanTiles tiles: scatter_scan_kernel follows the rank kernel
   // Only for moe_align_block_size (all zero / null for the scatter):
   const int32_t* expert_map;  // [E] global -> local expert id, -1 = not on this rank; null = identity
   int32_t block_size;         // > 0: starts are padded to multiples of block_size, expert_ids / total are written
@@ -55,7 +58,47 @@ __device__ __forceinline__ int mapped_expert(int e, int E, const int32_t* __rest
 
 __host__ __device__ inline int64_t scatter_tiles(int64_t tokens) { return (tokens + kTileTokens - 1) / kTileTokens; }
 
-// dynamic shared memory: bitmap [E][kTileWords] u32, then prefix [E][kTileWords] u16
+// Last step of the counting, run by one whole CTA: cnt_s[0, E) (shared memory, room for 3 E + 1 ints) holds the
+// experts' row counts; writes starts[] (exclusive prefix; of the counts padded to block_size in the align form) and,
+// in the align form, the expert of every block and the padded total.
+__device__ __forceinline__ void finish_experts(int32_t* cnt_s, const ScatterWs& ws, int32_t* __restrict__ starts, int E) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  const int bs = ws.block_size;
+  int32_t* pst_s = cnt_s + E;      // padded start and padded count of every expert (align form only)
+  int32_t* pcn_s = cnt_s + 2 * E;
+  if (warp == 0) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      int c = e < E ? cnt_s[e] : 0;
+      if (bs > 0) c = (c + bs - 1) / bs * bs;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      if (e < E) {
+        starts[e] = carry + inc - c;
+        if (bs > 0) { pst_s[e] = carry + inc - c; pcn_s[e] = c; }
+      }
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (bs > 0 && lane == 0) { *ws.total = carry; cnt_s[3 * E] = carry; }
+  }
+  if (bs > 0) {  // uniform over the CTA
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+      for (int i = pst_s[e]; i < pst_s[e] + pcn_s[e]; i += bs)
+        if (i / bs < ws.max_blocks) ws.expert_ids[i / bs] = e;
+    // blocks past the padded total belong to no expert: 0, as the reference fills them
+    for (int64_t i = cnt_s[3 * E] / bs + threadIdx.x; i < ws.max_blocks; i += blockDim.x) ws.expert_ids[i] = 0;
+  }
+}
+
+// dynamic shared memory: bitmap [E][kTileWords] u32, then prefix [E][kTileWords] u16 (16 E words: the 3 E + 1 ints
+// of finish_experts fit when the area is reused)
 __global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __restrict__ ids, ScatterWs ws,
                                                            int32_t* __restrict__ counts, int32_t* __restrict__ starts,
                                                            int64_t tokens, int topk, int E) {
@@ -112,7 +155,8 @@ __global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __rest
     }
     ws.rank[tok0 * topk + i] = r;
   }
-  // ticket: the last CTA to arrive finishes the job; nobody spins
+  if (ws.separate_scan) return;  // many tiles: scatter_scan_kernel turns the histograms into bases (one CTA per expert)
+  // few tiles - ticket: the last CTA to arrive finishes the job; nobody spins
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) is_last = (atomicAdd(ws.ticket, 1) == (int)gridDim.x - 1);
@@ -121,71 +165,64 @@ __global__ void __launch_bounds__(256) scatter_rank_kernel(const int32_t* __rest
   __threadfence();
   const int ntiles = gridDim.x;
   int32_t* cnt_s = reinterpret_cast<int32_t*>(smem_u32);  // reuse: E ints
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  if (ntiles <= 64) {
-    // few tiles: one thread per expert walks the tiles; the loads are coalesced over experts and independent of
-    // each other, so they overlap instead of paying one memory latency per expert
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-      int run = 0;
+  // one thread per expert walks the tiles; the loads are coalesced over experts and independent of each other, so
+  // they overlap instead of paying one memory latency per expert
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
 #pragma unroll 8
-      for (int t = 0; t < ntiles; ++t) {
-        const int c = __ldcg(&ws.tile_hist[(int64_t)t * E + e]);
-        ws.tile_hist[(int64_t)t * E + e] = run;
-        run += c;
-      }
-      cnt_s[e] = run;
-      counts[e] = run;
+    for (int t = 0; t < ntiles; ++t) {
+      const int c = __ldcg(&ws.tile_hist[(int64_t)t * E + e]);
+      ws.tile_hist[(int64_t)t * E + e] = run;
+      run += c;
     }
-  } else
-  for (int e = warp; e < E; e += nwarp) {
-    int carry = 0;
-#pragma unroll 4
-    for (int t0 = 0; t0 < ntiles; t0 += 32) {
-      const int t = t0 + lane;
-      const int c = t < ntiles ? __ldcg(&ws.tile_hist[(int64_t)t * E + e]) : 0;
-      int inc = c;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += v;
-      }
-      if (t < ntiles) ws.tile_hist[(int64_t)t * E + e] = carry + inc - c;
-      carry += __shfl_sync(0xffffffffu, inc, 31);
-    }
-    if (lane == 0) { cnt_s[e] = carry; counts[e] = carry; }
+    cnt_s[e] = run;
+    counts[e] = run;
   }
-  __syncthreads();
-  const int bs = ws.block_size;
-  int32_t* pst_s = cnt_s + E;      // padded start and padded count of every expert (align form only)
-  int32_t* pcn_s = cnt_s + 2 * E;  // (the bitmap area is 16 E words, so 3 E + 1 ints fit)
-  if (warp == 0) {
-    int carry = 0;
-    for (int e0 = 0; e0 < E; e0 += 32) {
-      const int e = e0 + lane;
-      int c = e < E ? cnt_s[e] : 0;
-      if (bs > 0) c = (c + bs - 1) / bs * bs;
-      int inc = c;
+  finish_experts(cnt_s, ws, starts, E);
+}
+
+// Second step when there are many tiles: CTA e turns column e of the [tiles, E] histogram into exclusive prefixes
+// over the tiles (256 tiles per round, block scan) and writes counts[e]; the last CTA to finish (ticket, nobody
+// waits) derives the experts' starts.
+__global__ void __launch_bounds__(256) scatter_scan_kernel(ScatterWs ws, int32_t* __restrict__ counts,
+                                                           int32_t* __restrict__ starts, int ntiles, int E) {
+  __shared__ int32_t wsum[8];
+  __shared__ int is_last;
+  __shared__ int32_t cnt_s[3 * kMaxExperts + 1];
+  const int e = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int carry = 0;
+  for (int t0 = 0; t0 < ntiles; t0 += 256) {
+    const int t = t0 + threadIdx.x;
+    const int c = t < ntiles ? __ldcg(&ws.tile_hist[(int64_t)t * E + e]) : 0;
+    int inc = c;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += v;
-      }
-      if (e < E) {
-        starts[e] = carry + inc - c;
-        if (bs > 0) { pst_s[e] = carry + inc - c; pcn_s[e] = c; }
-      }
-      carry += __shfl_sync(0xffffffffu, inc, 31);
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += v;
     }
-    if (bs > 0 && lane == 0) { *ws.total = carry; cnt_s[3 * E] = carry; }
-  }
-  if (bs > 0) {  // uniform over the CTA
+    if (lane == 31) wsum[warp] = inc;
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x)
-      for (int i = pst_s[e]; i < pst_s[e] + pcn_s[e]; i += bs)
-        if (i / bs < ws.max_blocks) ws.expert_ids[i / bs] = e;
-    // blocks past the padded total belong to no expert: 0, as the reference fills them
-    for (int64_t i = cnt_s[3 * E] / bs + threadIdx.x; i < ws.max_blocks; i += blockDim.x) ws.expert_ids[i] = 0;
+    int base = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int v = wsum[w];
+      if (w < warp) base += v;
+      tot += v;
+    }
+    if (t < ntiles) ws.tile_hist[(int64_t)t * E + e] = carry + base + inc - c;
+    carry += tot;
+    __syncthreads();  // wsum is rewritten by the next round
   }
+  if (threadIdx.x == 0) counts[e] = carry;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(ws.ticket, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < E; i += blockDim.x) cnt_s[i] = __ldcg(&counts[i]);
+  finish_experts(cnt_s, ws, starts, E);
 }
 
 // moe_align_block_size, second step: one thread per routing entry writes its flat index to its sorted position.
@@ -556,9 +593,15 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(&scatter_rank_kernel), smem);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   }
+  ws.separate_scan = tiles > kInKernelScanTiles;
   scatter_rank_kernel<<<(unsigned)tiles, 256, smem, s>>>(ids, ws, counts, starts, tokens, topk, E);
   int rc = check_launch("moe_scatter_quant_i8 (rank)");
   if (rc) return rc;
+  if (ws.separate_scan) {
+    scatter_scan_kernel<<<(unsigned)E, 256, 0, s>>>(ws, counts, starts, (int)tiles, E);
+    rc = check_launch("moe_scatter_quant_i8 (scan)");
+    if (rc) return rc;
+  }
   ScatterQuantParams p{};
   p.hidden = reinterpret_cast<const __nv_bfloat16*>(hidden); p.ids = ids; p.weights = weights; p.smooth = smooth;
   p.rows = rows; p.row_scales = row_scales; p.row2tok = row2tok; p.starts = starts; p.counts = counts; p.tok2row = tok2row;
@@ -649,9 +692,15 @@ extern "C" int mcop_moe_align_block_size(const int32_t* topk_ids, int64_t numel,
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(&scatter_rank_kernel), smem);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_align_block_size: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   }
+  ws.separate_scan = tiles > kInKernelScanTiles;
   scatter_rank_kernel<<<(unsigned)tiles, 256, smem, s>>>(topk_ids, ws, counts, starts, numel, 1, E);
   int rc = check_launch("moe_align_block_size (rank)");
   if (rc) return rc;
+  if (ws.separate_scan) {
+    scatter_scan_kernel<<<(unsigned)E, 256, 0, s>>>(ws, counts, starts, (int)tiles, E);
+    rc = check_launch("moe_align_block_size (scan)");
+    if (rc) return rc;
+  }
   align_fill_kernel<<<(unsigned)((numel + 255) / 256), 256, 0, s>>>(topk_ids, ws, starts, sorted_token_ids, numel, E, max_num_tokens_padded);
   return check_launch("moe_align_block_size (fill)");
 }

@@ -176,7 +176,8 @@ def _check_scatter(op, T, H, E, k, ids=None, w=None, smooth=None, seed=0):
 
 @pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (511, 1024, 8, 2), (512, 1024, 8, 2), (513, 1024, 8, 2), (2000, 2048, 64, 6),
                                      (1500, 7168, 256, 8), (300, 520, 16, 4), (64, 100, 8, 2), (130, 16384, 8, 2), (40, 32768, 4, 1),
-                                     (1030, 512, 200, 3), (1100, 4096, 8, 2), (600, 5120, 16, 4), (700, 6144, 8, 3), (1024, 8192, 8, 2)])
+                                     (1030, 512, 200, 3), (1100, 4096, 8, 2), (600, 5120, 16, 4), (700, 6144, 8, 3), (1024, 8192, 8, 2),
+                                     (33000, 256, 40, 3), (70000, 64, 256, 8)])  # the last two: more than 64 tiles (scan kernel)
 def test_scatter_matches_oracle(op, T, H, E, k):
     _check_scatter(op, T, H, E, k)
 
