@@ -335,6 +335,12 @@ int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, void* out, in
 int mcop_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size, int dtype,
                  mcop_stream_t stream);
 
+/* sglang's moe_sum_reduce, op/sglang/csrc/moe/moe_sum_reduce.cu:119-223,226-330 (schema op/sglang/csrc/common_extension.cc:252):
+ * output[t, :] = T((sum_k float(input[t, k, :])) * float(routed_scaling_factor)) - fp32 accumulation in slot order for
+ * every topk, one rounding.  Same layouts and types as mcop_moe_sum. */
+int mcop_moe_sum_reduce(const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size,
+                        double routed_scaling_factor, int dtype, mcop_stream_t stream);
+
 /* torch.ops._moe_C.moe_align_block_size, op/vllm/moe/moe_align_sum_kernels.cu:86-180,612-735
  * (schema op/vllm/moe/torch_bindings.cpp:18-24).  Index preparation of a block-sparse expert GEMM:
  *   sorted_token_ids [max_num_tokens_padded]: for every expert e in ascending order, the flat indices i = t*topk + j

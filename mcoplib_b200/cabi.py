@@ -41,6 +41,7 @@ SIGNATURES = {
     "mcop_moe_scatter_quant_i8": (I32, [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, P, SZ, P]),
     "mcop_moe_gather_workspace_bytes": (SZ, [I64, I64]),
     "mcop_moe_sum": (I32, [P, P, I64, I32, I64, I32, P]),
+    "mcop_moe_sum_reduce": (I32, [P, P, I64, I32, I64, C.c_double, I32, P]),
     "mcop_moe_align_block_size_workspace_bytes": (SZ, [I64, I32]),
     "mcop_moe_align_block_size": (I32, [P, I64, I32, I32, P, I64, P, I64, P, P, P, SZ, P]),
     "mcop_moe_gather": (I32, [P, P, P, P, I32, I64, I64, I64, P, SZ, P]),

@@ -498,7 +498,7 @@ extern "C" int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, vo
 namespace mcop {
 namespace {
 template <typename T, int K>
-__global__ void __launch_bounds__(256) moe_sum_vec(const T* __restrict__ in, T* __restrict__ out, int64_t tokens, int topk, int hidden) {
+__global__ void __launch_bounds__(256) moe_sum_vec(const T* __restrict__ in, T* __restrict__ out, int64_t tokens, int topk, int hidden, float scale) {
   const int nv = hidden >> 3;
   const int64_t total = tokens * nv;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -526,15 +526,18 @@ __global__ void __launch_bounds__(256) moe_sum_vec(const T* __restrict__ in, T* 
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], x[j]);
       }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __fmul_rn(acc[j], scale);  // 1 for moe_sum (exact), the routed scaling factor for moe_sum_reduce
     }
     Vec8<T>::store(out + t * (int64_t)hidden + v * 8, acc);
   }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) moe_sum_any(const T* __restrict__ in, T* __restrict__ out, int64_t tokens, int topk, int hidden) {
+__global__ void __launch_bounds__(256) moe_sum_any(const T* __restrict__ in, T* __restrict__ out, int64_t tokens, int topk, int hidden,
+                                                   float scale, int per_add_form) {
   const int64_t total = tokens * hidden;
-  const bool per_add = topk >= 2 && topk <= 4;
+  const bool per_add = per_add_form && topk >= 2 && topk <= 4;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / hidden;
     const int c = (int)(i - t * hidden);
@@ -544,12 +547,14 @@ __global__ void __launch_bounds__(256) moe_sum_any(const T* __restrict__ in, T* 
       acc = __fadd_rn(acc, ElemTraits<T>::to_float(src[(int64_t)k * hidden]));
       if (per_add) acc = round_to<T>(acc);
     }
+    if (!per_add) acc = __fmul_rn(acc, scale);
     out[i] = ElemTraits<T>::from_float(acc);
   }
 }
 
 template <typename T>
-int launch_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden, cudaStream_t stream) {
+int launch_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden, float scale, bool per_add_form,
+                   cudaStream_t stream) {
   const T* in = reinterpret_cast<const T*>(input);
   T* out = reinterpret_cast<T*>(output);
   const bool vec_ok = hidden % 8 == 0 && aligned16(input) && aligned16(output);
@@ -558,24 +563,36 @@ int launch_moe_sum(const void* input, void* output, int64_t tokens, int topk, in
   const int64_t cap = (int64_t)sm_count() * 16;  // grid-stride beyond a few waves of resident CTAs
   if (grid > cap) grid = cap;
   const int H = (int)hidden;
-  if (!vec_ok) moe_sum_any<T><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
-  else if (topk == 2) moe_sum_vec<T, 2><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
-  else if (topk == 3) moe_sum_vec<T, 3><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
-  else if (topk == 4) moe_sum_vec<T, 4><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
-  else moe_sum_vec<T, 0><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H);
+  if (!vec_ok) moe_sum_any<T><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H, scale, per_add_form ? 1 : 0);
+  else if (per_add_form && topk == 2) moe_sum_vec<T, 2><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H, scale);
+  else if (per_add_form && topk == 3) moe_sum_vec<T, 3><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H, scale);
+  else if (per_add_form && topk == 4) moe_sum_vec<T, 4><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H, scale);
+  else moe_sum_vec<T, 0><<<(unsigned)grid, 256, 0, stream>>>(in, out, tokens, topk, H, scale);
   return check_launch("moe_sum");
 }
 }  // namespace
 }  // namespace mcop
 
-extern "C" int mcop_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size, int dtype,
-                            mcop_stream_t stream) {
-  MCOP_REQUIRE(input && output, MCOP_ERR_ARGUMENT, "moe_sum: null pointer");
-  MCOP_REQUIRE(tokens >= 0 && topk >= 1 && hidden_size > 0 && hidden_size <= 0x7fffffff, MCOP_ERR_ARGUMENT, "moe_sum: bad sizes");
+static int moe_sum_entry(const char* name, const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size, float scale,
+                         bool per_add_form, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(input && output, MCOP_ERR_ARGUMENT, "%s: null pointer", name);
+  MCOP_REQUIRE(tokens >= 0 && topk >= 1 && hidden_size > 0 && hidden_size <= 0x7fffffff, MCOP_ERR_ARGUMENT, "%s: bad sizes", name);
   if (tokens == 0) return MCOP_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == MCOP_BF16) return launch_moe_sum<__nv_bfloat16>(input, output, tokens, topk, hidden_size, s);
-  if (dtype == MCOP_F16) return launch_moe_sum<__half>(input, output, tokens, topk, hidden_size, s);
-  if (dtype == MCOP_F32) return launch_moe_sum<float>(input, output, tokens, topk, hidden_size, s);
-  return set_error(MCOP_ERR_UNSUPPORTED, "moe_sum: dtype %d", dtype);
+  if (dtype == MCOP_BF16) return launch_moe_sum<__nv_bfloat16>(input, output, tokens, topk, hidden_size, scale, per_add_form, s);
+  if (dtype == MCOP_F16) return launch_moe_sum<__half>(input, output, tokens, topk, hidden_size, scale, per_add_form, s);
+  if (dtype == MCOP_F32) return launch_moe_sum<float>(input, output, tokens, topk, hidden_size, scale, per_add_form, s);
+  return set_error(MCOP_ERR_UNSUPPORTED, "%s: dtype %d", name, dtype);
+}
+
+extern "C" int mcop_moe_sum(const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size, int dtype,
+                            mcop_stream_t stream) {
+  return moe_sum_entry("moe_sum", input, output, tokens, topk, hidden_size, 1.0f, true, dtype, stream);
+}
+
+// sglang's moe_sum_reduce (op/sglang/csrc/moe/moe_sum_reduce.cu:119-223): fp32 accumulation in slot order for every topk,
+// times the routed scaling factor (as float), one rounding.
+extern "C" int mcop_moe_sum_reduce(const void* input, void* output, int64_t tokens, int topk, int64_t hidden_size,
+                                   double routed_scaling_factor, int dtype, mcop_stream_t stream) {
+  return moe_sum_entry("moe_sum_reduce", input, output, tokens, topk, hidden_size, (float)routed_scaling_factor, false, dtype, stream);
 }

@@ -448,6 +448,25 @@ void moe_sum(Tensor& input, Tensor& output) {
   check_rc(mcop_moe_sum(input.data_ptr(), output.data_ptr(), tokens, (int)input.size(1), hidden, dtype_code(input, "moe_sum"), cur_stream()));
 }
 
+// sglang's moe_sum_reduce (op/sglang/csrc/moe/moe_sum_reduce.cu:226-330): output = sum over dim 1 of input, times the factor
+void moe_sum_reduce(Tensor& input, Tensor& output, double routed_scaling_factor) {
+  MCOP_DEBUG_CALL("moe_sum_reduce", input, output, routed_scaling_factor);
+  TORCH_CHECK(input.is_cuda(), "input must be CUDA tensor");
+  TORCH_CHECK(output.is_cuda(), "output must be CUDA tensor");
+  TORCH_CHECK(input.dim() == 3, "input must be a 3D tensor like [token_num, topk_num, hidden_dim]");
+  TORCH_CHECK(output.dim() == 2, "output must be [token_num, hidden_dim]");
+  TORCH_CHECK(input.size(0) == output.size(0), "token dim mismatch");
+  TORCH_CHECK(input.size(2) == output.size(1), "hidden_dim mismatch");
+  TORCH_CHECK(input.is_contiguous(), "expect input to be contiguous");
+  TORCH_CHECK(output.is_contiguous(), "expect output to be contiguous");
+  TORCH_CHECK(input.scalar_type() == output.scalar_type(), "moe_sum_reduce: input and output dtypes differ");
+  if (input.size(0) == 0 || input.size(2) == 0) return;
+  TORCH_CHECK(input.size(1) >= 1, "moe_sum_reduce: topk_num must be at least 1");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(output));
+  check_rc(mcop_moe_sum_reduce(input.data_ptr(), output.data_ptr(), input.size(0), (int)input.size(1), input.size(2),
+                               routed_scaling_factor, dtype_code(input, "moe_sum_reduce"), cur_stream()));
+}
+
 // torch.ops._moe_C.moe_align_block_size (op/vllm/moe/moe_align_sum_kernels.cu:612-735)
 void moe_align_block_size(Tensor topk_ids, int64_t num_experts, int64_t block_size, Tensor sorted_token_ids, Tensor experts_ids,
                           Tensor num_tokens_post_pad, std::optional<Tensor> maybe_expert_map) {
@@ -892,6 +911,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("force_bf16_attn") = false);
   m.def("store_kv_cache_cuda_interface", &store_kv_cache_cuda_interface);
   m.def("moe_sum", &moe_sum, py::arg("input"), py::arg("output"));
+  m.def("moe_sum_reduce", &moe_sum_reduce, py::arg("input"), py::arg("output"), py::arg("routed_scaling_factor"));
   m.def("moe_align_block_size", &moe_align_block_size, py::arg("topk_ids"), py::arg("num_experts"), py::arg("block_size"),
         py::arg("sorted_token_ids"), py::arg("experts_ids"), py::arg("num_tokens_post_pad"), py::arg("maybe_expert_map") = py::none());
   m.def("moe_softmax_topk", &moe_softmax_topk);

@@ -871,6 +871,18 @@ def moe_sum(inp: torch.Tensor) -> torch.Tensor:
     return acc.to(inp.dtype)
 
 
+def moe_sum_reduce(inp: torch.Tensor, routed_scaling_factor: float) -> torch.Tensor:
+    """sglang moe_sum_reduce, op/sglang/csrc/moe/moe_sum_reduce.cu:119-223: acc = 0 (fp32); acc += float(in[k]) in slot
+    order; acc *= float(factor); one rounding to the element type.  The reference's own check
+    (unit_test/test_moe_sum_reduce_triton.py:77-88) is torch.sum(input, dim=1) * factor compared by cosine similarity."""
+    T, k, H = inp.shape
+    acc = torch.zeros(T, H, dtype=torch.float32)
+    for j in range(k):
+        acc = acc + inp[:, j].float()
+    acc = acc * torch.tensor(routed_scaling_factor, dtype=torch.float32)
+    return acc.to(inp.dtype)
+
+
 def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: int, max_num_tokens_padded: int,
                          expert_map: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """torch.ops._moe_C.moe_align_block_size, op/vllm/moe/moe_align_sum_kernels.cu:86-180 (counting, padded prefix,

@@ -151,6 +151,31 @@ def test_moe_sum_gpu(op, dtype, T, k, H):
     assert torch.allclose(out.float().cpu(), x.sum(dim=1).float(), rtol=tol, atol=8 * tol)  # an ulp of a partial sum of magnitude <= 8
 
 
+def test_oracle_moe_sum_reduce_against_the_reference_test_formula():
+    # unit_test/test_moe_sum_reduce_triton.py: torch.sum(input, dim=1) * factor, DeepSeek shape 32 x 6 x 2048 fp16, cosine similarity
+    x = torch.randn(32, 6, 2048, generator=torch.Generator().manual_seed(0)).half()
+    for factor in (1.0, 2.5):
+        ref = R.moe_sum_reduce(x, factor)
+        lib = torch.sum(x, dim=1) * factor
+        cos = torch.nn.functional.cosine_similarity(ref.flatten().float(), lib.flatten().float(), dim=0)
+        assert cos > 0.99999
+        assert torch.allclose(ref.float(), lib.float(), rtol=2.0 ** -9, atol=2.0 ** -9)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("T,k,H,factor", [(32, 6, 2048, 1.0), (300, 8, 7168, 2.5), (257, 2, 4096, 0.3), (5, 1, 520, 2.5), (9, 3, 100, 1.7)])
+def test_moe_sum_reduce_gpu(op, dtype, T, k, H, factor):
+    x = torch.randn(T, k, H, generator=torch.Generator().manual_seed(T + k)).to(dtype)
+    ref = R.moe_sum_reduce(x, factor)
+    out = torch.full((T, H), float("nan"), dtype=dtype, device=DEV)
+    op.moe_sum_reduce(x.to(DEV), out, factor)
+    view = torch.int16 if dtype != torch.float32 else torch.int32
+    C.assert_equal(out.cpu().view(view), ref.view(view))
+    with pytest.raises(RuntimeError):
+        op.moe_sum_reduce(x.to(DEV), out[:, :H - 4], factor)
+
+
 @gpu
 def test_moe_sum_rejects(op):
     x = torch.zeros(4, 2, 64, dtype=torch.bfloat16, device=DEV)
