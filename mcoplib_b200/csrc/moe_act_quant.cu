@@ -236,9 +236,72 @@ __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(SiluMulParams p
   }
 }
 
+// One WARP per row, for rows of exactly 32 * NVEC vectors of 8 (n = 1024, 2048): the whole row sits in the warp's
+// registers, the abs-max is one warp reduction, and there is no CTA barrier and no bounds test at all; every lane has
+// its 2 * NVEC 16-byte loads in flight before the first use.  Same grid conventions as the kernel above, four rows
+// per CTA step.
+template <typename T, int NVEC>
+__global__ void __launch_bounds__(128) silu_mul_quant_warp(SiluMulParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = p.n;
+  int64_t base = 0, count = p.rows;
+  if (p.mask) {
+    const int64_t g = blockIdx.y;
+    int64_t cnt = load_index(p.mask, p.mask_i64, g);
+    count = cnt < 0 ? 0 : (cnt > p.per_group ? p.per_group : cnt);
+    base = g * p.per_group;
+  }
+  for (int64_t m = (int64_t)blockIdx.x * 4 + warp; m < count; m += (int64_t)gridDim.x * 4) {
+    const int64_t row = base + m;
+    if (p.ids) {
+      const int64_t id = load_index(p.ids, p.ids_i64, row);
+      if (id < p.id_lo || id > p.id_hi) continue;  // uniform over the warp
+    }
+    const T* g = reinterpret_cast<const T*>(p.x) + row * 2 * (int64_t)n;
+    const T* u = g + n;
+    uint4 ga[NVEC], ub[NVEC];
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      ga[i] = ld_nc_u4(g + (lane + i * 32) * 8);
+      ub[i] = ld_nc_u4(u + (lane + i * 32) * 8);
+    }
+    float v[NVEC][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      float a[8], b[8];
+      if constexpr (sizeof(T) == 2 && ElemTraits<T>::code == MCOP_BF16) {
+        unpack_bf16x8(ga[i], a);
+        unpack_bf16x8(ub[i], b);
+      } else {
+        unpack_f16x8(ga[i], a);
+        unpack_f16x8(ub[i], b);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        v[i][q] = silu_mul_value(a[q], b[q]);
+        amax = fmaxf(amax, fabsf(v[i][q]));
+      }
+    }
+    amax = warp_max_nonneg(amax);
+    if (lane == 0) silu_mul_store_scale(p, row, amax);
+    const float mul = amax > 0.f ? 127.0f * (1.0f / amax) : 0.f;
+    int8_t* out = p.out + row * p.out_row_bytes;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) st_cs_u2(out + (lane + i * 32) * 8, quant8_rn_unclamped(v[i], mul));
+  }
+}
+
 template <typename T>
 int launch_silu_mul(const SiluMulParams& p, dim3 grid, bool vec_ok, cudaStream_t s, const char* what) {
   const int nv = p.n >> 3;
+  if (vec_ok && (nv == 128 || nv == 256)) {
+    // the grid was sized for one row per CTA step; a CTA of this kernel takes four
+    grid.x = (grid.x + 3) / 4;
+    if (nv == 128) silu_mul_quant_warp<T, 4><<<grid, 128, 0, s>>>(p);
+    else silu_mul_quant_warp<T, 8><<<grid, 128, 0, s>>>(p);
+    return check_launch(what);
+  }
   if (!vec_ok) silu_mul_quant_kernel<T, 256, 0><<<grid, 256, 0, s>>>(p);
   else if (nv <= 256) silu_mul_quant_kernel<T, 128, 2><<<grid, 128, 0, s>>>(p);
   else if (nv <= 1024) silu_mul_quant_kernel<T, 256, 4><<<grid, 256, 0, s>>>(p);
