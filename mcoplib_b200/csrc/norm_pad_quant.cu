@@ -52,7 +52,8 @@ template <typename T, int FORM> __device__ __forceinline__ float pq_norm_value(f
   return round_to<T>(round_to<T>(round_to<T>(s) * r) * w);
 }
 
-template <typename T, int FORM, int THREADS, int NVEC>
+// FULL: the row is exactly THREADS * NVEC vectors of 8, so the unrolled passes need no bounds test
+template <typename T, int FORM, int THREADS, int NVEC, bool FULL = false>
 __global__ void __launch_bounds__(THREADS) pad_quant_vec(PadQuantParams p) {
   __shared__ float red[33];
   __shared__ double red64[33];
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(THREADS) pad_quant_vec(PadQuantParams p) {
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * THREADS;
-    if (v < nv) {
+    if (FULL || v < nv) {
       float r8[8], w8[8];
       Vec8<T>::load_nc(x + v * 8, s[i]);
       Vec8<T>::load(res + v * 8, r8);
@@ -94,7 +95,7 @@ __global__ void __launch_bounds__(THREADS) pad_quant_vec(PadQuantParams p) {
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * THREADS;
-    if (v < nv) {
+    if (FULL || v < nv) {
       float w8[8], y[8];
       Vec8<T>::load_nc(w + v * 8, w8);
       int c[8];
@@ -160,6 +161,10 @@ int launch_pad_quant(const PadQuantParams& p, int64_t tokens, cudaStream_t s) {
   const unsigned grid = (unsigned)tokens;
   if (vec_ok) {
     if (nv <= 256) pad_quant_vec<T, FORM, 128, 2><<<grid, 128, 0, s>>>(p);
+    else if (nv == 512) pad_quant_vec<T, FORM, 128, 4, true><<<grid, 128, 0, s>>>(p);
+    else if (nv == 640) pad_quant_vec<T, FORM, 160, 4, true><<<grid, 160, 0, s>>>(p);
+    else if (nv == 768) pad_quant_vec<T, FORM, 192, 4, true><<<grid, 192, 0, s>>>(p);
+    else if (nv == 896) pad_quant_vec<T, FORM, 224, 4, true><<<grid, 224, 0, s>>>(p);
     else if (nv <= 1024) pad_quant_vec<T, FORM, 256, 4><<<grid, 256, 0, s>>>(p);
     else if (nv <= 2048) pad_quant_vec<T, FORM, 512, 4><<<grid, 512, 0, s>>>(p);
     else pad_quant_vec<T, FORM, 1024, 4><<<grid, 1024, 0, s>>>(p);

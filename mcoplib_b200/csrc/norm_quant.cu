@@ -602,8 +602,9 @@ __global__ void __launch_bounds__(256) dynamic_int8_quant_kernel(int8_t* q, floa
     qr[i] = (int8_t)q_rn_clamp(ElemTraits<T>::to_float(xr[i]) * inv, -128, 127);
 }
 
-// the same with the row held in registers: one 16-byte (fp32: two) load per 8 elements, one 8-byte store
-template <typename T, int THREADS, int NVEC>
+// the same with the row held in registers: one 16-byte (fp32: two) load per 8 elements, one 8-byte store.
+// FULL: the row is exactly THREADS * NVEC vectors, so the passes need no bounds test (hidden 4096 ... 7168 with THREADS = nv / 4).
+template <typename T, int THREADS, int NVEC, bool FULL = false>
 __global__ void __launch_bounds__(THREADS) dynamic_int8_quant_vec(int8_t* q, float* scales, const T* x, int hidden) {
   __shared__ float red[33];
   const int64_t row = blockIdx.x;
@@ -614,7 +615,7 @@ __global__ void __launch_bounds__(THREADS) dynamic_int8_quant_vec(int8_t* q, flo
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int k = threadIdx.x + i * THREADS;
-    if (k < nv) {
+    if (FULL || k < nv) {
       Vec8<T>::load_nc(xr + k * 8, v[i]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
@@ -627,7 +628,7 @@ __global__ void __launch_bounds__(THREADS) dynamic_int8_quant_vec(int8_t* q, flo
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int k = threadIdx.x + i * THREADS;
-    if (k < nv) {
+    if (FULL || k < nv) {
       st_cs_u2(qr + k * 8, quant8_rn_unclamped(v[i], inv));
     }
   }
@@ -640,6 +641,10 @@ int launch_dynamic_int8_quant(int8_t* out, float* scales, const T* x, int64_t to
   const bool vec_ok = hidden % 8 == 0 && nv <= 4096 && aligned16(x) && (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
   if (!vec_ok) dynamic_int8_quant_kernel<T><<<grid, 256, 0, s>>>(out, scales, x, hidden);
   else if (nv <= 256) dynamic_int8_quant_vec<T, 128, 2><<<grid, 128, 0, s>>>(out, scales, x, hidden);
+  else if (nv == 512) dynamic_int8_quant_vec<T, 128, 4, true><<<grid, 128, 0, s>>>(out, scales, x, hidden);
+  else if (nv == 640) dynamic_int8_quant_vec<T, 160, 4, true><<<grid, 160, 0, s>>>(out, scales, x, hidden);
+  else if (nv == 768) dynamic_int8_quant_vec<T, 192, 4, true><<<grid, 192, 0, s>>>(out, scales, x, hidden);
+  else if (nv == 896) dynamic_int8_quant_vec<T, 224, 4, true><<<grid, 224, 0, s>>>(out, scales, x, hidden);
   else if (nv <= 1024) dynamic_int8_quant_vec<T, 256, 4><<<grid, 256, 0, s>>>(out, scales, x, hidden);
   else if (nv <= 2048) dynamic_int8_quant_vec<T, 512, 4><<<grid, 512, 0, s>>>(out, scales, x, hidden);
   else dynamic_int8_quant_vec<T, 1024, 4><<<grid, 1024, 0, s>>>(out, scales, x, hidden);

@@ -29,7 +29,7 @@ def _case(rows_per_expert, H, seed=0):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("rows_per_expert,H", [([5, 0, 9, 6], 256), ([300, 200, 0, 17, 1], 2048), ([64] * 8, 7168),
-                                                ([3, 4], 100), ([10, 10], 16384), ([0, 0, 7], 520)])
+                                                ([3, 4], 100), ([10, 10], 16384), ([0, 0, 7], 520), ([7, 3, 0, 50], 1024), ([1, 2, 2], 2048)])
 def test_kernel_matches_oracle(rows_per_expert, H):
     from mcoplib_b200 import op
     from tests.gpu_util import DEV, Canary

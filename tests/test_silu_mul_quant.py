@@ -45,7 +45,8 @@ def _x(rows, n, dtype, seed=0):
 @pytest.mark.gpu
 @pytest.mark.parametrize("rows,n,dtype,idt", [(37, 256, torch.bfloat16, torch.int64), (300, 2048, torch.bfloat16, torch.int32),
                                               (64, 7168, torch.float16, torch.int64), (9, 100, torch.bfloat16, torch.int32),
-                                              (12, 16384, torch.bfloat16, torch.int64), (5, 36, torch.float16, torch.int32)])
+                                              (12, 16384, torch.bfloat16, torch.int64), (5, 36, torch.float16, torch.int32),
+                                              (131, 1024, torch.float16, torch.int64), (3, 2048, torch.float16, torch.int32)])
 def test_reorder_quant_matches_oracle(rows, n, dtype, idt):
     from mcoplib_b200 import op
     from tests.gpu_util import DEV
@@ -78,7 +79,7 @@ def test_unmasked_form_processes_every_row():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("G,M,n,counts,dtype,mdt", [(2, 40, 2048, [17, 40], torch.bfloat16, torch.int32),
-                                                    (1, 33, 512, [20], torch.bfloat16, torch.int64),
+                                                    (1, 33, 512, [20], torch.bfloat16, torch.int64), (3, 21, 1024, [21, 0, 5], torch.float16, torch.int64),
                                                     (5, 16, 7168, [0, 16, 3, 99, 1], torch.float16, torch.int32),
                                                     (3, 9, 36, [9, 0, 4], torch.bfloat16, torch.int64)])
 def test_mask_quant_pack_matches_oracle(G, M, n, counts, dtype, mdt):
