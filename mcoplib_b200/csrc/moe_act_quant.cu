@@ -43,7 +43,8 @@ __device__ __forceinline__ float swiglu_value(float gate, float up, float sm) {
   return up * sig * sm;
 }
 
-template <int THREADS, int NVEC>
+// FULL: the row is exactly THREADS * NVEC vectors of 8 (no bounds test in the unrolled passes)
+template <int THREADS, int NVEC, bool FULL>
 __global__ void __launch_bounds__(THREADS) swiglu_quant_vec(SwigluParams p) {
   __shared__ float red[33];
   const int64_t row = blockIdx.x;
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(THREADS) swiglu_quant_vec(SwigluParams p) {
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int k = threadIdx.x + i * THREADS;
-    if (k < nv) {
+    if (FULL || k < nv) {
       float a[8], b[8];
       Vec8<__nv_bfloat16>::load_nc(g + k * 8, a);
       Vec8<__nv_bfloat16>::load_nc(u + k * 8, b);
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(THREADS) swiglu_quant_vec(SwigluParams p) {
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int k = threadIdx.x + i * THREADS;
-    if (k < nv) {
+    if (FULL || k < nv) {
       st_cs_u2(out + k * 8, quant8_rn_unclamped(v[i], mul));
     }
   }
@@ -123,10 +124,15 @@ extern "C" int mcop_moe_swiglu_quant_i8(const void* x, const float* smooth, cons
   cudaStream_t s = (cudaStream_t)stream;
   const unsigned grid = (unsigned)rows;
   if (!vec_ok) swiglu_quant_any<<<grid, 256, 0, s>>>(p);
-  else if (nv <= 256) swiglu_quant_vec<128, 2><<<grid, 128, 0, s>>>(p);
-  else if (nv <= 1024) swiglu_quant_vec<256, 4><<<grid, 256, 0, s>>>(p);
-  else if (nv <= 2048) swiglu_quant_vec<512, 4><<<grid, 512, 0, s>>>(p);
-  else swiglu_quant_vec<1024, 4><<<grid, 1024, 0, s>>>(p);
+  else if (nv == 256) swiglu_quant_vec<128, 2, true><<<grid, 128, 0, s>>>(p);
+  else if (nv <= 256) swiglu_quant_vec<128, 2, false><<<grid, 128, 0, s>>>(p);
+  else if (nv == 512) swiglu_quant_vec<128, 4, true><<<grid, 128, 0, s>>>(p);
+  else if (nv == 896) swiglu_quant_vec<224, 4, true><<<grid, 224, 0, s>>>(p);
+  else if (nv == 1024) swiglu_quant_vec<256, 4, true><<<grid, 256, 0, s>>>(p);
+  else if (nv <= 1024) swiglu_quant_vec<256, 4, false><<<grid, 256, 0, s>>>(p);
+  else if (nv == 2048) swiglu_quant_vec<512, 4, true><<<grid, 512, 0, s>>>(p);
+  else if (nv <= 2048) swiglu_quant_vec<512, 4, false><<<grid, 512, 0, s>>>(p);
+  else swiglu_quant_vec<1024, 4, false><<<grid, 1024, 0, s>>>(p);
   return check_launch("moe_swiglu_quant_i8");
 }
 
