@@ -100,6 +100,8 @@ class Chain5:
     def __init__(self, tokens, hidden=7168, experts=8, topk=2, t0=0, device="cuda", gen_device="cuda", pinned_host=False):
         from mcoplib_b200 import workloads as W
         self.T, self.H, self.E, self.k, self.W = tokens, hidden, experts, topk, W
+        # more than 64 tiles of 512 tokens: the scatter's histogram scan is a kernel of its own
+        self.launches_per_step = 6 + (1 if (tokens + 511) // 512 > 64 else 0)
         self.dev = device
         d = W.norm_quant_inputs(tokens, hidden, t0, 0, gen_device, device)
         self.x, self.res, self.w = d["x"], d["residual"], d["weight"]
@@ -181,6 +183,7 @@ class Route3:
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W
         self.T, self.H, self.E, self.k, self.W = tokens, 7168, 256, 8, W
+        self.launches_per_step = 5 + (1 if (tokens + 511) // 512 > 64 else 0)  # + the scatter's scan kernel
         r = W.router_inputs(tokens, 256, t0, 0, gen_device, device)
         self.logits, self.bias = r["logits"], r["bias"]
         d = W.dispatch_inputs(tokens, 7168, 256, 8, t0, 0, gen_device, device)
@@ -244,7 +247,7 @@ class Next6:
             "silu_mul+quant, topk_softmax, moe_sum, moe_align_block_size")
     kernels = ["norm_quant_padded", "norm_quant_norm_out", "dynamic_int8_quant", "swiglu_quant", "silu_mul_quant", "topk_softmax",
                "moe_sum", "moe_align_block_size"]
-    launches_per_step = 9   # one kernel each, two for moe_align_block_size
+    launches_per_step = 10   # one kernel each, three (rank, scan, fill) for moe_align_block_size at this size
 
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W
