@@ -369,7 +369,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_RESULT_OUT or sys.stdout, flush=True)
     return 0
 
 
@@ -627,10 +627,13 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": r["threads"], "kind": "port",
                                     "sample": f"{len(r['seconds'])} passes over {r['tokens']} tokens of the same chain, torch CPU "
                                               f"oracle, {r['threads']} threads, {total:.1f} s of CPU work"}
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=_RESULT_OUT or sys.stdout, flush=True)
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+_RESULT_OUT = None  # the process's original standard output, kept for the one result line
 
 
 def main():
@@ -657,6 +660,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    # Standard output carries exactly one JSON line.  Libraries print there too (NCCL's version banner on the first
+    # collective), so file descriptor 1 is pointed at standard error for everything but that line.
+    global _RESULT_OUT
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3  # timing rule: at least three untimed steps
     if args.impl == "reference":
