@@ -293,6 +293,41 @@ def test_gather_linearity_at_full_size(op):
     assert torch.allclose(out.float(), w.sum(-1, keepdim=True).expand(T, H), rtol=1e-2)
 
 
+def test_scatter_config5_full_size_properties(op):
+    """Configuration 5 sizes (262,144 tokens x 7168, top-2 of 8: 524,288 rows, 512 tiles - the separate scan kernel):
+    the permutation is a bijection ordered by (expert, token), counts equal the histogram of the ids, every row spans
+    the code range, and de-quantised rows reproduce (x * w) * smooth to half a quantisation step (sampled rows)."""
+    T, H, E, k = 262144, 7168, 8, 2
+    logits = W.router_inputs(T, E, gen_device=DEV)["logits"]
+    w = torch.empty(T, k, device=DEV); ids = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    op.moe_softmax_topk(w, ids, logits, True)
+    hid = W.per_token("randn", 21, 0, T, H, torch.bfloat16, gen_device=DEV)
+    smooth = 0.5 + torch.rand(E, H, device=DEV)
+    Rn = T * k
+    rows = torch.empty(Rn, H, dtype=torch.int8, device=DEV); sc = torch.empty(Rn, device=DEV)
+    r2t = torch.empty(Rn, dtype=torch.int32, device=DEV); cnt = torch.empty(E, dtype=torch.int32, device=DEV)
+    st = torch.empty(E, dtype=torch.int32, device=DEV); t2r = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    op.moe_scatter_dynamic_quant(hid, ids, w, smooth, rows, sc, r2t, cnt, st, E, 0, 0, t2r)
+    assert int(cnt.sum()) == Rn and torch.equal(st, (torch.cumsum(cnt, 0) - cnt).int())
+    assert torch.equal(torch.bincount(ids.reshape(-1).long(), minlength=E).int(), cnt)
+    flat = t2r.reshape(-1)
+    assert torch.equal(torch.sort(flat).values, torch.arange(Rn, dtype=torch.int32, device=DEV))
+    assert torch.equal(r2t[flat.long()], torch.arange(T, device=DEV).repeat_interleave(k).int())
+    seg = torch.repeat_interleave(torch.arange(E, device=DEV), cnt.long())
+    assert torch.equal(seg.int(), ids.reshape(-1)[torch.argsort(flat)])
+    tok = r2t.long()
+    assert bool(((tok[1:] > tok[:-1]) | (seg[1:] != seg[:-1])).all())
+    sample = torch.randint(0, Rn, (4096,), device=DEV, generator=torch.Generator(device=DEV).manual_seed(0))
+    srows = rows[sample].float()
+    assert int(srows.abs().amax(1).min()) == 127
+    t_of = r2t[sample].long(); e_of = seg[sample]
+    slot = (ids[t_of] == e_of.int().unsqueeze(1)).float().argmax(1)
+    v = hid[t_of].float() * w[t_of, slot].unsqueeze(1) * smooth[e_of]
+    err = (srows * sc[sample].unsqueeze(1) - v).abs()
+    assert bool((err <= sc[sample].unsqueeze(1) * (0.5 + 1e-3) + 1e-12).all())
+    assert torch.allclose(sc[sample], v.abs().amax(1) / 127.0, rtol=1e-6)
+
+
 def test_c_abi_dispatch_called_directly(op):
     from mcoplib_b200 import cabi
     from tests.gpu_util import stream_ptr
