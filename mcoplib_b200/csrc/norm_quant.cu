@@ -63,7 +63,9 @@ __device__ __forceinline__ double block_sum_f64(double v, double* red) {
   return r;
 }
 
-template <typename T, typename WT, int MODE, int THREADS, int NVEC>
+// FULL: the row is exactly THREADS * NVEC vectors of 8 (hidden 4096 ... 7168 with THREADS = hidden / 32): no bounds
+// test in the unrolled passes.
+template <typename T, typename WT, int MODE, int THREADS, int NVEC, bool FULL = false>
 __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
   __shared__ float red[33];
   __shared__ double red64[33];
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * THREADS;
-    if (v < nv) {
+    if (FULL || v < nv) {
       // x is overwritten by this kernel only in kFusedAdd: use the coherent load there.
       if (MODE == kFusedAdd) Vec8<T>::load(x + v * 8, s[i]); else Vec8<T>::load_nc(x + v * 8, s[i]);
       if (rin) {
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
       }
       if (rout) Vec8<T>::store(rout + v * 8, s[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += (double)s[i][j] * (double)s[i][j];
+      for (int j = 0; j < 8; ++j) ss = fma((double)s[i][j], (double)s[i][j], ss);  // exact product: one instruction, same value
       if (MODE == kSmoothQuant) {
         // the later phases of the reference read the ROUNDED after_res back
 #pragma unroll
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * THREADS;
-      if (v < nv) {
+      if (FULL || v < nv) {
         float wv[8];
         Vec8<WT>::load_nc(w + v * 8, wv);
 #pragma unroll
@@ -129,7 +131,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * THREADS;
-    if (v < nv) {
+    if (FULL || v < nv) {
       float wv[8];
       Vec8<WT>::load_nc(w + v * 8, wv);
       if (MODE == kSmoothQuant) {
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(THREADS) norm_rows_vec(NormParams p) {
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * THREADS;
-    if (v < nv) {
+    if (FULL || v < nv) {
       int c[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(s[i][j] * inv, lo, 127);
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(256) norm_rows_any(NormParams p) {
     if (rin) s += ElemTraits<T>::to_float(rin[i]);
     if (MODE == kFusedAdd) s = round_to<T>(s);
     if (rout) rout[i] = ElemTraits<T>::from_float(s);
-    ss += (double)s * (double)s;
+    ss = fma((double)s, (double)s, ss);
     if (MODE == kSmoothQuant) s = round_to<T>(s);
     keep[i] = s;
   }
@@ -481,6 +483,10 @@ int launch_norm(const NormParams& p, int64_t tokens, bool vec_ok, cudaStream_t s
   }
   if (vec_ok && nv <= 4096) {
     if (nv <= 256) norm_rows_vec<T, WT, MODE, 128, 2><<<grid, 128, 0, stream>>>(p);
+    else if (nv == 512) norm_rows_vec<T, WT, MODE, 128, 4, true><<<grid, 128, 0, stream>>>(p);
+    else if (nv == 640) norm_rows_vec<T, WT, MODE, 160, 4, true><<<grid, 160, 0, stream>>>(p);
+    else if (nv == 768) norm_rows_vec<T, WT, MODE, 192, 4, true><<<grid, 192, 0, stream>>>(p);
+    else if (nv == 896) norm_rows_vec<T, WT, MODE, 224, 4, true><<<grid, 224, 0, stream>>>(p);
     else if (nv <= 1024) norm_rows_vec<T, WT, MODE, 256, 4><<<grid, 256, 0, stream>>>(p);
     else if (nv <= 2048) norm_rows_vec<T, WT, MODE, 512, 4><<<grid, 512, 0, stream>>>(p);
     else norm_rows_vec<T, WT, MODE, 1024, 4><<<grid, 1024, 0, stream>>>(p);
@@ -556,7 +562,7 @@ __global__ void head_rmsnorm_kernel(T* out, const T* x, const WT* w, int64_t tok
   double ss = 0.0;
   for (int i = lane; i < head_dim; i += 32) {
     const float v = ElemTraits<T>::to_float(src[i]);
-    ss += (double)v * (double)v;
+    ss = fma((double)v, (double)v, ss);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
