@@ -272,7 +272,11 @@ __device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
 //   true  - a barrier before the stage is read and the classic two-barrier block reductions (five per row).
 // Measured on B200: with 7 warps (hidden 7168) the loose form is 6 % faster (6.36 vs 5.97 TB/s); with 8 warps
 // (hidden 8192) the lock-step form is 14 % faster (6.26 vs 5.50 TB/s), so the launcher picks per CTA size.
-template <int THREADS, int NVEC, bool FULL, bool LOCKSTEP, bool NORM_OUT>
+// PMODE 0: norm + per-token int8 quant (a2 contract: the variance is taken from the unrounded fp32 sum).
+// PMODE 1: fused_add_rms_norm (a1 contract: r = bf16(x + res) is rounded BEFORE the variance; the normalised row
+//          bf16(bf16(r * rsqrt) * w) goes to p.out, which is x itself; nothing is quantised and the row needs one
+//          barrier less).
+template <int THREADS, int NVEC, bool FULL, bool LOCKSTEP, bool NORM_OUT, int PMODE = 0>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_bf16_pipe(NormParams p, int64_t tokens, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float red[2][32];
@@ -337,7 +341,9 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
           unpack_bf16x8(lds_u4(xs + row_bytes + v * 16), r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) sv[k][j] += r[j];
-          st_u4(rout + row * (int64_t)H + v * 8, pack_bf16x8(sv[k]));
+          const uint4 packed = pack_bf16x8(sv[k]);
+          st_u4(rout + row * (int64_t)H + v * 8, packed);
+          if constexpr (PMODE == 1) unpack_bf16x8(packed, sv[k]);  // the rounded sum is what gets normalised
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss = fma((double)sv[k][j], (double)sv[k][j], ss);  // the product is exact in double
@@ -378,6 +384,15 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
         n2[k][j] = *reinterpret_cast<const uint32_t*>(&nn);
         amax2 = __hmax2(amax2, __habs2(nn));
       }
+    }
+    if constexpr (PMODE == 1) {
+#pragma unroll
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (FULL || v < nv)
+          st_u4(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.out_stride + v * 8, make_uint4(n2[k][0], n2[k][1], n2[k][2], n2[k][3]));
+      }
+      continue;
     }
     float amax = fmaxf(__low2float(amax2), __high2float(amax2));  // never negative, never NaN
     if constexpr (LOCKSTEP) {
@@ -427,6 +442,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
 
 
 // Returns MCOP_OK / an error, or 1 when the shape does not fit the pipelined kernel.
+template <int PMODE>
 inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t stream) {
   const int nv = p.hidden >> 3;
   const size_t row_bytes = (size_t)p.hidden * 2;
@@ -446,7 +462,7 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > tokens) grid = tokens;
   int* err = pipe_error_ptr();
-  const bool no = p.out != nullptr;  // also write the normalised row
+  const bool no = PMODE == 0 && p.out != nullptr;  // also write the normalised row
   auto launch = [&](auto kernel, int) -> int {
     const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 220 * 1024);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "norm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -455,18 +471,18 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   };
 #define MCOP_NORM_TILED(T, SLOT)                                                                        \
   if (threads == T && full && T != 224)                                                                 \
-    return no ? launch(norm_quant_bf16_pipe<T, 4, true, false, true>, SLOT) : launch(norm_quant_bf16_pipe<T, 4, true, false, false>, SLOT + 1);
+    return no ? launch(norm_quant_bf16_pipe<T, 4, true, false, true, PMODE>, SLOT) : launch(norm_quant_bf16_pipe<T, 4, true, false, false, PMODE>, SLOT + 1);
   MCOP_NORM_TILED(128, 8)
   MCOP_NORM_TILED(160, 10)
   MCOP_NORM_TILED(192, 12)
 #undef MCOP_NORM_TILED
   if (threads == 224) {
-    if (full) return no ? launch(norm_quant_bf16_pipe<224, 4, true, false, true>, 0) : launch(norm_quant_bf16_pipe<224, 4, true, false, false>, 1);
-    return no ? launch(norm_quant_bf16_pipe<224, 4, false, false, true>, 2) : launch(norm_quant_bf16_pipe<224, 4, false, false, false>, 3);
+    if (full) return no ? launch(norm_quant_bf16_pipe<224, 4, true, false, true, PMODE>, 0) : launch(norm_quant_bf16_pipe<224, 4, true, false, false, PMODE>, 1);
+    return no ? launch(norm_quant_bf16_pipe<224, 4, false, false, true, PMODE>, 2) : launch(norm_quant_bf16_pipe<224, 4, false, false, false, PMODE>, 3);
   }
   if (threads == 256)
-    return no ? launch(norm_quant_bf16_pipe<256, 4, false, true, true>, 4) : launch(norm_quant_bf16_pipe<256, 4, false, true, false>, 5);
-  return no ? launch(norm_quant_bf16_pipe<512, 4, false, true, true>, 6) : launch(norm_quant_bf16_pipe<512, 4, false, true, false>, 7);
+    return no ? launch(norm_quant_bf16_pipe<256, 4, false, true, true, PMODE>, 4) : launch(norm_quant_bf16_pipe<256, 4, false, true, false, PMODE>, 5);
+  return no ? launch(norm_quant_bf16_pipe<512, 4, false, true, true, PMODE>, 6) : launch(norm_quant_bf16_pipe<512, 4, false, true, false, PMODE>, 7);
 }
 
 template <typename T, typename WT, int MODE>
@@ -477,8 +493,15 @@ int launch_norm(const NormParams& p, int64_t tokens, bool vec_ok, cudaStream_t s
   const dim3 grid((unsigned)tokens);
   if constexpr (MODE == kQuant && std::is_same<T, __nv_bfloat16>::value) {
     if (vec_ok && nv <= 2048) {
-      const int rc = launch_norm_pipe(p, tokens, stream);
+      const int rc = launch_norm_pipe<0>(p, tokens, stream);
       if (rc != 1) return rc;  // 1 = not applicable, fall through to the row-per-CTA kernel
+    }
+  }
+  if constexpr (MODE == kFusedAdd && std::is_same<T, __nv_bfloat16>::value && std::is_same<WT, __nv_bfloat16>::value) {
+    // a1 on bf16 rows streams through the same ring as a2 once there are a few waves of rows
+    if (vec_ok && nv <= 2048 && p.residual_in && tokens >= 1024) {
+      const int rc = launch_norm_pipe<1>(p, tokens, stream);
+      if (rc != 1) return rc;
     }
   }
   if (vec_ok && nv <= 4096) {

@@ -137,7 +137,8 @@ def test_torch_library_ops(op):
     C.assert_equal(bits(res), bits(r2_ref)); C.assert_close(x, o_ref)
 
 
-@pytest.mark.parametrize("T,H", [(1, 8), (64, 4096), (7, 1030), (33, 8192), (5, 777)])
+@pytest.mark.parametrize("T,H", [(1, 8), (64, 4096), (7, 1030), (33, 8192), (5, 777),
+                                 (1500, 7168), (1100, 8192), (2000, 4096), (1030, 1032), (1024, 5120), (1300, 16384)])  # >= 1024 rows: the pipelined kernel
 def test_fused_add_rms_norm(op, T, H):
     d = W.norm_quant_inputs(T, H)
     o_ref, r_ref = R.fused_add_rms_norm(d["x"], d["residual"], d["weight"], 1e-6)
@@ -146,6 +147,25 @@ def test_fused_add_rms_norm(op, T, H):
     C.assert_equal(bits(res), bits(r_ref), "residual"); C.assert_close(x, o_ref, "out")
     # at most a handful of bf16 roundings may flip through a 1-ulp difference of the row scalar
     assert int((bits(x) != bits(o_ref)).sum()) <= max(2, x.numel() // 2000)
+
+
+def test_fused_add_rms_norm_pipelined_and_row_kernels_agree_bit_for_bit(op):
+    """1500 rows go through the pipelined kernel, their first 1000 alone through the row-per-CTA kernel: same bits;
+    also with a strided input."""
+    d = W.norm_quant_inputs(1500, 7168)
+    w = d["weight"].to(DEV)
+    xa, ra = d["x"].to(DEV), d["residual"].to(DEV)
+    op.fused_add_rms_norm(xa, ra, w, 1e-6)
+    xb, rb = d["x"][:1000].to(DEV), d["residual"][:1000].to(DEV)
+    op.fused_add_rms_norm(xb, rb, w, 1e-6)
+    C.assert_equal(bits(xa[:1000]), bits(xb)); C.assert_equal(bits(ra[:1000]), bits(rb))
+    big = torch.zeros(1500, 2 * 7168, dtype=torch.bfloat16, device=DEV)
+    view = big[:, 7168:]
+    view.copy_(d["x"])
+    rc = d["residual"].to(DEV)
+    op.fused_add_rms_norm(view, rc, w, 1e-6)
+    C.assert_equal(bits(view), bits(xa)); C.assert_equal(bits(rc), bits(ra))
+    assert float(big[:, :7168].abs().max()) == 0
 
 
 def test_fused_add_rms_norm_strided_input(op):
