@@ -276,6 +276,8 @@ __device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
 // PMODE 1: fused_add_rms_norm (a1 contract: r = bf16(x + res) is rounded BEFORE the variance; the normalised row
 //          bf16(bf16(r * rsqrt) * w) goes to p.out, which is x itself; nothing is quantised and the row needs one
 //          barrier less).
+// PMODE 2: rms_norm (a4 contract: fp32 products (s * d) * w with d = rsqrt or, with rms_div, its reciprocal; one rounding;
+//          residual and after_res optional).
 template <int THREADS, int NVEC, bool FULL, bool LOCKSTEP, bool NORM_OUT, int PMODE = 0>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_bf16_pipe(NormParams p, int64_t tokens, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -342,7 +344,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
 #pragma unroll
           for (int j = 0; j < 8; ++j) sv[k][j] += r[j];
           const uint4 packed = pack_bf16x8(sv[k]);
-          st_u4(rout + row * (int64_t)H + v * 8, packed);
+          if (PMODE != 2 || rout) st_u4(rout + row * (int64_t)H + v * 8, packed);  // (rms_norm's after_res is optional)
           if constexpr (PMODE == 1) unpack_bf16x8(packed, sv[k]);  // the rounded sum is what gets normalised
         }
 #pragma unroll
@@ -372,6 +374,21 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     }
     const float r = inv_rms(ss, H, p.eps);
+    if constexpr (PMODE == 2) {
+      const float d = p.rms_div ? 1.0f / r : r;
+#pragma unroll
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (FULL || v < nv) {
+          float wf[8], o[8];
+          unpack_bf16x8(w2[k], wf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(__fmul_rn(sv[k][j], d), wf[j]);
+          st_u4(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.out_stride + v * 8, pack_bf16x8(o));
+        }
+      }
+      continue;
+    }
     uint32_t n2[NVEC][4];
     __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
@@ -495,6 +512,12 @@ int launch_norm(const NormParams& p, int64_t tokens, bool vec_ok, cudaStream_t s
     if (vec_ok && nv <= 2048) {
       const int rc = launch_norm_pipe<0>(p, tokens, stream);
       if (rc != 1) return rc;  // 1 = not applicable, fall through to the row-per-CTA kernel
+    }
+  }
+  if constexpr (MODE == kPlain && std::is_same<T, __nv_bfloat16>::value && std::is_same<WT, __nv_bfloat16>::value) {
+    if (vec_ok && nv >= 256 && nv <= 2048 && tokens >= 1024) {
+      const int rc = launch_norm_pipe<2>(p, tokens, stream);
+      if (rc != 1) return rc;
     }
   }
   if constexpr (MODE == kFusedAdd && std::is_same<T, __nv_bfloat16>::value && std::is_same<WT, __nv_bfloat16>::value) {

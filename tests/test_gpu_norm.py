@@ -204,7 +204,8 @@ def test_fused_rms_norm_dq_nine_arguments(op, wdtype, T, H, with_res):
 
 
 @pytest.mark.parametrize("rms_div", [False, True])
-@pytest.mark.parametrize("T,H,with_res", [(8, 1024, True), (5, 4096, False), (4, 999, True)])
+@pytest.mark.parametrize("T,H,with_res", [(8, 1024, True), (5, 4096, False), (4, 999, True),
+                                          (1100, 7168, True), (1500, 4096, False), (1024, 8192, True), (1200, 2056, False)])  # last four: pipelined kernel
 def test_rms_norm(op, rms_div, T, H, with_res, golden):
     d = W.norm_quant_inputs(T, H)
     res = d["residual"] if with_res else None
@@ -220,6 +221,24 @@ def test_rms_norm(op, rms_div, T, H, with_res, golden):
         out = torch.empty(8, 1024, dtype=torch.bfloat16, device=DEV); ar = torch.empty_like(out)
         op.rms_norm(out, g["x"].to(DEV), g["weight"].to(DEV), 1e-6, ar, g["residual"].to(DEV), True)
         C.assert_close(out, g["out"], key, rel=2e-2, abs_=2e-2)
+
+
+@pytest.mark.parametrize("rms_div", [False, True])
+def test_rms_norm_pipelined_and_row_kernels_agree_bit_for_bit(op, rms_div):
+    """1400 rows (pipelined kernel) against their first 900 alone (row-per-CTA kernel); with a residual and its
+    after_res output, and without a residual."""
+    d = W.norm_quant_inputs(1400, 7168)
+    x, res, w = d["x"].to(DEV), d["residual"].to(DEV), d["weight"].to(DEV)
+    for with_res, with_ar in ((True, True), (False, False)):  # the shim wants residual and after_res together
+        oa = torch.empty(1400, 7168, dtype=torch.bfloat16, device=DEV); ob = torch.empty(900, 7168, dtype=torch.bfloat16, device=DEV)
+        ara = torch.empty_like(oa) if with_ar else None
+        arb = torch.empty_like(ob) if with_ar else None
+        op.rms_norm(oa, x, w, 1e-6, ara, res if with_res else None, rms_div)
+        op.rms_norm(ob, x[:900], w, 1e-6, arb, res[:900] if with_res else None, rms_div)
+        C.assert_equal(bits(oa[:900]), bits(ob))
+        if with_ar:
+            C.assert_equal(bits(ara[:900]), bits(arb))
+    assert torch.equal(bits(x), bits(d["x"].to(DEV))) and torch.equal(bits(res), bits(d["residual"].to(DEV)))  # inputs untouched
 
 
 def test_head_rms_norm_and_scale_dynamic_quant(op, golden):
