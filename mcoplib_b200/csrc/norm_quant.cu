@@ -278,6 +278,9 @@ __device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
 //          barrier less).
 // PMODE 2: rms_norm (a4 contract: fp32 products (s * d) * w with d = rsqrt or, with rms_div, its reciprocal; one rounding;
 //          residual and after_res optional).
+// PMODE 3: the 9-argument norm + smooth quant (a3 contract: after_res = bf16(x + res) always written; the variance from
+//          the unrounded sum; nw = (after_res / rsqrt) * w with after_res read back ROUNDED, after_norm = bf16(nw);
+//          y = nw * smooth; scale = absmax(y) / 127; codes clamped to +-127).
 template <int THREADS, int NVEC, bool FULL, bool LOCKSTEP, bool NORM_OUT, int PMODE = 0>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_bf16_pipe(NormParams p, int64_t tokens, int stages, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -319,6 +322,15 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
     w2[i] = (FULL || v < nv) ? ld_nc_u4(reinterpret_cast<const __nv_bfloat16*>(p.weight) + v * 8) : make_uint4(0, 0, 0, 0);
   }
 
+  uint4 sm2[PMODE == 3 ? NVEC : 1];  // PMODE 3: the smooth scale too
+  if constexpr (PMODE == 3) {
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      sm2[i] = (FULL || v < nv) ? ld_nc_u4(reinterpret_cast<const __nv_bfloat16*>(p.smooth) + v * 8) : make_uint4(0, 0, 0, 0);
+    }
+  }
+
   int64_t i = 0;
   RingPos pos;
   uint32_t flip = 0;
@@ -337,18 +349,22 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
     for (int k = 0; k < NVEC; ++k) {
       const int v = threadIdx.x + k * THREADS;
       if (FULL || v < nv) {
-        unpack_bf16x8(lds_u4(xs + v * 16), sv[k]);
+        uint4 packed = lds_u4(xs + v * 16);
+        unpack_bf16x8(packed, sv[k]);
         if (has_res) {
           float r[8];
           unpack_bf16x8(lds_u4(xs + row_bytes + v * 16), r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) sv[k][j] += r[j];
-          const uint4 packed = pack_bf16x8(sv[k]);
+          packed = pack_bf16x8(sv[k]);
           if (PMODE != 2 || rout) st_u4(rout + row * (int64_t)H + v * 8, packed);  // (rms_norm's after_res is optional)
           if constexpr (PMODE == 1) unpack_bf16x8(packed, sv[k]);  // the rounded sum is what gets normalised
+        } else if constexpr (PMODE == 3) {
+          st_u4(rout + row * (int64_t)H + v * 8, packed);  // after_res is written even without a residual (= x)
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss = fma((double)sv[k][j], (double)sv[k][j], ss);  // the product is exact in double
+        if constexpr (PMODE == 3) unpack_bf16x8(packed, sv[k]);  // the later phases read the ROUNDED after_res back
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) sv[k][j] = 0.f;
@@ -391,6 +407,26 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
     }
     uint32_t n2[NVEC][4];
     __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
+    float amax3 = 0.f;
+    if constexpr (PMODE == 3) {
+      // literal convention of the 9-argument operator: divide by rsqrt; after_norm = T(nw), y = nw * smooth stays fp32
+#pragma unroll
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (FULL || v < nv) {
+          float wf[8], sf[8], nw[8];
+          unpack_bf16x8(w2[k], wf);
+          unpack_bf16x8(sm2[k], sf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            nw[j] = __fmul_rn(__fdiv_rn(sv[k][j], r), wf[j]);
+            sv[k][j] = __fmul_rn(nw[j], sf[j]);
+            amax3 = fmaxf(amax3, fabsf(sv[k][j]));
+          }
+          st_u4(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.out_stride + v * 8, pack_bf16x8(nw));
+        }
+      }
+    } else
 #pragma unroll
     for (int k = 0; k < NVEC; ++k) {
       const uint32_t wv[4] = {w2[k].x, w2[k].y, w2[k].z, w2[k].w};
@@ -411,7 +447,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
       }
       continue;
     }
-    float amax = fmaxf(__low2float(amax2), __high2float(amax2));  // never negative, never NaN
+    float amax = PMODE == 3 ? amax3 : fmaxf(__low2float(amax2), __high2float(amax2));  // never negative, never NaN
     if constexpr (LOCKSTEP) {
       amax = block_reduce<true>(amax, &red[0][0]);
     } else {
@@ -419,6 +455,23 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
       if (lane == 0) red[flip][warp] = amax;
       __syncthreads();  // second barrier of the row
       amax = warp_max_nonneg(lane < NWARP ? red[flip][lane] : 0.f);
+    }
+    if constexpr (PMODE == 3) {
+      const float scale3 = (float)((double)amax / 127.0);
+      const float inv3 = 1.0f / scale3;
+      if (threadIdx.x == 0) p.scales[row] = scale3;
+      int8_t* q3 = p.q + row * (int64_t)H;
+#pragma unroll
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (FULL || v < nv) {
+          int c[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(sv[k][j] * inv3, -127, 127);
+          st_cs_u2(q3 + v * 8, pack_i8x8(c));
+        }
+      }
+      continue;
     }
     const bool clamp = p.scale_ub != nullptr;  // only an upper bound on the scale can push codes out of range
     if (clamp) amax = fminf(amax, *p.scale_ub);
@@ -512,6 +565,12 @@ int launch_norm(const NormParams& p, int64_t tokens, bool vec_ok, cudaStream_t s
     if (vec_ok && nv <= 2048) {
       const int rc = launch_norm_pipe<0>(p, tokens, stream);
       if (rc != 1) return rc;  // 1 = not applicable, fall through to the row-per-CTA kernel
+    }
+  }
+  if constexpr (MODE == kSmoothQuant && std::is_same<T, __nv_bfloat16>::value && std::is_same<WT, __nv_bfloat16>::value) {
+    if (vec_ok && nv >= 256 && nv <= 2048 && tokens >= 1024) {
+      const int rc = launch_norm_pipe<3>(p, tokens, stream);
+      if (rc != 1) return rc;
     }
   }
   if constexpr (MODE == kPlain && std::is_same<T, __nv_bfloat16>::value && std::is_same<WT, __nv_bfloat16>::value) {

@@ -186,7 +186,8 @@ def test_fused_add_rms_norm_strided_input(op):
 
 
 @pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("T,H,with_res", [(16, 4096, True), (9, 1030, True), (16, 7168, False), (3, 333, False)])
+@pytest.mark.parametrize("T,H,with_res", [(16, 4096, True), (9, 1030, True), (16, 7168, False), (3, 333, False),
+                                          (1100, 7168, True), (1300, 4096, False), (1024, 8192, True), (1200, 2056, False)])  # last four (bf16 weights): pipelined kernel
 def test_fused_rms_norm_dq_nine_arguments(op, wdtype, T, H, with_res):
     """PARITY UNPINNED in the reference; checked against the restatement of op/fused_rms_norm_dq.cu:69-186."""
     d = W.norm_quant_inputs(T, H)
@@ -201,6 +202,27 @@ def test_fused_rms_norm_dq_nine_arguments(op, wdtype, T, H, with_res):
                                         res.to(DEV) if with_res else None)
     C.assert_equal(bits(ar), bits(ar_ref), "after_res"); C.assert_close(an, an_ref, "after_norm")
     C.assert_close(sc.reshape(-1, 1), s_ref, "scales"); C.assert_codes(out, q_ref)
+
+
+@pytest.mark.parametrize("with_res", [True, False])
+def test_fused_rms_norm_dq_pipelined_and_row_kernels_agree_bit_for_bit(op, with_res):
+    """1400 rows (pipelined kernel) against their first 900 alone (row-per-CTA kernel): every output has the same bits;
+    an all-zero row gives scale 0 and codes 0 in both."""
+    d = W.norm_quant_inputs(1400, 7168)
+    x = d["x"].clone(); res = d["residual"].clone()
+    x[5] = 0; res[5] = 0
+    x, res, w = x.to(DEV), res.to(DEV), d["weight"].to(DEV)
+    smooth = (0.5 + torch.rand(7168, generator=torch.Generator().manual_seed(3))).bfloat16().to(DEV)
+    outs = []
+    for n in (1400, 900):
+        q = torch.empty(n, 7168, dtype=torch.int8, device=DEV); sc = torch.empty(n, device=DEV)
+        ar = torch.empty(n, 7168, dtype=torch.bfloat16, device=DEV); an = torch.empty_like(ar)
+        op.rms_norm_dynamic_per_token_quant(q, x[:n], w, smooth, sc, 1e-6, ar, an, res[:n] if with_res else None)
+        outs.append((q, sc, ar, an))
+    (qa, sa, ara, ana), (qb, sb, arb, anb) = outs
+    C.assert_equal(qa[:900], qb); C.assert_equal(bits(ara[:900]), bits(arb)); C.assert_equal(bits(ana[:900]), bits(anb))
+    assert torch.equal(sa[:900].view(torch.int32), sb.view(torch.int32))
+    assert float(sa[5]) == 0.0 and int(qa[5].abs().max()) == 0
 
 
 @pytest.mark.parametrize("rms_div", [False, True])
