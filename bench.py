@@ -314,8 +314,45 @@ class Next6:
         ]
 
 
+class Part1:
+    """The other entry points of part 1 on bf16 rows of 7168, each timed on its own: fused_add_rms_norm (in place), rms_norm
+    with a residual, and the 9-argument norm + smooth quant."""
+    name = "part 1 entry points: fused_add_rms_norm, rms_norm (+residual), 9-argument rms_norm_dynamic_per_token_quant"
+    kernels = ["fused_add_rms_norm", "rms_norm", "norm_smooth_quant"]
+    launches_per_step = 3
+
+    def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
+        from mcoplib_b200 import workloads as W
+        self.T, self.H = tokens, 7168
+        d = W.norm_quant_inputs(tokens, 7168, t0, 0, gen_device, device)
+        self.x, self.res, self.w = d["x"], d["residual"], d["weight"]
+        o = dict(device=device)
+        # the in-place operator gets buffers of its own: it rewrites both of its inputs every step
+        self.x_io, self.res_io = self.x.clone(), self.res.clone()
+        self.smooth = torch.ones(7168, dtype=torch.bfloat16, **o)
+        self.out = torch.empty(tokens, 7168, dtype=torch.bfloat16, **o)
+        self.after_res = torch.empty_like(self.out)
+        self.after_norm = torch.empty_like(self.out)
+        self.codes = torch.empty(tokens, 7168, dtype=torch.int8, **o)
+        self.scales = torch.empty(tokens, dtype=torch.float32, **o)
+
+    def bytes_per_kernel(self):
+        n = self.T * self.H
+        return {"fused_add_rms_norm": 8 * n + 2 * self.H,          # x, residual read and written
+                "rms_norm": 8 * n + 2 * self.H,                    # x, residual read; out, after_res written
+                "norm_smooth_quant": 9 * n + 4 * self.H + 4 * self.T}  # + after_norm, codes, scale
+
+    def stages(self, ops):
+        return [
+            lambda: ops.fused_add_rms_norm(self.x_io, self.res_io, self.w, 1e-6),
+            lambda: ops.rms_norm(self.out, self.x, self.w, 1e-6, self.after_res, self.res, False),
+            lambda: ops.rms_norm_dynamic_per_token_quant(self.codes, self.x, self.w, self.smooth, self.scales, 1e-6, self.after_res,
+                                                         self.after_norm, self.res),
+        ]
+
+
 WORKLOADS = {"chain5": (Chain5, 262144), "chain4": (Chain4, 32768), "route3": (Route3, 8192), "rope2": (Rope2, 4096),
-             "next6": (Next6, 65536)}
+             "next6": (Next6, 65536), "part1": (Part1, 65536)}
 
 
 # ------------------------------------------------------------------------------------------------
