@@ -1,15 +1,17 @@
 #!/usr/bin/env python
 """Benchmark of the per-token hot path (default: benchmark configuration 5, the token-sharded chain).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload chain5|chain4|route3|rope2|next6]
-                    [--graph]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload chain5|chain4|route3|rope2|next6|part1]
+                    [--graph] [--verify]
 
 A step is one pass of the chain over the rank's token shard:
     chain5 : add+RMSNorm+int8 quant -> softmax top-2 of 8 -> scatter with per-row int8 quant -> weighted gather
 For N > 1 launch with torchrun (one rank per GPU); tokens are split evenly by rank, there is no collective on
 the data path, and the step time is the maximum over ranks of the device time between CUDA events.
-Rank 0 prints ONE JSON line.  `--impl reference` times the CPU restatement of the reference path (oracle/)
-on the host cores instead; it is a reported baseline, not a target.
+Rank 0 prints ONE JSON line.  The default run (one GPU, chain5) then also times the other configurations briefly
+(key `other_configs`).  `--verify` checks, off the clock, every rank's outputs against the CPU oracle (key `verify`).
+`--impl reference` times the CPU restatement of the reference path (oracle/) on the host cores instead; it is a
+reported baseline, not a target.
 """
 from __future__ import annotations
 
@@ -31,9 +33,9 @@ NOMINAL_HBM_GBS = 8000.0
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "fused_chain_tokens_per_s"
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per token of the norm+quant kernel at hidden 7168,
-# from the ncu capture summarised in profiles/norm_quant_bf16_pipe_chain5_32768x7168.md (939.8 MB read + 651.5 MB
-# written for 32,768 tokens); traffic grows in proportion to the tokens (every row is touched exactly once).
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per token of the norm+quant kernel at hidden 7168, from
+# an ncu capture of a 32,768-token launch (939.8 MB read + 651.5 MB written); traffic grows in proportion to the
+# tokens (every row is touched exactly once).
 NORM_QUANT_DRAM_BYTES_PER_TOKEN = (939_755_520 + 651_474_432) / 32768
 
 

@@ -37,11 +37,32 @@ enum {
 int mcop_version(void);
 /* Text of the last error on the calling thread ("" if none). */
 const char* mcop_last_error(void);
-/* Device-side status of the current device.  The row-pipeline kernels bound every wait on an asynchronous
- * copy; a kernel whose wait runs out records a non-zero code, stops and returns instead of hanging.
- * Returns that code (0 = none) and clears it, or a negative MCOP_ERR_*.  SYNCHRONISES with the device.
- * No counterpart in the reference (its kernels have no waits). */
+/* Device-side status of the current device: one word per device that kernels set and the host reads.
+ *   - the row-pipeline kernels bound every wait on an asynchronous copy; a kernel whose wait runs out records
+ *     MCOP_DEVERR_WAIT_FIRST .. MCOP_DEVERR_WAIT_LAST (which wait it was), stops issuing copies, drains those in
+ *     flight and returns instead of hanging;
+ *   - a value read from a caller's tensor is never turned into an address unchecked: a position outside the
+ *     cos / sin table, a cache slot or cache position outside the cache make the kernel SKIP that token (nothing of
+ *     it is read through the bad index, nothing is written for it) and record MCOP_DEVERR_POSITION / _SLOT / _KV_INDEX.
+ * The first code recorded wins.  Entry points return MCOP_OK when they have launched, so a caller that wants to know
+ * calls this after synchronising: it returns the code (0 = none) and clears it, or a negative MCOP_ERR_*.
+ * SYNCHRONISES with the device.  No counterpart in the reference (its kernels neither wait nor check). */
 int mcop_device_error(void);
+enum {
+  MCOP_DEVERR_WAIT_FIRST = 1,
+  MCOP_DEVERR_WAIT_LAST = 15,
+  MCOP_DEVERR_POSITION = 16, /* RoPE position outside [0, max_position) */
+  MCOP_DEVERR_SLOT = 17,     /* paged-cache slot >= num_blocks * block_size */
+  MCOP_DEVERR_KV_INDEX = 18, /* store_kv: slot id outside [0, num_slots) or cache position outside [0, max_len) */
+  MCOP_DEVERR_SELFTEST = 99  /* recorded by mcop_selftest_wait_timeout */
+};
+
+/* Self-test of the bounded-wait path; no counterpart in the reference.  Launches ONE small CTA that arms a ring stage
+ * for `bytes` bytes WITHOUT issuing any copy for it (nothing is in flight, nothing can land late), waits for it with a
+ * limit of `spin_limit` tries (1 .. 1 << 20), records MCOP_DEVERR_SELFTEST in the error word when the wait runs out -
+ * which it must - runs the same drain the pipeline kernels run, and returns.  The kernel neither faults nor hangs and
+ * the context stays usable; mcop_device_error() then yields MCOP_DEVERR_SELFTEST once and 0 afterwards. */
+int mcop_selftest_wait_timeout(int spin_limit, mcop_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Part 1 - residual add + RMSNorm (+ per-token int8 quantisation)
@@ -103,65 +124,84 @@ int mcop_dynamic_scaled_int8_quant(int8_t* out, float* scales, const void* x, in
  * ---------------------------------------------------------------------------------------------- */
 
 /* torch.ops._C.rotary_embedding, op/vllm/pos_encoding_kernels.cu:135-217 (schema torch_bindings.cpp:233-237).
- * In-place RoPE of query (and key unless NULL).  cos_sin_cache [max_pos, rot_dim] = cos || sin, in the
+ * In-place RoPE of query (and key unless NULL).  cos_sin_cache [max_position, rot_dim] = cos || sin, in the
  * activation dtype (arithmetic in T, rounded after every operation) or in fp32 (fp32 arithmetic, one rounding).
- * Strides are in elements: token strides of query/key, and the stride between heads. */
+ * Strides are in elements: token strides of query/key, and the stride between heads.
+ * A token whose position is outside [0, max_position) is left untouched (MCOP_DEVERR_POSITION). */
 int mcop_rope_inplace(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
-                      int cache_dtype, int64_t tokens, int num_heads, int num_kv_heads, int head_size,
-                      int rot_dim, int64_t query_stride, int64_t key_stride, int64_t head_stride,
+                      int cache_dtype, int64_t max_position, int64_t tokens, int num_heads, int num_kv_heads,
+                      int head_size, int rot_dim, int64_t query_stride, int64_t key_stride, int64_t head_stride,
                       int is_neox, int dtype, mcop_stream_t stream);
 
 /* mcoplib.op.rotary_embedding, op/rotary_embedding.cu:99-121 (include/rotary_embedding.h:3-5).
  * NeoX RoPE of the Q and K heads of packed_qkv [tokens, Hq+2Hkv, D] into output (same layout, V heads not
  * touched); position of token t of sequence b = cache_lens[b] + t - accum_q_lens[b];
- * cos, sin fp32 [max_pos, D/2]; fp32 arithmetic, one rounding. */
-int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, const float* sin,
+ * cos, sin fp32 [max_position, D/2]; fp32 arithmetic, one rounding.  A token whose position is outside
+ * [0, max_position) is not written (MCOP_DEVERR_POSITION). */
+int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, const float* sin, int64_t max_position,
                      const int32_t* accum_q_lens, const int32_t* cache_lens, int batch, int64_t tokens,
                      int q_heads, int kv_heads, int head_dim, int dtype, mcop_stream_t stream);
 
 /* mcoplib.op.fused_rope_fwd, op/fused_rope.cu:13-74 (kernel/fused_rope_kernel.h:6-96).
- * In-place NeoX RoPE of the Q and K planes of qkv [seq, planes>=2, heads, D]; cos, sin [*, D/2] in the
- * activation dtype; row = indexes[s] (int64) or s when indexes is NULL; fp32 arithmetic, one rounding. */
-int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
-                        int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
+ * In-place NeoX RoPE of the Q and K planes of qkv [seq, planes>=2, heads, D]; cos, sin [max_position, D/2] in the
+ * activation dtype; row = indexes[s] (int64) or s when indexes is NULL; fp32 arithmetic, one rounding.
+ * A row outside [0, max_position) leaves its token untouched (MCOP_DEVERR_POSITION). */
+int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
+                        int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
 
 /* mcoplib.op.fused_rope_bwd, op/fused_rope.cu:77-138 (kernel/fused_rope_kernel.h:101-191).
  * The transposed rotation (gradient of fused_rope_fwd), same layout and arguments:
  * x' = x*c + y*s, y' = y*c - x*s in fp32, one rounding. */
-int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
-                        int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
+int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
+                        int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
 
 /* mcoplib.op.store_kv_cache_cuda_interface, op/store_kv.cu:220-350 (include/store_kv.h:2-15).
  * code = clamp(rne(x * scale[h, d]), -127, 127) for the K and V heads of packed_qkv
  * (strides qkv_stride_token / qkv_stride_head, elements) written to cache[slot_ids[b], h, cache_lens[b] + i, :]
- * with cache strides in bytes-as-elements (int8): stride_slot, stride_head, stride_pos. */
+ * with cache strides in bytes-as-elements (int8): stride_slot, stride_head, stride_pos.  The caches hold num_slots
+ * slots of max_len positions; a token whose slot id or position falls outside is not stored (MCOP_DEVERR_KV_INDEX). */
 int mcop_kv_store_i8(const void* packed_qkv, int64_t qkv_stride_token, int64_t qkv_stride_head,
                      const int32_t* q_lens, const int32_t* accum_q_lens, const int32_t* cache_lens,
-                     const int32_t* cache_slot_ids, int8_t* k_cache, int8_t* v_cache,
+                     const int32_t* cache_slot_ids, int8_t* k_cache, int8_t* v_cache, int64_t num_slots, int64_t max_len,
                      int64_t k_stride_slot, int64_t k_stride_head, int64_t k_stride_pos,
                      int64_t v_stride_slot, int64_t v_stride_head, int64_t v_stride_pos,
                      const float* k_scale, const float* v_scale, int batch, int64_t tokens, int q_heads,
                      int kv_heads, int head_dim, int dtype, mcop_stream_t stream);
 
-/* torch.ops._C_cache_ops.reshape_and_cache_flash / reshape_and_cache with kv_cache_dtype "auto",
- * op/vllm/cache_kernels.cu:564-650 (schemas torch_bindings.cpp:403-420).
+/* torch.ops._C_cache_ops.reshape_and_cache_flash with kv_cache_dtype "auto",
+ * op/vllm/cache_kernels.cu:193-266,610-650 (schema torch_bindings.cpp:412-420).
  * Copies key/value [tokens, kv_heads, head_size] (token stride given) to the paged cache at
  * slot_mapping[t] (block = slot / block_size, offset = slot % block_size; negative = skip).
- * The cache is addressed by strides (elements): block, in-block position, head; head_size contiguous. */
+ * The cache is addressed by strides (elements): block, in-block position, head; head_size contiguous.
+ * A slot >= num_blocks * block_size is skipped (MCOP_DEVERR_SLOT). */
 int mcop_reshape_and_cache_flash(const void* key, const void* value, int64_t key_stride, int64_t value_stride,
                                  void* key_cache, void* value_cache, int64_t block_stride, int64_t page_stride,
                                  int64_t head_stride, const int64_t* slot_mapping, int64_t tokens,
-                                 int kv_heads, int head_size, int block_size, int elem_bytes,
+                                 int kv_heads, int head_size, int block_size, int64_t num_blocks, int elem_bytes,
                                  mcop_stream_t stream);
+
+/* torch.ops._C_cache_ops.reshape_and_cache with kv_cache_dtype "auto",
+ * op/vllm/cache_kernels.cu:133-190,564-593 (schema torch_bindings.cpp:403-409): the split layout of the paged cache,
+ * key_cache [num_blocks, kv_heads, head_size / x, block_size, x] and value_cache [num_blocks, kv_heads, head_size,
+ * block_size], both contiguous.  key/value [tokens, kv_heads, head_size] with token strides in elements;
+ * block = slot / block_size, offset = slot % block_size; a negative slot is skipped, a slot >= num_blocks * block_size
+ * is skipped and reported (MCOP_DEVERR_SLOT).  head_size % x == 0.  Every (head, group of x) is copied - the reference
+ * launches at most 512 threads per token and leaves the groups beyond them unwritten (:575). */
+int mcop_reshape_and_cache(const void* key, const void* value, int64_t key_stride, int64_t value_stride,
+                           void* key_cache, void* value_cache, const int64_t* slot_mapping, int64_t tokens,
+                           int kv_heads, int head_size, int block_size, int x, int64_t num_blocks, int elem_bytes,
+                           mcop_stream_t stream);
 
 /* Fused RoPE + int8 paged KV store.  No single reference operator: the composition of
  * rotary_embedding (op/vllm/pos_encoding_kernels.cu:135-217) -> int8 quantisation of the ROUNDED rotated K
  * and of V as in op/store_kv.cu:188-216 with per-head dequantisation scales (code = clamp(rne(v * (1/scale[h])), +-127))
  * -> paged addressing of op/vllm/cache_kernels.cu:204-222.  query and key are rotated in place.
  * key_cache/value_cache int8 [num_blocks, block_size, kv_heads, head_size] contiguous;
- * k_scale, v_scale fp32 [kv_heads]. */
+ * k_scale, v_scale fp32 [kv_heads].  A token whose position is outside [0, max_position) is left untouched and not
+ * stored (MCOP_DEVERR_POSITION); a slot >= num_blocks * block_size is rotated but not stored (MCOP_DEVERR_SLOT);
+ * a negative slot is rotated and not stored (the caller's "no store" mark, not an error). */
 int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query, void* key, const void* value,
-                                const void* cos_sin_cache, int cache_dtype, int8_t* key_cache,
+                                const void* cos_sin_cache, int cache_dtype, int64_t max_position, int8_t* key_cache,
                                 int8_t* value_cache, const int64_t* slot_mapping, const float* k_scale,
                                 const float* v_scale, int64_t tokens, int num_heads, int num_kv_heads,
                                 int head_size, int rot_dim, int64_t query_stride, int64_t key_stride,
@@ -185,17 +225,21 @@ int mcop_moe_softmax_topk(float* topk_weights, int32_t* topk_ids, const float* l
 int mcop_topk_softmax(float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices, const void* logits,
                       int64_t tokens, int experts, int k, int renormalize, int logits_dtype, mcop_stream_t stream);
 
-/* mcoplib.op.fused_moe_gate_deepseek (moegate_type 0), op/fused_moe_gate_deepseek.cu:63-138
- * (include/fused_moe_gate_deepseek.h:6-18).  Sigmoid scores + bias, group score = two best biased scores,
- * keep topk_group groups, top-k experts of the kept groups (ties to the lower index, descending biased
- * score), weights = score / sum(selected scores) (if renormalize) * routed_scaling.
+/* mcoplib.op.fused_moe_gate_deepseek, op/fused_moe_gate_deepseek.cu:63-138 (include/fused_moe_gate_deepseek.h:6-18;
+ * kernels kernel/fused_moe_gate_deepseek.cuh:129-243,316-374).  Sigmoid scores + bias, group score = two best biased
+ * scores, keep topk_group groups, top-k experts of the kept groups (ties to the lower index, descending biased score).
+ * moegate_type 0 (DEEPSEEK): weights = score / sum(selected scores) (if renormalize) * routed_scaling; no shared experts.
+ * moegate_type 1 (SGLANG): tot = fp32 sum of the routed scores; weights = T(score / T(tot)) if renormalize, else the
+ *   score; never scaled.  With num_fused_shared_experts == 1 the last of the topk slots is the fused shared expert:
+ *   id = experts, weight = T(T(tot) * T(1 / routed_scaling)), divided by T(tot) like the others when renormalize; topk - 1
+ *   routed experts are selected.  num_fused_shared_experts > 1 is rejected (the reference draws those ids from the clock).
  * experts % 32 == 0, experts <= 512; groups == 1, or experts/groups a multiple of experts/32 spanning a
  * power-of-two number of lanes.  group_mask (nullable) int32 [tokens]: bit g set iff group g was kept. */
 int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bias, float* topk_weights,
                                   int32_t* topk_ids, int32_t* group_mask, int64_t tokens, int experts,
                                   int groups, int topk_group, int topk, int renormalize,
-                                  float routed_scaling, int logits_dtype, int bias_dtype,
-                                  mcop_stream_t stream);
+                                  float routed_scaling, int num_fused_shared_experts, int moegate_type,
+                                  int logits_dtype, int bias_dtype, mcop_stream_t stream);
 
 /* mcoplib.op.fused_moe_gate_opt, op/moe_fused_gate_opt.cu:9-92 (kernels kernel/fused_moe_gate.cuh:137-251,346-463):
  * the same selection as mcop_moe_gate_grouped_sigmoid with logits and bias of one dtype, and sglang's weights:

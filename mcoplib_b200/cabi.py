@@ -25,17 +25,19 @@ SIGNATURES = {
     "mcop_head_rmsnorm": (I32, [P, P, P, I64, I64, I64, F32, I32, I32, I32, I32, P]),
     "mcop_scale_dynamic_quant_i8": (I32, [P, P, P, P, I64, I64, I32, P]),
     "mcop_dynamic_scaled_int8_quant": (I32, [P, P, P, I64, I64, I32, P]),
-    "mcop_rope_inplace": (I32, [P, P, P, P, I32, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
-    "mcop_rope_packed": (I32, [P, P, P, P, P, P, I32, I64, I32, I32, I32, I32, P]),
-    "mcop_fused_rope_fwd": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
-    "mcop_fused_rope_bwd": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
-    "mcop_kv_store_i8": (I32, [P, I64, I64, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, P, P, I32, I64, I32, I32, I32, I32, P]),
-    "mcop_reshape_and_cache_flash": (I32, [P, P, I64, I64, P, P, I64, I64, I64, P, I64, I32, I32, I32, I32, P]),
-    "mcop_rope_kv_store_i8_paged": (I32, [P, P, P, P, P, I32, P, P, P, P, P, I64, I32, I32, I32, I32, I64, I64, I64, I32, I64, I32, I32, P]),
+    "mcop_selftest_wait_timeout": (I32, [I32, P]),
+    "mcop_rope_inplace": (I32, [P, P, P, P, I32, I64, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
+    "mcop_rope_packed": (I32, [P, P, P, P, I64, P, P, I32, I64, I32, I32, I32, I32, P]),
+    "mcop_fused_rope_fwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, P]),
+    "mcop_fused_rope_bwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, P]),
+    "mcop_kv_store_i8": (I32, [P, I64, I64, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, I64, P, P, I32, I64, I32, I32, I32, I32, P]),
+    "mcop_reshape_and_cache_flash": (I32, [P, P, I64, I64, P, P, I64, I64, I64, P, I64, I32, I32, I32, I64, I32, P]),
+    "mcop_reshape_and_cache": (I32, [P, P, I64, I64, P, P, P, I64, I32, I32, I32, I32, I64, I32, P]),
+    "mcop_rope_kv_store_i8_paged": (I32, [P, P, P, P, P, I32, I64, P, P, P, P, P, I64, I32, I32, I32, I32, I64, I64, I64, I32, I64, I32, I32, P]),
     "mcop_moe_softmax_topk": (I32, [P, P, P, I64, I32, I32, P]),
     "mcop_grouped_topk": (I32, [P, P, P, P, I64, I32, I32, I32, I32, I32, C.c_double, I32, I32, I32, P]),
     "mcop_topk_softmax": (I32, [P, P, P, P, I64, I32, I32, I32, I32, P]),
-    "mcop_moe_gate_grouped_sigmoid": (I32, [P, P, P, P, P, I64, I32, I32, I32, I32, I32, F32, I32, I32, P]),
+    "mcop_moe_gate_grouped_sigmoid": (I32, [P, P, P, P, P, I64, I32, I32, I32, I32, I32, F32, I32, I32, I32, I32, P]),
     "mcop_moe_gate_grouped_sigmoid_shared": (I32, [P, P, P, P, I64, I32, I32, I32, I32, I32, I32, C.c_double, I32, P]),
     "mcop_moe_scatter_workspace_bytes": (SZ, [I64, I32, I32]),
     "mcop_moe_scatter_quant_i8": (I32, [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, P, SZ, P]),
@@ -57,6 +59,8 @@ SIGNATURES = {
 GATHER_NOALLOC_SCRATCH_BYTES = 4 << 20
 
 F32_CODE, BF16_CODE, F16_CODE = 0, 1, 2
+# codes of mcop_device_error()
+DEVERR_POSITION, DEVERR_SLOT, DEVERR_KV_INDEX, DEVERR_SELFTEST = 16, 17, 18, 99
 
 _lib = None
 

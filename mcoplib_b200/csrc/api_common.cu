@@ -86,6 +86,22 @@ cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
   return cudaSuccess;
 }
 
+// Self-test of the bounded wait: a stage is armed and no copy is ever issued for it, so the wait must run out.  The
+// kernel then does what the pipeline kernels do: the CTA agrees that the wait failed, one thread runs the (bounded)
+// drain, everybody returns.  Nothing is in flight at any time.
+__global__ void selftest_wait_kernel(uint32_t limit, int* err) {
+  __shared__ __align__(8) uint64_t bar[1];
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_expect_tx(&bar[0], 256);
+  __syncthreads();
+  const bool ok = mbar_wait_bounded(&bar[0], 0, err, MCOP_DEVERR_SELFTEST, limit);
+  if (!__syncthreads_and(ok) && threadIdx.x == 0) (void)mbar_wait_bounded(&bar[0], 0, err, MCOP_DEVERR_SELFTEST, limit);
+}
+
 int check_launch(const char* what) {
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return MCOP_OK;
@@ -107,4 +123,12 @@ extern "C" int mcop_device_error(void) {
     (void)cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
   }
   return v;
+}
+
+extern "C" int mcop_selftest_wait_timeout(int spin_limit, mcop_stream_t stream) {
+  MCOP_REQUIRE(spin_limit >= 1 && spin_limit <= (1 << 20), MCOP_ERR_ARGUMENT, "selftest_wait_timeout: spin_limit must be in [1, 2^20]");
+  int* err = mcop::pipe_error_ptr();
+  MCOP_REQUIRE(err != nullptr, MCOP_ERR_CUDA, "selftest_wait_timeout: the error word of the current device is not reachable");
+  mcop::selftest_wait_kernel<<<1, 64, 0, (cudaStream_t)stream>>>((uint32_t)spin_limit, err);
+  return mcop::check_launch("selftest_wait_timeout");
 }

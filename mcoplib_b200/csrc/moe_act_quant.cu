@@ -358,6 +358,10 @@ extern "C" int mcop_silu_mul_quant_i8_masked_pack(const void* x, int dtype, cons
   MCOP_REQUIRE(out_stride_elems * 2 >= n + 4, MCOP_ERR_ARGUMENT,
                "silu_mul_quant_i8_masked_pack: a row of %lld elements cannot hold %lld codes and the scale",
                (long long)out_stride_elems, (long long)n);
+  // the fp32 scale of a row is stored at byte n of its record: records must start on 4-byte boundaries
+  MCOP_REQUIRE((reinterpret_cast<uintptr_t>(out_packed) & 3u) == 0 && (out_stride_elems * 2) % 4 == 0, MCOP_ERR_ARGUMENT,
+               "silu_mul_quant_i8_masked_pack: out_packed must be 4-byte aligned and out_stride_elems even (the fp32 scale is "
+               "stored inside every record)");
   if (groups == 0 || rows_per_group == 0) return MCOP_OK;
   SiluMulParams p{};
   p.x = x; p.rows = groups * rows_per_group; p.n = (int)n;

@@ -200,12 +200,13 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
     if (threadIdx.x < ntok) {
       const int64_t t = t0 + threadIdx.x;
       int rows[kPipeMaxRows];
+      int slot[kPipeMaxRows];  // with tok2row: the routing slot a row came from
       int n = 0;
       bool overflow = false;
       if (p.tok2row) {
         for (int j = 0; j < p.topk; ++j) {
           const int r = p.tok2row[t * p.topk + j];
-          if (r >= 0 && r < p.rows) rows[n++] = r;
+          if (r >= 0 && r < p.rows) { rows[n] = r; slot[n] = j; ++n; }
         }
       } else {
         const int c0 = p.cnt[t];
@@ -215,14 +216,29 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
       }
       if (!overflow) {
         for (int a = 1; a < n; ++a) {  // insertion sort, n <= 16
-          const int key = rows[a];
+          const int key = rows[a], ks = slot[a];
           int b = a - 1;
-          while (b >= 0 && rows[b] > key) { rows[b + 1] = rows[b]; --b; }
-          rows[b + 1] = key;
+          while (b >= 0 && rows[b] > key) { rows[b + 1] = rows[b]; slot[b + 1] = slot[b]; --b; }
+          rows[b + 1] = key; slot[b + 1] = ks;
         }
         for (int j = 0; j < n; ++j) {
           s_rows[threadIdx.x][j] = rows[j];
-          if (p.weighted) s_w[threadIdx.x][j] = row_weight(p, t, rows[j]);
+          if (p.weighted) {
+            float w;
+            if (p.tok2row) {
+              // the row belongs to the expert named by its slot: the weight is that of the FIRST slot of the token that
+              // names this expert - the same value the search over the experts' starts would find, without the search
+              const int32_t* tid = p.topk_ids + t * p.topk;
+              const int e = tid[slot[j]];
+              int jf = slot[j];
+              for (int i = 0; i < slot[j]; ++i)
+                if (tid[i] == e) { jf = i; break; }
+              w = p.topk_weights[t * p.topk + jf];
+            } else {
+              w = row_weight(p, t, rows[j]);
+            }
+            s_w[threadIdx.x][j] = w;
+          }
         }
       }
       s_cnt[threadIdx.x] = overflow ? -1 : n;

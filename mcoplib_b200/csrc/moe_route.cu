@@ -138,9 +138,14 @@ struct GateParams {
   // T(0.5 * tanh(0.5 x) + 0.5) (scoring 1); biased = T(score + float(bias)); non-finite logits never win an expert slot,
   // non-finite group scores count as -inf, and a token whose topk_group-th group score is -inf gets ids 0..k-1 with
   // weights 1/k; weight = score * (scaling / (1e-20 + fp32 butterfly sum of the selected scores)) when renormalize.
+  // style 3: mcoplib.op.fused_moe_gate_deepseek with moegate_type 1 (kernel/fused_moe_gate_deepseek.cuh:334-374):
+  // tot = fp32 16-lane butterfly sum of the routed scores; the shared slot (if any) gets id = experts and
+  // T(T(tot) * T(scaling)); with renormalize every slot becomes T(T(w) / T(tot)); routed weights are not scaled
+  // (`scaling` holds 1 / routed_scaling_factor, as the reference's host code computes it).
   int style, shared;
   double shared_mul;  // style 1: weight of the shared slot = sum of the routed weights * shared_mul
   int scoring;        // style 2 only
+  int vec_ok;         // the logits rows are 16-byte aligned: fp32 logits may be read as float4
 };
 
 template <typename T1, typename T2, int V>
@@ -153,7 +158,7 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
   const T2* b = reinterpret_cast<const T2*>(p.bias) + first;
   float score[V], biased[V];
   float xin[V];
-  if (sizeof(T1) == 4 && V % 4 == 0) {
+  if (sizeof(T1) == 4 && V % 4 == 0 && p.vec_ok) {
 #pragma unroll
     for (int i = 0; i < V / 4; ++i) {
       const float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
@@ -264,6 +269,21 @@ __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
     }
     return;
   }
+  if (p.style == 3) {
+    float tot = lane < routed ? my_w : 0.f;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    if (p.shared && lane == p.topk - 1) {
+      my_id = p.experts;
+      my_w = round_code(round_code(tot, p.t1) * round_code(p.scaling, p.t1), p.t1);
+    }
+    if (p.renormalize) my_w = round_code(round_code(my_w, p.t1) / round_code(tot, p.t1), p.t1);
+    if (lane < p.topk) {
+      p.weights[row * p.topk + lane] = my_w;
+      p.ids[row * p.topk + lane] = my_id;
+    }
+    return;
+  }
   if (p.style == 1) {
     // fp32 sum over a 16-lane xor-butterfly (offsets 8, 4, 2, 1) of the routed scores, one rounding of the sum and
     // one of the quotient to the logits type (kernel/fused_moe_gate.cuh:361-385); lanes >= routed contribute 0
@@ -370,7 +390,7 @@ static int gate_entry(const void* logits, const void* bias, float* topk_weights,
   MCOP_REQUIRE(logits && bias && topk_weights && topk_ids, MCOP_ERR_ARGUMENT, "moe_gate: null pointer");
   MCOP_REQUIRE(shared >= 0 && shared <= 1 && topk_total - shared >= 1, MCOP_ERR_UNSUPPORTED,
                "moe_gate: %d fused shared experts (0 or 1 supported: the reference draws the ids of more from rand())", shared);
-  MCOP_REQUIRE(style != 1 || topk_total <= 16, MCOP_ERR_UNSUPPORTED, "moe_gate: at most 16 slots in this form");
+  MCOP_REQUIRE((style != 1 && style != 3) || topk_total <= 16, MCOP_ERR_UNSUPPORTED, "moe_gate: at most 16 slots in this form");
   const int topk = topk_total - shared;  // routed experts to select
   MCOP_REQUIRE(tokens >= 0 && experts > 0 && topk >= 1 && topk_total <= 32, MCOP_ERR_ARGUMENT, "moe_gate: bad sizes");
   MCOP_REQUIRE(experts % 32 == 0 && experts <= 512, MCOP_ERR_UNSUPPORTED,
@@ -389,7 +409,7 @@ static int gate_entry(const void* logits, const void* bias, float* topk_weights,
   }
   if (tokens == 0) return MCOP_OK;
   GateParams p{logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk_total,
-               renormalize, routed_scaling, logits_dtype, 0, style, shared, shared_mul, scoring};
+               renormalize, routed_scaling, logits_dtype, 0, style, shared, shared_mul, scoring, aligned16(logits) ? 1 : 0};
   const int s1 = logits_dtype == MCOP_F32 ? 4 : 2, s2 = bias_dtype == MCOP_F32 ? 4 : 2;
   p.ts = s1 >= s2 ? logits_dtype : bias_dtype;
   cudaStream_t s = (cudaStream_t)stream;
@@ -404,10 +424,18 @@ static int gate_entry(const void* logits, const void* bias, float* topk_weights,
 extern "C" int mcop_moe_gate_grouped_sigmoid(const void* logits, const void* bias, float* topk_weights,
                                              int32_t* topk_ids, int32_t* group_mask, int64_t tokens, int experts,
                                              int groups, int topk_group, int topk, int renormalize,
-                                             float routed_scaling, int logits_dtype, int bias_dtype,
-                                             mcop_stream_t stream) {
+                                             float routed_scaling, int num_fused_shared_experts, int moegate_type,
+                                             int logits_dtype, int bias_dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(moegate_type == 0 || moegate_type == 1, MCOP_ERR_ARGUMENT, "moe_gate: moegate_type must be 0 (DEEPSEEK) or 1 (SGLANG)");
+  if (moegate_type == 0) {
+    MCOP_REQUIRE(num_fused_shared_experts == 0, MCOP_ERR_UNSUPPORTED,
+                 "moe_gate: fused shared experts exist only with moegate_type 1 (as in the reference's dispatch table)");
+    return gate_entry(logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk, renormalize,
+                      routed_scaling, logits_dtype, bias_dtype, 0, 0, 0.0, 0, stream);
+  }
+  MCOP_REQUIRE(routed_scaling != 0.f, MCOP_ERR_ARGUMENT, "moe_gate: routed_scaling must not be 0");
   return gate_entry(logits, bias, topk_weights, topk_ids, group_mask, tokens, experts, groups, topk_group, topk, renormalize,
-                    routed_scaling, logits_dtype, bias_dtype, 0, 0, 0.0, 0, stream);
+                    1.0f / routed_scaling, logits_dtype, bias_dtype, 3, num_fused_shared_experts, 0.0, 0, stream);
 }
 
 extern "C" int mcop_moe_gate_grouped_sigmoid_shared(const void* logits, const void* bias, float* topk_weights,

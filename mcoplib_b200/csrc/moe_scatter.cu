@@ -1,20 +1,22 @@
 // Part 3b of the hot path: MoE dispatch (scatter + per-row int8 quantisation).
 //
-// Scatter is a deterministic counting sort, not a sort:
-//   rank kernel  - one CTA per tile of 512 tokens builds, in shared memory, one bitmap of the tile's tokens per
-//                  expert; popcounts give the tile's per-expert histogram and the rank of every (token, slot)
-//                  among the tile's rows of that expert.  With few tiles the last CTA to finish (one atomic ticket,
-//                  nobody waits) turns the histograms into per-tile bases, counts and starts; with many tiles a scan
-//                  kernel with one CTA per expert does (its last CTA derives the starts).
-//   fill kernel  - one thread per (token, slot): row = starts[e] + tile_base[tile][e] + rank; writes row2tok,
-//                  tok2row and the row's routing weight.  Rows end up ordered by (expert, token).
-//   quant kernel - persistent CTAs take work items (token super-tile, expert, part) in token-major order, so
-//                  the k readers of a token row run close together in time and the row comes from HBM once and
-//                  from L2 afterwards.  An item's rows are contiguous in the output and share the expert, so
-//                  the expert's smooth-scale slice sits in registers for the whole item while the token rows
-//                  stream through a ring of shared-memory stages filled by bulk asynchronous copies.
-// Shapes the quant kernel does not take (row length not a multiple of 8, misaligned buffers, very wide rows)
-// use a row-per-token kernel with the same arithmetic.
+// Scatter is a deterministic counting sort, not a sort.  Two launches on the main path, no memset, no inter-CTA wait:
+//   bitmap kernel - one CTA per tile of 512 tokens builds, in shared memory, one bitmap of the tile's tokens per
+//                   expert and writes the bitmaps and their popcounts (the tile's per-expert histogram) to scratch.
+//   quant kernel  - persistent CTAs.  Every CTA first folds the [tiles, experts] histogram into the experts' counts and
+//                   starts and into the row offset of every (super-tile, expert) pair, in its own shared memory (the
+//                   histogram is a few KB; recomputing it per CTA costs less than a scan kernel and its launch gap, and
+//                   needs no ticket that somebody would have to zero).  CTAs then take work items (super-tile, expert,
+//                   part) in token-major order, so the k readers of a token row run close together in time and the row
+//                   comes from HBM once and from L2 afterwards.  An item enumerates its own tokens from the bitmaps
+//                   (rank = popcount prefix), looks up each token's slot and routing weight, and writes row2tok /
+//                   tok2row itself.  An item's rows are contiguous in the output and share the expert, so the expert's
+//                   smooth-scale slice sits in registers for the whole item while the token rows stream through a ring
+//                   of shared-memory stages filled by bulk asynchronous copies.  Rows end up ordered by (expert, token).
+// Shapes the quant kernel does not take (row length not a multiple of 8, misaligned buffers, very wide rows, few rows,
+// more (super-tile, expert) pairs than its table holds) use the general path: a rank kernel (per-slot ranks; with few
+// tiles its last CTA - one atomic ticket, nobody waits - scans the histograms, with many tiles a scan kernel does) and a
+// row-per-token quant kernel with the same arithmetic.  moe_align_block_size runs on the rank kernel as well.
 #include <atomic>
 
 #include "common.cuh"
@@ -33,7 +35,6 @@ struct ScatterWs {
   int32_t* ticket;     // [0] ticket of the rank kernel, [1] work counter of the quant kernel (64 ints reserved)
   int32_t* tile_hist;  // [tiles, E] histogram, overwritten by the exclusive per-expert prefix over tiles
   int32_t* rank;       // [T*k] rank of the (token, slot) inside its tile and expert, -1 if dropped
-  float* row_w;        // [T*k] routing weight of every output row
   int32_t separate_scan;  // more than kInKernelScanTiles tiles: scatter_scan_kernel follows the rank kernel
   // Only for moe_align_block_size (all zero / null for the scatter):
   const int32_t* expert_map;  // [E] global -> local expert id, -1 = not on this rank; null = identity
@@ -240,8 +241,10 @@ __global__ void __launch_bounds__(256) align_fill_kernel(const int32_t* __restri
 
 struct ScatterQuantParams {
   const __nv_bfloat16* hidden; const int32_t* ids; const float* weights; const float* smooth;
-  int8_t* rows; float* row_scales; int32_t* row2tok; const int32_t* starts; const int32_t* counts; int32_t* tok2row;
-  const int32_t* tile_base; const int32_t* rank; float* row_w; int32_t* work_counter;
+  int8_t* rows; float* row_scales; int32_t* row2tok; int32_t* starts; int32_t* counts; int32_t* tok2row;
+  const int32_t* tile_base; const int32_t* rank;   // general path: per-tile bases and per-slot ranks of the rank kernel
+  const int32_t* hist; const uint32_t* bitmaps;     // main path: [tiles, E] histogram and [tiles, E, 16] token bitmaps
+  int32_t* work_counter;
   int64_t tokens; int hidden_size, topk, E;
   int supertile, parts;   // quant kernel work items: (super-tile of `supertile` tiles, expert, part of `parts`)
 };
@@ -258,95 +261,314 @@ __device__ __forceinline__ int scatter_row_of(const ScatterQuantParams& p, int64
   return p.starts[e] + p.tile_base[tile * p.E + e] + p.rank[t * p.topk + j];
 }
 
-__global__ void __launch_bounds__(256) scatter_fill_kernel(ScatterQuantParams p) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= p.tokens * p.topk) return;
-  const int64_t t = i / p.topk;
-  const int j = (int)(i % p.topk);
-  int e; float w = 0.f;
-  const int row = scatter_row_of(p, t, j, e, w);
-  if (p.tok2row) p.tok2row[i] = row;
-  if (row >= 0) {
-    p.row2tok[row] = (int32_t)t;
-    p.row_w[row] = w;
-  }
-}
-
 __device__ __forceinline__ void row_scale_from_amax(float amax, float& scale_out, float& mul) {
   scale_out = (float)((double)amax * 0.0078740157);
   mul = 127.0f * (1.0f / amax);   // amax == 0 -> inf -> 0 * inf = NaN -> code 0
 }
 
+// ---------------------------------------------------------------------------------------------
+// Main path, first launch: per tile, one bitmap of the tile's tokens per expert and its popcount.
+// Dynamic shared memory: bitmap [E][kTileWords] u32.  Also resets the work counter of the quant kernel that follows
+// in stream order (so nobody has to zero the scratch) and marks the dropped (token, slot) entries in tok2row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) scatter_bitmap_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ hist,
+                                                             uint32_t* __restrict__ bitmaps, int32_t* __restrict__ work_counter,
+                                                             int32_t* __restrict__ tok2row, int64_t tokens, int topk, int E) {
+  extern __shared__ uint32_t smem_u32[];
+  uint32_t* bitmap = smem_u32;
+  const int64_t tile = blockIdx.x;
+  const int64_t tok0 = tile * kTileTokens;
+  const int ntok = (int)min((int64_t)kTileTokens, tokens - tok0);
+  for (int i = threadIdx.x; i < E * kTileWords; i += blockDim.x) bitmap[i] = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0;
+  __syncthreads();
+  const int32_t* tids = ids + tok0 * topk;
+  const int n = ntok * topk;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = tids[i];
+    if (e >= 0 && e < E) {
+      const int tl = i / topk;
+      atomicOr(&bitmap[e * kTileWords + (tl >> 5)], 1u << (tl & 31));
+    } else if (tok2row) {
+      tok2row[tok0 * topk + i] = -1;
+    }
+  }
+  __syncthreads();
+  // one half-warp per expert: the 16 words go out as one 64-byte line, their popcounts are summed by shuffles
+  const int hw = threadIdx.x >> 4, l = threadIdx.x & 15, nhw = blockDim.x >> 4;
+  for (int e0 = 0; e0 < E; e0 += nhw) {  // trip count is uniform over the warp: the shuffles need every lane
+    const int e = e0 + hw;
+    const bool valid = e < E;
+    const uint32_t wv = valid ? bitmap[e * kTileWords + l] : 0u;
+    int c = __popc(wv);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o, 16);
+    if (valid) {
+      bitmaps[(tile * E + e) * kTileWords + l] = wv;
+      if (l == 0) hist[tile * E + e] = c;
+    }
+  }
+}
 
-// resident CTAs per SM the quant kernel is built for: 3 CTAs of 7-8 warps, 4 of 5-6 warps, 5 of 4 warps, 1 of 16
-constexpr int scatter_ctas_per_sm(int threads) { return threads > 256 ? 1 : (threads >= 192 ? 3 : (threads >= 160 ? 4 : 5)); }
+constexpr int kTableMax = 2048;  // (super-tile, expert) pairs whose row offsets a quant CTA keeps in shared memory
 
-// Persistent pipelined quant kernel.  Dynamic shared memory: 128 bytes of mbarriers, then `stages` row buffers.
-template <int THREADS, int NVEC, bool FULL>  // FULL: the row is exactly THREADS * NVEC vectors of 8, no lane is ever idle
-__global__ void __launch_bounds__(THREADS, scatter_ctas_per_sm(THREADS)) scatter_quant_pipe(ScatterQuantParams p, int stages, int* err) {
+__device__ __forceinline__ uint4 lds_u4_at(uint32_t addr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+  return r;
+}
+
+// Prologue of the quant kernel (every CTA, identical results): folds the [tiles, E] histogram into the experts' counts
+// and starts and the row offset of every (super-tile, expert) pair, all in the CTA's shared memory:
+// table = starts [E], counts [E], offsets [nsuper, E].  CTA 0 also writes the counts and starts to the caller.
+// Kept out of line: its registers are not wanted in the row loop.
+__device__ __noinline__ void scatter_fold_histogram(const ScatterQuantParams& p, int32_t* table, int ntiles, int nsuper) {
+  const int E = p.E, nthreads = blockDim.x, nwarp = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int32_t* s_starts = table;
+  int32_t* s_cnt = s_starts + E;
+  int32_t* s_base = s_cnt + E;
+  const int nent = nsuper * E;
+  for (int i = threadIdx.x; i < nent; i += nthreads) {
+    const int g = i / E, e = i - g * E;
+    const int tl = g * p.supertile, th = min(tl + p.supertile, ntiles);
+    int c = 0;
+    for (int t = tl; t < th; ++t) c += __ldg(p.hist + (int64_t)t * E + e);
+    s_base[i] = c;
+  }
+  __syncthreads();
+  if (E <= 32) {
+    // few experts, many super-tiles: one warp per expert column, shuffle scans of 32 super-tiles at a time
+    for (int e = warp; e < E; e += nwarp) {
+      int carry = 0;
+      for (int g0 = 0; g0 < nsuper; g0 += 32) {
+        const int g = g0 + lane;
+        const int c = g < nsuper ? s_base[g * E + e] : 0;
+        int inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += v;
+        }
+        if (g < nsuper) s_base[g * E + e] = carry + inc - c;
+        carry += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) s_cnt[e] = carry;
+    }
+  } else {
+    for (int e = threadIdx.x; e < E; e += nthreads) {
+      int run = 0;
+      for (int g = 0; g < nsuper; ++g) {
+        const int c = s_base[g * E + e];
+        s_base[g * E + e] = run;
+        run += c;
+      }
+      s_cnt[e] = run;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int c = e < E ? s_cnt[e] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      if (e < E) s_starts[e] = carry + inc - c;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e < E; e += nthreads) { p.counts[e] = s_cnt[e]; p.starts[e] = s_starts[e]; }
+}
+
+// One batch of an item (whole CTA): the tokens holding ranks [lo, lo + nb) of expert e inside tiles [tile_lo, tile_hi),
+// in ascending order, go to s_tok; their routing weights to s_wt; row2tok / tok2row of the rows b0 .. b0 + nb - 1 are
+// written.  Ends with a CTA barrier.  Kept out of line for the same reason as the prologue.
+// The CTA has nothing else to do while this runs, so dependent loads are kept to two round trips: the bitmaps of
+// the (few) tiles are fetched together with their counts, the weights of all slots together with the ids.
+__device__ __noinline__ void scatter_stage_batch(const ScatterQuantParams& p, int e, int tile_lo, int tile_hi, int lo, int nb, int b0,
+                                                 int32_t* s_tok, float* s_wt) {
+  const int E = p.E;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    const int hi = lo + nb;
+    if (tile_hi - tile_lo <= 2) {
+      // one or two tiles: lanes 0-15 take the words of the first tile, lanes 16-31 those of the second
+      const int half = lane >> 4, wi = lane & 15;
+      const int tt = tile_lo + half;
+      const bool have = tt < tile_hi;
+      uint32_t wv = have ? __ldg(p.bitmaps + ((int64_t)tt * E + e) * kTileWords + wi) : 0u;
+      const int pc = __popc(wv);
+      int winc = pc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, winc, o);
+        if (lane >= o) winc += v;
+      }
+      int r = winc - pc;  // rank of the word's first set bit (tiles in order, words in order)
+      while (wv) {
+        const int bit = __ffs(wv) - 1;
+        wv &= wv - 1;
+        if (r >= lo && r < hi) s_tok[r - lo] = tt * kTileTokens + wi * 32 + bit;
+        ++r;
+      }
+    } else {
+      int run = 0;  // rows of the (super-tile, expert) pair in the tiles before the current group of 32
+      for (int c0 = tile_lo; c0 < tile_hi && run < hi; c0 += 32) {
+        const int t = c0 + lane;
+        const int c = t < tile_hi ? __ldg(p.hist + (int64_t)t * E + e) : 0;
+        int inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += v;
+        }
+        const int first = run + inc - c;  // rank of the tile's first row
+        unsigned need = __ballot_sync(0xffffffffu, c > 0 && first < hi && first + c > lo);
+        while (need) {  // uniform over the warp
+          const int b = __ffs(need) - 1;
+          need &= need - 1;
+          const int tt = c0 + b;
+          const int base = __shfl_sync(0xffffffffu, first, b);
+          uint32_t wv = lane < kTileWords ? __ldg(p.bitmaps + ((int64_t)tt * E + e) * kTileWords + lane) : 0u;
+          const int pc = __popc(wv);
+          int winc = pc;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += v;
+          }
+          int r = base + winc - pc;  // rank of the word's first set bit
+          while (wv) {
+            const int bit = __ffs(wv) - 1;
+            wv &= wv - 1;
+            if (r >= lo && r < hi) s_tok[r - lo] = tt * kTileTokens + lane * 32 + bit;
+            ++r;
+          }
+        }
+        run += __shfl_sync(0xffffffffu, inc, 31);
+      }
+    }
+  }
+  __syncthreads();
+  // slot and routing weight of every token of the batch; the row's entries of row2tok / tok2row
+  if (threadIdx.x < nb) {
+    const int t = s_tok[threadIdx.x];
+    const int row = b0 + threadIdx.x;
+    const int32_t* tid = p.ids + (int64_t)t * p.topk;
+    const float* tw = p.weights + (int64_t)t * p.topk;
+    float w = 0.f;
+    if (p.topk <= 8) {
+      // ids and weights of all slots in flight at once, the choice afterwards
+      int idv[8]; float wv8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        idv[j] = j < p.topk ? tid[j] : -1;
+        wv8[j] = j < p.topk ? tw[j] : 0.f;
+      }
+      bool found = false;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (idv[j] == e) {
+          if (!found) { w = wv8[j]; found = true; }  // the weight is that of the FIRST slot of the token that holds this expert
+          if (p.tok2row) p.tok2row[(int64_t)t * p.topk + j] = row;
+        }
+      }
+    } else {
+      int jf = -1;
+      for (int j = 0; j < p.topk; ++j) {
+        if (tid[j] == e) {
+          if (jf < 0) jf = j;
+          if (p.tok2row) p.tok2row[(int64_t)t * p.topk + j] = row;
+        }
+      }
+      w = tw[jf < 0 ? 0 : jf];
+    }
+    s_wt[threadIdx.x] = w;
+    p.row2tok[row] = t;
+  }
+  __syncthreads();
+}
+
+// Main path, second launch: persistent pipelined quant kernel.
+// Dynamic shared memory: 128 bytes of mbarriers; the table (starts [E], counts [E], row offset of every
+// (super-tile, expert) pair [nsuper, E]) rounded up to 128 bytes; then `stages` row buffers.
+template <int THREADS, int NVEC, bool FULL, int CTAS>  // FULL: the row is exactly THREADS * NVEC vectors of 8, no lane is ever idle
+__global__ void __launch_bounds__(THREADS, CTAS) scatter_quant_pipe(ScatterQuantParams p, int stages, int table_bytes, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ float red[2][33];
+  constexpr int NWARP = THREADS / 32, RS = (NWARP + 7) / 8 * 8;  // warps, and the slots of one reduction
+  __shared__ float red[2][RS];
   __shared__ int32_t s_tok[kBatchRows];
   __shared__ float s_wt[kBatchRows];
   __shared__ int s_item;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  unsigned char* buf = smem + 128;
+  int32_t* s_starts = reinterpret_cast<int32_t*>(smem + 128);
+  const int E = p.E;
+  int32_t* s_cnt = s_starts + E;
+  int32_t* s_base = s_cnt + E;
+  unsigned char* buf = smem + 128 + table_bytes;
   const int H = p.hidden_size, nv = H >> 3;
   const uint32_t row_bytes = (uint32_t)H * 2u;
   const int ntiles = (int)scatter_tiles(p.tokens);
   const int nsuper = (ntiles + p.supertile - 1) / p.supertile;
-  const int64_t nitems = (int64_t)nsuper * p.E * p.parts;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int NWARP = THREADS / 32;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
   }
-  __syncthreads();
+  scatter_fold_histogram(p, s_starts, ntiles, nsuper);
 
+  const uint32_t buf_s = smem_addr(buf) + threadIdx.x * 16u;  // this thread's first vector of stage 0 (shared address)
   uint32_t it = 0, issued = 0, flip = 0;
   RingPos cons, prod;  // ring positions of the consumer (all threads) and of the producer (thread 0)
   bool alive = true;
+  const int64_t nitems = (int64_t)nsuper * E * p.parts;
   while (alive) {
+    // work items (super-tile, expert, part) from an atomic counter, in token-major order: the CTAs move through the
+    // tokens together, so the k readers of a token row run close together in time
     if (threadIdx.x == 0) s_item = atomicAdd(p.work_counter, 1);
     __syncthreads();
     const int64_t item = s_item;
     __syncthreads();  // s_item may be rewritten only after everybody has read it
     if (item >= nitems) break;
     const int part = (int)(item % p.parts);
-    const int e = (int)((item / p.parts) % p.E);
-    const int sup = (int)(item / ((int64_t)p.parts * p.E));
+    const int e = (int)((item / p.parts) % E);
+    const int sup = (int)(item / ((int64_t)p.parts * E));
     const int tile_lo = sup * p.supertile;
     const int tile_hi = min(tile_lo + p.supertile, ntiles);
-    const int base_e = p.starts[e];
-    const int rb_all = base_e + p.tile_base[(int64_t)tile_lo * p.E + e];
-    const int re_all = tile_hi < ntiles ? base_e + p.tile_base[(int64_t)tile_hi * p.E + e] : base_e + p.counts[e];
-    const int nall = re_all - rb_all;
-    const int rb = rb_all + (int)(((int64_t)nall * part) / p.parts);
-    const int re = rb_all + (int)(((int64_t)nall * (part + 1)) / p.parts);
-    if (re <= rb) continue;  // uniform over the CTA
+    const int off_lo = s_base[sup * E + e];
+    const int nall = (sup + 1 < nsuper ? s_base[(sup + 1) * E + e] : s_cnt[e]) - off_lo;
+    const int rb_all = s_starts[e] + off_lo;
+    const int lo_part = (int)(((int64_t)nall * part) / p.parts);
+    const int hi_part = (int)(((int64_t)nall * (part + 1)) / p.parts);
+    if (hi_part <= lo_part) continue;  // uniform over the CTA
     // the expert's smooth-scale slice stays in registers for the whole item
-    // (kept as pairs: the arithmetic below uses the packed fp32x2 multiply / add of sm_100)
+    // (kept as pairs: the arithmetic below uses the packed fp32x2 multiply of sm_100)
     float2 sm[NVEC][4];
-    const float* smp = p.smooth + (int64_t)e * H;
+    {
+      const float* smp = p.smooth + (int64_t)e * H;
 #pragma unroll
-    for (int k = 0; k < NVEC; ++k) {
-      const int v = threadIdx.x + k * THREADS;
-      if (FULL || v < nv) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(smp + v * 8));
-        const float4 b = __ldg(reinterpret_cast<const float4*>(smp + v * 8) + 1);
-        sm[k][0] = make_float2(a.x, a.y); sm[k][1] = make_float2(a.z, a.w);
-        sm[k][2] = make_float2(b.x, b.y); sm[k][3] = make_float2(b.z, b.w);
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (FULL || v < nv) {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(smp + v * 8));
+          const float4 b = __ldg(reinterpret_cast<const float4*>(smp + v * 8) + 1);
+          sm[k][0] = make_float2(a.x, a.y); sm[k][1] = make_float2(a.z, a.w);
+          sm[k][2] = make_float2(b.x, b.y); sm[k][3] = make_float2(b.z, b.w);
+        }
       }
     }
-    for (int b0 = rb; b0 < re && alive; b0 += kBatchRows) {
-      const int nb = min(kBatchRows, re - b0);
-      if (threadIdx.x < nb) {
-        s_tok[threadIdx.x] = p.row2tok[b0 + threadIdx.x];
-        s_wt[threadIdx.x] = p.row_w[b0 + threadIdx.x];
-      }
-      __syncthreads();
+    for (int lo = lo_part; lo < hi_part && alive; lo += kBatchRows) {
+      const int nb = min(kBatchRows, hi_part - lo);
+      const int b0 = rb_all + lo;  // output row of the batch's first token
+      scatter_stage_batch(p, e, tile_lo, tile_hi, lo, nb, b0, s_tok, s_wt);
       int pi = 0;  // producer cursor inside the batch (thread 0)
       auto issue_next = [&]() {
         if (pi >= nb) return;
@@ -359,20 +581,18 @@ __global__ void __launch_bounds__(THREADS, scatter_ctas_per_sm(THREADS)) scatter
       if (threadIdx.x == 0)
         for (int s = 0; s < stages; ++s) issue_next();
       for (int i = 0; i < nb; ++i) {
-        const int s = cons.s;
-        const bool ok = mbar_wait_bounded(&full[s], cons.phase, err, 5);
-        const float w = s_wt[i];
-        const int row = b0 + i;
+        const int st = cons.s;
+        const bool ok = mbar_wait_bounded(&full[st], cons.phase, err, 5);
         float2 vv[NVEC][4];
         float amax = 0.f;
         if (ok) {
-          const unsigned char* src = buf + (size_t)s * row_bytes;
+          const uint32_t src = buf_s + (uint32_t)st * row_bytes;
+          const float w = s_wt[i];
           const float2 w2 = make_float2(w, w);
 #pragma unroll
           for (int k = 0; k < NVEC; ++k) {
-            const int v = threadIdx.x + k * THREADS;
-            if (FULL || v < nv) {
-              const uint4 raw = lds_u4(src + v * 16);
+            if (FULL || threadIdx.x + k * THREADS < nv) {
+              const uint4 raw = lds_u4_at(src + (uint32_t)(k * THREADS * 16));
               const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -401,12 +621,12 @@ __global__ void __launch_bounds__(THREADS, scatter_ctas_per_sm(THREADS)) scatter
         // all-zero row: codes 0 (keeps NaN out of the bit-level conversion below)
         const float mul = m > 0.f ? 127.0f * (1.0f / m) : 0.f;
         const float2 mul2 = make_float2(mul, mul);
+        const int row = b0 + i;
         if (threadIdx.x == 0) p.row_scales[row] = (float)((double)m * 0.0078740157);
-        int8_t* out = p.rows + (int64_t)row * H;
+        int8_t* out = p.rows + (int64_t)row * H + threadIdx.x * 8;
 #pragma unroll
         for (int k = 0; k < NVEC; ++k) {
-          const int v = threadIdx.x + k * THREADS;
-          if (FULL || v < nv) {
+          if (FULL || threadIdx.x + k * THREADS < nv) {
             // |v * mul| <= 127 * (1 + 2^-22): rounds into [-127, 127], no clamp needed
             uint32_t c[8];
 #pragma unroll
@@ -416,7 +636,7 @@ __global__ void __launch_bounds__(THREADS, scatter_ctas_per_sm(THREADS)) scatter
               c[2 * q] = rn_low_byte(pr.x);
               c[2 * q + 1] = rn_low_byte(pr.y);
             }
-            st_cs_u2(out + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
+            st_cs_u2(out + k * THREADS * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
           }
         }
       }
@@ -505,45 +725,52 @@ __global__ void __launch_bounds__(256) scatter_quant_any(ScatterQuantParams p) {
   }
 }
 
-template <int THREADS>
+// Returns MCOP_OK / an error, or 1 when the problem does not fit the main path (more (super-tile, expert) pairs than the
+// table holds, or no room for the ring).
+template <int THREADS, int NVEC, int CTAS>
 int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   const size_t row_bytes = (size_t)p.hidden_size * 2;
-  // about 21-24 warps per SM (the kernel is compiled for <= 80 registers): three CTAs of 7-8 warps, more of the
-  // smaller ones; each CTA gets its share of the shared memory for its ring of row buffers
-  const int want_per_sm = scatter_ctas_per_sm(THREADS);
-  int stages = (int)(((227 * 1024) / want_per_sm - 3 * 1024) / row_bytes);
-  stages = stages < 2 ? 2 : (stages > 6 ? 6 : stages);
-  const size_t smem = 128 + (size_t)stages * row_bytes;
-  int per_sm = (int)((227 * 1024) / (smem + 2 * 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > want_per_sm ? want_per_sm : per_sm);
+  const int64_t ntiles = scatter_tiles(p.tokens);
   // work items: ~40 rows each amortise the per-item set-up; with few rows in total they shrink (down to 16) so that
   // every CTA still gets half a dozen items from the counter and the tail of the last wave stays short
   const double total_rows = (double)p.tokens * p.topk;
   // (measured at 8192 tokens x top-8 of 256: items of 16 rows +1 %, of 8 rows -4 % against this rule)
-  double target = total_rows / ((double)sm_count() * per_sm * 6.0);
+  double target = total_rows / ((double)sm_count() * CTAS * 6.0);
   target = target < 16.0 ? 16.0 : (target > 40.0 ? 40.0 : target);
   const double rows_per_tile_expert = (double)kTileTokens * p.topk / p.E;
-  int supertile = (int)((target + rows_per_tile_expert - 1e-9) / rows_per_tile_expert);
+  int64_t supertile = (int64_t)((target + rows_per_tile_expert - 1e-9) / rows_per_tile_expert);
   if (supertile < 1) supertile = 1;
-  if (supertile > 64) supertile = 64;
+  // the (super-tile, expert) table of a CTA holds kTableMax pairs: coarser super-tiles (cut into more parts) when needed
+  const int64_t max_super = kTableMax / p.E;
+  if (max_super < 1) return 1;
+  const int64_t need_supertile = (ntiles + max_super - 1) / max_super;
+  if (supertile < need_supertile) supertile = need_supertile;
+  if (supertile > 64) return 1;
   int parts = (int)(supertile * rows_per_tile_expert / target);
   if (parts < 1) parts = 1;
   if (parts > 64) parts = 64;
-  p.supertile = supertile;
+  p.supertile = (int)supertile;
   p.parts = parts;
-  const int64_t ntiles = scatter_tiles(p.tokens);
-  const int64_t nitems = ((ntiles + supertile - 1) / supertile) * p.E * parts;
-  int64_t grid = (int64_t)sm_count() * per_sm;
+  const int64_t nsuper = (ntiles + supertile - 1) / supertile;
+  const int64_t nitems = nsuper * p.E * parts;
+  const int table_bytes = (int)(((2 * (int64_t)p.E + nsuper * p.E) * sizeof(int32_t) + 127) / 128 * 128);
+  // each of the CTAS resident CTAs gets its share of the shared memory: barriers, table, ring of row buffers
+  const int64_t budget = (227 * 1024) / CTAS - 2 * 1024 - 128 - table_bytes;
+  int stages = (int)(budget / (int64_t)row_bytes);
+  if (stages < 2) return 1;
+  if (stages > 8) stages = 8;
+  const size_t smem = 128 + (size_t)table_bytes + (size_t)stages * row_bytes;
+  int64_t grid = (int64_t)sm_count() * CTAS;
   if (grid > nitems) grid = nitems;
-  const bool full = (p.hidden_size >> 3) == THREADS * 4;
-  const void* fn = full ? reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, true>)
-                        : reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, 4, false>);
-  const cudaError_t e = ensure_dynamic_smem(fn, 200 * 1024);
+  const bool full = (p.hidden_size >> 3) == THREADS * NVEC;
+  const void* fn = full ? reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, NVEC, true, CTAS>)
+                        : reinterpret_cast<const void*>(&scatter_quant_pipe<THREADS, NVEC, false, CTAS>);
+  const cudaError_t e = ensure_dynamic_smem(fn, 224 * 1024);
   MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   if (full)
-    scatter_quant_pipe<THREADS, 4, true><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
+    scatter_quant_pipe<THREADS, NVEC, true, CTAS><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, table_bytes, pipe_error_ptr());
   else
-    scatter_quant_pipe<THREADS, 4, false><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, pipe_error_ptr());
+    scatter_quant_pipe<THREADS, NVEC, false, CTAS><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, table_bytes, pipe_error_ptr());
   return check_launch("moe_scatter_quant_i8 (quant, pipelined)");
 }
 
@@ -555,7 +782,9 @@ using namespace mcop;
 extern "C" size_t mcop_moe_scatter_workspace_bytes(int64_t tokens, int topk, int experts_per_rank) {
   if (tokens < 0 || topk < 0 || experts_per_rank < 0) return 0;
   const int64_t tiles = scatter_tiles(tokens);
-  return (size_t)(64 + tiles * experts_per_rank + 2 * tokens * topk) * sizeof(int32_t);
+  // header, [tiles, E] histogram, then the larger of the main path's bitmaps and the general path's ranks
+  const int64_t bitmaps = tiles * experts_per_rank * kTileWords, ranks = tokens * topk;
+  return (size_t)(64 + tiles * experts_per_rank + (bitmaps > ranks ? bitmaps : ranks)) * sizeof(int32_t);
 }
 
 extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids, const float* weights,
@@ -580,13 +809,48 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
   ws.ticket = reinterpret_cast<int32_t*>(workspace);
   ws.tile_hist = ws.ticket + 64;
   ws.rank = ws.tile_hist + tiles * E;
-  ws.row_w = reinterpret_cast<float*>(ws.rank + tokens * topk);
   if (tokens == 0) {
     cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int32_t) * E, s);
     if (e == cudaSuccess) e = cudaMemsetAsync(starts, 0, sizeof(int32_t) * E, s);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: memset: %s", cudaGetErrorString(e));
     return MCOP_OK;
   }
+  ScatterQuantParams p{};
+  p.hidden = reinterpret_cast<const __nv_bfloat16*>(hidden); p.ids = ids; p.weights = weights; p.smooth = smooth;
+  p.rows = rows; p.row_scales = row_scales; p.row2tok = row2tok; p.starts = starts; p.counts = counts; p.tok2row = tok2row;
+  p.tile_base = ws.tile_hist; p.rank = ws.rank; p.work_counter = ws.ticket + 1;
+  p.hist = ws.tile_hist; p.bitmaps = reinterpret_cast<const uint32_t*>(ws.rank);
+  p.tokens = tokens; p.hidden_size = (int)hidden_size; p.topk = topk; p.E = E;
+  const int nv = (int)(hidden_size >> 3);
+  const bool vec_ok = hidden_size % 8 == 0 && aligned16(hidden) && aligned16(smooth) && (reinterpret_cast<uintptr_t>(rows) & 7u) == 0 && nv <= 4096;
+  int rc;
+  if (vec_ok && nv > 256 && nv <= 2048 && tokens * topk >= 2048) {
+    // ---- main path: bitmap kernel + pipelined quant kernel
+    const size_t bsmem = (size_t)E * kTileWords * sizeof(uint32_t);
+    if (bsmem > 48 * 1024) {
+      const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&scatter_bitmap_kernel), bsmem);
+      MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
+    scatter_bitmap_kernel<<<(unsigned)tiles, 256, bsmem, s>>>(ids, ws.tile_hist, reinterpret_cast<uint32_t*>(ws.rank), ws.ticket + 1, tok2row, tokens,
+                                                               topk, E);
+    rc = check_launch("moe_scatter_quant_i8 (bitmaps)");
+    if (rc) return rc;
+    // a CTA of nv / 4 threads tiles the row exactly (hidden 4096, 5120, 6144, 7168 = 4 x 128 ... 224 vectors of 8):
+    // no idle lanes and no bounds tests in the passes, worth 25 % at hidden 7168
+    // CTAs of 4 warps whose threads hold 4 to 8 vectors of 8 each tile the usual row lengths exactly (hidden 4096 ... 8192):
+    // no idle lanes and no bounds tests in the passes (worth 25 % at hidden 7168), few warps per row barrier, and with
+    // 12 to 16 warps per SM enough registers (128 to 168) for the row and the smooth slice of a thread without spills
+    if (nv == 896) rc = launch_quant_pipe<128, 7, 3>(p, s);
+    else if (nv == 1024) rc = launch_quant_pipe<128, 8, 3>(p, s);
+    else if (nv == 768) rc = launch_quant_pipe<128, 6, 3>(p, s);
+    else if (nv == 640) rc = launch_quant_pipe<128, 5, 4>(p, s);
+    else if (nv == 512) rc = launch_quant_pipe<128, 4, 4>(p, s);
+    else if (nv <= 1024) rc = launch_quant_pipe<256, 4, 2>(p, s);
+    else rc = launch_quant_pipe<512, 4, 1>(p, s);
+    if (rc != 1) return rc;
+    // the table of the quant kernel cannot hold this problem: the general path below redoes the counting its own way
+  }
+  // ---- general path: rank kernel (+ scan kernel), row-per-token quant kernel
   cudaError_t e = cudaMemsetAsync(ws.ticket, 0, 2 * sizeof(int32_t), s);
   MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: memset: %s", cudaGetErrorString(e));
   const size_t smem = (size_t)E * kTileWords * (sizeof(uint32_t) + sizeof(uint16_t));
@@ -596,38 +860,14 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
   }
   ws.separate_scan = tiles > kInKernelScanTiles;
   scatter_rank_kernel<<<(unsigned)tiles, 256, smem, s>>>(ids, ws, counts, starts, tokens, topk, E);
-  int rc = check_launch("moe_scatter_quant_i8 (rank)");
+  rc = check_launch("moe_scatter_quant_i8 (rank)");
   if (rc) return rc;
   if (ws.separate_scan) {
     scatter_scan_kernel<<<(unsigned)E, 256, 0, s>>>(ws, counts, starts, (int)tiles, E);
     rc = check_launch("moe_scatter_quant_i8 (scan)");
     if (rc) return rc;
   }
-  ScatterQuantParams p{};
-  p.hidden = reinterpret_cast<const __nv_bfloat16*>(hidden); p.ids = ids; p.weights = weights; p.smooth = smooth;
-  p.rows = rows; p.row_scales = row_scales; p.row2tok = row2tok; p.starts = starts; p.counts = counts; p.tok2row = tok2row;
-  p.tile_base = ws.tile_hist; p.rank = ws.rank; p.row_w = ws.row_w; p.work_counter = ws.ticket + 1;
-  p.tokens = tokens; p.hidden_size = (int)hidden_size; p.topk = topk; p.E = E;
-  const int nv = (int)(hidden_size >> 3);
-  const bool vec_ok = hidden_size % 8 == 0 && aligned16(hidden) && aligned16(smooth) && (reinterpret_cast<uintptr_t>(rows) & 7u) == 0 && nv <= 4096;
   const unsigned grid = (unsigned)tokens;
-  if (vec_ok && nv > 256 && nv <= 2048 && tokens * topk >= 2048) {
-    const int64_t n = tokens * topk;
-    scatter_fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p);
-    rc = check_launch("moe_scatter_quant_i8 (fill)");
-    if (rc) return rc;
-    // a CTA of nv / 4 threads tiles the row exactly (hidden 4096, 5120, 6144, 7168, 8192 = 4 x 128 ... 256 vectors of 8):
-    // no idle lanes and no bounds tests in the passes, worth 25 % at hidden 7168
-    switch (nv) {
-      case 512: return launch_quant_pipe<128>(p, s);
-      case 640: return launch_quant_pipe<160>(p, s);
-      case 768: return launch_quant_pipe<192>(p, s);
-      case 896: return launch_quant_pipe<224>(p, s);
-    }
-    if (nv <= 896 && nv % 224 == 0) return launch_quant_pipe<224>(p, s);
-    if (nv <= 1024) return launch_quant_pipe<256>(p, s);
-    return launch_quant_pipe<512>(p, s);
-  }
   if (!vec_ok) scatter_quant_any<<<grid, 256, 0, s>>>(p);
   else if (nv <= 256) scatter_quant_vec<128, 2><<<grid, 128, 0, s>>>(p);
   else if (nv <= 1024) scatter_quant_vec<256, 4><<<grid, 256, 0, s>>>(p);

@@ -36,7 +36,14 @@ struct RopeParams {
   int8_t* k_cache; int8_t* v_cache;
   const int64_t* slot_mapping; const float* k_scale; const float* v_scale;
   int block_size; int64_t num_slots;
+  // every position is checked against the rows of the cos / sin table before it becomes an address; a token whose
+  // position is outside [0, max_pos) is left untouched and MCOP_DEVERR_POSITION is recorded in the error word
+  int64_t max_pos; int* err;
 };
+
+__device__ __forceinline__ void report_device_error(int* err, int code) {
+  if (err) atomicCAS(err, 0, code);
+}
 
 __device__ __forceinline__ int64_t token_position(const RopeParams& p, int64_t t) {
   if (p.positions) return p.positions[t];
@@ -119,6 +126,10 @@ __global__ void __launch_bounds__(256) rope_neox_vec(RopeParams p) {
   const int hv = half >> 3;                 // slices per head
   const int j = threadIdx.x % hv;           // slice index: constant per thread (blockDim % hv == 0)
   const int64_t pos = token_position(p, t);
+  if (pos < 0 || pos >= p.max_pos) {  // uniform over the CTA
+    if (threadIdx.x == 0) report_device_error(p.err, MCOP_DEVERR_POSITION);
+    return;
+  }
   float c[8], s[8];
   Vec8<CT>::load_nc(reinterpret_cast<const CT*>(p.cos) + pos * p.cs_row_stride + j * 8, c);
   Vec8<CT>::load_nc(reinterpret_cast<const CT*>(p.sin) + pos * p.cs_row_stride + j * 8, s);
@@ -130,7 +141,10 @@ __global__ void __launch_bounds__(256) rope_neox_vec(RopeParams p) {
   int64_t slot = -1;
   if (STORE) {
     slot = p.slot_mapping[t];
-    if (slot >= p.num_slots) slot = -1;     // out-of-range slots are skipped like negative ones
+    if (slot >= p.num_slots) {  // out-of-range slots are skipped like negative ones, and reported
+      if (threadIdx.x == 0) report_device_error(p.err, MCOP_DEVERR_SLOT);
+      slot = -1;
+    }
   }
   const int heads_per_iter = blockDim.x / hv;
   const int nqk = p.num_heads + p.num_kv_heads;
@@ -189,12 +203,19 @@ __global__ void __launch_bounds__(256) rope_any(RopeParams p, int is_neox) {
   const int64_t t = blockIdx.x;
   const int half = p.rot_dim >> 1;
   const int64_t pos = token_position(p, t);
+  if (pos < 0 || pos >= p.max_pos) {  // uniform over the CTA
+    if (threadIdx.x == 0) report_device_error(p.err, MCOP_DEVERR_POSITION);
+    return;
+  }
   const CT* cr = reinterpret_cast<const CT*>(p.cos) + pos * p.cs_row_stride;
   const CT* sr = reinterpret_cast<const CT*>(p.sin) + pos * p.cs_row_stride;
   int64_t slot = -1;
   if (STORE) {
     slot = p.slot_mapping[t];
-    if (slot >= p.num_slots) slot = -1;
+    if (slot >= p.num_slots) {
+      if (threadIdx.x == 0) report_device_error(p.err, MCOP_DEVERR_SLOT);
+      slot = -1;
+    }
   }
   const int nqk = p.num_heads + p.num_kv_heads;
   for (int i = threadIdx.x; i < nqk * half; i += blockDim.x) {
@@ -302,21 +323,35 @@ struct KvStoreParams {
   int64_t ks_slot, ks_head, ks_pos, vs_slot, vs_head, vs_pos;
   const float* k_scale; const float* v_scale;
   int batch, q_heads, kv_heads, head_dim;
+  int64_t num_slots, max_len;  // extents of the cache: a slot id or a position outside them is never turned into an address
+  int* err;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256) kv_store_kernel(KvStoreParams p) {
-  const int64_t t = blockIdx.x;
+// Sequence, in-sequence index and destination of token t; false when the token belongs to no sequence or its
+// destination lies outside the cache (then MCOP_DEVERR_KV_INDEX is recorded and nothing is stored).
+__device__ __forceinline__ bool kv_store_locate(const KvStoreParams& p, int64_t t, int64_t& slot, int64_t& pos) {
   int lo = 0, hi = p.batch - 1;
   while (lo < hi) {
     const int mid = (lo + hi) >> 1;
     if (p.accum[mid + 1] > t) hi = mid; else lo = mid + 1;
   }
-  const int b = lo;
-  const int64_t i = t - p.accum[b];
-  if (i < 0 || i >= p.q_lens[b]) return;   // token outside every sequence
-  const int64_t pos = (int64_t)p.cache_lens[b] + i;
-  const int64_t slot = p.slot_ids[b];
+  const int64_t i = t - p.accum[lo];
+  if (i < 0 || i >= p.q_lens[lo]) return false;   // token outside every sequence
+  pos = (int64_t)p.cache_lens[lo] + i;
+  slot = p.slot_ids[lo];
+  if (slot < 0 || slot >= p.num_slots || pos < 0 || pos >= p.max_len) {
+    if (threadIdx.x == 0) report_device_error(p.err, MCOP_DEVERR_KV_INDEX);
+    return false;
+  }
+  return true;
+}
+
+// One CTA per token, one element per thread and step (any head size, any alignment).
+template <typename T>
+__global__ void __launch_bounds__(256) kv_store_kernel(KvStoreParams p) {
+  const int64_t t = blockIdx.x;
+  int64_t slot, pos;
+  if (!kv_store_locate(p, t, slot, pos)) return;
   const T* tok = reinterpret_cast<const T*>(p.qkv) + t * p.stride_token;
   const int n = p.kv_heads * p.head_dim;
   for (int e = threadIdx.x; e < n; e += blockDim.x) {
@@ -330,13 +365,67 @@ __global__ void __launch_bounds__(256) kv_store_kernel(KvStoreParams p) {
   }
 }
 
+// Vector form: a thread takes 16 consecutive elements of one K or V head - two 16-byte loads, four 16-byte loads of
+// the fp32 multipliers, one 16-byte int8 store.  TPB tokens per CTA so that small head counts still fill the CTA.
+// Needs head_dim % 16 == 0 and 16-byte aligned rows on both sides.
+template <typename T>
+__global__ void __launch_bounds__(256) kv_store_vec(KvStoreParams p, int64_t tokens, int tokens_per_cta) {
+  const int per_head = p.head_dim >> 4;
+  const int per_token = 2 * p.kv_heads * per_head;   // K items, then V items
+  const int tl = threadIdx.x / per_token;
+  const int64_t t = (int64_t)blockIdx.x * tokens_per_cta + tl;
+  if (tl >= tokens_per_cta || t >= tokens) return;
+  int64_t slot, pos;
+  {
+    // one lane per token would do the search; all of the token's threads run it (same addresses: one broadcast load each)
+    int lo = 0, hi = p.batch - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (p.accum[mid + 1] > t) hi = mid; else lo = mid + 1;
+    }
+    const int64_t i = t - p.accum[lo];
+    if (i < 0 || i >= p.q_lens[lo]) return;
+    pos = (int64_t)p.cache_lens[lo] + i;
+    slot = p.slot_ids[lo];
+    if (slot < 0 || slot >= p.num_slots || pos < 0 || pos >= p.max_len) {
+      if (threadIdx.x % per_token == 0) report_device_error(p.err, MCOP_DEVERR_KV_INDEX);
+      return;
+    }
+  }
+  const int it = threadIdx.x % per_token;
+  const bool is_v = it >= p.kv_heads * per_head;
+  const int r = is_v ? it - p.kv_heads * per_head : it;
+  const int h = r / per_head, d = (r % per_head) * 16;
+  const T* src = reinterpret_cast<const T*>(p.qkv) + t * p.stride_token + (p.q_heads + (is_v ? p.kv_heads : 0) + h) * p.stride_head + d;
+  const float* sc = (is_v ? p.v_scale : p.k_scale) + h * p.head_dim + d;
+  float a[8], b[8];
+  Vec8<T>::load_nc(src, a);
+  Vec8<T>::load_nc(src + 8, b);
+  const float4 s0 = __ldg(reinterpret_cast<const float4*>(sc)), s1 = __ldg(reinterpret_cast<const float4*>(sc) + 1);
+  const float4 s2 = __ldg(reinterpret_cast<const float4*>(sc) + 2), s3 = __ldg(reinterpret_cast<const float4*>(sc) + 3);
+  const float m[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
+  int qa[8], qb[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    qa[j] = q_rn_clamp(__fmul_rn(a[j], m[j]), -127, 127);
+    qb[j] = q_rn_clamp(__fmul_rn(b[j], m[8 + j]), -127, 127);
+  }
+  const uint2 pa = pack_i8x8(qa), pb = pack_i8x8(qb);
+  int8_t* dst = is_v ? p.v_cache + slot * p.vs_slot + h * p.vs_head + pos * p.vs_pos + d
+                     : p.k_cache + slot * p.ks_slot + h * p.ks_head + pos * p.ks_pos + d;
+  st_cs_u4(dst, make_uint4(pa.x, pa.y, pb.x, pb.y));
+}
+
 // ---------------------------------------------------------------------------------------------
-// Paged copy (reshape_and_cache_flash / reshape_and_cache with kv_cache_dtype "auto").
+// Paged copies with kv_cache_dtype "auto": reshape_and_cache_flash ([blocks, block_size, heads, head_size] by strides)
+// and reshape_and_cache (K as [blocks, heads, head_size / x, block_size, x], V as [blocks, heads, head_size, block_size]).
+// A negative slot is the caller's "no store" mark; a slot past the cache is skipped and reported (MCOP_DEVERR_SLOT).
 // ---------------------------------------------------------------------------------------------
 struct CacheCopyParams {
   const char* key; const char* value; int64_t key_stride, value_stride;   // bytes
   char* key_cache; char* value_cache; int64_t block_stride, page_stride, head_stride;  // bytes
   const int64_t* slot_mapping; int kv_heads, head_bytes, block_size;
+  int64_t num_slots; int* err;
 };
 
 template <typename V>
@@ -344,6 +433,10 @@ __global__ void __launch_bounds__(256) cache_copy_kernel(CacheCopyParams p) {
   const int64_t t = blockIdx.x;
   const int64_t slot = p.slot_mapping[t];
   if (slot < 0) return;
+  if (slot >= p.num_slots) {
+    if (threadIdx.x == 0) report_device_error(p.err, MCOP_DEVERR_SLOT);
+    return;
+  }
   const int64_t blk = slot / p.block_size, off = slot % p.block_size;
   const int per_head = p.head_bytes / (int)sizeof(V);
   const int n = p.kv_heads * per_head;
@@ -356,18 +449,57 @@ __global__ void __launch_bounds__(256) cache_copy_kernel(CacheCopyParams p) {
   }
 }
 
+struct CacheSplitParams {
+  const void* key; const void* value; int64_t key_stride, value_stride;  // elements
+  void* key_cache; void* value_cache;
+  const int64_t* slot_mapping; int kv_heads, head_size, block_size, x;
+  int64_t num_slots; int* err;
+};
+
+// One CTA per token; a work item is one group of x consecutive elements of one head: the K group stays together
+// (x elements at [.., head, group, offset, :]), the V elements go x rows of block_size apart.
+template <typename E, typename KV>  // element, and the vector type one K group is moved as (sizeof(KV) == x * sizeof(E)), or E itself
+__global__ void __launch_bounds__(256) cache_split_kernel(CacheSplitParams p) {
+  const int64_t t = blockIdx.x;
+  const int64_t slot = p.slot_mapping[t];
+  if (slot < 0) return;
+  if (slot >= p.num_slots) {
+    if (threadIdx.x == 0) report_device_error(p.err, MCOP_DEVERR_SLOT);
+    return;
+  }
+  const int64_t blk = slot / p.block_size, off = slot % p.block_size;
+  const int groups = p.head_size / p.x;
+  const int n = p.kv_heads * groups;
+  const E* key = reinterpret_cast<const E*>(p.key) + t * p.key_stride;
+  const E* value = reinterpret_cast<const E*>(p.value) + t * p.value_stride;
+  E* kc = reinterpret_cast<E*>(p.key_cache);
+  E* vc = reinterpret_cast<E*>(p.value_cache);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int h = i / groups, g = i % groups;
+    const int64_t src = (int64_t)h * p.head_size + (int64_t)g * p.x;
+    const int64_t kdst = (((blk * p.kv_heads + h) * groups + g) * p.block_size + off) * p.x;
+    const int64_t vdst = ((blk * p.kv_heads + h) * (int64_t)p.head_size + (int64_t)g * p.x) * p.block_size + off;
+    if (sizeof(KV) > sizeof(E)) {
+      *reinterpret_cast<KV*>(kc + kdst) = *reinterpret_cast<const KV*>(key + src);
+    } else {
+      for (int j = 0; j < p.x; ++j) kc[kdst + j] = key[src + j];
+    }
+    for (int j = 0; j < p.x; ++j) vc[vdst + (int64_t)j * p.block_size] = value[src + j];
+  }
+}
+
 }  // namespace
 }  // namespace mcop
 
 using namespace mcop;
 
 extern "C" int mcop_rope_inplace(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
-                                 int cache_dtype, int64_t tokens, int num_heads, int num_kv_heads, int head_size,
-                                 int rot_dim, int64_t query_stride, int64_t key_stride, int64_t head_stride,
+                                 int cache_dtype, int64_t max_position, int64_t tokens, int num_heads, int num_kv_heads,
+                                 int head_size, int rot_dim, int64_t query_stride, int64_t key_stride, int64_t head_stride,
                                  int is_neox, int dtype, mcop_stream_t stream) {
   MCOP_REQUIRE(positions && query && cos_sin_cache, MCOP_ERR_ARGUMENT, "rope_inplace: null pointer");
   MCOP_REQUIRE(tokens >= 0 && num_heads > 0 && num_kv_heads >= 0 && head_size > 0 && rot_dim > 0 && rot_dim % 2 == 0 &&
-                   rot_dim <= head_size, MCOP_ERR_ARGUMENT, "rope_inplace: bad sizes");
+                   rot_dim <= head_size && max_position > 0, MCOP_ERR_ARGUMENT, "rope_inplace: bad sizes");
   RopeParams p{};
   p.q_src = query; p.q_dst = query; p.q_stride = query_stride;
   p.k_src = key; p.k_dst = key; p.k_stride = key_stride; p.head_stride = head_stride;
@@ -375,14 +507,15 @@ extern "C" int mcop_rope_inplace(const int64_t* positions, void* query, void* ke
   const int cs = cache_dtype == MCOP_F32 ? 4 : 2;
   p.cos = cos_sin_cache; p.sin = reinterpret_cast<const char*>(cos_sin_cache) + (size_t)(rot_dim / 2) * cs;
   p.cs_row_stride = rot_dim; p.positions = positions;
+  p.max_pos = max_position; p.err = pipe_error_ptr();
   return launch_rope<false>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
 }
 
-extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, const float* sin,
+extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, const float* sin, int64_t max_position,
                                 const int32_t* accum_q_lens, const int32_t* cache_lens, int batch, int64_t tokens,
                                 int q_heads, int kv_heads, int head_dim, int dtype, mcop_stream_t stream) {
   MCOP_REQUIRE(packed_qkv && output && cos && sin && accum_q_lens && cache_lens, MCOP_ERR_ARGUMENT, "rope_packed: null pointer");
-  MCOP_REQUIRE(tokens >= 0 && batch > 0 && q_heads > 0 && kv_heads >= 0 && head_dim > 0 && head_dim % 2 == 0,
+  MCOP_REQUIRE(tokens >= 0 && batch > 0 && q_heads > 0 && kv_heads >= 0 && head_dim > 0 && head_dim % 2 == 0 && max_position > 0,
                MCOP_ERR_ARGUMENT, "rope_packed: bad sizes");
   const int64_t tok_stride = (int64_t)(q_heads + 2 * kv_heads) * head_dim;
   const int es = dtype == MCOP_F32 ? 4 : 2;
@@ -394,13 +527,15 @@ extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const floa
   p.num_heads = q_heads; p.num_kv_heads = kv_heads; p.head_size = head_dim; p.rot_dim = head_dim;
   p.cos = cos; p.sin = sin; p.cs_row_stride = head_dim / 2;
   p.accum_q_lens = accum_q_lens; p.cache_lens = cache_lens; p.batch = batch;
+  p.max_pos = max_position; p.err = pipe_error_ptr();
   return launch_rope<false>(p, tokens, 1, dtype, MCOP_F32, true, (cudaStream_t)stream);
 }
 
-static int fused_rope_planes(const char* name, void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
-                             int planes, int heads, int head_dim, int dtype, uint32_t sin_flip, mcop_stream_t stream) {
+static int fused_rope_planes(const char* name, void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
+                             int64_t seq, int planes, int heads, int head_dim, int dtype, uint32_t sin_flip, mcop_stream_t stream) {
   MCOP_REQUIRE(qkv && cos && sin, MCOP_ERR_ARGUMENT, "%s: null pointer", name);
-  MCOP_REQUIRE(seq >= 0 && planes >= 2 && heads > 0 && head_dim > 0 && head_dim % 2 == 0, MCOP_ERR_ARGUMENT, "%s: bad sizes", name);
+  MCOP_REQUIRE(seq >= 0 && planes >= 2 && heads > 0 && head_dim > 0 && head_dim % 2 == 0 && max_position > 0, MCOP_ERR_ARGUMENT,
+               "%s: bad sizes", name);
   MCOP_REQUIRE(dtype == MCOP_BF16 || dtype == MCOP_F16, MCOP_ERR_UNSUPPORTED, "%s: only f16 and bf16", name);
   const int64_t tok_stride = (int64_t)planes * heads * head_dim;
   RopeParams p{};
@@ -411,23 +546,25 @@ static int fused_rope_planes(const char* name, void* qkv, const void* cos, const
   p.num_heads = heads; p.num_kv_heads = heads; p.head_size = head_dim; p.rot_dim = head_dim;
   p.cos = cos; p.sin = sin; p.cs_row_stride = head_dim / 2; p.positions = indexes;
   p.sin_flip = sin_flip;
+  p.max_pos = max_position; p.err = pipe_error_ptr();
   return launch_rope<false>(p, seq, 1, dtype, dtype, true, (cudaStream_t)stream);
 }
 
-extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
-                                   int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
-  return fused_rope_planes("fused_rope_fwd", qkv, cos, sin, indexes, seq, planes, heads, head_dim, dtype, 0u, stream);
+extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
+                                   int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
+  return fused_rope_planes("fused_rope_fwd", qkv, cos, sin, max_position, indexes, seq, planes, heads, head_dim, dtype, 0u, stream);
 }
 
 // x' = x*c + y*s, y' = y*c - x*s: the forward rotation with the sine negated (negation is exact, so every product
 // and sum rounds as in the forward form).
-extern "C" int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, const int64_t* indexes, int64_t seq,
-                                   int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
-  return fused_rope_planes("fused_rope_bwd", qkv, cos, sin, indexes, seq, planes, heads, head_dim, dtype, 0x80000000u, stream);
+extern "C" int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
+                                   int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
+  return fused_rope_planes("fused_rope_bwd", qkv, cos, sin, max_position, indexes, seq, planes, heads, head_dim, dtype, 0x80000000u,
+                           stream);
 }
 
 extern "C" int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query, void* key, const void* value,
-                                           const void* cos_sin_cache, int cache_dtype, int8_t* key_cache,
+                                           const void* cos_sin_cache, int cache_dtype, int64_t max_position, int8_t* key_cache,
                                            int8_t* value_cache, const int64_t* slot_mapping, const float* k_scale,
                                            const float* v_scale, int64_t tokens, int num_heads, int num_kv_heads,
                                            int head_size, int rot_dim, int64_t query_stride, int64_t key_stride,
@@ -436,7 +573,7 @@ extern "C" int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query
   MCOP_REQUIRE(positions && query && key && value && cos_sin_cache && key_cache && value_cache && slot_mapping && k_scale && v_scale,
                MCOP_ERR_ARGUMENT, "rope_kv_store_i8_paged: null pointer");
   MCOP_REQUIRE(tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && head_size > 0 && rot_dim > 0 && rot_dim % 2 == 0 &&
-                   rot_dim <= head_size && block_size > 0 && num_blocks >= 0,
+                   rot_dim <= head_size && block_size > 0 && num_blocks >= 0 && max_position > 0,
                MCOP_ERR_ARGUMENT, "rope_kv_store_i8_paged: bad sizes");
   RopeParams p{};
   p.q_src = query; p.q_dst = query; p.q_stride = query_stride;
@@ -448,44 +585,58 @@ extern "C" int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query
   p.v_src = value; p.v_stride = value_stride; p.k_cache = key_cache; p.v_cache = value_cache;
   p.slot_mapping = slot_mapping; p.k_scale = k_scale; p.v_scale = v_scale;
   p.block_size = block_size; p.num_slots = num_blocks * block_size;
+  p.max_pos = max_position; p.err = pipe_error_ptr();
   return launch_rope<true>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
 }
 
 extern "C" int mcop_kv_store_i8(const void* packed_qkv, int64_t qkv_stride_token, int64_t qkv_stride_head,
                                 const int32_t* q_lens, const int32_t* accum_q_lens, const int32_t* cache_lens,
-                                const int32_t* cache_slot_ids, int8_t* k_cache, int8_t* v_cache,
+                                const int32_t* cache_slot_ids, int8_t* k_cache, int8_t* v_cache, int64_t num_slots, int64_t max_len,
                                 int64_t k_stride_slot, int64_t k_stride_head, int64_t k_stride_pos,
                                 int64_t v_stride_slot, int64_t v_stride_head, int64_t v_stride_pos,
                                 const float* k_scale, const float* v_scale, int batch, int64_t tokens, int q_heads,
                                 int kv_heads, int head_dim, int dtype, mcop_stream_t stream) {
   MCOP_REQUIRE(packed_qkv && q_lens && accum_q_lens && cache_lens && cache_slot_ids && k_cache && v_cache && k_scale && v_scale,
                MCOP_ERR_ARGUMENT, "kv_store_i8: null pointer");
-  MCOP_REQUIRE(batch > 0 && tokens >= 0 && tokens <= 0x7fffffffLL && q_heads >= 0 && kv_heads > 0 && head_dim > 0,
-               MCOP_ERR_ARGUMENT, "kv_store_i8: bad sizes");
+  MCOP_REQUIRE(batch > 0 && tokens >= 0 && tokens <= 0x7fffffffLL && q_heads >= 0 && kv_heads > 0 && head_dim > 0 && num_slots > 0 &&
+                   max_len > 0, MCOP_ERR_ARGUMENT, "kv_store_i8: bad sizes");
+  MCOP_REQUIRE(dtype == MCOP_BF16 || dtype == MCOP_F16, MCOP_ERR_UNSUPPORTED, "kv_store_i8: only f16 and bf16");
   if (tokens == 0) return MCOP_OK;
   KvStoreParams p{packed_qkv, qkv_stride_token, qkv_stride_head, q_lens, accum_q_lens, cache_lens, cache_slot_ids,
                   k_cache, v_cache, k_stride_slot, k_stride_head, k_stride_pos, v_stride_slot, v_stride_head, v_stride_pos,
-                  k_scale, v_scale, batch, q_heads, kv_heads, head_dim};
+                  k_scale, v_scale, batch, q_heads, kv_heads, head_dim, num_slots, max_len, pipe_error_ptr()};
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == MCOP_BF16) kv_store_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(p);
-  else if (dtype == MCOP_F16) kv_store_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(p);
-  else return set_error(MCOP_ERR_UNSUPPORTED, "kv_store_i8: only f16 and bf16");
+  const int per_token = 2 * kv_heads * (head_dim >> 4);
+  const auto m16 = [](int64_t v) { return v % 16 == 0; };
+  const bool vec_ok = head_dim % 16 == 0 && per_token <= 256 && aligned16(packed_qkv) && (qkv_stride_token * 2) % 16 == 0 &&
+                      (qkv_stride_head * 2) % 16 == 0 && aligned16(k_cache) && aligned16(v_cache) && aligned16(k_scale) && aligned16(v_scale) &&
+                      m16(k_stride_slot) && m16(k_stride_head) && m16(k_stride_pos) && m16(v_stride_slot) && m16(v_stride_head) && m16(v_stride_pos);
+  if (vec_ok) {
+    const int tpc = 256 / per_token;
+    const unsigned grid = (unsigned)((tokens + tpc - 1) / tpc);
+    if (dtype == MCOP_BF16) kv_store_vec<__nv_bfloat16><<<grid, tpc * per_token, 0, s>>>(p, tokens, tpc);
+    else kv_store_vec<__half><<<grid, tpc * per_token, 0, s>>>(p, tokens, tpc);
+  } else {
+    if (dtype == MCOP_BF16) kv_store_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(p);
+    else kv_store_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(p);
+  }
   return check_launch("kv_store_i8");
 }
 
 extern "C" int mcop_reshape_and_cache_flash(const void* key, const void* value, int64_t key_stride, int64_t value_stride,
                                             void* key_cache, void* value_cache, int64_t block_stride, int64_t page_stride,
                                             int64_t head_stride, const int64_t* slot_mapping, int64_t tokens,
-                                            int kv_heads, int head_size, int block_size, int elem_bytes,
+                                            int kv_heads, int head_size, int block_size, int64_t num_blocks, int elem_bytes,
                                             mcop_stream_t stream) {
   MCOP_REQUIRE(key && value && key_cache && value_cache && slot_mapping, MCOP_ERR_ARGUMENT, "reshape_and_cache_flash: null pointer");
-  MCOP_REQUIRE(tokens >= 0 && tokens <= 0x7fffffffLL && kv_heads > 0 && head_size > 0 && block_size > 0 &&
+  MCOP_REQUIRE(tokens >= 0 && tokens <= 0x7fffffffLL && kv_heads > 0 && head_size > 0 && block_size > 0 && num_blocks >= 0 &&
                    (elem_bytes == 1 || elem_bytes == 2 || elem_bytes == 4),
                MCOP_ERR_ARGUMENT, "reshape_and_cache_flash: bad sizes");
   if (tokens == 0) return MCOP_OK;
   CacheCopyParams p{(const char*)key, (const char*)value, key_stride * elem_bytes, value_stride * elem_bytes,
                     (char*)key_cache, (char*)value_cache, block_stride * elem_bytes, page_stride * elem_bytes,
-                    head_stride * elem_bytes, slot_mapping, kv_heads, head_size * elem_bytes, block_size};
+                    head_stride * elem_bytes, slot_mapping, kv_heads, head_size * elem_bytes, block_size,
+                    num_blocks * block_size, pipe_error_ptr()};
   const bool v16 = p.head_bytes % 16 == 0 && aligned16(key) && aligned16(value) && aligned16(key_cache) && aligned16(value_cache) &&
                    p.key_stride % 16 == 0 && p.value_stride % 16 == 0 && p.block_stride % 16 == 0 && p.page_stride % 16 == 0 &&
                    p.head_stride % 16 == 0;
@@ -495,4 +646,38 @@ extern "C" int mcop_reshape_and_cache_flash(const void* key, const void* value, 
   else if (elem_bytes == 2) cache_copy_kernel<uint16_t><<<(unsigned)tokens, 256, 0, s>>>(p);
   else cache_copy_kernel<uint8_t><<<(unsigned)tokens, 256, 0, s>>>(p);
   return check_launch("reshape_and_cache_flash");
+}
+
+extern "C" int mcop_reshape_and_cache(const void* key, const void* value, int64_t key_stride, int64_t value_stride,
+                                      void* key_cache, void* value_cache, const int64_t* slot_mapping, int64_t tokens,
+                                      int kv_heads, int head_size, int block_size, int x, int64_t num_blocks, int elem_bytes,
+                                      mcop_stream_t stream) {
+  MCOP_REQUIRE(key && value && key_cache && value_cache && slot_mapping, MCOP_ERR_ARGUMENT, "reshape_and_cache: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && tokens <= 0x7fffffffLL && kv_heads > 0 && head_size > 0 && block_size > 0 && num_blocks >= 0 && x > 0 &&
+                   head_size % x == 0 && (elem_bytes == 1 || elem_bytes == 2 || elem_bytes == 4),
+               MCOP_ERR_ARGUMENT, "reshape_and_cache: bad sizes (head_size must be a multiple of x)");
+  if (tokens == 0) return MCOP_OK;
+  CacheSplitParams p{key, value, key_stride, value_stride, key_cache, value_cache, slot_mapping, kv_heads, head_size, block_size, x,
+                     num_blocks * block_size, pipe_error_ptr()};
+  cudaStream_t s = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)tokens;
+  // a K group of x elements moves as one 16- or 8-byte vector when it is one and everything is aligned to it
+  const int gb = x * elem_bytes;
+  const auto al = [&](const void* q, int a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
+  const bool g16 = gb == 16 && al(key, 16) && al(key_cache, 16) && (key_stride * elem_bytes) % 16 == 0;
+  const bool g8 = gb == 8 && al(key, 8) && al(key_cache, 8) && (key_stride * elem_bytes) % 8 == 0;
+  if (elem_bytes == 2) {
+    if (g16) cache_split_kernel<uint16_t, uint4><<<grid, 256, 0, s>>>(p);
+    else if (g8) cache_split_kernel<uint16_t, uint2><<<grid, 256, 0, s>>>(p);
+    else cache_split_kernel<uint16_t, uint16_t><<<grid, 256, 0, s>>>(p);
+  } else if (elem_bytes == 4) {
+    if (g16) cache_split_kernel<uint32_t, uint4><<<grid, 256, 0, s>>>(p);
+    else if (g8) cache_split_kernel<uint32_t, uint2><<<grid, 256, 0, s>>>(p);
+    else cache_split_kernel<uint32_t, uint32_t><<<grid, 256, 0, s>>>(p);
+  } else {
+    if (g16) cache_split_kernel<uint8_t, uint4><<<grid, 256, 0, s>>>(p);
+    else if (g8) cache_split_kernel<uint8_t, uint2><<<grid, 256, 0, s>>>(p);
+    else cache_split_kernel<uint8_t, uint8_t><<<grid, 256, 0, s>>>(p);
+  }
+  return check_launch("reshape_and_cache");
 }

@@ -53,10 +53,18 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
   for (int64_t t0 = tok_begin; t0 < tok_end && alive; t0 += chunk) {
     const int ntok = (int)min((int64_t)chunk, tok_end - t0);
     if (threadIdx.x < ntok) {
-      s_pos[threadIdx.x] = p.positions[t0 + threadIdx.x];
+      int64_t pos = p.positions[t0 + threadIdx.x];
+      if (pos < 0 || pos >= p.max_pos) {  // never becomes an address: the token is skipped (marked by -1) and reported
+        report_device_error(p.err, MCOP_DEVERR_POSITION);
+        pos = -1;
+      }
+      s_pos[threadIdx.x] = pos;
       if (STORE) {
         int64_t slot = p.slot_mapping[t0 + threadIdx.x];
-        if (slot >= p.num_slots) slot = -1;
+        if (slot >= p.num_slots) {
+          report_device_error(p.err, MCOP_DEVERR_SLOT);
+          slot = -1;
+        }
         s_slot[threadIdx.x] = slot;
       }
     }
@@ -71,7 +79,9 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
       bulk_g2s(dst, reinterpret_cast<const T*>(p.q_src) + t * p.q_stride, q_bytes, &full[s]);
       bulk_g2s(dst + q_bytes, reinterpret_cast<const T*>(p.k_src) + t * p.k_stride, k_bytes, &full[s]);
       if (STORE) bulk_g2s(dst + q_bytes + k_bytes, reinterpret_cast<const T*>(p.v_src) + t * p.v_stride, v_bytes, &full[s]);
-      bulk_g2s(dst + q_bytes + k_bytes + v_bytes, reinterpret_cast<const CT*>(p.cos) + s_pos[pi] * p.cs_row_stride, cs_bytes, &full[s]);
+      // a skipped token still fills its stage (row 0 of the table stands in): the ring stays in step, nothing is used
+      const int64_t cs_row = s_pos[pi] < 0 ? 0 : s_pos[pi];
+      bulk_g2s(dst + q_bytes + k_bytes + v_bytes, reinterpret_cast<const CT*>(p.cos) + cs_row * p.cs_row_stride, cs_bytes, &full[s]);
       ++issued; ++pi;
       prod.advance(stages);
     };
@@ -80,7 +90,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
     for (int tl = 0; tl < ntok; ++tl) {
       const int s = cons.s;
       const bool ok = mbar_wait_bounded(&full[s], cons.phase, err, 7);
-      if (ok) {
+      if (ok && s_pos[tl] >= 0) {
         const int64_t t = t0 + tl;
         const unsigned char* st = buf + (size_t)s * stage_bytes;
         const T* qs = reinterpret_cast<const T*>(st);

@@ -55,9 +55,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (after recording `code`) if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* err, int code) {
-  for (uint32_t i = 0; i < kPipeSpinLimit; ++i)
+// Bounded wait.  Returns false (after recording `code`) if the phase did not complete within `limit` tries.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* err, int code, uint32_t limit = kPipeSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   if (err) atomicCAS(err, 0, code);
   return false;

@@ -104,6 +104,17 @@ void rms_norm_dynamic_per_token_quant_vllm(Tensor& out, const Tensor& input, con
                                      (float)var_epsilon, dtype_code(input, "rms_norm_dynamic_per_token_quant"), cur_stream()));
 }
 
+// torch.ops._C.rms_norm_dynamic_per_token_quant: the reference allows scale_ub only with the fp8 output
+// (fused_layernorm_dynamic_per_token_quant.cu:178-180: `if (scale_ub.has_value()) TORCH_CHECK(out.dtype() == kFp8Type)`);
+// this build's output is int8, so the vLLM flavour refuses a bound while the `_custom` operator keeps honouring it.
+void rms_norm_dynamic_per_token_quant_C(Tensor& out, const Tensor& input, const Tensor& weight, Tensor& scales, double var_epsilon,
+                                        std::optional<Tensor> scale_ub, std::optional<Tensor> residual) {
+  TORCH_CHECK(!(scale_ub.has_value() && out.scalar_type() == at::kChar),
+              "rms_norm_dynamic_per_token_quant: scale_ub goes with the fp8 output only (the reference's rule); "
+              "the int8 output takes no upper bound");
+  rms_norm_dynamic_per_token_quant_vllm(out, input, weight, scales, var_epsilon, scale_ub, residual);
+}
+
 // sglang's rms_norm_dynamic_per_token_quant_custom with the extra normalised output
 // (op/sglang/include/sgl_kernel_ops.h:138-145, op/sglang/csrc/elementwise/fused_layernorm_dynamic_per_token_quant_custom.cu:434-460)
 void rms_norm_dynamic_per_token_quant_sgl(Tensor& out, Tensor& out_bf16, const Tensor& input, const Tensor& weight, Tensor& scales,
@@ -244,6 +255,7 @@ void rotary_embedding_vllm(Tensor& positions, Tensor& query, std::optional<Tenso
   const int num_heads = (int)(query_hidden / head_size);
   const int num_kv_heads = key.has_value() ? (int)(key_hidden / head_size) : num_heads;
   TORCH_CHECK(num_kv_heads == 0 || num_heads % num_kv_heads == 0);
+  TORCH_CHECK(cos_sin_cache.dim() == 2 && cos_sin_cache.size(0) > 0, "cos_sin_cache must be [max_position, rot_dim]");
   const int rot_dim = (int)cos_sin_cache.size(1);
   TORCH_CHECK(cos_sin_cache.is_contiguous());
   TORCH_CHECK(cos_sin_cache.scalar_type() == query.scalar_type() || cos_sin_cache.scalar_type() == at::kFloat,
@@ -256,9 +268,9 @@ void rotary_embedding_vllm(Tensor& positions, Tensor& query, std::optional<Tenso
   if (key.has_value()) TORCH_CHECK(key->scalar_type() == query.scalar_type());
   const c10::cuda::OptionalCUDAGuard guard(device_of(query));
   check_rc(mcop_rope_inplace(positions.data_ptr<int64_t>(), query.data_ptr(), key.has_value() ? key->data_ptr() : nullptr,
-                             cos_sin_cache.data_ptr(), dtype_code(cos_sin_cache, "cos_sin_cache"), num_tokens, num_heads,
-                             num_kv_heads, (int)head_size, rot_dim, query_stride, key_stride, head_stride, is_neox ? 1 : 0,
-                             dtype_code(query, "rotary_embedding"), cur_stream()));
+                             cos_sin_cache.data_ptr(), dtype_code(cos_sin_cache, "cos_sin_cache"), cos_sin_cache.size(0), num_tokens,
+                             num_heads, num_kv_heads, (int)head_size, rot_dim, query_stride, key_stride, head_stride,
+                             is_neox ? 1 : 0, dtype_code(query, "rotary_embedding"), cur_stream()));
 }
 
 // mcoplib.op.rotary_embedding (op/rotary_embedding.cu:99-121)
@@ -280,13 +292,15 @@ void rotary_embedding_packed(Tensor packed_qkv, Tensor q_len, Tensor accum_q_len
   const int batch = (int)cache_lens.numel();
   TORCH_CHECK(accum_q_lens.numel() >= batch + 1, "accum_q_lens must hold batch+1 entries");
   const c10::cuda::OptionalCUDAGuard guard(device_of(packed_qkv));
-  check_rc(mcop_rope_packed(packed_qkv.data_ptr(), output.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(),
+  const int64_t max_position = std::min(cos.numel(), sin.numel()) / (head_dim / 2);  // table rows both tensors hold
+  TORCH_CHECK(max_position > 0, "cos/sin tables are empty");
+  check_rc(mcop_rope_packed(packed_qkv.data_ptr(), output.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), max_position,
                             accum_q_lens.data_ptr<int32_t>(), cache_lens.data_ptr<int32_t>(), batch, tokens, q_head_num, kv_head_num,
                             head_dim, MCOP_BF16, cur_stream()));
 }
 
 // mcoplib.op.fused_rope_fwd / fused_rope_bwd (op/fused_rope.cu:13-74, 77-138): same checks, the rotation or its transpose
-using FusedRopeFn = int (*)(void*, const void*, const void*, const int64_t*, int64_t, int, int, int, int, mcop_stream_t);
+using FusedRopeFn = int (*)(void*, const void*, const void*, int64_t, const int64_t*, int64_t, int, int, int, int, mcop_stream_t);
 static Tensor fused_rope_planes(const char* name, FusedRopeFn fn, Tensor qkv, const Tensor& cos, const Tensor& sin,
                                 const std::optional<Tensor>& indexes, bool force_bf16_attn) {
   check_cuda(qkv, "qkv"); check_cuda(cos, "cos"); check_cuda(sin, "sin");
@@ -301,7 +315,10 @@ static Tensor fused_rope_planes(const char* name, FusedRopeFn fn, Tensor qkv, co
   TORCH_CHECK(cos.scalar_type() == qkv.scalar_type() && sin.scalar_type() == qkv.scalar_type());
   TORCH_CHECK(cos.size(-1) * 2 == qkv.size(3));
   const c10::cuda::OptionalCUDAGuard guard(device_of(qkv));
-  check_rc(fn(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), indexes.has_value() ? indexes->data_ptr<int64_t>() : nullptr,
+  const int64_t max_position = std::min(cos.numel(), sin.numel()) / cos.size(-1);
+  TORCH_CHECK(max_position > 0, "cos/sin tables are empty");
+  if (indexes.has_value()) TORCH_CHECK(indexes->numel() >= qkv.size(0), "indexes must hold one row number per sequence position");
+  check_rc(fn(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), max_position, indexes.has_value() ? indexes->data_ptr<int64_t>() : nullptr,
               qkv.size(0), (int)qkv.size(1), (int)qkv.size(2), (int)qkv.size(3), dtype_code(qkv, name), cur_stream()));
   return qkv;
 }
@@ -325,6 +342,11 @@ void store_kv_cache_cuda_interface(Tensor packed_qkv, Tensor q_lens, Tensor accu
   TORCH_CHECK(packed_qkv.scalar_type() == at::kHalf || packed_qkv.scalar_type() == at::kBFloat16, "Only float16, bfloat16 are supported");
   TORCH_CHECK(packed_qkv.dim() == 3 && packed_qkv.stride(2) == 1);
   TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.stride(3) == 1 && v_cache.stride(3) == 1);
+  TORCH_CHECK(k_cache.size(1) >= kv_head_num && v_cache.size(1) >= kv_head_num && k_cache.size(3) >= packed_qkv.size(2) &&
+                  v_cache.size(3) >= packed_qkv.size(2), "caches must be [slots, kv_heads, max_len, head_dim]");
+  TORCH_CHECK(q_lens.numel() >= batch_size && accum_q_lens.numel() >= batch_size + 1 && cache_lens.numel() >= batch_size &&
+                  cache_slot_ids.numel() >= batch_size && packed_qkv.size(1) >= q_head_num + 2 * kv_head_num,
+              "length tensors must hold batch_size entries (accum_q_lens one more) and packed_qkv q + 2 kv heads");
   TORCH_CHECK(k_cache.scalar_type() == at::kChar && v_cache.scalar_type() == at::kChar);
   TORCH_CHECK(k_scale.scalar_type() == at::kFloat && v_scale.scalar_type() == at::kFloat && k_scale.is_contiguous() && v_scale.is_contiguous());
   TORCH_CHECK(q_lens.scalar_type() == at::kInt && accum_q_lens.scalar_type() == at::kInt && cache_lens.scalar_type() == at::kInt &&
@@ -335,7 +357,8 @@ void store_kv_cache_cuda_interface(Tensor packed_qkv, Tensor q_lens, Tensor accu
   const c10::cuda::OptionalCUDAGuard guard(device_of(packed_qkv));
   check_rc(mcop_kv_store_i8(packed_qkv.data_ptr(), packed_qkv.stride(0), packed_qkv.stride(1), q_lens.data_ptr<int32_t>(),
                             accum_q_lens.data_ptr<int32_t>(), cache_lens.data_ptr<int32_t>(), cache_slot_ids.data_ptr<int32_t>(),
-                            k_cache.data_ptr<int8_t>(), v_cache.data_ptr<int8_t>(), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
+                            k_cache.data_ptr<int8_t>(), v_cache.data_ptr<int8_t>(), std::min(k_cache.size(0), v_cache.size(0)),
+                            std::min(k_cache.size(2), v_cache.size(2)), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
                             v_cache.stride(0), v_cache.stride(1), v_cache.stride(2), k_scale.data_ptr<float>(), v_scale.data_ptr<float>(),
                             batch_size, packed_qkv.size(0), q_head_num, kv_head_num, head_dim, dtype_code(packed_qkv, "store_kv"), cur_stream()));
 }
@@ -355,11 +378,44 @@ void reshape_and_cache_flash(Tensor& key, Tensor& value, Tensor& key_cache, Tens
   TORCH_CHECK(key_cache.strides() == value_cache.strides(), "key_cache and value_cache must share a layout");
   const int64_t tokens = slot_mapping.size(0);
   const int kv_heads = (int)key.size(1), head_size = (int)key.size(2), block_size = (int)key_cache.size(1);
+  TORCH_CHECK(key.size(0) >= tokens && value.size(0) >= tokens && value.size(1) == kv_heads && value.size(2) == head_size &&
+                  key_cache.size(2) == kv_heads && key_cache.size(3) == head_size && key_cache.sizes() == value_cache.sizes(),
+              "key/value must be [tokens, kv_heads, head_size] and the caches [num_blocks, block_size, kv_heads, head_size]");
   const c10::cuda::OptionalCUDAGuard guard(device_of(key));
   check_rc(mcop_reshape_and_cache_flash(key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0), key_cache.data_ptr(),
                                         value_cache.data_ptr(), key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
-                                        slot_mapping.data_ptr<int64_t>(), tokens, kv_heads, head_size, block_size,
+                                        slot_mapping.data_ptr<int64_t>(), tokens, kv_heads, head_size, block_size, key_cache.size(0),
                                         (int)key.element_size(), cur_stream()));
+}
+
+// torch.ops._C_cache_ops.reshape_and_cache (op/vllm/cache_kernels.cu:564-593): only kv_cache_dtype "auto";
+// key_cache [num_blocks, kv_heads, head_size / x, block_size, x], value_cache [num_blocks, kv_heads, head_size, block_size]
+void reshape_and_cache(Tensor& key, Tensor& value, Tensor& key_cache, Tensor& value_cache, Tensor& slot_mapping,
+                       const std::string& kv_cache_dtype, Tensor& k_scale, Tensor& v_scale) {
+  MCOP_DEBUG_CALL("reshape_and_cache", key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale, v_scale);
+  (void)k_scale; (void)v_scale;
+  check_cuda(key, "key");
+  TORCH_CHECK(kv_cache_dtype == "auto", "only kv_cache_dtype \"auto\" is built (as in the reference)");
+  TORCH_CHECK(key.dim() == 3 && value.dim() == 3 && key_cache.dim() == 5 && value_cache.dim() == 4,
+              "key/value must be [tokens, heads, head_size], key_cache [blocks, heads, head_size/x, block_size, x], "
+              "value_cache [blocks, heads, head_size, block_size]");
+  TORCH_CHECK(key_cache.scalar_type() == key.scalar_type() && value_cache.scalar_type() == value.scalar_type() &&
+              key.scalar_type() == value.scalar_type());
+  TORCH_CHECK(slot_mapping.scalar_type() == at::kLong && slot_mapping.is_contiguous());
+  TORCH_CHECK(key_cache.is_contiguous() && value_cache.is_contiguous(), "the caches must be contiguous");
+  TORCH_CHECK(key.stride(2) == 1 && value.stride(2) == 1 && key.stride(1) == key.size(2) && value.stride(1) == value.size(2),
+              "heads of key/value must be contiguous");
+  const int64_t tokens = slot_mapping.size(0);
+  const int kv_heads = (int)key.size(1), head_size = (int)key.size(2);
+  const int block_size = (int)key_cache.size(3), x = (int)key_cache.size(4);
+  TORCH_CHECK(key.size(0) >= tokens && value.size(0) >= tokens && value.size(1) == kv_heads && value.size(2) == head_size);
+  TORCH_CHECK(x > 0 && key_cache.size(1) == kv_heads && key_cache.size(2) * x == head_size && value_cache.size(0) == key_cache.size(0) &&
+                  value_cache.size(1) == kv_heads && value_cache.size(2) == head_size && value_cache.size(3) == block_size,
+              "cache shapes do not match key/value");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(key));
+  check_rc(mcop_reshape_and_cache(key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0), key_cache.data_ptr(),
+                                  value_cache.data_ptr(), slot_mapping.data_ptr<int64_t>(), tokens, kv_heads, head_size, block_size, x,
+                                  key_cache.size(0), (int)key.element_size(), cur_stream()));
 }
 
 // Fused RoPE + int8 paged store (addition of this build, composition of the three ops above)
@@ -382,10 +438,11 @@ void rope_kv_store_int8(Tensor& positions, Tensor& query, Tensor& key, Tensor& v
   TORCH_CHECK(key_cache.size(2) == num_kv_heads && key_cache.size(3) == head_size);
   TORCH_CHECK(k_scale.scalar_type() == at::kFloat && v_scale.scalar_type() == at::kFloat && k_scale.numel() == num_kv_heads &&
               v_scale.numel() == num_kv_heads && k_scale.is_contiguous() && v_scale.is_contiguous());
-  TORCH_CHECK(cos_sin_cache.is_contiguous() && cos_sin_cache.dim() == 2);
+  TORCH_CHECK(cos_sin_cache.is_contiguous() && cos_sin_cache.dim() == 2 && cos_sin_cache.size(0) > 0);
   const c10::cuda::OptionalCUDAGuard guard(device_of(query));
   check_rc(mcop_rope_kv_store_i8_paged(positions.data_ptr<int64_t>(), query.data_ptr(), key.data_ptr(), value.data_ptr(),
-                                       cos_sin_cache.data_ptr(), dtype_code(cos_sin_cache, "cos_sin_cache"), key_cache.data_ptr<int8_t>(),
+                                       cos_sin_cache.data_ptr(), dtype_code(cos_sin_cache, "cos_sin_cache"), cos_sin_cache.size(0),
+                                       key_cache.data_ptr<int8_t>(),
                                        value_cache.data_ptr<int8_t>(), slot_mapping.data_ptr<int64_t>(), k_scale.data_ptr<float>(),
                                        v_scale.data_ptr<float>(), tokens, num_heads, num_kv_heads, (int)head_size, (int)cos_sin_cache.size(1),
                                        query.stride(0), key.stride(0), value.stride(0), (int)key_cache.size(1), key_cache.size(0),
@@ -527,7 +584,7 @@ void store_kv_cache(Tensor k_cache, Tensor v_cache, Tensor out_loc, Tensor k, Te
   const c10::cuda::OptionalCUDAGuard guard(device_of(k));
   const Tensor loc = out_loc.scalar_type() == at::kLong ? out_loc : out_loc.to(at::kLong);
   check_rc(mcop_reshape_and_cache_flash(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
-                                        k_cache.stride(0), 0, 0, loc.data_ptr<int64_t>(), num_tokens, 1, (int)k.size(-1), 1,
+                                        k_cache.stride(0), 0, 0, loc.data_ptr<int64_t>(), num_tokens, 1, (int)k.size(-1), 1, max_tokens,
                                         (int)k.element_size(), cur_stream()));
 }
 
@@ -567,7 +624,9 @@ void apply_rope_pos_ids_cos_sin_cache(Tensor q, Tensor k, Tensor q_rope, Tensor 
   if (q_rope.data_ptr() != q.data_ptr()) q_rope.copy_(q);
   if (k_rope.data_ptr() != k.data_ptr()) k_rope.copy_(k);
   TORCH_CHECK(q_rope.stride(1) == k_rope.stride(1), "q_rope and k_rope must have one head stride");
-  check_rc(mcop_rope_inplace(pos_ids.data_ptr<int64_t>(), q_rope.data_ptr(), k_rope.data_ptr(), cos_sin_cache.data_ptr(), MCOP_F32, nnz, heads,
+  TORCH_CHECK(pos_ids.numel() >= nnz && cos_sin_cache.size(0) > 0);
+  check_rc(mcop_rope_inplace(pos_ids.data_ptr<int64_t>(), q_rope.data_ptr(), k_rope.data_ptr(), cos_sin_cache.data_ptr(), MCOP_F32,
+                             cos_sin_cache.size(0), nnz, heads,
                              kv_heads, head_dim, rot, q_rope.stride(0), k_rope.stride(0), q_rope.stride(1), interleave ? 0 : 1,
                              dtype_code(q, "apply_rope_pos_ids_cos_sin_cache"), cur_stream()));
   if (save_kv_cache) {
@@ -578,8 +637,8 @@ void apply_rope_pos_ids_cos_sin_cache(Tensor q, Tensor k, Tensor q_rope, Tensor 
                 "k_buffer and v_buffer must share one [*, kv_heads, head_dim] layout");
     check_rc(mcop_reshape_and_cache_flash(k_rope.data_ptr(), v->data_ptr(), k_rope.stride(0), v->stride(0), k_buffer->data_ptr(),
                                           v_buffer->data_ptr(), k_buffer->stride(0), 0, k_buffer->stride(1),
-                                          kv_cache_loc->data_ptr<int64_t>(), nnz, kv_heads, head_dim, 1, (int)q.element_size(),
-                                          cur_stream()));
+                                          kv_cache_loc->data_ptr<int64_t>(), nnz, kv_heads, head_dim, 1,
+                                          std::min(k_buffer->size(0), v_buffer->size(0)), (int)q.element_size(), cur_stream()));
   }
 }
 
@@ -614,8 +673,15 @@ int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Ten
   TORCH_CHECK(gating_outputs.dim() == 2 && gating_outputs.is_contiguous() && correction_bias.is_contiguous());
   TORCH_CHECK(out_routing_weights.scalar_type() == at::kFloat && out_routing_weights.is_contiguous());
   TORCH_CHECK(out_selected_experts.scalar_type() == at::kInt && out_selected_experts.is_contiguous(), "selected experts must be int32");
-  TORCH_CHECK(num_fused_shared_experts.value_or(0) == 0, "fused shared experts are not built");
-  TORCH_CHECK(moegate_type.value_or(0) == 0, "only moegate_type 0 is built");
+  // the reference's argument checks, in its order (op/fused_moe_gate_deepseek.cpp:77-101)
+  const int moe_type = moegate_type.value_or(0);
+  TORCH_CHECK(moe_type >= 0 && moe_type < 2, "Expected moegate_type == DEEPSEEK(0) or SGLANG(1), but get ", moe_type);
+  TORCH_CHECK(((topk == 8) || (topk == 9)) || debug_group_mask.has_value() || gating_outputs.size(1) % 32 == 0,
+              "Expected topk = 8, but get topk = ", topk);
+  const int num_shared = num_fused_shared_experts.value_or(0);
+  if (num_shared > 0) TORCH_CHECK(topk >= 9, "Expected topk >= 9 when fused_num_shared_experts > 0, but get topk = ", topk);
+  TORCH_CHECK(num_shared == 0 || moe_type == 1, "Invalid arguments: fused shared experts go with moegate_type 1 only");
+  TORCH_CHECK(num_shared <= 1, "more than one fused shared expert is not built (the reference draws their ids from the clock)");
   const int64_t tokens = gating_outputs.size(0);
   const int experts = (int)gating_outputs.size(1);
   TORCH_CHECK(correction_bias.numel() == experts);
@@ -628,8 +694,9 @@ int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Ten
   const c10::cuda::OptionalCUDAGuard guard(device_of(gating_outputs));
   check_rc(mcop_moe_gate_grouped_sigmoid(gating_outputs.data_ptr(), correction_bias.data_ptr(), out_routing_weights.data_ptr<float>(),
                                          out_selected_experts.data_ptr<int32_t>(), gm, tokens, experts, num_expert_group, topk_group, topk,
-                                         renormalize ? 1 : 0, routed_scaling_factor.value_or(1.0f), dtype_code(gating_outputs, "gating_outputs"),
-                                         dtype_code(correction_bias, "correction_bias"), cur_stream()));
+                                         renormalize ? 1 : 0, routed_scaling_factor.value_or(1.0f), num_shared, moe_type,
+                                         dtype_code(gating_outputs, "gating_outputs"), dtype_code(correction_bias, "correction_bias"),
+                                         cur_stream()));
   return 0;
 }
 
@@ -941,6 +1008,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fused_add_rms_norm", &fused_add_rms_norm);
   m.def("vllm_rotary_embedding", &rotary_embedding_vllm);
   m.def("reshape_and_cache_flash", &reshape_and_cache_flash);
+  m.def("reshape_and_cache", &reshape_and_cache);
   m.def("store_kv_cache", &store_kv_cache);
   m.def("apply_rope_pos_ids_cos_sin_cache", &apply_rope_pos_ids_cos_sin_cache, py::arg("q"), py::arg("k"), py::arg("q_rope"),
         py::arg("k_rope"), py::arg("cos_sin_cache"), py::arg("pos_ids"), py::arg("interleave"), py::arg("enable_pdl") = false,
@@ -961,7 +1029,7 @@ TORCH_LIBRARY(MCOP_TORCH_NS, ops) {
   ops.def(
       "rms_norm_dynamic_per_token_quant(Tensor! result, Tensor input, Tensor weight, Tensor! scale, float epsilon, "
       "Tensor? scale_ub, Tensor!? residual) -> ()");
-  ops.impl("rms_norm_dynamic_per_token_quant", torch::kCUDA, &rms_norm_dynamic_per_token_quant_vllm);
+  ops.impl("rms_norm_dynamic_per_token_quant", torch::kCUDA, &rms_norm_dynamic_per_token_quant_C);
   ops.def("dynamic_scaled_int8_quant(Tensor! result, Tensor input, Tensor! scale, Tensor!? azp) -> ()");
   ops.impl("dynamic_scaled_int8_quant", torch::kCUDA, &dynamic_scaled_int8_quant);
   ops.def(
@@ -991,6 +1059,10 @@ TORCH_LIBRARY(MCOP_TORCH_NS_MOE, moe_ops) {
 }
 
 TORCH_LIBRARY(MCOP_TORCH_NS_CACHE, cache_ops) {
+  cache_ops.def(
+      "reshape_and_cache(Tensor key, Tensor value, Tensor! key_cache, Tensor! value_cache, Tensor slot_mapping, "
+      "str kv_cache_dtype, Tensor k_scale, Tensor v_scale) -> ()");
+  cache_ops.impl("reshape_and_cache", torch::kCUDA, &reshape_and_cache);
   cache_ops.def(
       "reshape_and_cache_flash(Tensor key, Tensor value, Tensor! key_cache, Tensor! value_cache, Tensor slot_mapping, "
       "str kv_cache_dtype, Tensor k_scale, Tensor v_scale) -> ()");

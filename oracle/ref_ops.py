@@ -392,6 +392,27 @@ def reshape_and_cache_flash(key: torch.Tensor, value: torch.Tensor, key_cache: t
     return kc, vc
 
 
+def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                      slot_mapping: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """torch.ops._C_cache_ops.reshape_and_cache with kv_cache_dtype "auto", op/vllm/cache_kernels.cu:133-190:
+    key_cache [num_blocks, H, D/x, block_size, x], value_cache [num_blocks, H, D, block_size];
+    blk = slot / block_size, off = slot % block_size, negative slots are skipped;
+    key_cache[blk, h, g, off, i] = key[t, h, g*x + i], value_cache[blk, h, d, off] = value[t, h, d]."""
+    kc = key_cache.clone()
+    vc = value_cache.clone()
+    nb, H, G, bs, x = kc.shape
+    slots = slot_mapping.long()
+    keep = slots >= 0
+    blk = torch.div(slots[keep], bs, rounding_mode="floor")
+    off = slots[keep] % bs
+    n = key.shape[0]
+    k = key.reshape(n, H, G, x)[keep].to(kc.dtype)
+    v = value.reshape(n, H, G * x)[keep].to(vc.dtype)
+    kc[blk, :, :, off, :] = k
+    vc[blk, :, :, off] = v
+    return kc, vc
+
+
 def rope_kv_store_int8(positions: torch.Tensor, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                        head_size: int, cos_sin_cache: torch.Tensor, is_neox: bool,
                        key_cache: torch.Tensor, value_cache: torch.Tensor, slot_mapping: torch.Tensor,

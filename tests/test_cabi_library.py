@@ -41,7 +41,7 @@ def test_ctypes_binding_matches_header():
 def test_every_declaration_cites_the_reference():
     hdr = open(HEADER).read()
     for name in _declarations():
-        if name in ("mcop_version", "mcop_last_error", "mcop_device_error", "mcop_moe_scatter_workspace_bytes", "mcop_moe_gather_workspace_bytes"):
+        if name in ("mcop_version", "mcop_last_error", "mcop_moe_scatter_workspace_bytes", "mcop_moe_gather_workspace_bytes"):
             continue
         pos = hdr.index(name + "(")
         comment = hdr[hdr.rfind("/*", 0, pos):pos]
@@ -53,7 +53,9 @@ def test_every_declaration_cites_the_reference():
 def test_version_and_workspace_queries():
     lib = cabi.load()
     assert lib.mcop_version() >= 100
-    assert lib.mcop_moe_scatter_workspace_bytes(8192, 8, 256) == (64 + 16 * 256 + 2 * 8192 * 8) * 4
+    # header + [tiles, E] histogram + the larger of the bitmaps (16 words per tile and expert) and the per-slot ranks
+    assert lib.mcop_moe_scatter_workspace_bytes(8192, 8, 256) == (64 + 16 * 256 + max(16 * 256 * 16, 8192 * 8)) * 4
+    assert lib.mcop_moe_scatter_workspace_bytes(512, 1, 1024) == (64 + 1024 + max(1024 * 16, 512)) * 4
     assert lib.mcop_moe_gather_workspace_bytes(1000, 2000) == (1024 + 1000 * 2) * 4
     assert lib.mcop_moe_gather_workspace_bytes(0, 0) == 0
 
@@ -63,11 +65,19 @@ def test_version_and_workspace_queries():
     lambda lib: lib.mcop_add_rmsnorm_quant_i8(16, 16, 16, 8, 16, None, None, 4, 64, 1e-6, 1, None),   # row stride < hidden
     lambda lib: lib.mcop_moe_softmax_topk(16, 16, 16, 4, 8, 9, None),                                # k > experts
     lambda lib: lib.mcop_moe_softmax_topk(16, 16, 16, 4, 2048, 2, None),                             # too many experts
-    lambda lib: lib.mcop_moe_gate_grouped_sigmoid(16, 16, 16, 16, None, 4, 250, 8, 4, 8, 1, 1.0, 0, 0, None),  # experts % 32
-    lambda lib: lib.mcop_moe_gate_grouped_sigmoid(16, 16, 16, 16, None, 4, 256, 8, 1, 40, 1, 1.0, 0, 0, None),  # topk too large
+    lambda lib: lib.mcop_moe_gate_grouped_sigmoid(16, 16, 16, 16, None, 4, 250, 8, 4, 8, 1, 1.0, 0, 0, 0, 0, None),  # experts % 32
+    lambda lib: lib.mcop_moe_gate_grouped_sigmoid(16, 16, 16, 16, None, 4, 256, 8, 1, 40, 1, 1.0, 0, 0, 0, 0, None),  # topk too large
+    lambda lib: lib.mcop_moe_gate_grouped_sigmoid(16, 16, 16, 16, None, 4, 256, 8, 4, 9, 1, 1.0, 1, 0, 0, 0, None),  # shared expert with type 0
+    lambda lib: lib.mcop_moe_gate_grouped_sigmoid(16, 16, 16, 16, None, 4, 256, 8, 4, 9, 1, 1.0, 2, 1, 0, 0, None),  # two shared experts
+    lambda lib: lib.mcop_moe_gate_grouped_sigmoid(16, 16, 16, 16, None, 4, 256, 8, 4, 8, 1, 1.0, 0, 2, 0, 0, None),  # moegate_type 2
     lambda lib: lib.mcop_moe_scatter_quant_i8(16, 16, 16, 16, 16, 16, 16, 16, 16, None, 4, 64, 2, 8, None, 0, None),  # no workspace
     lambda lib: lib.mcop_moe_gather(16, 16, 16, None, 0, 4, 8, 64, None, 0, None),                   # no workspace, no tok2row
-    lambda lib: lib.mcop_rope_inplace(16, 16, 16, 16, 1, 4, 8, 2, 128, 130, 1024, 256, 128, 1, 1, None),  # rot_dim > head_size
+    lambda lib: lib.mcop_rope_inplace(16, 16, 16, 16, 1, 64, 4, 8, 2, 128, 130, 1024, 256, 128, 1, 1, None),  # rot_dim > head_size
+    lambda lib: lib.mcop_rope_inplace(16, 16, 16, 16, 1, 0, 4, 8, 2, 128, 128, 1024, 256, 128, 1, 1, None),   # empty cos/sin table
+    lambda lib: lib.mcop_reshape_and_cache(16, 16, 256, 256, 16, 16, 16, 4, 2, 128, 16, 7, 8, 2, None),        # head_size % x
+    lambda lib: lib.mcop_silu_mul_quant_i8_masked_pack(16, 1, 16, 0, 18, 2, 4, 64, 256, None),                 # out_packed not 4-byte aligned
+    lambda lib: lib.mcop_silu_mul_quant_i8_masked_pack(16, 1, 16, 0, 16, 2, 4, 64, 255, None),                 # odd record stride
+    lambda lib: lib.mcop_selftest_wait_timeout(0, None),                                                      # limit out of range
     lambda lib: lib.mcop_rmsnorm(16, 16, 16, 16, None, 4, 64, 1e-6, 0, 1, 1, None),                  # after_res without residual
 ])
 def test_bad_arguments_are_rejected_without_a_launch(call):
@@ -94,3 +104,4 @@ def test_op_module_refuses_cpu_tensors():
     assert op.torch_namespace == "mcop_C"
     assert hasattr(torch.ops.mcop_C, "rms_norm_dynamic_per_token_quant")
     assert hasattr(torch.ops.mcop_C_cache_ops, "reshape_and_cache_flash")
+    assert hasattr(torch.ops.mcop_C_cache_ops, "reshape_and_cache")

@@ -105,6 +105,21 @@ def test_gate_shapes(op, E, G, tg, topk, renorm):
     C.assert_close(w[same], w_ref[same], rel=1e-4, abs_=1e-6); C.assert_equal(gm[same], gm_ref[same])
 
 
+def test_gate_logits_that_start_off_a_16_byte_boundary(op):
+    """A contiguous fp32 logits view whose first element sits 4 bytes into its storage: the 16-byte loads of the fast
+    path do not apply, the gate must take element loads and produce the same result."""
+    d = W.router_inputs(300, 256)
+    w_ref, ids_ref, gm_ref = R.fused_moe_gate_deepseek(d["logits"], d["bias"], 8, True, 8, 4, 2.5)
+    flat = torch.zeros(300 * 256 + 1, device=DEV)
+    view = flat[1:].view(300, 256)
+    view.copy_(d["logits"])
+    assert view.is_contiguous() and view.data_ptr() % 16 == 4
+    w = torch.empty(300, 8, device=DEV); i = torch.empty(300, 8, dtype=torch.int32, device=DEV)
+    op.fused_moe_gate_deepseek(view, d["bias"].to(DEV), w, i, 8, True, 8, 4, None, 2.5, 0)
+    w0, i0, _ = _gate(op, d["logits"], d["bias"], 8, 8, 4, 2.5)
+    C.assert_equal(i.cpu(), i0); C.assert_equal(bits(w.cpu()), bits(w0))
+
+
 @pytest.mark.parametrize("dtype,bias_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16),
                                               (torch.bfloat16, torch.float32), (torch.float16, torch.float32)])
 def test_gate_half_precision_logits(op, dtype, bias_dtype):

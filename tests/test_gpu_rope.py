@@ -78,7 +78,10 @@ def test_fused_skips_negative_and_out_of_range_slots(op):
     d2["slot_mapping"][5] = 8 * 16 + 3                                              # beyond the cache: skipped, not written
     keep = torch.ones(64, dtype=torch.bool); keep[5] = False
     ks, vs = W.kv_scales(R.rotary_embedding(d2["positions"], d2["query"], d2["key"], 128, d2["cos_sin_cache"], True)[1], d2["value"], 2, 128)
+    from mcoplib_b200 import cabi
+    assert cabi.load().mcop_device_error() == 0, "negative slots are the caller's no-store mark, not an error"
     _fused(op, d2, ks, vs)
+    assert cabi.load().mcop_device_error() == cabi.DEVERR_SLOT, "a slot past the cache is skipped AND reported"
 
 
 def test_fused_gptj_and_partial_rotation_use_the_generic_kernel(op):
@@ -274,9 +277,152 @@ def test_c_abi_rope_called_directly(op):
     ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
     g = to_dev(d); ksg, vsg = ks.to(DEV), vs.to(DEV)
     rc = lib.mcop_rope_kv_store_i8_paged(g["positions"].data_ptr(), g["query"].data_ptr(), g["key"].data_ptr(), g["value"].data_ptr(),
-                                         g["cos_sin_cache"].data_ptr(), cabi.F32_CODE, g["key_cache"].data_ptr(), g["value_cache"].data_ptr(),
+                                         g["cos_sin_cache"].data_ptr(), cabi.F32_CODE, 512, g["key_cache"].data_ptr(), g["value_cache"].data_ptr(),
                                          g["slot_mapping"].data_ptr(), ksg.data_ptr(), vsg.data_ptr(), 64, 8, 2, 128, 128, 8 * 128, 2 * 128,
                                          2 * 128, 16, 8, 1, cabi.BF16_CODE, stream_ptr())
     cabi.check(rc, lib)
     torch.cuda.synchronize()
     C.assert_equal(bits(g["query"]), bits(q_ref)); C.assert_codes(g["key_cache"], kc_ref); C.assert_codes(g["value_cache"], vc_ref)
+
+
+def test_reshape_and_cache_split_layout(op):
+    """torch.ops._C_cache_ops.reshape_and_cache: K as [blocks, heads, head_size/x, block_size, x], V as
+    [blocks, heads, head_size, block_size] (op/vllm/cache_kernels.cu:133-190), negative slots skipped."""
+    ns = getattr(torch.ops, op.torch_namespace + "_cache_ops")
+    one = torch.ones(1, device=DEV)
+    for dtype, x, T, Hkv, D, bs, nb in [(torch.bfloat16, 8, 200, 4, 128, 16, 32), (torch.float16, 4, 33, 2, 64, 8, 16),
+                                       (torch.float32, 4, 50, 3, 32, 4, 64), (torch.bfloat16, 8, 40, 40, 128, 16, 8)]:
+        key = W.per_token("randn", 42, 0, T, Hkv * D, dtype).reshape(T, Hkv, D)
+        val = W.per_token("randn", 43, 0, T, Hkv * D, dtype).reshape(T, Hkv, D)
+        slots = torch.randperm(nb * bs, generator=torch.Generator().manual_seed(3))[:T].to(torch.int64)
+        slots[5] = -1
+        kc0 = torch.full((nb, Hkv, D // x, bs, x), 7.0, dtype=dtype)
+        vc0 = torch.full((nb, Hkv, D, bs), 7.0, dtype=dtype)
+        kc_ref, vc_ref = R.reshape_and_cache(key, val, kc0, vc0, slots)
+        kc, vc = kc0.to(DEV), vc0.to(DEV)
+        # key/value as strided views of a wider tensor: the token stride is not heads * head_size
+        wide = torch.zeros(T, 2 * Hkv * D + 16, dtype=dtype, device=DEV)
+        wide[:, :Hkv * D] = key.reshape(T, -1).to(DEV)
+        wide[:, Hkv * D:2 * Hkv * D] = val.reshape(T, -1).to(DEV)
+        kview = wide[:, :Hkv * D].view(T, Hkv, D)
+        vview = wide[:, Hkv * D:2 * Hkv * D].view(T, Hkv, D)
+        ns.reshape_and_cache(kview, vview, kc, vc, slots.to(DEV), "auto", one, one)
+        C.assert_equal(bits(kc), bits(kc_ref), f"key cache {dtype} x={x}")
+        C.assert_equal(bits(vc), bits(vc_ref), f"value cache {dtype} x={x}")
+        # gather back through the slot mapping, as the reference's runner checks the flash form
+        ok = slots >= 0
+        blk, off = (slots[ok] // bs), (slots[ok] % bs)
+        back = kc.cpu()[blk, :, :, off, :].reshape(int(ok.sum()), Hkv, D)
+        assert torch.equal(back, key[ok])
+    with pytest.raises(RuntimeError):
+        ns.reshape_and_cache(kview, vview, kc, vc, slots.to(DEV), "fp8", one, one)
+    with pytest.raises(RuntimeError):   # a flash-layout cache is not a split-layout cache
+        ns.reshape_and_cache(kview, vview, torch.zeros(8, 16, 40, 128, dtype=dtype, device=DEV), vc, slots.to(DEV), "auto", one, one)
+
+
+def _device_error():
+    from mcoplib_b200 import cabi
+    torch.cuda.synchronize()
+    return cabi.load().mcop_device_error()
+
+
+@pytest.mark.parametrize("T", [48, 4096])   # token-per-CTA kernel, pipelined kernel
+def test_out_of_range_position_skips_the_token_and_is_reported(op, T):
+    """A position outside the cos/sin table never becomes an address: the token (and nothing else) is left untouched,
+    nothing is stored for it, and the device error word carries MCOP_DEVERR_POSITION."""
+    from mcoplib_b200 import cabi
+    d = W.rope_kv_inputs(T, 8, 2, 128, 512, num_blocks=max(8, T // 16))
+    ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
+    assert _device_error() == 0
+    bad = [3, T - 2]
+    pos = d["positions"].clone()
+    pos[bad[0]] = 512          # one past the table
+    pos[bad[1]] = -1
+    g = to_dev(d)
+    q0, k0 = g["query"].clone(), g["key"].clone()
+    kc = Canary(tuple(d["key_cache"].shape), torch.int8); vc = Canary(tuple(d["value_cache"].shape), torch.int8)
+    op.rope_kv_store_int8(pos.to(DEV), g["query"], g["key"], g["value"], 128, g["cos_sin_cache"], True, kc.t, vc.t,
+                          g["slot_mapping"], ks.to(DEV), vs.to(DEV))
+    assert _device_error() == cabi.DEVERR_POSITION
+    assert _device_error() == 0, "reading the word clears it"
+    kc.check("key cache"); vc.check("value cache")
+    good = torch.ones(T, dtype=torch.bool); good[bad] = False
+    C.assert_equal(bits(g["query"].cpu()[good]), bits(q_ref[good]), "other tokens rotate as usual")
+    C.assert_equal(bits(g["key"].cpu()[good]), bits(k_ref[good]))
+    assert torch.equal(g["query"][bad], q0[bad]) and torch.equal(g["key"][bad], k0[bad]), "the bad tokens are untouched"
+    # cache: the bad tokens' slots keep their zeros, every other slot holds the oracle's codes
+    slots = d["slot_mapping"]
+    kcc, vcc = kc.t.cpu().view(-1, 2, 128), vc.t.cpu().view(-1, 2, 128)
+    assert int(kcc[slots[bad]].abs().max()) == 0 and int(vcc[slots[bad]].abs().max()) == 0
+    C.assert_codes(kcc[slots[good]], kc_ref.view(-1, 2, 128)[slots[good]]); C.assert_codes(vcc[slots[good]], vc_ref.view(-1, 2, 128)[slots[good]])
+    # the unfused operator checks the same way
+    q2 = q0.clone()
+    op.vllm_rotary_embedding(pos.to(DEV), q2, None, 128, g["cos_sin_cache"], True)
+    assert _device_error() == cabi.DEVERR_POSITION
+    assert torch.equal(q2[bad], q0[bad])
+    # and a following normal call is exact
+    g2 = to_dev(d)
+    op.vllm_rotary_embedding(g2["positions"], g2["query"], g2["key"], 128, g2["cos_sin_cache"], True)
+    assert _device_error() == 0
+    C.assert_equal(bits(g2["query"]), bits(q_ref))
+
+
+def test_out_of_range_slot_is_skipped_and_reported(op):
+    from mcoplib_b200 import cabi
+    d = W.rope_kv_inputs(64, 8, 2, 128, 512, num_blocks=8)
+    ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
+    slots = d["slot_mapping"].clone()
+    slots[10] = 8 * 16          # one past the cache
+    g = to_dev(d)
+    kc = Canary(tuple(d["key_cache"].shape), torch.int8); vc = Canary(tuple(d["value_cache"].shape), torch.int8)
+    op.rope_kv_store_int8(g["positions"], g["query"], g["key"], g["value"], 128, g["cos_sin_cache"], True, kc.t, vc.t,
+                          slots.to(DEV), ks.to(DEV), vs.to(DEV))
+    assert _device_error() == cabi.DEVERR_SLOT
+    kc.check("key cache"); vc.check("value cache")
+    C.assert_equal(bits(g["query"]), bits(q_ref), "rotation does not depend on the slot")
+    assert int(kc.t.cpu().view(-1, 2, 128)[d["slot_mapping"][10]].abs().max()) == 0
+    # paged copy
+    ns = getattr(torch.ops, op.torch_namespace + "_cache_ops")
+    key = g["key"].view(64, 2, 128); one = torch.ones(1, device=DEV)
+    kcf = Canary((8, 16, 2, 128), torch.bfloat16); vcf = Canary((8, 16, 2, 128), torch.bfloat16)
+    ns.reshape_and_cache_flash(key, key, kcf.t, vcf.t, slots.to(DEV), "auto", one, one)
+    assert _device_error() == cabi.DEVERR_SLOT
+    kcf.check("flash cache"); vcf.check("flash cache")
+
+
+def test_store_kv_bad_slot_or_length_is_skipped_and_reported(op, golden):
+    from mcoplib_b200 import cabi
+    key, g = records(golden, "ref:unit_test/test_store_kv.py:run_reference_impl")[0]
+    kc = Canary(tuple(g["k_cache"].shape), torch.int8); vc = Canary(tuple(g["v_cache"].shape), torch.int8)
+    args = lambda slots, lens: (g["packed_qkv"].to(DEV), g["q_lens"].to(DEV), g["accum_q_lens"].to(DEV), lens.to(DEV), slots.to(DEV),
+                                kc.t, vc.t, g["k_scale"].to(DEV), g["v_scale"].to(DEV), len(g["q_lens"]), g["q_head_num"], g["kv_head_num"])
+    bad_slots = g["cache_slot_ids"].clone(); bad_slots[0] = g["k_cache"].shape[0]
+    op.store_kv_cache_cuda_interface(*args(bad_slots, g["cache_lens"]))
+    assert _device_error() == cabi.DEVERR_KV_INDEX
+    kc.check("k cache"); vc.check("v cache")
+    bad_lens = g["cache_lens"].clone(); bad_lens[0] = g["k_cache"].shape[2]
+    op.store_kv_cache_cuda_interface(*args(g["cache_slot_ids"], bad_lens))
+    assert _device_error() == cabi.DEVERR_KV_INDEX
+    kc.check("k cache"); vc.check("v cache")
+    kc.t.zero_(); vc.t.zero_()
+    op.store_kv_cache_cuda_interface(*args(g["cache_slot_ids"], g["cache_lens"]))
+    assert _device_error() == 0
+    C.assert_equal(kc.t, g["k_cache"], key + " k"); C.assert_equal(vc.t, g["v_cache"], key + " v")
+
+
+def test_bounded_wait_runs_out_and_is_reported(op):
+    """The bounded-wait path of the pipeline kernels, exercised without any copy in flight: the self-test kernel arms a
+    stage that nothing fills, its wait runs out after a few thousand tries, the code is recorded, the drain runs, the
+    kernel returns; the context stays usable and the next operator call is exact."""
+    from mcoplib_b200 import cabi
+    from tests.gpu_util import stream_ptr
+    lib = cabi.load()
+    assert _device_error() == 0
+    cabi.check(lib.mcop_selftest_wait_timeout(2048, stream_ptr()), lib)
+    assert _device_error() == cabi.DEVERR_SELFTEST
+    assert _device_error() == 0
+    d = W.rope_kv_inputs(4096, 8, 2, 128, 512, num_blocks=256)   # a pipelined kernel right after
+    ks, vs, q_ref, k_ref, kc_ref, vc_ref = _oracle_fused(d)
+    q, k, kc, vc = _fused(op, d, ks, vs)
+    C.assert_equal(bits(q), bits(q_ref)); C.assert_codes(kc, kc_ref)
+    assert _device_error() == 0
