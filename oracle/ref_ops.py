@@ -555,6 +555,41 @@ def fused_moe_gate_deepseek(gating: torch.Tensor, bias: torch.Tensor, topk: int,
     return w.float(), ids.to(torch.int32), bits.to(torch.int32)
 
 
+def fused_moe_gate_deepseek_sglang(gating: torch.Tensor, bias: torch.Tensor, topk: int, renormalize: bool,
+                                   num_expert_group: int, topk_group: int, routed_scaling_factor: Optional[float] = None,
+                                   num_fused_shared_experts: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """mcoplib.op.fused_moe_gate_deepseek with moegate_type 1 (SGLANG), kernel/fused_moe_gate_deepseek.cuh:334-374;
+    host side op/fused_moe_gate_deepseek.cu:88-101 (scale_factor = 1.0f / routed_scaling_factor).
+    PARITY UNPINNED (the reference's test covers moegate_type 0 only).
+
+    Selection as moegate_type 0 (the shared expert replaces the LAST selected slot, so topk - shared routed experts
+    remain).  s = T(sigmoid) of the routed experts; tot = fp32 sum in the order of a 16-lane xor-butterfly.
+    One fused shared expert: last slot id = E, value T(T(tot) * T(scale_factor)).  With renormalize EVERY slot
+    (the shared one too) becomes T(T(value) / T(tot)); routed weights are never scaled.
+    Returns (weights fp32 [T, topk], ids int32 [T, topk])."""
+    n, E = gating.shape
+    shared = int(num_fused_shared_experts or 0)
+    assert shared in (0, 1)
+    routed = topk - shared
+    assert routed <= 8
+    _, ids, _ = fused_moe_gate_deepseek(gating, bias, routed, False, num_expert_group, topk_group, 1.0)
+    T = gating.dtype
+    score = _gate_scores(gating, bias)[0]
+    w = torch.gather(score, 1, ids.long())
+    p = torch.zeros(n, 8)
+    p[:, :routed] = w
+    tot = _butterfly_sum8(p, torch.float32)
+    if shared:
+        sf = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(
+            1.0 if routed_scaling_factor is None else routed_scaling_factor, dtype=torch.float32)
+        ws = rt(rt(tot, T) * rt(sf, T), T)
+        w = torch.cat([w, ws.unsqueeze(-1)], dim=1)
+        ids = torch.cat([ids, torch.full((n, 1), E, dtype=torch.int32)], dim=1)
+    if renormalize:
+        w = rt(rt(w, T) / rt(tot, T).unsqueeze(-1), T)
+    return w.float(), ids.to(torch.int32)
+
+
 def fused_moe_gate_opt(gating: torch.Tensor, bias: torch.Tensor, topk: int, renormalize: bool, num_expert_group: int,
                        topk_group: int, num_fused_shared_experts: int = 0,
                        routed_scaling_factor: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -668,6 +703,34 @@ def gate_margins(gating: torch.Tensor, bias: torch.Tensor, topk: int, num_expert
     return gap_group, (srt[:, :topk] - srt[:, 1:topk + 1]).abs()
 
 
+def _scatter_order(ids: torch.Tensor, experts_per_rank: int):
+    """Counting-sort order of the routing entries: (expert ascending, token ascending), ids outside
+    [0, experts_per_rank) dropped (op/moe_scatter_dynamic_quant.cu:49-141,152-225).
+    Returns (row2tok int32 [T*k] (-1 past the routed rows), counts, starts int32 [E], tok2row int32 [T,k] (-1 if dropped),
+    order = flat (token, slot) index of every routed row)."""
+    Tn, k = ids.shape
+    R = Tn * k
+    flat = ids.reshape(-1).long()
+    tok = torch.arange(Tn).repeat_interleave(k)
+    valid = (flat >= 0) & (flat < experts_per_rank)
+    key = torch.where(valid, flat, torch.full_like(flat, experts_per_rank))
+    order = torch.sort(key * Tn + tok, stable=True).indices
+    nvalid = int(valid.sum())
+    order = order[:nvalid]
+    counts = torch.bincount(flat[valid], minlength=experts_per_rank).to(torch.int32)
+    starts = (torch.cumsum(counts, 0) - counts).to(torch.int32)
+    row2tok = torch.full((R,), -1, dtype=torch.int32)
+    row2tok[:nvalid] = tok[order].to(torch.int32)
+    tok2row = torch.full((Tn, k), -1, dtype=torch.int32)
+    tok2row.reshape(-1)[order] = torch.arange(nvalid, dtype=torch.int32)
+    return row2tok, counts, starts, tok2row, order
+
+
+def moe_scatter_permutation(ids: torch.Tensor, experts_per_rank: int):
+    """The index outputs of moe_scatter_dynamic_quant alone (no row arithmetic): (row2tok, counts, starts, tok2row)."""
+    return _scatter_order(ids, experts_per_rank)[:4]
+
+
 def moe_scatter_dynamic_quant(hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                               smooth: torch.Tensor, experts_per_rank: int):
     """mcoplib.op.moe_scatter_dynamic_quant with no shared experts,
@@ -685,20 +748,10 @@ def moe_scatter_dynamic_quant(hidden: torch.Tensor, ids: torch.Tensor, weights: 
     Tn, H = hidden.shape
     k = ids.shape[1]
     R = Tn * k
+    row2tok, counts, starts, tok2row, order = _scatter_order(ids, experts_per_rank)
+    nvalid = order.numel()
     flat = ids.reshape(-1).long()
     tok = torch.arange(Tn).repeat_interleave(k)
-    slot = torch.arange(k).repeat(Tn)
-    valid = (flat >= 0) & (flat < experts_per_rank)
-    key = torch.where(valid, flat, torch.full_like(flat, experts_per_rank))
-    order = torch.sort(key * Tn + tok, stable=True).indices
-    nvalid = int(valid.sum())
-    order = order[:nvalid]
-    counts = torch.bincount(flat[valid], minlength=experts_per_rank).to(torch.int32)
-    starts = (torch.cumsum(counts, 0) - counts).to(torch.int32)
-    row2tok = torch.full((R,), -1, dtype=torch.int32)
-    row2tok[:nvalid] = tok[order].to(torch.int32)
-    tok2row = torch.full((Tn, k), -1, dtype=torch.int32)
-    tok2row.reshape(-1)[order] = torch.arange(nvalid, dtype=torch.int32)
     rows = torch.zeros(R, H, dtype=torch.int8)
     scales = torch.zeros(R, dtype=torch.float32)
     t_sel = tok[order]

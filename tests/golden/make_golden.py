@@ -67,10 +67,13 @@ def put(store: dict, key: str, **tensors):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MCOPLIB_REFERENCE", ""),
+                    help="checkout of MetaX-MACA/mcoplib (default: the environment variable MCOPLIB_REFERENCE)")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz"))
     args = ap.parse_args()
     ref = args.reference
+    if not ref or not os.path.isdir(ref):
+        ap.error("give the reference checkout with --reference or MCOPLIB_REFERENCE")
     store: dict = {}
 
     # ---------------------------------------------------------------- a11: grouped sigmoid gate

@@ -135,6 +135,32 @@ def test_gate_half_precision_logits(op, dtype, bias_dtype):
     C.assert_equal(gm[same], gm_ref[same]); C.assert_close(w[same], w_ref[same], rel=1e-2, abs_=1e-3)
 
 
+@pytest.mark.parametrize("E,G,tg", [(256, 8, 4), (384, 1, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shared,renorm", [(0, True), (0, False), (1, True), (1, False)])
+def test_gate_sglang_form_with_fused_shared_expert(op, E, G, tg, dtype, shared, renorm):
+    """moegate_type 1 of fused_moe_gate_deepseek: unscaled weights, optional fused shared expert in the last slot."""
+    g = torch.Generator().manual_seed(7)
+    logits = torch.randn(300, E, generator=g).to(dtype)
+    bias = (0.01 * torch.randn(E, generator=g)).to(dtype)
+    topk = 8 + shared
+    w_ref, ids_ref = R.fused_moe_gate_deepseek_sglang(logits, bias, topk, renorm, G, tg, 2.5, shared)
+    w = torch.empty(300, topk, device=DEV); i = torch.empty(300, topk, dtype=torch.int32, device=DEV)
+    rc = op.fused_moe_gate_deepseek(logits.to(DEV), bias.to(DEV), w, i, topk, renorm, G, tg, shared, 2.5, 1)
+    assert rc == 0
+    w, i = w.cpu(), i.cpu()
+    same = (i == ids_ref).all(-1)
+    assert int((~same).sum()) <= (0 if dtype == torch.float32 else 3)   # 16-bit scores tie on rounding boundaries
+    if shared:
+        assert bool((i[:, -1] == E).all())
+    tol = dict(rel=1e-5, abs_=1e-7) if dtype == torch.float32 else dict(rel=1e-2, abs_=1e-3)
+    C.assert_close(w[same], w_ref[same], "sglang-form weights", **tol)
+    with pytest.raises(RuntimeError):   # shared experts exist only in the SGLANG form; two of them are not built
+        op.fused_moe_gate_deepseek(logits.to(DEV), bias.to(DEV), w.to(DEV), i.to(DEV), 9, renorm, G, tg, 1, 2.5, 0)
+    with pytest.raises(RuntimeError):
+        op.fused_moe_gate_deepseek(logits.to(DEV), bias.to(DEV), w.to(DEV), i.to(DEV), 9, renorm, G, tg, 2, 2.5, 1)
+
+
 def test_gate_against_golden(op, golden):
     """The reference test's own criterion: row-sorted ids equal, row-sorted weights within 1e-3."""
     for key, g in records(golden, "ref:unit_test/test_fused_moe_gate_deepseek.py:biased_grouped_topk"):
@@ -258,6 +284,36 @@ def test_gather_matches_oracle_bit_for_bit(op, T, H, E, k):
     seq = R.moe_gather_bf16_sequential(y[:min(len(y), 400)], ref[2][:min(len(y), 400)], out0) if T <= 300 else None
     if seq is not None and T * k <= 400:
         assert float((g_ref.float() - seq.float()).abs().max()) <= 0.02 * float(seq.float().abs().max()) + 1e-3
+
+
+def test_gather_fixed_order_against_legal_orders_of_the_reference_at_top8_hidden_7168(op):
+    """The reference sums a token's rows with bf16 atomics in whatever order the hardware takes them; the build sums in
+    fp32 in ascending row order and rounds once.  At the DeepSeek-V3 shape (8 rows per token, hidden 7168) the result
+    must stay within the bf16 rounding noise of two legal orders of the reference (ascending and descending rows, a
+    rounding after every add), and lie closer to the exact sum than either of them on average."""
+    T, H, E, k = 256, 7168, 256, 8
+    d = W.dispatch_inputs(T, H, E, k, seed=3)
+    w, ids = R.moe_softmax_topk(W.router_inputs(T, E, seed=3)["logits"], k)
+    r2t, cnt, st, t2r = R.moe_scatter_permutation(ids, E)
+    y = d["y"]
+    out0 = W.per_token("randn", 53, 0, T, H, torch.bfloat16)
+    o = out0.clone().to(DEV)
+    op.moe_gather(y.to(DEV), r2t.to(DEV), o, t2r.to(DEV))
+    got = o.cpu().float()
+    C.assert_equal(bits(o), bits(R.moe_gather(y, r2t, out0)), "fixed-order oracle")
+    rows = torch.sort(t2r.long(), dim=1).values                     # ascending rows of every token
+    exact = out0.double() + y[rows].double().sum(dim=1)
+    def legal(order):
+        acc = out0.clone()
+        for j in order:
+            acc = (acc.float() + y[rows[:, j]].float()).to(torch.bfloat16)
+        return acc.float()
+    asc, desc = legal(range(k)), legal(reversed(range(k)))
+    scale = float(exact.abs().max())
+    for name, ref in (("ascending", asc), ("descending", desc)):
+        assert float((got - ref).abs().max()) <= 0.02 * scale + 1e-3, name
+    err = lambda v: float((v.double() - exact).abs().mean())
+    assert err(got) <= err(asc) and err(got) <= err(desc), "one rounding is closer to the exact sum than eight"
 
 
 def test_gather_arbitrary_row_map(op):

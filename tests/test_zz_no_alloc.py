@@ -5,8 +5,8 @@ already handed the whole device to its own memory pool, a plain C program that w
 output buffers, a latency-critical loop that must not run into the device synchronisation an allocation
 implies.  For them the library keeps a fixed 4 MiB table of its own and `mcop_moe_gather_noalloc` uses it
 instead of a caller workspace.  This test calls it through the C ABI (ctypes, raw device pointers) and checks
-that it writes exactly what the workspace-taking `mcop_moe_gather` writes, on two calls in a row of different
-shapes (the table keeps the first call's contents, which must not leak into the second), and that a problem
+that it writes exactly what the workspace-taking `mcop_moe_gather` writes - and what the CPU oracle computes - on two
+calls in a row of different shapes (the table keeps the first call's contents, which must not leak into the second), and that a problem
 too large for the table is refused before anything runs.
 
 The file name sorts last so that a run which stops at the first failure has already executed every other test.
@@ -15,6 +15,7 @@ import pytest
 import torch
 
 from mcoplib_b200 import cabi
+from oracle import ref_ops as R
 
 pytestmark = pytest.mark.gpu
 
@@ -60,6 +61,9 @@ def test_noalloc_gather_equals_workspace_gather_on_two_calls_in_a_row():
         torch.cuda.synchronize()
         # integer-exact: both run the same kernels, only the home of the scratch table differs
         assert torch.equal(got.view(torch.int16), expect.view(torch.int16)), (tokens, rows, hidden)
+        # and both are what the CPU oracle computes: fp32 sum in ascending row order, one rounding, bad entries skipped
+        oracle = R.moe_gather(y.cpu(), r2t.cpu(), out0.cpu())
+        assert torch.equal(got.cpu().view(torch.int16), oracle.view(torch.int16)), (tokens, rows, hidden)
         assert torch.equal(got[3].view(torch.int16), out0[3].view(torch.int16)), "a token without rows keeps its value"
         assert not torch.equal(got, out0)
     assert lib.mcop_device_error() == 0
