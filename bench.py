@@ -314,11 +314,13 @@ class Next6:
 
 
 class Part1:
-    """The other entry points of part 1 on bf16 rows of 7168, each timed on its own: fused_add_rms_norm (in place), rms_norm
-    with a residual, and the 9-argument norm + smooth quant."""
-    name = "part 1 entry points: fused_add_rms_norm, rms_norm (+residual), 9-argument rms_norm_dynamic_per_token_quant"
-    kernels = ["fused_add_rms_norm", "rms_norm", "norm_smooth_quant"]
-    launches_per_step = 3
+    """The other entry points of parts 1 and 2, each timed on its own on bf16 rows of 7168: fused_add_rms_norm (in place), rms_norm
+    with a residual, the 9-argument norm + smooth quant, scale_dynamic_quant, head_rms_norm (56 heads of 128) and the unpaged
+    int8 store of packed K/V (64 Q + 8 + 8 KV heads of 128, one sequence per 4096 tokens)."""
+    name = ("other entry points: fused_add_rms_norm, rms_norm (+residual), 9-argument rms_norm_dynamic_per_token_quant, "
+            "scale_dynamic_quant, head_rms_norm, store_kv_cache_cuda_interface")
+    kernels = ["fused_add_rms_norm", "rms_norm", "norm_smooth_quant", "scale_dynamic_quant", "head_rms_norm", "store_kv"]
+    launches_per_step = 6
 
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W
@@ -329,24 +331,49 @@ class Part1:
         # the in-place operator gets buffers of its own: it rewrites both of its inputs every step
         self.x_io, self.res_io = self.x.clone(), self.res.clone()
         self.smooth = torch.ones(7168, dtype=torch.bfloat16, **o)
+        self.smooth32 = torch.ones(7168, dtype=torch.float32, **o)
         self.out = torch.empty(tokens, 7168, dtype=torch.bfloat16, **o)
         self.after_res = torch.empty_like(self.out)
         self.after_norm = torch.empty_like(self.out)
         self.codes = torch.empty(tokens, 7168, dtype=torch.int8, **o)
         self.scales = torch.empty(tokens, dtype=torch.float32, **o)
+        self.head_w = torch.ones(56, 128, dtype=torch.bfloat16, **o)
+        # packed qkv for the unpaged store: 64 Q heads (not read), 8 K + 8 V heads of 128; sequences of 4096 tokens
+        self.Hq, self.Hkv, self.D, seq = 64, 8, 128, 4096
+        self.qkv = W.per_token("randn", 70, t0, t0 + tokens, (self.Hq + 2 * self.Hkv) * self.D, torch.bfloat16, 0, gen_device, device)
+        self.qkv = self.qkv.view(tokens, self.Hq + 2 * self.Hkv, self.D)
+        nseq = max(1, tokens // seq)
+        self.q_lens = torch.full((nseq,), tokens // nseq, dtype=torch.int32, **o)
+        self.accum = (torch.arange(nseq + 1, **o) * (tokens // nseq)).to(torch.int32)
+        self.cache_lens = torch.zeros(nseq, dtype=torch.int32, **o)
+        self.slot_ids = torch.arange(nseq, dtype=torch.int32, **o)
+        self.k_cache = torch.empty(nseq, self.Hkv, tokens // nseq, self.D, dtype=torch.int8, **o)
+        self.v_cache = torch.empty_like(self.k_cache)
+        self.kv_scale = torch.full((self.Hkv, self.D), 30.0, dtype=torch.float32, **o)
+        self.nseq = nseq
 
     def bytes_per_kernel(self):
         n = self.T * self.H
+        kv = self.T * self.Hkv * self.D
         return {"fused_add_rms_norm": 8 * n + 2 * self.H,          # x, residual read and written
                 "rms_norm": 8 * n + 2 * self.H,                    # x, residual read; out, after_res written
-                "norm_smooth_quant": 9 * n + 4 * self.H + 4 * self.T}  # + after_norm, codes, scale
+                "norm_smooth_quant": 9 * n + 4 * self.H + 4 * self.T,  # + after_norm, codes, scale
+                "scale_dynamic_quant": 3 * n + 4 * self.H + 4 * self.T,  # x read, codes + scale written
+                "head_rms_norm": 4 * n + 2 * self.H,               # every head read and written
+                "store_kv": 2 * kv * 2 + 2 * kv + 8 * self.Hkv * self.D}   # K, V heads read, two int8 caches written
 
     def stages(self, ops):
+        x3 = self.x.view(self.T, 56, 128)
+        out3 = self.out.view(self.T, 56, 128)
         return [
             lambda: ops.fused_add_rms_norm(self.x_io, self.res_io, self.w, 1e-6),
             lambda: ops.rms_norm(self.out, self.x, self.w, 1e-6, self.after_res, self.res, False),
             lambda: ops.rms_norm_dynamic_per_token_quant(self.codes, self.x, self.w, self.smooth, self.scales, 1e-6, self.after_res,
                                                          self.after_norm, self.res),
+            lambda: ops.scale_dynamic_quant(self.x, self.smooth32),
+            lambda: ops.head_rms_norm(out3, x3, self.head_w, 1e-6, 0, 56),
+            lambda: ops.store_kv_cache_cuda_interface(self.qkv, self.q_lens, self.accum, self.cache_lens, self.slot_ids, self.k_cache,
+                                                      self.v_cache, self.kv_scale, self.kv_scale, self.nseq, self.Hq, self.Hkv),
         ]
 
 

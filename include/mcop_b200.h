@@ -145,15 +145,17 @@ int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, con
 /* mcoplib.op.fused_rope_fwd, op/fused_rope.cu:13-74 (kernel/fused_rope_kernel.h:6-96).
  * In-place NeoX RoPE of the Q and K planes of qkv [seq, planes>=2, heads, D]; cos, sin [max_position, D/2] in the
  * activation dtype; row = indexes[s] (int64) or s when indexes is NULL; fp32 arithmetic, one rounding.
- * A row outside [0, max_position) leaves its token untouched (MCOP_DEVERR_POSITION). */
+ * A row outside [0, max_position) leaves its token untouched (MCOP_DEVERR_POSITION).
+ * out_bf16 != 0 (the reference's force_bf16_attn, f16 data only, :44-52): the rotated Q and K heads are rounded to and
+ * stored as bf16 in place of the f16 values; the other planes keep their f16 bits, as in the reference. */
 int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
-                        int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
+                        int64_t seq, int planes, int heads, int head_dim, int dtype, int out_bf16, mcop_stream_t stream);
 
 /* mcoplib.op.fused_rope_bwd, op/fused_rope.cu:77-138 (kernel/fused_rope_kernel.h:101-191).
  * The transposed rotation (gradient of fused_rope_fwd), same layout and arguments:
  * x' = x*c + y*s, y' = y*c - x*s in fp32, one rounding. */
 int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
-                        int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream);
+                        int64_t seq, int planes, int heads, int head_dim, int dtype, int out_bf16, mcop_stream_t stream);
 
 /* mcoplib.op.store_kv_cache_cuda_interface, op/store_kv.cu:220-350 (include/store_kv.h:2-15).
  * code = clamp(rne(x * scale[h, d]), -127, 127) for the K and V heads of packed_qkv

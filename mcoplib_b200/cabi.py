@@ -28,8 +28,8 @@ SIGNATURES = {
     "mcop_selftest_wait_timeout": (I32, [I32, P]),
     "mcop_rope_inplace": (I32, [P, P, P, P, I32, I64, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
     "mcop_rope_packed": (I32, [P, P, P, P, I64, P, P, I32, I64, I32, I32, I32, I32, P]),
-    "mcop_fused_rope_fwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, P]),
-    "mcop_fused_rope_bwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, P]),
+    "mcop_fused_rope_fwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, I32, P]),
+    "mcop_fused_rope_bwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, I32, P]),
     "mcop_kv_store_i8": (I32, [P, I64, I64, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, I64, P, P, I32, I64, I32, I32, I32, I32, P]),
     "mcop_reshape_and_cache_flash": (I32, [P, P, I64, I64, P, P, I64, I64, I64, P, I64, I32, I32, I32, I64, I32, P]),
     "mcop_reshape_and_cache": (I32, [P, P, I64, I64, P, P, P, I64, I32, I32, I32, I32, I64, I32, P]),

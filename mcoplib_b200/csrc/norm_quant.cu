@@ -676,9 +676,102 @@ __global__ void head_rmsnorm_kernel(T* out, const T* x, const WT* w, int64_t tok
     dst[i] = ElemTraits<T>::from_float(ElemTraits<T>::to_float(src[i]) / r * ElemTraits<WT>::to_float(wh[i]));
 }
 
+// The same with 16-byte accesses: a head of 8 * G elements is held by G lanes (G = 8, 16 or 32: head_dim 64, 128, 256),
+// so a warp takes 32 / G heads at a time; one vector load, one group reduction, one vector store per lane.
+template <typename T, typename WT, int G>
+__global__ void __launch_bounds__(256) head_rmsnorm_vec(T* out, const T* x, const WT* w, int64_t tokens, int heads, float eps,
+                                                        int head_offset, int head_norm) {
+  constexpr int HPW = 32 / G;  // heads per warp
+  constexpr int D = 8 * G;
+  const int lane = threadIdx.x & 31, gl = lane % G;
+  const int64_t item = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + lane / G;
+  const bool live = item < tokens * head_norm;
+  const int64_t t = live ? item / head_norm : 0;
+  const int h = head_offset + (live ? (int)(item % head_norm) : 0);
+  const int64_t off = (t * heads + h) * (int64_t)D + gl * 8;
+  float v[8];
+  if (live) Vec8<T>::load_nc(x + off, v);
+  else
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  double ss = 0.0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss = fma((double)v[j], (double)v[j], ss);
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!live) return;
+  const float r = inv_rms(ss, D, eps);
+  float wv[8], o8[8];
+  Vec8<WT>::load_nc(w + (int64_t)h * D + gl * 8, wv);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o8[j] = __fmul_rn(__fdiv_rn(v[j], r), wv[j]);   // the divide-by-rsqrt convention
+  Vec8<T>::store(out + off, o8);
+}
+
 // ---------------------------------------------------------------------------------------------
 // scale_dynamic_quant: y = x * smooth; scale = max|y| / 127; q = rne(y / scale).
 // ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void scale_quant_kernel(int8_t* q, float* scales, const T* x, const float* smooth, int hidden);
+
+// Row in registers: x and the smooth vector are read once (the any-shape kernel below reads both twice).
+// FULL: the row is exactly THREADS * NVEC vectors of 8.
+template <typename T, int THREADS, int NVEC, bool FULL = false>
+__global__ void __launch_bounds__(THREADS) scale_quant_vec(int8_t* q, float* scales, const T* x, const float* smooth, int hidden) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const int nv = hidden >> 3;
+  const T* xr = x + row * (int64_t)hidden;
+  float y[NVEC][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int k = threadIdx.x + i * THREADS;
+    if (FULL || k < nv) {
+      float v[8];
+      Vec8<T>::load_nc(xr + k * 8, v);
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(smooth + k * 8)), s1 = __ldg(reinterpret_cast<const float4*>(smooth + k * 8) + 1);
+      const float sm[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        y[i][j] = __fmul_rn(v[j], sm[j]);
+        amax = fmaxf(amax, fabsf(y[i][j]));
+      }
+    }
+  }
+  amax = block_reduce<true>(amax, red);
+  const float scale = amax / 127.0f;
+  if (threadIdx.x == 0) scales[row] = scale;
+  int8_t* qr = q + row * (int64_t)hidden;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int k = threadIdx.x + i * THREADS;
+    if (FULL || k < nv) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(__fdiv_rn(y[i][j], scale), -128, 127);   // the contract divides by the scale
+      st_cs_u2(qr + k * 8, pack_i8x8(c));
+    }
+  }
+}
+
+template <typename T>
+int launch_scale_quant(int8_t* out, float* scales, const T* x, const float* smooth, int64_t tokens, int hidden, cudaStream_t s) {
+  const int nv = hidden >> 3;
+  const unsigned grid = (unsigned)tokens;
+  const bool vec_ok = hidden % 8 == 0 && nv <= 4096 && aligned16(x) && aligned16(smooth) && (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
+  if (!vec_ok) scale_quant_kernel<T><<<grid, 256, 0, s>>>(out, scales, x, smooth, hidden);
+  else if (nv <= 256) scale_quant_vec<T, 128, 2><<<grid, 128, 0, s>>>(out, scales, x, smooth, hidden);
+  else if (nv == 512) scale_quant_vec<T, 128, 4, true><<<grid, 128, 0, s>>>(out, scales, x, smooth, hidden);
+  else if (nv == 640) scale_quant_vec<T, 160, 4, true><<<grid, 160, 0, s>>>(out, scales, x, smooth, hidden);
+  else if (nv == 768) scale_quant_vec<T, 192, 4, true><<<grid, 192, 0, s>>>(out, scales, x, smooth, hidden);
+  else if (nv == 896) scale_quant_vec<T, 224, 4, true><<<grid, 224, 0, s>>>(out, scales, x, smooth, hidden);
+  else if (nv <= 1024) scale_quant_vec<T, 256, 4><<<grid, 256, 0, s>>>(out, scales, x, smooth, hidden);
+  else if (nv <= 2048) scale_quant_vec<T, 512, 4><<<grid, 512, 0, s>>>(out, scales, x, smooth, hidden);
+  else scale_quant_vec<T, 1024, 4><<<grid, 1024, 0, s>>>(out, scales, x, smooth, hidden);
+  return check_launch("scale_dynamic_quant_i8");
+}
+// (the any-shape kernel:)
 template <typename T>
 __global__ void __launch_bounds__(256) scale_quant_kernel(int8_t* q, float* scales, const T* x, const float* smooth, int hidden) {
   __shared__ float red[33];
@@ -859,6 +952,24 @@ static int head_rmsnorm_wt(void* out, const void* x, const void* weight, int64_t
   const int warps = 8;
   const int64_t blocks = (items + warps - 1) / warps;
   MCOP_REQUIRE(blocks <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "head_rmsnorm: too many rows");
+  MCOP_REQUIRE(wdtype == dtype || wdtype == MCOP_F32, MCOP_ERR_UNSUPPORTED, "head_rmsnorm: weight dtype %d with activation dtype %d", wdtype, dtype);
+  // heads of 64, 128 or 256 elements on 16-byte aligned buffers: vector kernel, a head on 8, 16 or 32 lanes
+  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && aligned16(out) && aligned16(x) && aligned16(weight)) {
+    const int G = (int)head_dim / 8, hpw = 32 / G;
+    const int64_t vblocks = (items + warps * hpw - 1) / (warps * hpw);
+#define MCOP_HEAD_CASE(GG)                                                                                                          \
+  if (G == GG) {                                                                                                                     \
+    if (wdtype == dtype)                                                                                                             \
+      head_rmsnorm_vec<T, T, GG><<<(unsigned)vblocks, warps * 32, 0, stream>>>((T*)out, (const T*)x, (const T*)weight, tokens,       \
+                                                                               (int)heads, eps, head_offset, head_norm);            \
+    else                                                                                                                             \
+      head_rmsnorm_vec<T, float, GG><<<(unsigned)vblocks, warps * 32, 0, stream>>>((T*)out, (const T*)x, (const float*)weight,       \
+                                                                                   tokens, (int)heads, eps, head_offset, head_norm); \
+    return check_launch("head_rmsnorm");                                                                                             \
+  }
+    MCOP_HEAD_CASE(8) MCOP_HEAD_CASE(16) MCOP_HEAD_CASE(32)
+#undef MCOP_HEAD_CASE
+  }
   if (wdtype == dtype)
     head_rmsnorm_kernel<T, T><<<(unsigned)blocks, warps * 32, 0, stream>>>((T*)out, (const T*)x, (const T*)weight, tokens,
                                                                            (int)heads, (int)head_dim, eps, head_offset, head_norm);
@@ -894,10 +1005,9 @@ extern "C" int mcop_scale_dynamic_quant_i8(int8_t* out, float* scales, const voi
   if (tokens == 0) return MCOP_OK;
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
-    case MCOP_BF16: scale_quant_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __nv_bfloat16*)x, smooth, (int)hidden); break;
-    case MCOP_F16: scale_quant_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const __half*)x, smooth, (int)hidden); break;
-    case MCOP_F32: scale_quant_kernel<float><<<(unsigned)tokens, 256, 0, s>>>(out, scales, (const float*)x, smooth, (int)hidden); break;
-    default: return set_error(MCOP_ERR_UNSUPPORTED, "scale_dynamic_quant_i8: unknown dtype code %d", dtype);
+    case MCOP_BF16: return launch_scale_quant(out, scales, (const __nv_bfloat16*)x, smooth, tokens, (int)hidden, s);
+    case MCOP_F16: return launch_scale_quant(out, scales, (const __half*)x, smooth, tokens, (int)hidden, s);
+    case MCOP_F32: return launch_scale_quant(out, scales, (const float*)x, smooth, tokens, (int)hidden, s);
   }
-  return check_launch("scale_dynamic_quant_i8");
+  return set_error(MCOP_ERR_UNSUPPORTED, "scale_dynamic_quant_i8: unknown dtype code %d", dtype);
 }

@@ -39,6 +39,9 @@ struct RopeParams {
   // every position is checked against the rows of the cos / sin table before it becomes an address; a token whose
   // position is outside [0, max_pos) is left untouched and MCOP_DEVERR_POSITION is recorded in the error word
   int64_t max_pos; int* err;
+  // fused_rope_fwd / bwd with force_bf16_attn on f16 data: the rotated heads are rounded to and stored as bf16 in the
+  // same 16-bit slots (the caller then views the tensor as bf16); only the any-shape kernel takes this form
+  int out_bf16;
 };
 
 __device__ __forceinline__ void report_device_error(int* err, int code) {
@@ -231,6 +234,11 @@ __global__ void __launch_bounds__(256) rope_any(RopeParams p, int is_neox) {
     const float c = ElemTraits<CT>::to_float(cr[r]);
     const float s = __uint_as_float(__float_as_uint(ElemTraits<CT>::to_float(sr[r])) ^ p.sin_flip);
     float xo, yo;
+    if (sizeof(T) == 2 && p.out_bf16) {  // fp32 arithmetic, one rounding - to bf16 instead of T
+      reinterpret_cast<__nv_bfloat16*>(dst)[xi] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s)));
+      reinterpret_cast<__nv_bfloat16*>(dst)[yi] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(y, c), __fmul_rn(x, s)));
+      continue;
+    }
     if (PER_OP) {
       xo = round_to<T>(__fsub_rn(round_to<T>(__fmul_rn(x, c)), round_to<T>(__fmul_rn(y, s))));
       yo = round_to<T>(__fadd_rn(round_to<T>(__fmul_rn(y, c)), round_to<T>(__fmul_rn(x, s))));
@@ -293,6 +301,7 @@ int launch_rope(const RopeParams& p, int64_t tokens, int is_neox, int dtype, int
                 aligned16(p.q_src) && aligned16(p.q_dst) && (p.q_stride * esize(dtype)) % 16 == 0 &&
                 (p.head_stride * esize(dtype)) % 16 == 0 && aligned16(p.cos) && aligned16(p.sin) &&
                 (p.cs_row_stride * esize(cache_dtype)) % 16 == 0;
+  if (p.out_bf16) vec_ok = false;
   if (p.k_src) vec_ok = vec_ok && aligned16(p.k_src) && aligned16(p.k_dst) && (p.k_stride * esize(dtype)) % 16 == 0;
   if (STORE) vec_ok = vec_ok && aligned16(p.v_src) && (p.v_stride * esize(dtype)) % 16 == 0 && aligned16(p.k_cache) && aligned16(p.v_cache);
 #define MCOP_ROPE_CASE(T, CT, PER)  return launch_rope_t<T, CT, PER, STORE>(p, tokens, is_neox, vec_ok, stream)
@@ -532,11 +541,13 @@ extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const floa
 }
 
 static int fused_rope_planes(const char* name, void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
-                             int64_t seq, int planes, int heads, int head_dim, int dtype, uint32_t sin_flip, mcop_stream_t stream) {
+                             int64_t seq, int planes, int heads, int head_dim, int dtype, int out_bf16, uint32_t sin_flip,
+                             mcop_stream_t stream) {
   MCOP_REQUIRE(qkv && cos && sin, MCOP_ERR_ARGUMENT, "%s: null pointer", name);
   MCOP_REQUIRE(seq >= 0 && planes >= 2 && heads > 0 && head_dim > 0 && head_dim % 2 == 0 && max_position > 0, MCOP_ERR_ARGUMENT,
                "%s: bad sizes", name);
   MCOP_REQUIRE(dtype == MCOP_BF16 || dtype == MCOP_F16, MCOP_ERR_UNSUPPORTED, "%s: only f16 and bf16", name);
+  MCOP_REQUIRE(!out_bf16 || dtype == MCOP_F16, MCOP_ERR_ARGUMENT, "%s: the bf16 output form applies to f16 data only", name);
   const int64_t tok_stride = (int64_t)planes * heads * head_dim;
   RopeParams p{};
   p.q_src = qkv; p.q_dst = qkv; p.q_stride = tok_stride;
@@ -546,21 +557,23 @@ static int fused_rope_planes(const char* name, void* qkv, const void* cos, const
   p.num_heads = heads; p.num_kv_heads = heads; p.head_size = head_dim; p.rot_dim = head_dim;
   p.cos = cos; p.sin = sin; p.cs_row_stride = head_dim / 2; p.positions = indexes;
   p.sin_flip = sin_flip;
+  p.out_bf16 = out_bf16 ? 1 : 0;
   p.max_pos = max_position; p.err = pipe_error_ptr();
   return launch_rope<false>(p, seq, 1, dtype, dtype, true, (cudaStream_t)stream);
 }
 
 extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
-                                   int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
-  return fused_rope_planes("fused_rope_fwd", qkv, cos, sin, max_position, indexes, seq, planes, heads, head_dim, dtype, 0u, stream);
+                                   int64_t seq, int planes, int heads, int head_dim, int dtype, int out_bf16, mcop_stream_t stream) {
+  return fused_rope_planes("fused_rope_fwd", qkv, cos, sin, max_position, indexes, seq, planes, heads, head_dim, dtype, out_bf16, 0u,
+                           stream);
 }
 
 // x' = x*c + y*s, y' = y*c - x*s: the forward rotation with the sine negated (negation is exact, so every product
 // and sum rounds as in the forward form).
 extern "C" int mcop_fused_rope_bwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
-                                   int64_t seq, int planes, int heads, int head_dim, int dtype, mcop_stream_t stream) {
-  return fused_rope_planes("fused_rope_bwd", qkv, cos, sin, max_position, indexes, seq, planes, heads, head_dim, dtype, 0x80000000u,
-                           stream);
+                                   int64_t seq, int planes, int heads, int head_dim, int dtype, int out_bf16, mcop_stream_t stream) {
+  return fused_rope_planes("fused_rope_bwd", qkv, cos, sin, max_position, indexes, seq, planes, heads, head_dim, dtype, out_bf16,
+                           0x80000000u, stream);
 }
 
 extern "C" int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query, void* key, const void* value,

@@ -300,7 +300,7 @@ void rotary_embedding_packed(Tensor packed_qkv, Tensor q_len, Tensor accum_q_len
 }
 
 // mcoplib.op.fused_rope_fwd / fused_rope_bwd (op/fused_rope.cu:13-74, 77-138): same checks, the rotation or its transpose
-using FusedRopeFn = int (*)(void*, const void*, const void*, int64_t, const int64_t*, int64_t, int, int, int, int, mcop_stream_t);
+using FusedRopeFn = int (*)(void*, const void*, const void*, int64_t, const int64_t*, int64_t, int, int, int, int, int, mcop_stream_t);
 static Tensor fused_rope_planes(const char* name, FusedRopeFn fn, Tensor qkv, const Tensor& cos, const Tensor& sin,
                                 const std::optional<Tensor>& indexes, bool force_bf16_attn) {
   check_cuda(qkv, "qkv"); check_cuda(cos, "cos"); check_cuda(sin, "sin");
@@ -311,16 +311,17 @@ static Tensor fused_rope_planes(const char* name, FusedRopeFn fn, Tensor qkv, co
   }
   TORCH_CHECK(qkv.dim() == 4, "qkv must be [seq, 3, heads, head_dim]");
   TORCH_CHECK(qkv.scalar_type() == at::kHalf || qkv.scalar_type() == at::kBFloat16, "Only float16 and bfloat16 are supported");
-  TORCH_CHECK(!(force_bf16_attn && qkv.scalar_type() == at::kHalf), "the half -> bf16 reinterpreting output is not built");
   TORCH_CHECK(cos.scalar_type() == qkv.scalar_type() && sin.scalar_type() == qkv.scalar_type());
   TORCH_CHECK(cos.size(-1) * 2 == qkv.size(3));
   const c10::cuda::OptionalCUDAGuard guard(device_of(qkv));
   const int64_t max_position = std::min(cos.numel(), sin.numel()) / cos.size(-1);
   TORCH_CHECK(max_position > 0, "cos/sin tables are empty");
+  const bool to_bf16 = force_bf16_attn && qkv.scalar_type() == at::kHalf;  // with bf16 data the flag changes nothing (op/fused_rope.cu:44-60)
   if (indexes.has_value()) TORCH_CHECK(indexes->numel() >= qkv.size(0), "indexes must hold one row number per sequence position");
   check_rc(fn(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), max_position, indexes.has_value() ? indexes->data_ptr<int64_t>() : nullptr,
-              qkv.size(0), (int)qkv.size(1), (int)qkv.size(2), (int)qkv.size(3), dtype_code(qkv, name), cur_stream()));
-  return qkv;
+              qkv.size(0), (int)qkv.size(1), (int)qkv.size(2), (int)qkv.size(3), dtype_code(qkv, name), to_bf16 ? 1 : 0, cur_stream()));
+  // as the reference: the same storage, now holding bf16 in its Q and K planes, returned as a bf16 view
+  return to_bf16 ? qkv.view(at::kBFloat16) : qkv;
 }
 Tensor fused_rope_fwd(Tensor qkv, Tensor cos, Tensor sin, std::optional<Tensor> indexes, bool force_bf16_attn) {
   MCOP_DEBUG_CALL("fused_rope_fwd", qkv, cos, sin, indexes, force_bf16_attn);

@@ -343,3 +343,40 @@ def test_dynamic_scaled_int8_quant(op, dtype):
     assert int(out.t[7].abs().max()) == 0
     with pytest.raises(RuntimeError):
         ns.dynamic_scaled_int8_quant(out.t, x.to(DEV), sc.t, torch.zeros(130, 1, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("T,H", [(3000, 7168), (500, 4096), (64, 520), (33, 100)])
+def test_scale_dynamic_quant_is_exact_on_wide_ranges(op, dtype, T, H):
+    """The vector kernel (row in registers, x and smooth read once) against the oracle, bit for bit: rows spread over
+    40 binades (f16 rows overflow to infinity there: codes 0 like the oracle's), an all-zero row."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(T, H, generator=g) * torch.exp2(torch.randint(-20, 20, (T, 1), generator=g).float())
+    x[7] = 0
+    x = x.to(dtype)
+    smooth = 0.25 + 2 * torch.rand(H, generator=g)
+    q_ref, s_ref = R.scale_dynamic_quant(x, smooth)
+    q, s = op.scale_dynamic_quant(x.to(DEV), smooth.to(DEV))
+    C.assert_equal(bits(s.cpu()), bits(s_ref.reshape(-1)), "scales")
+    C.assert_equal(q.cpu(), q_ref, "codes")
+    assert int(q[7].abs().max()) == 0
+
+
+@pytest.mark.parametrize("dtype,wdtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float32), (torch.float32, torch.float32)])
+@pytest.mark.parametrize("D", [64, 128, 256, 80])
+def test_head_rms_norm_vector_kernel_is_exact(op, dtype, wdtype, D):
+    """Heads of 64, 128 and 256 elements take the 16-byte kernel (80 stays on the element kernel): the oracle's
+    x / r * w to the last bit on all but a handful of elements (the CPU's and the GPU's sqrt / division chain may differ
+    by an fp32 ulp, which can move a 16-bit rounding), heads outside [head_offset, head_offset + head_norm) untouched."""
+    T, heads = 700, 12
+    g = torch.Generator().manual_seed(12)
+    x = (torch.randn(T, heads, D, generator=g) * torch.exp2(torch.randint(-8, 8, (T, heads, 1), generator=g).float())).to(dtype)
+    w = (1 + 0.1 * torch.randn(heads, D, generator=g)).to(wdtype)
+    ref = R.head_rms_norm(x, w, 1e-5, 3, 7)
+    out = torch.full_like(x, 9.0).to(DEV)
+    op.head_rms_norm(out, x.to(DEV), w.to(DEV), 1e-5, 3, 7)
+    got, want = out[:, 3:10].cpu(), ref[:, 3:10]
+    C.assert_close(got, want, "normalised heads", rel=1e-2 if dtype != torch.float32 else 1e-6, abs_=1e-6)
+    if dtype != torch.float32:   # (in fp32 the ulp of the scalar r shows directly: the tolerance above is the check)
+        assert int((bits(got) != bits(want)).sum()) <= max(3, got.numel() // 100000), "more than a few last-bit differences"
+    assert bool((out[:, :3] == 9).all()) and bool((out[:, 10:] == 9).all())

@@ -158,6 +158,30 @@ def test_fused_rope_fwd(op):
         op.fused_rope_fwd(qkv.float().to(DEV), cos.to(DEV), sin.to(DEV), None, False)
 
 
+def test_fused_rope_fwd_force_bf16_attn(op):
+    """force_bf16_attn on f16 data (op/fused_rope.cu:44-52): fp32 rotation of the f16 inputs, Q and K rounded once to bf16
+    and stored in place, V keeps its f16 bits, the result is the same storage viewed as bf16."""
+    S, H, D = 70, 8, 128
+    qkv = W.per_token("randn", 32, 0, S, 3 * H * D, torch.float16).reshape(S, 3, H, D)
+    cs = W.cos_sin_cache(256, D, 10000.0)
+    cos, sin = cs[:, :D // 2].half().contiguous(), cs[:, D // 2:].half().contiguous()
+    idx = torch.randint(0, 256, (S,), generator=torch.Generator().manual_seed(1))
+    c, sn = cos[idx].float()[:, None, None, :], sin[idx].float()[:, None, None, :]
+    x, y = qkv[:, :2, :, :D // 2].float(), qkv[:, :2, :, D // 2:].float()
+    ref_x = (x * c - y * sn).bfloat16()     # products and difference rounded separately in fp32, one rounding to bf16
+    ref_y = (y * c + x * sn).bfloat16()
+    g = qkv.to(DEV)
+    ret = op.fused_rope_fwd(g, cos.to(DEV), sin.to(DEV), idx.to(DEV), True)
+    assert ret.dtype == torch.bfloat16 and ret.data_ptr() == g.data_ptr()
+    C.assert_equal(bits(ret[:, :2, :, :D // 2]), bits(ref_x)); C.assert_equal(bits(ret[:, :2, :, D // 2:]), bits(ref_y))
+    C.assert_equal(bits(g[:, 2]), bits(qkv[:, 2]))   # V: untouched f16 bits
+    # with bf16 data the flag changes nothing
+    qb = qkv.bfloat16()
+    a = op.fused_rope_fwd(qb.to(DEV), cos.bfloat16().to(DEV), sin.bfloat16().to(DEV), idx.to(DEV), True)
+    b = op.fused_rope_fwd(qb.to(DEV), cos.bfloat16().to(DEV), sin.bfloat16().to(DEV), idx.to(DEV), False)
+    assert a.dtype == torch.bfloat16 and torch.equal(a, b)
+
+
 def _fused_rope_bwd_literal(qkv, cos, sin, indexes):
     """kernel/fused_rope_kernel.h:172-176 written out: x' = x*c + y*s, y' = -x*s + y*c in fp32, one rounding."""
     S, _, H, D = qkv.shape
