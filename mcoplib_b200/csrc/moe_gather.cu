@@ -5,7 +5,7 @@
 //
 // Rows of a token are found through an inverse map: tok2row [tokens, topk] as written by the scatter, or a
 // (count, list) table built by a small inversion pre-pass when only the reference's 3-argument signature is
-// available.  The main kernel is persistent: a CTA takes chunks of up to 64 consecutive tokens, sorts each token's row
+// available.  The main kernel is persistent: a CTA takes chunks of up to 128 consecutive tokens, sorts each token's row
 // list in shared memory, and then streams the y rows through a ring of shared-memory stages filled by bulk
 // asynchronous copies, so the loads of the rows ahead overlap the adds of the current row.
 #include <atomic>
@@ -25,7 +25,7 @@ struct GatherParams {
 };
 
 constexpr int kMaxList = 64;    // rows of one token the row-per-CTA kernels handle without the slow scan
-constexpr int kChunkTokens = 64;
+constexpr int kChunkTokens = 128;  // tokens whose row lists a CTA of the pipelined kernel prepares at a time
 constexpr int kPipeMaxRows = 16;  // rows per token the pipelined kernel keeps in shared memory
 
 // Inversion pre-pass: per token a counter and up to `cap` row ids (unordered; the gather sorts them).
@@ -358,10 +358,10 @@ int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t strea
   int stages = (int)((96 * 1024) / row_bytes);
   stages = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
   const size_t smem = 128 + (size_t)stages * row_bytes;
-  int per_sm = (int)((227 * 1024) / (smem + 10 * 1024));
+  int per_sm = (int)((227 * 1024) / (smem + 18 * 1024));  // + the static row-list tables
   per_sm = per_sm < 1 ? 1 : (per_sm > 2048 / THREADS ? 2048 / THREADS : per_sm);
   if (per_sm > 4) per_sm = 4;
-  // every CTA gets an equal contiguous share of the tokens and prepares it in chunks of up to 64 tokens
+  // every CTA gets an equal contiguous share of the tokens and prepares it in chunks of up to kChunkTokens tokens
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > (tokens + 7) / 8) grid = (tokens + 7) / 8;
   const int chunk = kChunkTokens;
