@@ -1,6 +1,7 @@
 // Error reporting and version of the mcop_b200 C ABI.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
@@ -42,6 +43,14 @@ int* pipe_error_ptr() {
   }
   g_err_ptr[dev].store(static_cast<int*>(sym), std::memory_order_release);
   return static_cast<int*>(sym);
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("MCOP_DISABLE_PDL");
+    return !(v && v[0] && v[0] != '0');
+  }();
+  return on;
 }
 
 int sm_count() {

@@ -180,11 +180,13 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
   const int H = p.hidden_size, nv = H >> 3;
   const uint32_t row_bytes = (uint32_t)H * 2u;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
   }
   __syncthreads();
+  pdl_wait();  // nothing of global memory is touched before the kernels ahead in the stream have completed
 
   uint32_t it = 0;        // items consumed so far by this CTA
   RingPos cons, prod;     // ring positions of the consumer (all threads) and of the producer (thread 0)
@@ -367,7 +369,7 @@ int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t strea
   const int chunk = kChunkTokens;
   const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&gather_pipe<THREADS, 4>), 200 * 1024);
   MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_gather: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  gather_pipe<THREADS, 4><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, chunk, pipe_error_ptr());
+  (void)launch_pdl(gather_pipe<THREADS, 4>, dim3((unsigned)grid), dim3(THREADS), smem, stream, p, stages, chunk, pipe_error_ptr());
   return check_launch("moe_gather (pipelined)");
 }
 

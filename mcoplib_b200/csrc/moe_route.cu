@@ -6,6 +6,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "tma_pipe.cuh"
 
 namespace mcop {
 namespace {
@@ -32,6 +33,8 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(float* __restrict__ w
                                                            int32_t* __restrict__ src_rows, const LT* __restrict__ logits,
                                                            int64_t tokens, int experts, int k, bool vec_ok, bool renorm) {
   constexpr int ROWS_PER_WARP = 32 / TPR;
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int g = lane % TPR;
   const int64_t row = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROWS_PER_WARP + lane / TPR;
@@ -106,7 +109,8 @@ int launch_softmax(float* w, int32_t* ids, int32_t* src_rows, const LT* logits, 
   const int64_t blocks = (tokens + rows_per_block - 1) / rows_per_block;
   MCOP_REQUIRE(blocks <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "moe_softmax_topk: too many tokens");
   const bool vec_ok = experts == VPT * TPR && aligned16(logits);
-  softmax_topk_kernel<LT, VPT, TPR><<<(unsigned)blocks, WARPS * 32, 0, s>>>(w, ids, src_rows, logits, tokens, experts, k, vec_ok, renorm);
+  (void)launch_pdl(softmax_topk_kernel<LT, VPT, TPR>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, s, w, ids, src_rows, logits, tokens, experts, k,
+                   vec_ok, renorm);
   return check_launch("moe_softmax_topk");
 }
 
@@ -150,6 +154,8 @@ struct GateParams {
 
 template <typename T1, typename T2, int V>
 __global__ void __launch_bounds__(128) gate_kernel(GateParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= p.tokens) return;  // whole warp leaves together
@@ -334,7 +340,7 @@ int launch_gate_v(const GateParams& p, cudaStream_t s) {
   MCOP_REQUIRE(blocks <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "moe_gate: too many tokens");
   const unsigned gb = (unsigned)blocks;
   switch (p.experts / 32) {
-#define MCOP_GATE_CASE(V) case V: gate_kernel<T1, T2, V><<<gb, WARPS * 32, 0, s>>>(p); break;
+#define MCOP_GATE_CASE(V) case V: (void)launch_pdl(gate_kernel<T1, T2, V>, dim3(gb), dim3(WARPS * 32), 0, s, p); break;
     MCOP_GATE_CASE(1) MCOP_GATE_CASE(2) MCOP_GATE_CASE(3) MCOP_GATE_CASE(4) MCOP_GATE_CASE(5) MCOP_GATE_CASE(6) MCOP_GATE_CASE(8)
     MCOP_GATE_CASE(10) MCOP_GATE_CASE(12) MCOP_GATE_CASE(14) MCOP_GATE_CASE(16)
 #undef MCOP_GATE_CASE

@@ -279,7 +279,9 @@ __global__ void __launch_bounds__(256) scatter_bitmap_kernel(const int32_t* __re
   const int64_t tile = blockIdx.x;
   const int64_t tok0 = tile * kTileTokens;
   const int ntok = (int)min((int64_t)kTileTokens, tokens - tok0);
+  pdl_launch_dependents();
   for (int i = threadIdx.x; i < E * kTileWords; i += blockDim.x) bitmap[i] = 0;
+  pdl_wait();  // nothing of global memory is touched before the kernels ahead in the stream have completed
   if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0;
   __syncthreads();
   const int32_t* tids = ids + tok0 * topk;
@@ -519,10 +521,12 @@ __global__ void __launch_bounds__(THREADS, CTAS) scatter_quant_pipe(ScatterQuant
   const int nsuper = (ntiles + p.supertile - 1) / p.supertile;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
   }
+  pdl_wait();  // nothing of global memory is touched before the kernels ahead in the stream have completed
   scatter_fold_histogram(p, s_starts, ntiles, nsuper);
 
   const uint32_t buf_s = smem_addr(buf) + threadIdx.x * 16u;  // this thread's first vector of stage 0 (shared address)
@@ -768,9 +772,11 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   const cudaError_t e = ensure_dynamic_smem(fn, 224 * 1024);
   MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   if (full)
-    scatter_quant_pipe<THREADS, NVEC, true, CTAS><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, table_bytes, pipe_error_ptr());
+    (void)launch_pdl(scatter_quant_pipe<THREADS, NVEC, true, CTAS>, dim3((unsigned)grid), dim3(THREADS), smem, stream, p, stages, table_bytes,
+                     pipe_error_ptr());
   else
-    scatter_quant_pipe<THREADS, NVEC, false, CTAS><<<(unsigned)grid, THREADS, smem, stream>>>(p, stages, table_bytes, pipe_error_ptr());
+    (void)launch_pdl(scatter_quant_pipe<THREADS, NVEC, false, CTAS>, dim3((unsigned)grid), dim3(THREADS), smem, stream, p, stages, table_bytes,
+                     pipe_error_ptr());
   return check_launch("moe_scatter_quant_i8 (quant, pipelined)");
 }
 
@@ -831,8 +837,8 @@ extern "C" int mcop_moe_scatter_quant_i8(const void* hidden, const int32_t* ids,
       const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&scatter_bitmap_kernel), bsmem);
       MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_scatter_quant_i8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     }
-    scatter_bitmap_kernel<<<(unsigned)tiles, 256, bsmem, s>>>(ids, ws.tile_hist, reinterpret_cast<uint32_t*>(ws.rank), ws.ticket + 1, tok2row, tokens,
-                                                               topk, E);
+    (void)launch_pdl(scatter_bitmap_kernel, dim3((unsigned)tiles), dim3(256), bsmem, s, ids, ws.tile_hist, reinterpret_cast<uint32_t*>(ws.rank),
+                     ws.ticket + 1, tok2row, tokens, topk, E);
     rc = check_launch("moe_scatter_quant_i8 (bitmaps)");
     if (rc) return rc;
     // a CTA of nv / 4 threads tiles the row exactly (hidden 4096, 5120, 6144, 7168 = 4 x 128 ... 224 vectors of 8):

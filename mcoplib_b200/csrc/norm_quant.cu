@@ -300,11 +300,13 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
   const int64_t first = blockIdx.x, step = gridDim.x;
   const int64_t n = first < tokens ? (tokens - first + step - 1) / step : 0;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
   }
   __syncthreads();
+  pdl_wait();  // nothing of global memory is touched before the kernels ahead in the stream have completed
   auto issue = [&](int s, int64_t row) {
     unsigned char* dst = buf + (size_t)s * stage_bytes;
     mbar_expect_tx(&full[s], stage_bytes);
@@ -536,7 +538,7 @@ inline int launch_norm_pipe(const NormParams& p, int64_t tokens, cudaStream_t st
   auto launch = [&](auto kernel, int) -> int {
     const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 220 * 1024);
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "norm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kernel<<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, err);
+    (void)launch_pdl(kernel, dim3((unsigned)grid), dim3(threads), smem, stream, p, tokens, stages, err);
     return check_launch("norm (pipelined)");
   };
 #define MCOP_NORM_TILED(T, SLOT)                                                                        \

@@ -31,10 +31,12 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
   const int heads_per_iter = blockDim.x / hv;
   const int nqk = p.num_heads + p.num_kv_heads;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
   }
+  pdl_wait();  // nothing of global memory is touched before the kernels ahead in the stream have completed
   if (STORE) {
     // reciprocal scales once per CTA: the token loop then reads them from shared memory, not from global memory
     for (int h = threadIdx.x; h < p.num_kv_heads; h += blockDim.x) {
@@ -225,6 +227,7 @@ int launch_rope_pipe(const RopeParams& p, int64_t tokens, cudaStream_t stream) {
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > (tokens + 7) / 8) grid = (tokens + 7) / 8;
   const int chunk = kRopeChunk;
-  rope_neox_pipe<T, CT, PER_OP, STORE><<<(unsigned)grid, threads, smem, stream>>>(p, tokens, stages, chunk, pipe_error_ptr());
+  (void)launch_pdl(rope_neox_pipe<T, CT, PER_OP, STORE>, dim3((unsigned)grid), dim3(threads), smem, stream, p, tokens, stages, chunk,
+                   pipe_error_ptr());
   return check_launch("rope (pipelined)");
 }

@@ -102,6 +102,34 @@ __device__ __forceinline__ uint4 lds_u4(const void* p) {
   return r;
 }
 
+// Programmatic dependent launch.  The kernels of the path are launched with the stream-serialisation attribute, which
+// lets the NEXT kernel's CTAs be scheduled (and run their set-up: barrier initialisation, shared-memory carve-up) while
+// the previous kernel is still finishing, instead of after its last CTA has retired and the launch latency has passed.
+//   pdl_launch_dependents(): "the kernel after me may start being scheduled" - called first thing in every such kernel;
+//   pdl_wait(): blocks until every kernel ahead in the stream has COMPLETED and its writes are visible - called before
+//               the kernel's first access to global memory (so nothing is read early and nothing is overwritten early).
+// A kernel launched without the attribute, before or after, is ordered as usual.  MCOP_DISABLE_PDL=1 in the environment
+// (read once) launches everything without the attribute, for comparisons.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Number of SMs of the current device (cached per device; no allocation, no synchronisation).
 int sm_count();
 
