@@ -225,6 +225,13 @@ __device__ __forceinline__ float max3_abs(float a, float b, float c) {
   return d;
 }
 
+// min(|a|, |b|, |c|) likewise.
+__device__ __forceinline__ float min3_abs(float a, float b, float c) {
+  float d;
+  asm("min.abs.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool IS_MAX> __device__ __forceinline__ float block_reduce(float v, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
   v = IS_MAX ? warp_max(v) : warp_sum(v);

@@ -678,36 +678,240 @@ __global__ void head_rmsnorm_kernel(T* out, const T* x, const WT* w, int64_t tok
     dst[i] = ElemTraits<T>::from_float(ElemTraits<T>::to_float(src[i]) / r * ElemTraits<WT>::to_float(wh[i]));
 }
 
-// The same with 16-byte accesses: a head of 8 * G elements is held by G lanes (G = 8, 16 or 32: head_dim 64, 128, 256),
-// so a warp takes 32 / G heads at a time; one vector load, one group reduction, one vector store per lane.
+// The same with 16-byte accesses, for heads of 8 * G elements (G = 8, 16 or 32 lanes per head: head_dim 64, 128, 256).
+// A warp takes 32 / G heads per turn and walks the heads with a grid stride; the vector of the next turn is loaded before
+// the current one is reduced, and token / head of a turn follow from the previous turn by an add and a carry (the stride's
+// quotient and remainder by head_norm come from the host) instead of a division per head.
+//
+// The kernel is bound by instruction issue, not by memory, so the eight quotients x / r of a lane (one divisor) are not
+// eight IEEE division sequences: with inv = rn(1 / r), q0 = rn(x * inv) is within two ulps of x / r; one step
+// q1 = rn(q0 + rn(x - q0 * r) * inv) (the residual is exact in a fused multiply-add) makes it a faithful rounding, and a
+// second step the correctly rounded quotient (Markstein's theorem: a faithful quotient corrected with the correctly
+// rounded reciprocal rounds correctly), five packed operations per pair of elements.  That argument needs every
+// intermediate in the normal range, so the lane's vector goes through the division itself when r is outside
+// [2^-30, 2^30] (also a NaN r) or an element is nonzero and below 2^-60 (|x| <= sqrt(D) / r bounds the elements from
+// above).  The mean of squares is ss * (1 / D): D is a power of two, the product equals the quotient.
+__device__ __forceinline__ uint4 ld_nc_keep_u4(const void* p) {  // read-only path, kept in L1 (the weight table)
+  uint4 r;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+template <typename WT> __device__ __forceinline__ void load_weight8(const WT* p, float (&v)[8]) {
+  if constexpr (sizeof(WT) == 4) {
+    const uint4 a = ld_nc_keep_u4(p), b = ld_nc_keep_u4(p + 4);
+    v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+    v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+  } else if constexpr (ElemTraits<WT>::code == MCOP_BF16) {
+    unpack_bf16x8(ld_nc_keep_u4(p), v);
+  } else {
+    unpack_f16x8(ld_nc_keep_u4(p), v);
+  }
+}
+
 template <typename T, typename WT, int G>
-__global__ void __launch_bounds__(256) head_rmsnorm_vec(T* out, const T* x, const WT* w, int64_t tokens, int heads, float eps,
-                                                        int head_offset, int head_norm) {
-  constexpr int HPW = 32 / G;  // heads per warp
+__global__ void __launch_bounds__(256) head_rmsnorm_vec(T* out, const T* x, const WT* w, int64_t total, int heads, float eps,
+                                                        int head_offset, int head_norm, int64_t stride_tokens, int stride_heads) {
+  constexpr int HPW = 32 / G;  // heads per warp and turn
   constexpr int D = 8 * G;
   const int lane = threadIdx.x & 31, gl = lane % G;
-  const int64_t item = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + lane / G;
-  const bool live = item < tokens * head_norm;
-  const int64_t t = live ? item / head_norm : 0;
-  const int h = head_offset + (live ? (int)(item % head_norm) : 0);
-  const int64_t off = (t * heads + h) * (int64_t)D + gl * 8;
-  float v[8];
-  if (live) Vec8<T>::load_nc(x + off, v);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  int64_t item = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + lane / G;
+  const int64_t step = nwarps * HPW;  // = stride_tokens * head_norm + stride_heads
+  // token and head of the first turn: the one division of the thread
+  int64_t t = item / head_norm;
+  int h = (int)(item - t * head_norm);
+  float cur[8], nxt[8];
+  auto load = [&](float (&v)[8], int64_t tt, int hh) { Vec8<T>::load_nc(x + (tt * heads + head_offset + hh) * (int64_t)D + gl * 8, v); };
+  if (item < total) load(cur, t, h);
   else
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = 0.f;
-  double ss = 0.0;
+    for (int j = 0; j < 8; ++j) cur[j] = 0.f;
+  for (; __any_sync(0xffffffffu, item < total); item += step) {
+    const bool live = item < total;
+    // the turn after this one
+    int64_t tn = t + stride_tokens;
+    int hn = h + stride_heads;
+    if (hn >= head_norm) { hn -= head_norm; ++tn; }
+    if (item + step < total) load(nxt, tn, hn);
+    else
 #pragma unroll
-  for (int j = 0; j < 8; ++j) ss = fma((double)v[j], (double)v[j], ss);
+      for (int j = 0; j < 8; ++j) nxt[j] = 0.f;
+
+    double ss = 0.0;
 #pragma unroll
-  for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (!live) return;
-  const float r = inv_rms(ss, D, eps);
-  float wv[8], o8[8];
-  Vec8<WT>::load_nc(w + (int64_t)h * D + gl * 8, wv);
+    for (int j = 0; j < 8; ++j) ss = fma((double)cur[j], (double)cur[j], ss);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o8[j] = __fmul_rn(__fdiv_rn(v[j], r), wv[j]);   // the divide-by-rsqrt convention
-  Vec8<T>::store(out + off, o8);
+    for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (live) {
+      const float var = (float)(ss * (1.0 / D));
+      const float r = 1.0f / sqrtf(var + eps);
+      float wv[8], o8[8];
+      load_weight8(w + (int64_t)(head_offset + h) * D + gl * 8, wv);
+      bool exact = !(r >= 9.31322574615478515625e-10f && r <= 1073741824.0f);  // outside 2^-30 .. 2^30, or a NaN
+#pragma unroll
+      for (int j = 0; j < 8; ++j) exact |= (fabsf(cur[j]) < 8.67361737988403547206e-19f) & (cur[j] != 0.f);  // below 2^-60
+      if (!exact) {
+        const float inv = __frcp_rn(r);
+        const float2 inv2 = make_float2(inv, inv), nr2 = make_float2(-r, -r);
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float2 a = make_float2(cur[j], cur[j + 1]);
+          const float2 q0 = mul2_rn(a, inv2);
+          const float2 q1 = __ffma2_rn(__ffma2_rn(q0, nr2, a), inv2, q0);
+          const float2 q2 = __ffma2_rn(__ffma2_rn(q1, nr2, a), inv2, q1);
+          const float2 nw = mul2_rn(q2, make_float2(wv[j], wv[j + 1]));
+          o8[j] = nw.x;
+          o8[j + 1] = nw.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o8[j] = __fmul_rn(__fdiv_rn(cur[j], r), wv[j]);   // the divide-by-rsqrt convention
+      }
+      Vec8<T>::store(out + (t * heads + head_offset + h) * (int64_t)D + gl * 8, o8);
+    }
+    t = tn;
+    h = hn;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+  }
+}
+
+// Persistent, pipelined form for many tokens.  The heads to normalise of one token are one contiguous run of
+// head_norm * D elements; a CTA walks the tokens blockIdx.x, blockIdx.x + gridDim.x, ... with the runs of the tokens
+// `stages` ahead on their way into shared memory (bulk asynchronous copies completing on an mbarrier): the loads of the
+// kernel above are one 16-byte vector per lane and turn, too few bytes in flight to cover the memory latency (3.5 TB/s).
+//
+// A head of D = 8 * G * V elements is held by G lanes with V vectors of 8 each (vector c of lane g is vector c * G + g of
+// the head), so a warp takes 32 / G heads per round and a lane has R rounds per token.  Which heads a lane works on does
+// not depend on the token: their weights stay in registers (R * V <= 4 vectors).  What costs here is instructions, not
+// bytes (sqrt, two reciprocals, the 64-bit shuffles and the address arithmetic are per head and lane): with V = 1 a
+// lane-head of 8 elements costs 165 warp instructions, 20 per element, and the kernel runs at 4 TB/s with half of the
+// issue slots used; V = 4 spreads the per-head part over 32 elements (5.4 TB/s at 56 heads of 128; 118 registers, two
+// CTAs per SM - capped at 80 registers for three CTAs it spills and measured 7 % slower).  Same arithmetic as above, the tiny-element test
+// folded into one three-input minimum per pair (a zero element sends its lane through the division too: merely slower).
+template <typename T, typename WT, int G, int V>
+__global__ void __launch_bounds__(256, (V == 4 ? 2 : 3)) head_rmsnorm_pipe(T* out, const T* x, const WT* w, int64_t tokens, int heads, float eps,
+                                                            int head_offset, int head_norm, int stages, int* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int HPW = 32 / G, D = 8 * G * V, R = 4 / V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, gl = lane % G;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // `stages` (<= 8) barriers in the first 128 bytes
+  unsigned char* buf = smem + 128;
+  const uint32_t row_bytes = (uint32_t)head_norm * D * (uint32_t)sizeof(T);
+  const int64_t first = blockIdx.x, step = gridDim.x;
+  const int64_t n = first < tokens ? (tokens - first + step - 1) / step : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  auto issue = [&](int s, int64_t t) {
+    mbar_expect_tx(&full[s], row_bytes);
+    bulk_g2s(buf + (size_t)s * row_bytes, x + (t * heads + head_offset) * (int64_t)D, row_bytes, &full[s]);
+  };
+  if (threadIdx.x == 0)
+    for (int s = 0; s < stages && s < n; ++s) issue(s, first + s * step);
+
+  // round k of this lane works on head (k * nwarp + warp) * HPW + lane / G of the run
+  float wv[R][V][8];
+#pragma unroll
+  for (int k = 0; k < R; ++k) {
+    const int h = (k * nwarp + warp) * HPW + lane / G;
+#pragma unroll
+    for (int c = 0; c < V; ++c) {
+      if (h < head_norm) load_weight8(w + (int64_t)(head_offset + h) * D + (c * G + gl) * 8, wv[k][c]);
+      else
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wv[k][c][j] = 0.f;
+    }
+  }
+
+  int64_t i = 0;
+  RingPos pos;
+  for (; i < n; ++i, pos.advance(stages)) {
+    const int s = pos.s;
+    const bool ok = mbar_wait_bounded(&full[s], pos.phase, err, 13);
+    const int64_t t = first + i * step;
+    const unsigned char* xs = buf + (size_t)s * row_bytes;
+    if (ok) {
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        if (((k * nwarp + warp) * HPW) >= head_norm) break;  // warp-uniform: the shuffles below see whole warps
+        const int h = (k * nwarp + warp) * HPW + lane / G;
+        const bool live = h < head_norm;
+        float cur[V][8];
+        double s0 = 0.0, s1 = 0.0;  // two partial sums: half the length of the dependent chain
+        float amin = 1.0f;
+#pragma unroll
+        for (int c = 0; c < V; ++c) {
+          if (live) {
+            const unsigned char* src = xs + ((size_t)h * D + (c * G + gl) * 8) * sizeof(T);
+            if constexpr (sizeof(T) == 4) {
+              const uint4 a = lds_u4(src), b = lds_u4(src + 16);
+              cur[c][0] = __uint_as_float(a.x); cur[c][1] = __uint_as_float(a.y); cur[c][2] = __uint_as_float(a.z); cur[c][3] = __uint_as_float(a.w);
+              cur[c][4] = __uint_as_float(b.x); cur[c][5] = __uint_as_float(b.y); cur[c][6] = __uint_as_float(b.z); cur[c][7] = __uint_as_float(b.w);
+            } else if constexpr (ElemTraits<T>::code == MCOP_BF16) {
+              unpack_bf16x8(lds_u4(src), cur[c]);
+            } else {
+              unpack_f16x8(lds_u4(src), cur[c]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cur[c][j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            s0 = fma((double)cur[c][j], (double)cur[c][j], s0);
+            s1 = fma((double)cur[c][j + 1], (double)cur[c][j + 1], s1);
+            amin = min3_abs(cur[c][j], cur[c][j + 1], amin);
+          }
+        }
+        double ss = s0 + s1;
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (live) {
+          const float var = (float)(ss * (1.0 / D));
+          const float r = 1.0f / sqrtf(var + eps);
+          // fast path: r within 2^-30 .. 2^30 (not a NaN) and no element of this lane below 2^-60
+          const bool fast = r >= 9.31322574615478515625e-10f && r <= 1073741824.0f && amin >= 8.67361737988403547206e-19f;
+          const float inv = __frcp_rn(r);
+          const float2 inv2 = make_float2(inv, inv), nr2 = make_float2(-r, -r);
+#pragma unroll
+          for (int c = 0; c < V; ++c) {
+            float o8[8];
+            if (fast) {
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const float2 a = make_float2(cur[c][j], cur[c][j + 1]);
+                const float2 q0 = mul2_rn(a, inv2);
+                const float2 q1 = __ffma2_rn(__ffma2_rn(q0, nr2, a), inv2, q0);
+                const float2 q2 = __ffma2_rn(__ffma2_rn(q1, nr2, a), inv2, q1);
+                const float2 nw = mul2_rn(q2, make_float2(wv[k][c][j], wv[k][c][j + 1]));
+                o8[j] = nw.x;
+                o8[j + 1] = nw.y;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o8[j] = __fmul_rn(__fdiv_rn(cur[c][j], r), wv[k][c][j]);   // the divide-by-rsqrt convention
+            }
+            Vec8<T>::store(out + (t * heads + head_offset + h) * (int64_t)D + (c * G + gl) * 8, o8);
+          }
+        }
+      }
+    }
+    // the barrier of the token: agrees on success and tells that every thread has left the stage buffer
+    if (!__syncthreads_and(ok)) break;
+    if (threadIdx.x == 0 && i + stages < n) {
+      proxy_fence_before_reuse();
+      issue(s, first + (i + stages) * step);
+    }
+  }
+  if (i < n && threadIdx.x == 0) {
+    // a wait ran out: drain (bounded) what is still in flight so that no copy lands after the CTA has exited
+    for (int64_t k = i; k < n && k < i + stages; ++k, pos.advance(stages))
+      (void)mbar_wait_bounded(&full[pos.s], pos.phase, err, 14);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -715,6 +919,9 @@ __global__ void __launch_bounds__(256) head_rmsnorm_vec(T* out, const T* x, cons
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void scale_quant_kernel(int8_t* q, float* scales, const T* x, const float* smooth, int hidden);
+// the persistent, pipelined form (defined after the row-per-CTA kernels): returns 1 when the shape does not fit it
+template <typename T, bool SMOOTH>
+int launch_row_quant_pipe(int8_t* out, float* scales, const T* x, const float* smooth, int64_t tokens, int hidden, cudaStream_t stream);
 
 // Row in registers: x and the smooth vector are read once (the any-shape kernel below reads both twice).
 // FULL: the row is exactly THREADS * NVEC vectors of 8.
@@ -761,6 +968,10 @@ template <typename T>
 int launch_scale_quant(int8_t* out, float* scales, const T* x, const float* smooth, int64_t tokens, int hidden, cudaStream_t s) {
   const int nv = hidden >> 3;
   const unsigned grid = (unsigned)tokens;
+  {
+    const int rc = launch_row_quant_pipe<T, true>(out, scales, x, smooth, tokens, hidden, s);
+    if (rc != 1) return rc;  // 1 = not applicable: the row-per-CTA kernels below
+  }
   const bool vec_ok = hidden % 8 == 0 && nv <= 4096 && aligned16(x) && aligned16(smooth) && (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
   if (!vec_ok) scale_quant_kernel<T><<<grid, 256, 0, s>>>(out, scales, x, smooth, hidden);
   else if (nv <= 256) scale_quant_vec<T, 128, 2><<<grid, 128, 0, s>>>(out, scales, x, smooth, hidden);
@@ -844,6 +1055,10 @@ template <typename T>
 int launch_dynamic_int8_quant(int8_t* out, float* scales, const T* x, int64_t tokens, int hidden, cudaStream_t s) {
   const int nv = hidden >> 3;
   const unsigned grid = (unsigned)tokens;
+  {
+    const int rc = launch_row_quant_pipe<T, false>(out, scales, x, nullptr, tokens, hidden, s);
+    if (rc != 1) return rc;  // 1 = not applicable: the row-per-CTA kernels below
+  }
   const bool vec_ok = hidden % 8 == 0 && nv <= 4096 && aligned16(x) && (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
   if (!vec_ok) dynamic_int8_quant_kernel<T><<<grid, 256, 0, s>>>(out, scales, x, hidden);
   else if (nv <= 256) dynamic_int8_quant_vec<T, 128, 2><<<grid, 128, 0, s>>>(out, scales, x, hidden);
@@ -855,6 +1070,201 @@ int launch_dynamic_int8_quant(int8_t* out, float* scales, const T* x, int64_t to
   else if (nv <= 2048) dynamic_int8_quant_vec<T, 512, 4><<<grid, 512, 0, s>>>(out, scales, x, hidden);
   else dynamic_int8_quant_vec<T, 1024, 4><<<grid, 1024, 0, s>>>(out, scales, x, hidden);
   return check_launch("dynamic_scaled_int8_quant");
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Persistent, pipelined form of the two per-row absmax quantisers for 2-byte activations:
+//   SMOOTH = true : scale_dynamic_quant        y = x * smooth; scale = max|y| / 127; q = clamp(rne(y / scale))
+//   SMOOTH = false: dynamic_scaled_int8_quant  scale = max|x| / 127; q = rne(x * (127 / max|x|))
+// A CTA walks the rows blockIdx.x, blockIdx.x + gridDim.x, ...; the rows `stages` ahead are on their way into shared
+// memory (bulk asynchronous copies completing on an mbarrier), the smooth vector stays in registers for every row of
+// the CTA (the row-per-CTA kernels fetch its 4 bytes per element again for every row: twice the row's own bytes), and
+// a row costs one CTA barrier (the warps' maxima go to slots that alternate between consecutive rows).
+//
+// y / scale without a division per element.  d = rn(y / scale) lies between the exact products y * lo and y * hi, where
+// lo = rn(inv * (1 - 2^-21)), hi = rn(inv * (1 + 2^-21)) and inv = rn(1 / scale) (each rounding moves a value by at
+// most 2^-24 of itself, the margin is 2^-22).  fma(y, lo, 1.5 * 2^23) and fma(y, hi, 1.5 * 2^23) round those exact
+// products to the nearest integer, ties to even, and leave it in the low mantissa bits; rounding is monotonic, so when
+// both give the same integer, rne(d) is that integer.  When they differ (a tie k + 0.5 falls inside the interval, whose
+// width is at most 127 * 2^-20: about one element in 16,000), when y is a NaN (the comparison is unordered), and for
+// rows whose scale is zero, infinite or outside [2^-100, 2^100] (there 1 / scale overflows or loses bits), the codes
+// come from the division itself.  Two packed fused multiply-adds and a compare per pair instead of two divisions.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int THREADS, int NVEC, bool FULL, bool SMOOTH>
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1))
+row_quant_pipe(int8_t* q, float* scales, const T* x, const float* smooth, int hidden, int64_t tokens, int stages, int* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ float red[2][32];
+  constexpr int NWARP = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // `stages` (<= 8) barriers in the first 128 bytes
+  unsigned char* buf = smem + 128;
+  const int nv = hidden >> 3;
+  const uint32_t row_bytes = (uint32_t)hidden * 2u;
+  const int64_t first = blockIdx.x, step = gridDim.x;
+  const int64_t n = first < tokens ? (tokens - first + step - 1) / step : 0;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  pdl_wait();  // nothing of global memory is touched before the kernels ahead in the stream have completed
+  auto issue = [&](int s, int64_t row) {
+    mbar_expect_tx(&full[s], row_bytes);
+    bulk_g2s(buf + (size_t)s * row_bytes, x + row * (int64_t)hidden, row_bytes, &full[s]);
+  };
+  if (threadIdx.x == 0)
+    for (int s = 0; s < stages && s < n; ++s) issue(s, first + s * step);
+
+  float sm[SMOOTH ? NVEC : 1][8];
+  if constexpr (SMOOTH) {
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      const int v = threadIdx.x + k * THREADS;
+      if (FULL || v < nv) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(smooth + v * 8)), b = __ldg(reinterpret_cast<const float4*>(smooth + v * 8) + 1);
+        sm[k][0] = a.x; sm[k][1] = a.y; sm[k][2] = a.z; sm[k][3] = a.w;
+        sm[k][4] = b.x; sm[k][5] = b.y; sm[k][6] = b.z; sm[k][7] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sm[k][j] = 0.f;
+      }
+    }
+  }
+
+  int64_t i = 0;
+  RingPos pos;
+  uint32_t flip = 0;
+  for (; i < n; ++i, pos.advance(stages), flip ^= 1u) {
+    const int s = pos.s;
+    const bool ok = mbar_wait_bounded(&full[s], pos.phase, err, 11);
+    const int64_t row = first + i * step;
+    const unsigned char* xs = buf + (size_t)s * row_bytes;
+    float y[NVEC][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      const int v = threadIdx.x + k * THREADS;
+      if (ok && (FULL || v < nv)) {  // when the wait ran out the stage is not read; the barrier below then ends the loop
+        if (ElemTraits<T>::code == MCOP_BF16) unpack_bf16x8(lds_u4(xs + v * 16), y[k]);
+        else unpack_f16x8(lds_u4(xs + v * 16), y[k]);
+        if constexpr (SMOOTH) {
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const float2 pr = mul2_rn(make_float2(y[k][j], y[k][j + 1]), make_float2(sm[k][j], sm[k][j + 1]));
+            y[k][j] = pr.x;
+            y[k][j + 1] = pr.y;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) amax = max3_abs(y[k][j], y[k][j + 1], amax);  // amax >= 0, NaNs ignored
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[k][j] = 0.f;
+      }
+    }
+    amax = warp_max_nonneg(amax);
+    if (lane == 0) red[flip][warp] = amax;
+    // the barrier of the row: agrees on success, publishes the warps' maxima, tells that every thread has left the stage
+    if (!__syncthreads_and(ok)) break;
+    if (threadIdx.x == 0 && i + stages < n) {
+      proxy_fence_before_reuse();
+      issue(s, first + (i + stages) * step);
+    }
+    amax = warp_max_nonneg(lane < NWARP ? red[flip][lane] : 0.f);
+    const float scale = __fdiv_rn(amax, 127.0f);
+    if (threadIdx.x == 0) scales[row] = scale;
+    int8_t* qr = q + row * (int64_t)hidden;
+    if constexpr (!SMOOTH) {
+      const float inv = amax == 0.f ? 0.f : __fdiv_rn(127.0f, amax);
+#pragma unroll
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (FULL || v < nv) st_cs_u2(qr + v * 8, quant8_rn_unclamped(y[k], inv));
+      }
+    } else {
+      const bool fast = scale >= 7.888609e-31f && scale <= 1.2676506e30f;  // 2^-100 .. 2^100
+      const float inv = __fdiv_rn(1.0f, scale);
+      const float lo = __fmul_rn(inv, 0.99999952316284179688f), hi = __fmul_rn(inv, 1.00000047683715820312f);  // 1 -+ 2^-21
+      const float2 lo2 = make_float2(lo, lo), hi2 = make_float2(hi, hi), magic2 = make_float2(12582912.0f, 12582912.0f);
+#pragma unroll
+      for (int k = 0; k < NVEC; ++k) {
+        const int v = threadIdx.x + k * THREADS;
+        if (FULL || v < nv) {
+          uint32_t c[8];
+          float other[8];
+          bool exact = !fast;
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const float2 yy = make_float2(y[k][j], y[k][j + 1]);
+            const float2 a = __ffma2_rn(yy, lo2, magic2), b = __ffma2_rn(yy, hi2, magic2);
+            exact |= (a.x != b.x) | (a.y != b.y);  // a NaN compares unequal too
+            c[j] = __float_as_uint(a.x);
+            c[j + 1] = __float_as_uint(a.y);
+            other[j] = b.x;
+            other[j + 1] = b.y;
+          }
+          if (exact) {
+            // some element of these eight is undecided (or the whole row is): the division for exactly those elements.
+            // Rows of few-bit values meet exact ties often (x = max|x| / 2 gives 63.5), so this path is kept narrow.
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (!fast || __uint_as_float(c[j]) != other[j]) c[j] = (uint32_t)q_rn_clamp(__fdiv_rn(y[k][j], scale), -128, 127);
+          }
+          st_cs_u2(qr + v * 8, make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7])));
+        }
+      }
+    }
+  }
+  if (i < n && threadIdx.x == 0) {
+    // a wait ran out: drain (bounded) what is still in flight so that no copy lands after the CTA has exited
+    for (int64_t k = i; k < n && k < i + stages; ++k, pos.advance(stages))
+      (void)mbar_wait_bounded(&full[pos.s], pos.phase, err, 12);
+  }
+}
+
+// Returns MCOP_OK / an error, or 1 when the shape does not fit the pipelined kernel.
+template <typename T, bool SMOOTH>
+int launch_row_quant_pipe(int8_t* out, float* scales, const T* x, const float* smooth, int64_t tokens, int hidden, cudaStream_t stream) {
+  if constexpr (sizeof(T) != 2) {
+    return 1;
+  } else {
+    const int nv = hidden >> 3;
+    if (hidden % 8 != 0 || nv < 256 || nv > 2048 || tokens < 1024 || !aligned16(x) || (SMOOTH && !aligned16(smooth)) ||
+        (reinterpret_cast<uintptr_t>(out) & 7u) != 0)
+      return 1;
+    const size_t row_bytes = (size_t)hidden * 2;
+    int stages = (int)((64 * 1024) / row_bytes);
+    stages = stages < 2 ? 2 : (stages > 4 ? 4 : stages);
+    const size_t smem = 128 + (size_t)stages * row_bytes;
+    const bool tiles = nv == 512 || nv == 640 || nv == 768 || nv == 896;
+    const int threads = tiles ? nv / 4 : (nv <= 1024 ? 256 : 512);
+    int* err = pipe_error_ptr();
+    auto launch = [&](auto kernel) -> int {
+      const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 200 * 1024);
+      MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "row quant: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) {
+        (void)cudaGetLastError();
+        per_sm = 0;
+      }
+      if (per_sm < 1) return 1;
+      if (per_sm > 4) per_sm = 4;
+      int64_t grid = (int64_t)sm_count() * per_sm;
+      if (grid > tokens) grid = tokens;
+      (void)launch_pdl(kernel, dim3((unsigned)grid), dim3(threads), smem, stream, out, scales, x, smooth, hidden, tokens, stages, err);
+      return check_launch("row quant (pipelined)");
+    };
+    if (threads == 128 && tiles) return launch(row_quant_pipe<T, 128, 4, true, SMOOTH>);
+    if (threads == 160 && tiles) return launch(row_quant_pipe<T, 160, 4, true, SMOOTH>);
+    if (threads == 192 && tiles) return launch(row_quant_pipe<T, 192, 4, true, SMOOTH>);
+    if (threads == 224 && tiles) return launch(row_quant_pipe<T, 224, 4, true, SMOOTH>);
+    if (threads == 256) return launch(row_quant_pipe<T, 256, 4, false, SMOOTH>);
+    return launch(row_quant_pipe<T, 512, 4, false, SMOOTH>);
+  }
 }
 
 }  // namespace
@@ -958,16 +1368,68 @@ static int head_rmsnorm_wt(void* out, const void* x, const void* weight, int64_t
   // heads of 64, 128 or 256 elements on 16-byte aligned buffers: vector kernel, a head on 8, 16 or 32 lanes
   if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && aligned16(out) && aligned16(x) && aligned16(weight)) {
     const int G = (int)head_dim / 8, hpw = 32 / G;
-    const int64_t vblocks = (items + warps * hpw - 1) / (warps * hpw);
-#define MCOP_HEAD_CASE(GG)                                                                                                          \
-  if (G == GG) {                                                                                                                     \
-    if (wdtype == dtype)                                                                                                             \
-      head_rmsnorm_vec<T, T, GG><<<(unsigned)vblocks, warps * 32, 0, stream>>>((T*)out, (const T*)x, (const T*)weight, tokens,       \
-                                                                               (int)heads, eps, head_offset, head_norm);            \
-    else                                                                                                                             \
-      head_rmsnorm_vec<T, float, GG><<<(unsigned)vblocks, warps * 32, 0, stream>>>((T*)out, (const T*)x, (const float*)weight,       \
-                                                                                   tokens, (int)heads, eps, head_offset, head_norm); \
-    return check_launch("head_rmsnorm");                                                                                             \
+    // many tokens: the pipelined kernel, if the run of heads of a token fits its ring and its rounds.  Four vectors of
+    // 8 per lane when that still leaves four warps of heads per token, else one.
+    if (tokens >= 1024 && head_norm > 0) {
+      const size_t row_bytes = (size_t)head_norm * head_dim * sizeof(T);
+      int V = 4;
+      if (G % 4 != 0 || (head_norm + 32 / (G / 4) - 1) / (32 / (G / 4)) < 4) V = 1;
+      const int lanes = G / V, hpw_v = 32 / lanes;
+      const int witems = (head_norm + hpw_v - 1) / hpw_v;  // warp-sized groups of heads per token
+      int nwarp = 0, waste = 1 << 30;
+      for (int nw = 8; nw >= 4; --nw) {
+        const int rounds = (witems + nw - 1) / nw;
+        if (rounds <= 4 / V && rounds * nw - witems < waste) { waste = rounds * nw - witems; nwarp = nw; }
+      }
+      int st = (int)((64 * 1024) / row_bytes);
+      if (st > 4) st = 4;
+      if (nwarp && st >= 2) {
+        const size_t smem = 128 + (size_t)st * row_bytes;
+        auto launch_pipe = [&](auto kernel, const auto* wt) -> int {
+          const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 200 * 1024);
+          MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "head_rmsnorm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+          int per_sm = 0;
+          if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, nwarp * 32, smem) != cudaSuccess || per_sm < 1) {
+            (void)cudaGetLastError();
+            return 1;
+          }
+          int64_t grid = (int64_t)sm_count() * per_sm;
+          if (grid > tokens) grid = tokens;
+          kernel<<<(unsigned)grid, nwarp * 32, smem, stream>>>((T*)out, (const T*)x, wt, tokens, (int)heads, eps, head_offset, head_norm, st,
+                                                               pipe_error_ptr());
+          return check_launch("head_rmsnorm (pipelined)");
+        };
+        int rc = 1;
+#define MCOP_HEAD_PIPE(GG, VV)                                                                                       \
+  if (lanes == GG && V == VV) rc = wdtype == dtype ? launch_pipe(head_rmsnorm_pipe<T, T, GG, VV>, (const T*)weight)  \
+                                                   : launch_pipe(head_rmsnorm_pipe<T, float, GG, VV>, (const float*)weight);
+        MCOP_HEAD_PIPE(8, 1) MCOP_HEAD_PIPE(16, 1) MCOP_HEAD_PIPE(32, 1) MCOP_HEAD_PIPE(2, 4) MCOP_HEAD_PIPE(4, 4) MCOP_HEAD_PIPE(8, 4)
+#undef MCOP_HEAD_PIPE
+        if (rc != 1) return rc;  // 1 = not applicable: the grid-stride kernel below
+      }
+    }
+    // persistent grid: every warp walks the heads with a stride of (all warps) x (heads per warp and turn); as many CTAs
+    // as are resident at once, so that the grid runs as one even wave
+    const int64_t need = (items + warps * hpw - 1) / (warps * hpw);
+    auto launch = [&](auto kernel, const auto* wt) -> int {
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, warps * 32, 0) != cudaSuccess || per_sm < 1) {
+        (void)cudaGetLastError();
+        per_sm = 4;
+      }
+      int64_t grid = (int64_t)sm_count() * per_sm;
+      if (grid > need) grid = need;
+      const int64_t step = grid * warps * hpw;
+      const int64_t stride_tokens = step / head_norm;
+      const int stride_heads = (int)(step - stride_tokens * head_norm);
+      kernel<<<(unsigned)grid, warps * 32, 0, stream>>>((T*)out, (const T*)x, wt, items, (int)heads, eps, head_offset, head_norm, stride_tokens,
+                                                        stride_heads);
+      return check_launch("head_rmsnorm");
+    };
+#define MCOP_HEAD_CASE(GG)                                                                                   \
+  if (G == GG) {                                                                                              \
+    if (wdtype == dtype) return launch(head_rmsnorm_vec<T, T, GG>, (const T*)weight);                         \
+    return launch(head_rmsnorm_vec<T, float, GG>, (const float*)weight);                                      \
   }
     MCOP_HEAD_CASE(8) MCOP_HEAD_CASE(16) MCOP_HEAD_CASE(32)
 #undef MCOP_HEAD_CASE

@@ -17,6 +17,12 @@ pytestmark = pytest.mark.gpu
 FLT_EPSILON = 1.1920928955078125e-07
 
 
+def _device_error_word():
+    from mcoplib_b200 import cabi
+    torch.cuda.synchronize()
+    return cabi.load().mcop_device_error()
+
+
 @pytest.fixture(scope="module")
 def op():
     from mcoplib_b200 import op as _op
@@ -362,6 +368,52 @@ def test_scale_dynamic_quant_is_exact_on_wide_ranges(op, dtype, T, H):
     assert int(q[7].abs().max()) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,H", [(2048, 4096), (1100, 8192), (1024, 2056), (4000, 7168), (1500, 5120)])
+def test_scale_dynamic_quant_pipelined_shapes_ties_and_special_rows(op, dtype, T, H):
+    """From 1024 rows of 2048 .. 16384 two-byte elements the persistent, pipelined kernel takes over.  It forms y / scale
+    as y * (1 / scale) and falls back to the division near a tie, so the cases are: random rows over 40 binades, rows of
+    small integers whose scale is exactly 2 (every other code is an exact tie k + 0.5: round half to even), a row with an
+    infinity, an all-zero row, a row so small that 1 / scale overflows - all bit for bit."""
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(T, H, generator=g) * torch.exp2(torch.randint(-20, 20, (T, 1), generator=g).float())
+    ties = torch.randint(-254, 255, (64, H), generator=g).float()
+    ties[:, 0] = 254.0                      # scale = 254 / 127 = 2 exactly
+    x[100:164] = ties
+    x[5] = 0
+    x[11, 17] = float("inf")
+    x[13] = torch.randn(H, generator=g) * 1e-38
+    x = x.to(dtype)
+    smooth = 0.25 + 2 * torch.rand(H, generator=g)
+    smooth_one = torch.ones(H)
+    for sm in (smooth, smooth_one):
+        q_ref, s_ref = R.scale_dynamic_quant(x, sm)
+        q, s = op.scale_dynamic_quant(x.to(DEV), sm.to(DEV))
+        assert _device_error_word() == 0
+        C.assert_equal(bits(s.cpu()), bits(s_ref.reshape(-1)), "scales")
+        C.assert_equal(q.cpu(), q_ref, "codes")
+    assert int((q_ref[100:164].abs() == 127).sum()) >= 64  # the tie rows really are scaled by 2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,H", [(2048, 4096), (1100, 8192), (1024, 2056), (4000, 7168)])
+def test_dynamic_scaled_int8_quant_pipelined_shapes(op, dtype, T, H):
+    """The same persistent kernel without the smooth vector (torch.ops._C.dynamic_scaled_int8_quant, symmetric form)."""
+    ns = getattr(torch.ops, op.torch_namespace)
+    g = torch.Generator().manual_seed(22)
+    x = (torch.randn(T, H, generator=g) * torch.exp2(torch.randint(-12, 12, (T, 1), generator=g).float()))
+    x[7] = 0
+    x = x.to(dtype)
+    q_ref, s_ref = R.dynamic_scaled_int8_quant(x)
+    out = Canary((T, H), torch.int8); sc = Canary((T, 1), torch.float32)
+    ns.dynamic_scaled_int8_quant(out.t, x.to(DEV), sc.t, None)
+    torch.cuda.synchronize()
+    out.check(); sc.check()
+    assert _device_error_word() == 0
+    C.assert_equal(out.t.cpu(), q_ref, "codes"); C.assert_equal(bits(sc.t.cpu()), bits(s_ref), "scales")
+    assert int(out.t[7].abs().max()) == 0
+
+
 @pytest.mark.parametrize("dtype,wdtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float32), (torch.float32, torch.float32)])
 @pytest.mark.parametrize("D", [64, 128, 256, 80])
 def test_head_rms_norm_vector_kernel_is_exact(op, dtype, wdtype, D):
@@ -380,3 +432,40 @@ def test_head_rms_norm_vector_kernel_is_exact(op, dtype, wdtype, D):
     if dtype != torch.float32:   # (in fp32 the ulp of the scalar r shows directly: the tolerance above is the check)
         assert int((bits(got) != bits(want)).sum()) <= max(3, got.numel() // 100000), "more than a few last-bit differences"
     assert bool((out[:, :3] == 9).all()) and bool((out[:, 10:] == 9).all())
+
+
+@pytest.mark.parametrize("dtype,wdtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16), (torch.float32, torch.float32)])
+@pytest.mark.parametrize("T,heads,D,off,hn", [(9000, 12, 128, 3, 7), (20000, 8, 64, 0, 8), (5000, 5, 256, 1, 3),
+                                              (3000, 40, 128, 4, 32), (2000, 70, 64, 0, 70), (1500, 20, 256, 2, 17), (1200, 56, 128, 0, 56)])
+def test_head_rms_norm_grid_stride_and_corrected_quotients(op, dtype, wdtype, T, heads, D, off, hn):
+    """Both pipelined forms (one and four vectors per lane: the latter from 25 heads of 128 to normalise), more heads than
+    one turn of the grid holds (the walk's add-and-carry of token and head), and the value ranges the
+    quotient correction has to treat apart: heads spread over 60 binades, a head of zeros, a head whose nonzero values sit
+    below 2^-60 (they take the division itself).  Against the oracle: a handful of last-bit
+    differences at most in 16-bit outputs (the scalar r may differ by an fp32 ulp between CPU and GPU), 1e-6 in fp32."""
+    g = torch.Generator().manual_seed(31)
+    lo, hi = (-30, 30) if dtype != torch.float16 else (-10, 6)
+    x = torch.randn(T, heads, D, generator=g) * torch.exp2(torch.randint(lo, hi, (T, heads, 1), generator=g).float())
+    x[3, off] = 0
+    x[4, off] = 0
+    if dtype != torch.float16:
+        x[4, off, 5] = 2.0 ** -70
+        x[5, off + hn - 1] = torch.randn(D, generator=g) * 2.0 ** -75
+    x = x.to(dtype)
+    w = (1 + 0.1 * torch.randn(heads, D, generator=g)).to(wdtype)
+    ref = R.head_rms_norm(x, w, 1e-5, off, hn)
+    out = torch.full_like(x, 9.0).to(DEV)
+    op.head_rms_norm(out, x.to(DEV), w.to(DEV), 1e-5, off, hn)
+    got, want = out[:, off:off + hn].cpu(), ref[:, off:off + hn]
+    assert bool(torch.isfinite(got.float()).all())
+    if dtype == torch.float32:
+        C.assert_close(got, want, "normalised heads", rel=1e-6, abs_=1e-30)
+    else:
+        diff = bits(got) != bits(want)
+        assert int(diff.sum()) <= max(3, got.numel() // 100000), f"{int(diff.sum())} last-bit differences"
+        C.assert_close(got, want, "normalised heads", rel=1e-2, abs_=1e-30)
+    assert bool((out[:, :off] == 9).all()) and bool((out[:, off + hn:] == 9).all())
+    # in place, as the reference's callers use it
+    xin = x.to(DEV)
+    op.head_rms_norm(xin, xin, w.to(DEV), 1e-5, off, hn)
+    assert torch.equal(bits(xin[:, off:off + hn]), bits(out[:, off:off + hn]))
