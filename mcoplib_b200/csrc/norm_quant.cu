@@ -333,6 +333,18 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
     }
   }
 
+  bool wnan = false;  // PMODE 3: a NaN among this thread's weights or smooth scales (checked once, not per row)
+  if constexpr (PMODE == 3) {
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+      float a[8], b[8];
+      unpack_bf16x8(w2[k], a);
+      unpack_bf16x8(sm2[k], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wnan |= (a[j] != a[j]) | (b[j] != b[j]);
+    }
+  }
+
   int64_t i = 0;
   RingPos pos;
   uint32_t flip = 0;
@@ -410,8 +422,17 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
     uint32_t n2[NVEC][4];
     __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
     float amax3 = 0.f;
+    const bool r_ok3 = r >= 9.31322574615478515625e-10f && r <= 1073741824.0f;  // (PMODE 3) 2^-30 .. 2^30, not a NaN
     if constexpr (PMODE == 3) {
-      // literal convention of the 9-argument operator: divide by rsqrt; after_norm = T(nw), y = nw * smooth stays fp32
+      // literal convention of the 9-argument operator: divide by rsqrt; after_norm = T(nw), y = nw * smooth stays fp32.
+      // The quotients s / r of a row share the divisor: with inv = rn(1 / r), q0 = rn(s * inv) corrected twice by
+      // q + rn(s - q * r) * inv is the correctly rounded quotient (the first step makes q faithful, the second rounds it
+      // correctly: Markstein), five packed operations per pair instead of two division sequences.  Every intermediate must
+      // stay in the normal range: rows whose r is outside 2^-30 .. 2^30 (or a NaN) and vectors with an element below 2^-60
+      // (a zero counts: merely slower) take the division itself.
+      const bool r_ok = r_ok3;
+      const float inv_r = __frcp_rn(r);
+      const float2 inv2 = make_float2(inv_r, inv_r), nr2 = make_float2(-r, -r);
 #pragma unroll
       for (int k = 0; k < NVEC; ++k) {
         const int v = threadIdx.x + k * THREADS;
@@ -419,12 +440,30 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
           float wf[8], sf[8], nw[8];
           unpack_bf16x8(w2[k], wf);
           unpack_bf16x8(sm2[k], sf);
+          float amin = min3_abs(sv[k][0], sv[k][1], 1.0f);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            nw[j] = __fmul_rn(__fdiv_rn(sv[k][j], r), wf[j]);
-            sv[k][j] = __fmul_rn(nw[j], sf[j]);
-            amax3 = fmaxf(amax3, fabsf(sv[k][j]));
+          for (int j = 2; j < 8; j += 2) amin = min3_abs(sv[k][j], sv[k][j + 1], amin);
+          if (r_ok && amin >= 8.67361737988403547206e-19f) {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              const float2 a = make_float2(sv[k][j], sv[k][j + 1]);
+              const float2 q0 = mul2_rn(a, inv2);
+              const float2 q1 = __ffma2_rn(__ffma2_rn(q0, nr2, a), inv2, q0);
+              const float2 q2 = __ffma2_rn(__ffma2_rn(q1, nr2, a), inv2, q1);
+              const float2 n2v = mul2_rn(q2, make_float2(wf[j], wf[j + 1]));
+              const float2 y2 = mul2_rn(n2v, make_float2(sf[j], sf[j + 1]));
+              nw[j] = n2v.x; nw[j + 1] = n2v.y;
+              sv[k][j] = y2.x; sv[k][j + 1] = y2.y;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              nw[j] = __fmul_rn(__fdiv_rn(sv[k][j], r), wf[j]);
+              sv[k][j] = __fmul_rn(nw[j], sf[j]);
+            }
           }
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) amax3 = max3_abs(sv[k][j], sv[k][j + 1], amax3);
           st_u4(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.out_stride + v * 8, pack_bf16x8(nw));
         }
       }
@@ -463,14 +502,25 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) norm_quant_
       const float inv3 = 1.0f / scale3;
       if (threadIdx.x == 0) p.scales[row] = scale3;
       int8_t* q3 = p.q + row * (int64_t)H;
+      // |y * inv3| <= 127 * (1 + 2^-22) for every finite row with a normal scale: no clamp, and the fp32 adder rounds
+      // (eight conversions per vector on the quarter-rate conversion unit otherwise).  Rows with a NaN or an infinity
+      // (r is then outside its range), a zero, tiny or huge scale, or a NaN in this thread's weights keep the conversion.
+      if (r_ok3 && !wnan && scale3 >= 7.888609e-31f && scale3 <= 1.2676506e30f) {
 #pragma unroll
-      for (int k = 0; k < NVEC; ++k) {
-        const int v = threadIdx.x + k * THREADS;
-        if (FULL || v < nv) {
-          int c[8];
+        for (int k = 0; k < NVEC; ++k) {
+          const int v = threadIdx.x + k * THREADS;
+          if (FULL || v < nv) st_cs_u2(q3 + v * 8, quant8_rn_unclamped(sv[k], inv3));
+        }
+      } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(sv[k][j] * inv3, -127, 127);
-          st_cs_u2(q3 + v * 8, pack_i8x8(c));
+        for (int k = 0; k < NVEC; ++k) {
+          const int v = threadIdx.x + k * THREADS;
+          if (FULL || v < nv) {
+            int c[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(sv[k][j] * inv3, -127, 127);
+            st_cs_u2(q3 + v * 8, pack_i8x8(c));
+          }
         }
       }
       continue;

@@ -374,55 +374,74 @@ __global__ void __launch_bounds__(256) kv_store_kernel(KvStoreParams p) {
   }
 }
 
-// Vector form: a thread takes 16 consecutive elements of one K or V head - two 16-byte loads, four 16-byte loads of
-// the fp32 multipliers, one 16-byte int8 store.  TPB tokens per CTA so that small head counts still fill the CTA.
-// Needs head_dim % 16 == 0 and 16-byte aligned rows on both sides.
-template <typename T>
-__global__ void __launch_bounds__(256) kv_store_vec(KvStoreParams p, int64_t tokens, int tokens_per_cta) {
+// Vector form: a thread takes 16 consecutive elements of one K or V head of U consecutive tokens.  The four 16-byte
+// loads of the fp32 multipliers (which depend on head and element only) are made once for the U tokens, the 2 * U
+// 16-byte loads of the activations are all issued before the first conversion - one token per thread left a single
+// pair of loads in flight per thread behind a dependent chain of four index loads (3.7 TB/s) - and the token's
+// sequence is searched once per group: the tokens after the first step forward from the first one's sequence.
+// TPB token groups per CTA so that small head counts still fill the CTA.  Needs head_dim % 16 == 0 and 16-byte aligned
+// rows on both sides.
+template <typename T, int U>
+__global__ void __launch_bounds__(256) kv_store_vec(KvStoreParams p, int64_t tokens, int groups_per_cta) {
   const int per_head = p.head_dim >> 4;
   const int per_token = 2 * p.kv_heads * per_head;   // K items, then V items
-  const int tl = threadIdx.x / per_token;
-  const int64_t t = (int64_t)blockIdx.x * tokens_per_cta + tl;
-  if (tl >= tokens_per_cta || t >= tokens) return;
-  int64_t slot, pos;
-  {
-    // one lane per token would do the search; all of the token's threads run it (same addresses: one broadcast load each)
-    int lo = 0, hi = p.batch - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (p.accum[mid + 1] > t) hi = mid; else lo = mid + 1;
-    }
-    const int64_t i = t - p.accum[lo];
-    if (i < 0 || i >= p.q_lens[lo]) return;
-    pos = (int64_t)p.cache_lens[lo] + i;
-    slot = p.slot_ids[lo];
-    if (slot < 0 || slot >= p.num_slots || pos < 0 || pos >= p.max_len) {
-      if (threadIdx.x % per_token == 0) report_device_error(p.err, MCOP_DEVERR_KV_INDEX);
-      return;
-    }
-  }
+  const int gl = threadIdx.x / per_token;
+  const int64_t t0 = ((int64_t)blockIdx.x * groups_per_cta + gl) * U;
+  if (gl >= groups_per_cta || t0 >= tokens) return;
   const int it = threadIdx.x % per_token;
   const bool is_v = it >= p.kv_heads * per_head;
   const int r = is_v ? it - p.kv_heads * per_head : it;
   const int h = r / per_head, d = (r % per_head) * 16;
-  const T* src = reinterpret_cast<const T*>(p.qkv) + t * p.stride_token + (p.q_heads + (is_v ? p.kv_heads : 0) + h) * p.stride_head + d;
+
+  // sequence of the first token (all threads of the group run the search: same addresses, one broadcast load each)
+  int lo = 0, hi = p.batch - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (p.accum[mid + 1] > t0) hi = mid; else lo = mid + 1;
+  }
+  int8_t* dst[U];
+  uint4 ra[U], rb[U];  // the raw 16-byte vectors: unpacked only when they are used
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int64_t t = t0 + u;
+    dst[u] = nullptr;
+    if (t >= tokens) continue;
+    while (lo < p.batch - 1 && p.accum[lo + 1] <= t) ++lo;  // at most `batch` steps over the whole group
+    const int64_t i = t - p.accum[lo];
+    if (i < 0 || i >= p.q_lens[lo]) continue;                // token outside every sequence
+    const int64_t pos = (int64_t)p.cache_lens[lo] + i;
+    const int64_t slot = p.slot_ids[lo];
+    if (slot < 0 || slot >= p.num_slots || pos < 0 || pos >= p.max_len) {  // never becomes an address
+      if (it == 0) report_device_error(p.err, MCOP_DEVERR_KV_INDEX);
+      continue;
+    }
+    dst[u] = is_v ? p.v_cache + slot * p.vs_slot + h * p.vs_head + pos * p.vs_pos + d
+                  : p.k_cache + slot * p.ks_slot + h * p.ks_head + pos * p.ks_pos + d;
+    const T* src = reinterpret_cast<const T*>(p.qkv) + t * p.stride_token + (p.q_heads + (is_v ? p.kv_heads : 0) + h) * p.stride_head + d;
+    ra[u] = ld_nc_u4(src);
+    rb[u] = ld_nc_u4(src + 8);
+  }
   const float* sc = (is_v ? p.v_scale : p.k_scale) + h * p.head_dim + d;
-  float a[8], b[8];
-  Vec8<T>::load_nc(src, a);
-  Vec8<T>::load_nc(src + 8, b);
   const float4 s0 = __ldg(reinterpret_cast<const float4*>(sc)), s1 = __ldg(reinterpret_cast<const float4*>(sc) + 1);
   const float4 s2 = __ldg(reinterpret_cast<const float4*>(sc) + 2), s3 = __ldg(reinterpret_cast<const float4*>(sc) + 3);
   const float m[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
-  int qa[8], qb[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    qa[j] = q_rn_clamp(__fmul_rn(a[j], m[j]), -127, 127);
-    qb[j] = q_rn_clamp(__fmul_rn(b[j], m[8 + j]), -127, 127);
+  for (int u = 0; u < U; ++u) {
+    if (!dst[u]) continue;
+    float a[8], b[8];
+    if (ElemTraits<T>::code == MCOP_BF16) { unpack_bf16x8(ra[u], a); unpack_bf16x8(rb[u], b); }
+    else { unpack_f16x8(ra[u], a); unpack_f16x8(rb[u], b); }
+    // (clamping and rounding with the fp32 adder instead of the float-to-int conversion measured slower here: 99 against
+    // 90 us at 65,536 tokens of 8 + 8 heads - the NaN test it needs costs more than the conversion unit saves)
+    int qa[8], qb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      qa[j] = q_rn_clamp(__fmul_rn(a[j], m[j]), -127, 127);
+      qb[j] = q_rn_clamp(__fmul_rn(b[j], m[8 + j]), -127, 127);
+    }
+    const uint2 pa = pack_i8x8(qa), pb = pack_i8x8(qb);
+    st_cs_u4(dst[u], make_uint4(pa.x, pa.y, pb.x, pb.y));
   }
-  const uint2 pa = pack_i8x8(qa), pb = pack_i8x8(qb);
-  int8_t* dst = is_v ? p.v_cache + slot * p.vs_slot + h * p.vs_head + pos * p.vs_pos + d
-                     : p.k_cache + slot * p.ks_slot + h * p.ks_head + pos * p.ks_pos + d;
-  st_cs_u4(dst, make_uint4(pa.x, pa.y, pb.x, pb.y));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -625,10 +644,11 @@ extern "C" int mcop_kv_store_i8(const void* packed_qkv, int64_t qkv_stride_token
                       (qkv_stride_head * 2) % 16 == 0 && aligned16(k_cache) && aligned16(v_cache) && aligned16(k_scale) && aligned16(v_scale) &&
                       m16(k_stride_slot) && m16(k_stride_head) && m16(k_stride_pos) && m16(v_stride_slot) && m16(v_stride_head) && m16(v_stride_pos);
   if (vec_ok) {
-    const int tpc = 256 / per_token;
-    const unsigned grid = (unsigned)((tokens + tpc - 1) / tpc);
-    if (dtype == MCOP_BF16) kv_store_vec<__nv_bfloat16><<<grid, tpc * per_token, 0, s>>>(p, tokens, tpc);
-    else kv_store_vec<__half><<<grid, tpc * per_token, 0, s>>>(p, tokens, tpc);
+    constexpr int U = 4;  // consecutive tokens per thread
+    const int gpc = 256 / per_token;  // token groups per CTA
+    const unsigned grid = (unsigned)((tokens + (int64_t)gpc * U - 1) / ((int64_t)gpc * U));
+    if (dtype == MCOP_BF16) kv_store_vec<__nv_bfloat16, U><<<grid, gpc * per_token, 0, s>>>(p, tokens, gpc);
+    else kv_store_vec<__half, U><<<grid, gpc * per_token, 0, s>>>(p, tokens, gpc);
   } else {
     if (dtype == MCOP_BF16) kv_store_kernel<__nv_bfloat16><<<(unsigned)tokens, 256, 0, s>>>(p);
     else kv_store_kernel<__half><<<(unsigned)tokens, 256, 0, s>>>(p);

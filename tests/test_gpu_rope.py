@@ -237,6 +237,33 @@ def test_store_kv_cache_against_golden(op, golden):
     C.assert_equal(kc, g["k_cache"]); C.assert_equal(vc, g["v_cache"])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 8, 128), (2, 1, 64), (3, 5, 80)])
+def test_store_kv_cache_ragged_sequences(op, dtype, Hq, Hkv, D):
+    """Sequences of 1 .. 37 tokens whose boundaries fall inside the groups of four consecutive tokens a thread of the
+    vector kernel takes, tokens between two sequences that belong to none (q_len shorter than the gap to the next
+    offset), non-zero cache lengths, a shuffled slot order; head_dim 80 takes the element kernel.  Bit-exact."""
+    g = torch.Generator().manual_seed(5)
+    q_lens = torch.tensor([1, 5, 37, 2, 16, 7, 3, 30], dtype=torch.int32)
+    gaps = torch.tensor([0, 2, 0, 1, 0, 0, 3, 0], dtype=torch.int32)          # unowned tokens after each sequence
+    accum = torch.zeros(len(q_lens) + 1, dtype=torch.int32)
+    accum[1:] = torch.cumsum(q_lens + gaps, 0)
+    T = int(accum[-1])
+    cache_lens = torch.tensor([0, 3, 1, 0, 9, 2, 0, 4], dtype=torch.int32)
+    slots = torch.randperm(len(q_lens), generator=g).to(torch.int32)
+    max_len = 48
+    qkv = (torch.randn(T, Hq + 2 * Hkv, D, generator=g) * 3).to(dtype)
+    ks = 20 + 10 * torch.rand(Hkv, D, generator=g); vs = 20 + 10 * torch.rand(Hkv, D, generator=g)
+    kc0 = torch.full((len(q_lens), Hkv, max_len, D), 55, dtype=torch.int8); vc0 = torch.full_like(kc0, -55)
+    kc_ref, vc_ref = R.store_kv_cache(qkv, q_lens, accum[:-1], cache_lens, slots, kc0, vc0, ks, vs, Hq, Hkv)
+    kc, vc = kc0.to(DEV), vc0.to(DEV)
+    op.store_kv_cache_cuda_interface(qkv.to(DEV), q_lens.to(DEV), accum.to(DEV), cache_lens.to(DEV), slots.to(DEV), kc, vc,
+                                     ks.to(DEV), vs.to(DEV), len(q_lens), Hq, Hkv)
+    torch.cuda.synchronize()
+    assert _device_error() == 0
+    C.assert_equal(kc.cpu(), kc_ref, "k cache"); C.assert_equal(vc.cpu(), vc_ref, "v cache")
+
+
 def test_reshape_and_cache_flash(op):
     ns = getattr(torch.ops, op.torch_namespace + "_cache_ops")
     T, Hkv, D, bs, nb = 200, 4, 128, 16, 32
