@@ -738,7 +738,8 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   // work items: ~40 rows each amortise the per-item set-up; with few rows in total they shrink (down to 16) so that
   // every CTA still gets half a dozen items from the counter and the tail of the last wave stays short
   const double total_rows = (double)p.tokens * p.topk;
-  // (measured at 8192 tokens x top-8 of 256: items of 16 rows +1 %, of 8 rows -4 % against this rule)
+  // (measured at 8192 tokens x top-8 of 256: items of 16 rows +1 %, of 8 rows -4 % against this rule; at 32,768 tokens x
+  // top-2 of 8 items of 12 / 16 / 20 / 24 / 32 / 40 / 56 rows: 213 / 209 / 202 / 199 / 197 / 200 / 220 us - flat around the rule's 25)
   double target = total_rows / ((double)sm_count() * CTAS * 6.0);
   target = target < 16.0 ? 16.0 : (target > 40.0 ? 40.0 : target);
   const double rows_per_tile_expert = (double)kTileTokens * p.topk / p.E;
