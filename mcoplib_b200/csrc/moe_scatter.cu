@@ -537,6 +537,8 @@ __global__ void __launch_bounds__(THREADS, CTAS) scatter_quant_pipe(ScatterQuant
   while (alive) {
     // work items (super-tile, expert, part) from an atomic counter, in token-major order: the CTAs move through the
     // tokens together, so the k readers of a token row run close together in time
+    // (asking the counter for the next item while this one runs, so that the atomic's round trip hides behind the rows,
+    // measured the same: 1357 / 201 us against 1349-1354 / 199-203 us at 262,144 / 32,768 tokens)
     if (threadIdx.x == 0) s_item = atomicAdd(p.work_counter, 1);
     __syncthreads();
     const int64_t item = s_item;
