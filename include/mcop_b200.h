@@ -368,7 +368,7 @@ int mcop_silu_mul_quant_i8_masked_pack(const void* x, int dtype, const void* gro
  * (e.g. 65536 tokens x 8 rows each); larger problems are rejected with MCOP_ERR_WORKSPACE and nothing runs.
  * The first call on a device resolves the device address of the array (cudaGetSymbolAddress with that device
  * current); make that first call outside any stream capture.  All calls on a device share the one array and it
- * keeps the previous call's contents: every call re-zeroes the counters it needs, but two calls whose kernels
+ * keeps the previous call's contents: every call resets the chain heads it needs, but two calls whose kernels
  * overlap on the GPU (different streams, no ordering between them) race on it - serialise them. */
 int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, void* out, int64_t tokens, int64_t rows,
                             int64_t hidden_size, mcop_stream_t stream);

@@ -19,7 +19,7 @@ namespace {
 struct GatherParams {
   const __nv_bfloat16* y; const int32_t* row2tok; __nv_bfloat16* out;
   const int32_t* tok2row; int topk;                      // direct inverse (nullable)
-  const int32_t* cnt; const int32_t* list; int cap;      // inverse built by the pre-pass
+  const int32_t* head; const int32_t* next;              // inverse built by the pre-pass: per-token chains of row ids
   const int32_t* topk_ids; const float* topk_weights; const int32_t* starts; int experts;  // weighted form
   int64_t rows; int64_t tokens; int hidden_size; int weighted; int accumulate;
 };
@@ -28,15 +28,27 @@ constexpr int kMaxList = 64;    // rows of one token the row-per-CTA kernels han
 constexpr int kChunkTokens = 128;  // tokens whose row lists a CTA of the pipelined kernel prepares at a time
 constexpr int kPipeMaxRows = 16;  // rows per token the pipelined kernel keeps in shared memory
 
-// Inversion pre-pass: per token a counter and up to `cap` row ids (unordered; the gather sorts them).
-__global__ void gather_invert_kernel(const int32_t* __restrict__ row2tok, int32_t* cnt, int32_t* list, int64_t rows,
-                                     int64_t tokens, int cap) {
+// Inversion pre-pass: the rows of a token form a chain, head[t] -> r1 -> next[r1] -> ... -> -1 (unordered; the gather sorts
+// them).  Exact for every distribution of the rows over the tokens: a token of a map with dropped rows may own far more
+// rows than rows / tokens, and a table with that average as its width sent such tokens through the scan of the whole map.
+// head[] is set to -1 (memset 0xff) before the launch.
+__global__ void gather_invert_kernel(const int32_t* __restrict__ row2tok, int32_t* head, int32_t* next, int64_t rows, int64_t tokens) {
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const int t = row2tok[r];
   if (t < 0 || t >= tokens) return;
-  const int pos = atomicAdd(&cnt[t], 1);
-  if (pos < cap) list[(int64_t)t * cap + pos] = (int32_t)r;
+  next[r] = atomicExch(&head[t], (int32_t)r);
+}
+
+// Walks the chain of token t into out[0 .. limit): returns the number of rows, or -1 when there are more than `limit`
+// (or the chain is broken: an id outside [0, rows) ends it the same way).
+__device__ __forceinline__ int gather_walk_chain(const GatherParams& p, int64_t t, int* out, int limit) {
+  int n = 0;
+  for (int r = p.head[t]; r >= 0; r = p.next[r]) {
+    if (n >= limit || r >= p.rows) return -1;
+    out[n++] = r;
+  }
+  return n;
 }
 
 // Weight of row r of token t: the expert owning r is the first e with starts[e+1] > r; the weight is that of
@@ -85,9 +97,11 @@ __device__ int gather_collect(const GatherParams& p, int64_t t, int32_t* s_rows,
     n = p.topk;
     if (threadIdx.x < n) s_tmp[threadIdx.x] = p.tok2row[t * p.topk + threadIdx.x];
   } else {
-    n = p.cnt[t];
-    if (n > p.cap || n > kMaxList) return -1;
-    if (threadIdx.x < n) s_tmp[threadIdx.x] = p.list[t * (int64_t)p.cap + threadIdx.x];
+    if (threadIdx.x == 0) s_n = gather_walk_chain(p, t, s_tmp, kMaxList);
+    __syncthreads();
+    n = s_n;
+    __syncthreads();  // s_n is reset below
+    if (n < 0) return -1;
   }
   if (threadIdx.x == 0) s_n = 0;
   __syncthreads();
@@ -211,10 +225,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
           if (r >= 0 && r < p.rows) { rows[n] = r; slot[n] = j; ++n; }
         }
       } else {
-        const int c0 = p.cnt[t];
-        if (c0 > p.cap) overflow = true;
-        else
-          for (int j = 0; j < c0; ++j) rows[n++] = p.list[t * (int64_t)p.cap + j];
+        n = gather_walk_chain(p, t, rows, kPipeMaxRows);
+        if (n < 0) { overflow = true; n = 0; }
       }
       if (!overflow) {
         for (int a = 1; a < n; ++a) {  // insertion sort, n <= 16
@@ -346,6 +358,8 @@ __global__ void __launch_bounds__(256) gather_any(GatherParams p) {
   }
 }
 
+// Average rows per token, rounded up and capped: sizes the workspace (tokens * gather_cap >= rows words hold next[]) and
+// tells which kernel a map without `tok2row` most likely suits.
 int gather_cap(int64_t tokens, int64_t rows) {
   if (tokens <= 0) return 1;
   int64_t c = (rows + tokens - 1) / tokens;
@@ -384,15 +398,15 @@ int launch_gather(GatherParams p, int64_t tokens, void* workspace, size_t worksp
     MCOP_REQUIRE(workspace && workspace_bytes >= need, MCOP_ERR_WORKSPACE, "moe_gather: workspace of %zu bytes needed, %zu given",
                  need, workspace_bytes);
     MCOP_REQUIRE(aligned16(workspace), MCOP_ERR_ARGUMENT, "moe_gather: workspace must be 16-byte aligned");
-    int32_t* cnt = reinterpret_cast<int32_t*>(workspace);
-    p.cap = gather_cap(tokens, p.rows);
-    p.cnt = cnt;
-    p.list = cnt + ((tokens + 63) / 64) * 64;
-    cudaError_t e = cudaMemsetAsync(cnt, 0, (size_t)tokens * sizeof(int32_t), stream);
+    int32_t* head = reinterpret_cast<int32_t*>(workspace);
+    int32_t* next = head + ((tokens + 63) / 64) * 64;
+    p.head = head;
+    p.next = next;
+    cudaError_t e = cudaMemsetAsync(head, 0xff, (size_t)tokens * sizeof(int32_t), stream);  // every chain empty (-1)
     MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_gather: memset: %s", cudaGetErrorString(e));
     if (p.rows > 0) {
       const int64_t blocks = (p.rows + 255) / 256;
-      gather_invert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.row2tok, cnt, const_cast<int32_t*>(p.list), p.rows, tokens, p.cap);
+      gather_invert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.row2tok, head, next, p.rows, tokens);
       const int rc = check_launch("moe_gather (invert)");
       if (rc) return rc;
     }
@@ -400,7 +414,8 @@ int launch_gather(GatherParams p, int64_t tokens, void* workspace, size_t worksp
   const int nv = p.hidden_size >> 3;
   const bool vec_ok = p.hidden_size % 8 == 0 && aligned16(p.y) && aligned16(p.out) && nv <= 4096;
   const unsigned grid = (unsigned)tokens;
-  const int per_token = p.tok2row ? p.topk : p.cap;
+  const int per_token = p.tok2row ? p.topk : gather_cap(tokens, p.rows);  // without tok2row: the average (a token with more
+                                                                         // rows than a kernel's table holds takes the scan)
   // the pipelined kernel pays off once there are a few waves of tokens; rows wider than 2048 vectors or more
   // rows per token than its table holds take the row-per-CTA kernel
   if (vec_ok && nv > 256 && nv <= 2048 && per_token <= kPipeMaxRows && tokens >= 1024) {
@@ -456,7 +471,7 @@ extern "C" int mcop_moe_gather_weighted(const void* y, const int32_t* row2tok, c
 // Allocation-free variant: the inversion table lives in a fixed array inside the library.
 // ---------------------------------------------------------------------------------------------
 namespace {
-// Scratch of mcop_moe_gather_noalloc: per-token counters followed by the per-token row lists.
+// Scratch of mcop_moe_gather_noalloc: the per-token chain heads followed by the per-row links.
 // Every device that loads the library holds these 4 MiB until the process exits.
 static __device__ __align__(256) int32_t g_gather_noalloc_scratch[MCOP_GATHER_NOALLOC_SCRATCH_BYTES / sizeof(int32_t)];
 
@@ -501,7 +516,7 @@ extern "C" int mcop_moe_gather_noalloc(const void* y, const int32_t* row2tok, vo
   GatherParams p{};
   p.y = reinterpret_cast<const __nv_bfloat16*>(y); p.row2tok = row2tok; p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.tok2row = nullptr; p.topk = 0; p.rows = rows; p.hidden_size = (int)hidden_size; p.weighted = 0; p.accumulate = 1;
-  // launch_gather zeroes the counters it reads (cudaMemsetAsync on the stream) before the inversion pass, so
+  // launch_gather resets the chain heads it reads (cudaMemsetAsync on the stream) before the inversion pass, so
   // whatever the previous call left in the array is harmless.
   return launch_gather(p, tokens, scratch, MCOP_GATHER_NOALLOC_SCRATCH_BYTES, (cudaStream_t)stream);
 }

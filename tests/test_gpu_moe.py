@@ -318,7 +318,7 @@ def test_gather_fixed_order_against_legal_orders_of_the_reference_at_top8_hidden
 
 def test_gather_arbitrary_row_map(op):
     """The 3-argument operator accepts any row -> token map: unequal counts, a token owning more rows than the
-    inverse table holds (the slow scan), tokens with no rows, and entries outside [0, tokens) that are skipped."""
+    kernels' row tables hold (the slow scan), tokens with no rows, and entries outside [0, tokens) that are skipped."""
     T, H, Rn = 50, 1024, 400
     g = torch.Generator().manual_seed(8)
     r2t = torch.randint(0, T, (Rn,), generator=g).to(torch.int32)
@@ -332,6 +332,28 @@ def test_gather_arbitrary_row_map(op):
     op.moe_gather(y.to(DEV), r2t.to(DEV), o)
     C.assert_equal(bits(o), bits(ref))
     assert torch.equal(bits(o[11]), bits(out0[11]))
+
+
+@pytest.mark.parametrize("T,H", [(4096, 4096), (300, 1024)])
+def test_gather_skewed_map_without_tok2row(op, T, H):
+    """The expert-parallel case of the 3-argument operator: three quarters of the routing rows were dropped, so the map holds
+    about two rows per token on average while the tokens that kept theirs own eight (and a few own 12, 16 and 17: at, and
+    one past, what the pipelined kernel's table holds; 40 and 70: around what the row-per-CTA kernels hold).  The inverse
+    is a chain per token, exact whatever the spread; bit-exact against the oracle at both sizes (the pipelined kernel from
+    1024 tokens, one CTA per token below)."""
+    g = torch.Generator().manual_seed(9)
+    owners = torch.randperm(T, generator=g)[: T // 4]
+    r2t = owners.repeat_interleave(8)
+    extra = torch.cat([owners[:1].repeat(4), owners[1:2].repeat(8), owners[2:3].repeat(9), owners[3:4].repeat(32), owners[4:5].repeat(62)])
+    r2t = torch.cat([r2t, extra])
+    r2t = r2t[torch.randperm(r2t.numel(), generator=g)].to(torch.int32)
+    Rn = r2t.numel()
+    y = W.per_token("randn", 53, 0, Rn, H, torch.bfloat16)
+    out0 = W.per_token("randn", 54, 0, T, H, torch.bfloat16)
+    ref = R.moe_gather(y, r2t, out0)
+    o = out0.clone().to(DEV)
+    op.moe_gather(y.to(DEV), r2t.to(DEV), o)
+    C.assert_equal(bits(o), bits(ref))
 
 
 def test_gather_linearity_at_full_size(op):
