@@ -980,11 +980,18 @@ int launch_row_quant_pipe(int8_t* out, float* scales, const T* x, const float* s
 // so when both give the same integer, rne(d) is that integer.  When they differ (a tie k + 0.5 falls inside the interval,
 // whose width is at most 127 * 2^-20: about one element in 16,000 of random data, more in rows of few-bit values, where
 // x = max|x| / 2 gives 63.5), when y is a NaN (the comparison is unordered), and for rows whose scale is zero, infinite or
-// outside [2^-100, 2^100] (`fast` false: 1 / scale overflows or loses bits), the code comes from the division itself, for
-// exactly those elements.  Two packed fused multiply-adds and a compare per pair instead of two division sequences.
+// outside [2^-100, 2^100] (`fast` false: 1 / scale overflows or loses bits), the codes come from the quotient itself.
+// Two packed fused multiply-adds and a compare per pair instead of two division sequences.
+//
+// The quotient itself, for a vector with an undecided element: in a `fast` row all eight are formed as q0 = rn(y * inv)
+// corrected twice by q + rn(y - q * scale) * inv - the first step makes q a faithful rounding of y / scale (q0 is within
+// two ulps, the fused residual is exact), the second the correctly rounded one (Markstein's theorem; inv is the correctly
+// rounded reciprocal and every intermediate that matters is normal: a code other than 0 means |y| >= scale / 2 >= 2^-101) -
+// five packed operations per pair, no branch per element; a NaN becomes 0 as the float-to-int conversion makes it.  Rows
+// outside the `fast` range take the IEEE division per element.
 struct ScaleDivisor {
   float scale;
-  float2 lo2, hi2;
+  float2 lo2, hi2, inv2, nscale2;
   bool fast;
   __device__ __forceinline__ explicit ScaleDivisor(float s) : scale(s) {
     fast = s >= 7.888609e-31f && s <= 1.2676506e30f;  // 2^-100 .. 2^100
@@ -992,12 +999,13 @@ struct ScaleDivisor {
     const float lo = __fmul_rn(inv, 0.99999952316284179688f), hi = __fmul_rn(inv, 1.00000047683715820312f);  // 1 -+ 2^-21
     lo2 = make_float2(lo, lo);
     hi2 = make_float2(hi, hi);
+    inv2 = make_float2(inv, inv);
+    nscale2 = make_float2(-s, -s);
   }
 };
 __device__ __forceinline__ uint2 quant8_by_scale(const float (&y)[8], const ScaleDivisor& dv) {
   const float2 magic2 = make_float2(12582912.0f, 12582912.0f);
   uint32_t c[8];
-  float other[8];
   bool exact = !dv.fast;
 #pragma unroll
   for (int j = 0; j < 8; j += 2) {
@@ -1006,13 +1014,22 @@ __device__ __forceinline__ uint2 quant8_by_scale(const float (&y)[8], const Scal
     exact |= (a.x != b.x) | (a.y != b.y);  // a NaN compares unequal too
     c[j] = __float_as_uint(a.x);
     c[j + 1] = __float_as_uint(a.y);
-    other[j] = b.x;
-    other[j + 1] = b.y;
   }
   if (exact) {
+    if (dv.fast) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (!dv.fast || __uint_as_float(c[j]) != other[j]) c[j] = (uint32_t)q_rn_clamp(__fdiv_rn(y[j], dv.scale), -128, 127);
+      for (int j = 0; j < 8; j += 2) {
+        const float2 yy = make_float2(y[j], y[j + 1]);
+        const float2 q0 = mul2_rn(yy, dv.inv2);
+        const float2 q1 = __ffma2_rn(__ffma2_rn(q0, dv.nscale2, yy), dv.inv2, q0);
+        const float2 q2 = __ffma2_rn(__ffma2_rn(q1, dv.nscale2, yy), dv.inv2, q1);
+        c[j] = q2.x == q2.x ? rn_low_byte(q2.x) : 0u;          // |q| <= 127 * (1 + 2^-23): in range without a clamp
+        c[j + 1] = q2.y == q2.y ? rn_low_byte(q2.y) : 0u;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = (uint32_t)q_rn_clamp(__fdiv_rn(y[j], dv.scale), -128, 127);
+    }
   }
   return make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7]));
 }

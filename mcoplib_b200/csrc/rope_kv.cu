@@ -432,15 +432,21 @@ __global__ void __launch_bounds__(256) kv_store_vec(KvStoreParams p, int64_t tok
     if (ElemTraits<T>::code == MCOP_BF16) { unpack_bf16x8(ra[u], a); unpack_bf16x8(rb[u], b); }
     else { unpack_f16x8(ra[u], a); unpack_f16x8(rb[u], b); }
     // (clamping and rounding with the fp32 adder instead of the float-to-int conversion measured slower here: 99 against
-    // 90 us at 65,536 tokens of 8 + 8 heads - the NaN test it needs costs more than the conversion unit saves)
-    int qa[8], qb[8];
+    // 90 us at 65,536 tokens of 8 + 8 heads - the NaN test it needs costs more than the conversion unit saves; packed
+    // products and byte permutes instead of shifts and ors: 90 -> 84 us)
+    uint32_t c[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      qa[j] = q_rn_clamp(__fmul_rn(a[j], m[j]), -127, 127);
-      qb[j] = q_rn_clamp(__fmul_rn(b[j], m[8 + j]), -127, 127);
+    for (int j = 0; j < 8; j += 2) {
+      const float2 pa = mul2_rn(make_float2(a[j], a[j + 1]), make_float2(m[j], m[j + 1]));
+      const float2 pb = mul2_rn(make_float2(b[j], b[j + 1]), make_float2(m[8 + j], m[9 + j]));
+      c[j] = (uint32_t)q_rn_clamp(pa.x, -127, 127);
+      c[j + 1] = (uint32_t)q_rn_clamp(pa.y, -127, 127);
+      c[8 + j] = (uint32_t)q_rn_clamp(pb.x, -127, 127);
+      c[9 + j] = (uint32_t)q_rn_clamp(pb.y, -127, 127);
     }
-    const uint2 pa = pack_i8x8(qa), pb = pack_i8x8(qb);
-    st_cs_u4(dst[u], make_uint4(pa.x, pa.y, pb.x, pb.y));
+    // the low bytes of the clamped integers are the codes: three byte permutes per four codes
+    st_cs_u4(dst[u], make_uint4(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7]),
+                                pack4_low_bytes(c[8], c[9], c[10], c[11]), pack4_low_bytes(c[12], c[13], c[14], c[15])));
   }
 }
 
@@ -644,7 +650,7 @@ extern "C" int mcop_kv_store_i8(const void* packed_qkv, int64_t qkv_stride_token
                       (qkv_stride_head * 2) % 16 == 0 && aligned16(k_cache) && aligned16(v_cache) && aligned16(k_scale) && aligned16(v_scale) &&
                       m16(k_stride_slot) && m16(k_stride_head) && m16(k_stride_pos) && m16(v_stride_slot) && m16(v_stride_head) && m16(v_stride_pos);
   if (vec_ok) {
-    constexpr int U = 4;  // consecutive tokens per thread
+    constexpr int U = 4;  // consecutive tokens per thread (measured at 65,536 tokens of 8 + 8 heads: 2 / 4 / 8 -> 93 / 84 / 99 us)
     const int gpc = 256 / per_token;  // token groups per CTA
     const unsigned grid = (unsigned)((tokens + (int64_t)gpc * U - 1) / ((int64_t)gpc * U));
     if (dtype == MCOP_BF16) kv_store_vec<__nv_bfloat16, U><<<grid, gpc * per_token, 0, s>>>(p, tokens, gpc);
