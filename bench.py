@@ -315,12 +315,13 @@ class Next6:
 
 class Part1:
     """The other entry points of parts 1 and 2, each timed on its own on bf16 rows of 7168: fused_add_rms_norm (in place), rms_norm
-    with a residual, the 9-argument norm + smooth quant, scale_dynamic_quant, head_rms_norm (56 heads of 128) and the unpaged
-    int8 store of packed K/V (64 Q + 8 + 8 KV heads of 128, one sequence per 4096 tokens)."""
+    with a residual, the 9-argument norm + smooth quant, scale_dynamic_quant, head_rms_norm (56 heads of 128), the unpaged
+    int8 store of packed K/V (64 Q + 8 + 8 KV heads of 128, one sequence per 4096 tokens) and sglang's RoPE with the save of the
+    rotated K and of V into token-indexed buffers (same heads, positions below 8192, a random permutation of rows)."""
     name = ("other entry points: fused_add_rms_norm, rms_norm (+residual), 9-argument rms_norm_dynamic_per_token_quant, "
-            "scale_dynamic_quant, head_rms_norm, store_kv_cache_cuda_interface")
-    kernels = ["fused_add_rms_norm", "rms_norm", "norm_smooth_quant", "scale_dynamic_quant", "head_rms_norm", "store_kv"]
-    launches_per_step = 6
+            "scale_dynamic_quant, head_rms_norm, store_kv_cache_cuda_interface, apply_rope_pos_ids_cos_sin_cache with save")
+    kernels = ["fused_add_rms_norm", "rms_norm", "norm_smooth_quant", "scale_dynamic_quant", "head_rms_norm", "store_kv", "rope_kv_save"]
+    launches_per_step = 7
 
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W
@@ -351,6 +352,15 @@ class Part1:
         self.v_cache = torch.empty_like(self.k_cache)
         self.kv_scale = torch.full((self.Hkv, self.D), 30.0, dtype=torch.float32, **o)
         self.nseq = nseq
+        # sglang's rope + save: an fp32 cos || sin cache of 8192 positions, buffers of one row per token
+        g = torch.Generator(device=device).manual_seed(71 + t0)
+        self.rope_pos = torch.randint(0, 8192, (tokens,), generator=g, device=device, dtype=torch.int64)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, self.D, 2, dtype=torch.float32, device=device) / self.D))
+        f = torch.outer(torch.arange(8192, dtype=torch.float32, device=device), inv)
+        self.rope_cache = torch.cat([f.cos(), f.sin()], dim=-1).contiguous()
+        self.kv_loc = torch.randperm(tokens, generator=g, device=device).to(torch.int64)
+        self.k_buffer = torch.empty(tokens, self.Hkv, self.D, dtype=torch.bfloat16, **o)
+        self.v_buffer = torch.empty_like(self.k_buffer)
 
     def bytes_per_kernel(self):
         n = self.T * self.H
@@ -360,11 +370,16 @@ class Part1:
                 "norm_smooth_quant": 9 * n + 4 * self.H + 4 * self.T,  # + after_norm, codes, scale
                 "scale_dynamic_quant": 3 * n + 4 * self.H + 4 * self.T,  # x read, codes + scale written
                 "head_rms_norm": 4 * n + 2 * self.H,               # every head read and written
-                "store_kv": 2 * kv * 2 + 2 * kv + 8 * self.Hkv * self.D}   # K, V heads read, two int8 caches written
+                "store_kv": 2 * kv * 2 + 2 * kv + 8 * self.Hkv * self.D,   # K, V heads read, two int8 caches written
+                # q, k, v read; q, k written in place; rotated k and v written to the buffers; cos || sin row, position, row id
+                "rope_kv_save": self.T * ((self.Hq + 2 * self.Hkv) * self.D * 2 + (self.Hq + self.Hkv) * self.D * 2
+                                          + 2 * self.Hkv * self.D * 2 + 4 * self.D + 16)}
 
     def stages(self, ops):
         x3 = self.x.view(self.T, 56, 128)
         out3 = self.out.view(self.T, 56, 128)
+        q, k = self.qkv[:, :self.Hq], self.qkv[:, self.Hq:self.Hq + self.Hkv]   # rotated in place: norms are kept, values stay put
+        v = self.qkv[:, self.Hq + self.Hkv:]
         return [
             lambda: ops.fused_add_rms_norm(self.x_io, self.res_io, self.w, 1e-6),
             lambda: ops.rms_norm(self.out, self.x, self.w, 1e-6, self.after_res, self.res, False),
@@ -374,6 +389,8 @@ class Part1:
             lambda: ops.head_rms_norm(out3, x3, self.head_w, 1e-6, 0, 56),
             lambda: ops.store_kv_cache_cuda_interface(self.qkv, self.q_lens, self.accum, self.cache_lens, self.slot_ids, self.k_cache,
                                                       self.v_cache, self.kv_scale, self.kv_scale, self.nseq, self.Hq, self.Hkv),
+            lambda: ops.apply_rope_pos_ids_cos_sin_cache(q, k, q, k, self.rope_cache, self.rope_pos, False, False, v=v,
+                                                         k_buffer=self.k_buffer, v_buffer=self.v_buffer, kv_cache_loc=self.kv_loc),
         ]
 
 

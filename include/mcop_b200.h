@@ -194,6 +194,18 @@ int mcop_reshape_and_cache(const void* key, const void* value, int64_t key_strid
                            int kv_heads, int head_size, int block_size, int x, int64_t num_blocks, int elem_bytes,
                            mcop_stream_t stream);
 
+/* sglang's apply_rope_pos_ids_cos_sin_cache with save_kv_cache (op/sglang/csrc/elementwise/rope.cu:28-171, the kernel it
+ * calls fuses rotation and save): NeoX RoPE over the whole head from an fp32 cos||sin cache [max_position, head_size] at
+ * explicit positions, query and key rotated in place (fp32 products and sum, one rounding), then
+ * k_buffer[kv_loc[t]] = rotated key row, v_buffer[kv_loc[t]] = value row, in the element type; the buffers hold
+ * buffer_rows rows of kv_heads * head_size elements, buffer_row_stride elements apart.  One launch from 2048 tokens on
+ * 16-byte aligned rows; otherwise the rotation followed by the copy.  Positions and row ids are checked like those of
+ * mcop_rope_kv_store_i8_paged (MCOP_DEVERR_POSITION / MCOP_DEVERR_SLOT; a negative row id rotates and does not store). */
+int mcop_rope_kv_copy(const int64_t* positions, void* query, void* key, const void* value, const float* cos_sin_cache,
+                      int64_t max_position, void* k_buffer, void* v_buffer, const int64_t* kv_loc, int64_t buffer_rows,
+                      int64_t buffer_row_stride, int64_t tokens, int num_heads, int num_kv_heads, int head_size,
+                      int64_t query_stride, int64_t key_stride, int64_t value_stride, int dtype, mcop_stream_t stream);
+
 /* Fused RoPE + int8 paged KV store.  No single reference operator: the composition of
  * rotary_embedding (op/vllm/pos_encoding_kernels.cu:135-217) -> int8 quantisation of the ROUNDED rotated K
  * and of V as in op/store_kv.cu:188-216 with per-head dequantisation scales (code = clamp(rne(v * (1/scale[h])), +-127))

@@ -27,6 +27,7 @@ SIGNATURES = {
     "mcop_dynamic_scaled_int8_quant": (I32, [P, P, P, I64, I64, I32, P]),
     "mcop_selftest_wait_timeout": (I32, [I32, P]),
     "mcop_rope_inplace": (I32, [P, P, P, P, I32, I64, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
+    "mcop_rope_kv_copy": (I32, [P, P, P, P, P, I64, P, P, P, I64, I64, I64, I32, I32, I32, I64, I64, I64, I32, P]),
     "mcop_rope_packed": (I32, [P, P, P, P, I64, P, P, I32, I64, I32, I32, I32, I32, P]),
     "mcop_fused_rope_fwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, I32, P]),
     "mcop_fused_rope_bwd": (I32, [P, P, P, I64, P, I64, I32, I32, I32, I32, I32, P]),

@@ -36,6 +36,9 @@ struct RopeParams {
   int8_t* k_cache; int8_t* v_cache;
   const int64_t* slot_mapping; const float* k_scale; const float* v_scale;
   int block_size; int64_t num_slots;
+  // fused copy store (STORE 2 of the pipelined kernel): the rotated K row and the V row of token t go, in the element type, to
+  // row slot_mapping[t] of k_copy / v_copy (rows of copy_stride elements, num_slots of them; a negative row id skips)
+  void* k_copy; void* v_copy; int64_t copy_stride;
   // every position is checked against the rows of the cos / sin table before it becomes an address; a token whose
   // position is outside [0, max_pos) is left untouched and MCOP_DEVERR_POSITION is recorded in the error word
   int64_t max_pos; int* err;
@@ -269,6 +272,9 @@ inline int esize(int dtype) { return dtype == MCOP_F32 ? 4 : 2; }
 #include "rope_pipe.inl"
 
 template <typename T, typename CT, bool PER_OP, bool STORE>
+int launch_rope_rows(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok, cudaStream_t stream);
+
+template <typename T, typename CT, bool PER_OP, int STORE>
 int launch_rope_t(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok, cudaStream_t stream) {
   if (tokens == 0) return MCOP_OK;
   MCOP_REQUIRE(tokens <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "rope: %lld tokens exceed the grid limit", (long long)tokens);
@@ -282,6 +288,16 @@ int launch_rope_t(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok,
       if (rc != 1) return rc;
     }
   }
+  if constexpr (STORE == 2) {
+    return 1;  // only the pipelined kernel has the copy store: the caller rotates and copies in two launches instead
+  } else {
+    return launch_rope_rows<T, CT, PER_OP, STORE != 0>(p, tokens, is_neox, vec_ok, stream);
+  }
+}
+
+// The row-per-CTA kernels (few tokens, gathered positions, strided heads, odd shapes).
+template <typename T, typename CT, bool PER_OP, bool STORE>
+int launch_rope_rows(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok, cudaStream_t stream) {
   if (vec_ok) {
     const int hv = p.rot_dim >> 4;
     const int threads = hv * (256 / hv > 0 ? 256 / hv : 1);
@@ -293,7 +309,7 @@ int launch_rope_t(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok,
 }
 
 // cache_dtype == dtype -> arithmetic in T unless force_fp32_math; cache fp32 -> fp32 math.
-template <bool STORE>
+template <int STORE>
 int launch_rope(const RopeParams& p, int64_t tokens, int is_neox, int dtype, int cache_dtype, bool fp32_math,
                 cudaStream_t stream) {
   const int half = p.rot_dim / 2;
@@ -303,7 +319,10 @@ int launch_rope(const RopeParams& p, int64_t tokens, int is_neox, int dtype, int
                 (p.cs_row_stride * esize(cache_dtype)) % 16 == 0;
   if (p.out_bf16) vec_ok = false;
   if (p.k_src) vec_ok = vec_ok && aligned16(p.k_src) && aligned16(p.k_dst) && (p.k_stride * esize(dtype)) % 16 == 0;
-  if (STORE) vec_ok = vec_ok && aligned16(p.v_src) && (p.v_stride * esize(dtype)) % 16 == 0 && aligned16(p.k_cache) && aligned16(p.v_cache);
+  if (STORE == 1) vec_ok = vec_ok && aligned16(p.v_src) && (p.v_stride * esize(dtype)) % 16 == 0 && aligned16(p.k_cache) && aligned16(p.v_cache);
+  if (STORE == 2)
+    vec_ok = vec_ok && aligned16(p.v_src) && (p.v_stride * esize(dtype)) % 16 == 0 && aligned16(p.k_copy) && aligned16(p.v_copy) &&
+             (p.copy_stride * esize(dtype)) % 16 == 0;
 #define MCOP_ROPE_CASE(T, CT, PER)  return launch_rope_t<T, CT, PER, STORE>(p, tokens, is_neox, vec_ok, stream)
   if (cache_dtype == MCOP_F32) {
     if (dtype == MCOP_BF16) MCOP_ROPE_CASE(__nv_bfloat16, float, false);
@@ -542,7 +561,7 @@ extern "C" int mcop_rope_inplace(const int64_t* positions, void* query, void* ke
   p.cos = cos_sin_cache; p.sin = reinterpret_cast<const char*>(cos_sin_cache) + (size_t)(rot_dim / 2) * cs;
   p.cs_row_stride = rot_dim; p.positions = positions;
   p.max_pos = max_position; p.err = pipe_error_ptr();
-  return launch_rope<false>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
+  return launch_rope<0>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
 }
 
 extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const float* cos, const float* sin, int64_t max_position,
@@ -562,7 +581,7 @@ extern "C" int mcop_rope_packed(const void* packed_qkv, void* output, const floa
   p.cos = cos; p.sin = sin; p.cs_row_stride = head_dim / 2;
   p.accum_q_lens = accum_q_lens; p.cache_lens = cache_lens; p.batch = batch;
   p.max_pos = max_position; p.err = pipe_error_ptr();
-  return launch_rope<false>(p, tokens, 1, dtype, MCOP_F32, true, (cudaStream_t)stream);
+  return launch_rope<0>(p, tokens, 1, dtype, MCOP_F32, true, (cudaStream_t)stream);
 }
 
 static int fused_rope_planes(const char* name, void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
@@ -584,7 +603,7 @@ static int fused_rope_planes(const char* name, void* qkv, const void* cos, const
   p.sin_flip = sin_flip;
   p.out_bf16 = out_bf16 ? 1 : 0;
   p.max_pos = max_position; p.err = pipe_error_ptr();
-  return launch_rope<false>(p, seq, 1, dtype, dtype, true, (cudaStream_t)stream);
+  return launch_rope<0>(p, seq, 1, dtype, dtype, true, (cudaStream_t)stream);
 }
 
 extern "C" int mcop_fused_rope_fwd(void* qkv, const void* cos, const void* sin, int64_t max_position, const int64_t* indexes,
@@ -624,7 +643,44 @@ extern "C" int mcop_rope_kv_store_i8_paged(const int64_t* positions, void* query
   p.slot_mapping = slot_mapping; p.k_scale = k_scale; p.v_scale = v_scale;
   p.block_size = block_size; p.num_slots = num_blocks * block_size;
   p.max_pos = max_position; p.err = pipe_error_ptr();
-  return launch_rope<true>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
+  return launch_rope<1>(p, tokens, is_neox, dtype, cache_dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" int mcop_rope_kv_copy(const int64_t* positions, void* query, void* key, const void* value, const float* cos_sin_cache,
+                                 int64_t max_position, void* k_buffer, void* v_buffer, const int64_t* kv_loc, int64_t buffer_rows,
+                                 int64_t buffer_row_stride, int64_t tokens, int num_heads, int num_kv_heads, int head_size,
+                                 int64_t query_stride, int64_t key_stride, int64_t value_stride, int dtype, mcop_stream_t stream) {
+  MCOP_REQUIRE(positions && query && key && value && cos_sin_cache && k_buffer && v_buffer && kv_loc, MCOP_ERR_ARGUMENT,
+               "rope_kv_copy: null pointer");
+  MCOP_REQUIRE(tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && head_size > 0 && head_size % 2 == 0 && max_position > 0 &&
+                   buffer_rows >= 0 && buffer_row_stride >= (int64_t)num_kv_heads * head_size,
+               MCOP_ERR_ARGUMENT, "rope_kv_copy: bad sizes");
+  MCOP_REQUIRE(dtype == MCOP_BF16 || dtype == MCOP_F16, MCOP_ERR_UNSUPPORTED, "rope_kv_copy: only f16 and bf16");
+  if (tokens == 0) return MCOP_OK;
+  RopeParams p{};
+  p.q_src = query; p.q_dst = query; p.q_stride = query_stride;
+  p.k_src = key; p.k_dst = key; p.k_stride = key_stride; p.head_stride = head_size;
+  p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_size = head_size; p.rot_dim = head_size;
+  p.cos = cos_sin_cache; p.sin = cos_sin_cache + head_size / 2;
+  p.cs_row_stride = head_size; p.positions = positions;
+  p.v_src = value; p.v_stride = value_stride; p.k_copy = k_buffer; p.v_copy = v_buffer; p.copy_stride = buffer_row_stride;
+  p.slot_mapping = kv_loc; p.num_slots = buffer_rows;
+  p.max_pos = max_position; p.err = pipe_error_ptr();
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool vec_ok = head_size % 16 == 0 && head_size / 16 <= 256 && aligned16(query) && aligned16(key) && aligned16(value) &&
+                      aligned16(cos_sin_cache) && aligned16(k_buffer) && aligned16(v_buffer) && (query_stride * 2) % 16 == 0 &&
+                      (key_stride * 2) % 16 == 0 && (value_stride * 2) % 16 == 0 && (buffer_row_stride * 2) % 16 == 0;
+  int rc = 1;
+  if (vec_ok)
+    rc = dtype == MCOP_BF16 ? launch_rope_t<__nv_bfloat16, float, false, 2>(p, tokens, 1, true, s)
+                            : launch_rope_t<__half, float, false, 2>(p, tokens, 1, true, s);
+  if (rc != 1) return rc;
+  // few tokens or an odd layout: the rotation, then the copy of the rotated K rows and the V rows (two launches)
+  rc = dtype == MCOP_BF16 ? launch_rope_t<__nv_bfloat16, float, false, 0>(p, tokens, 1, vec_ok, s)
+                          : launch_rope_t<__half, float, false, 0>(p, tokens, 1, vec_ok, s);
+  if (rc) return rc;
+  return mcop_reshape_and_cache_flash(key, value, key_stride, value_stride, k_buffer, v_buffer, buffer_row_stride, 0, head_size, kv_loc, tokens,
+                                      num_kv_heads, head_size, 1, buffer_rows, 2, stream);
 }
 
 extern "C" int mcop_kv_store_i8(const void* packed_qkv, int64_t qkv_stride_token, int64_t qkv_stride_head,

@@ -1,7 +1,8 @@
 // Included by rope_kv.cu inside namespace mcop::{anonymous}, after RopeParams, rotate8 and quant8.
 //
-// Persistent, pipelined NeoX RoPE (+ optional fused int8 paged KV store) for bf16/f16 activations whose heads are
-// contiguous.  A CTA takes chunks of up to 64 consecutive tokens; the positions and slots of the chunk are staged
+// Persistent, pipelined NeoX RoPE (+ optional fused KV store: STORE 1 = int8 codes into a paged cache, STORE 2 = the rotated
+// K and the V rows copied in the element type to k_copy / v_copy at row slot_mapping[t]) for bf16/f16 activations whose
+// heads are contiguous.  A CTA takes chunks of up to 64 consecutive tokens; the positions and slots of the chunk are staged
 // in shared memory, then every token's q row, k row, (v row) and cos||sin row arrive in one ring stage by bulk
 // asynchronous copies while the CTA rotates, stores and quantises the token before it.
 //
@@ -13,7 +14,7 @@ constexpr int kRopeMaxKvHeads = 128;  // more KV heads than this use the token-p
 
 // 80 registers per thread (no spills in any instantiation): four CTAs of six warps then fit the register file of an
 // SM, which is split over its four schedulers (24 warps = 6 per scheduler x 32 lanes x 80 registers).
-template <typename T, typename CT, bool PER_OP, bool STORE>
+template <typename T, typename CT, bool PER_OP, int STORE>
 __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int stages, int chunk, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int64_t s_pos[kRopeChunk];
@@ -37,7 +38,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
     mbar_init_fence();
   }
   pdl_wait();  // nothing of global memory is touched before the kernels ahead in the stream have completed
-  if (STORE) {
+  if (STORE == 1) {
     // reciprocal scales once per CTA: the token loop then reads them from shared memory, not from global memory
     for (int h = threadIdx.x; h < p.num_kv_heads; h += blockDim.x) {
       s_kinv[h] = 1.0f / p.k_scale[h];
@@ -127,9 +128,14 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
             rotate_bf16x8_packed(lds_u4(src + j * 8), lds_u4(src + half + j * 8), cs8, xp, yp);
             st_u4(dst + j * 8, xp);
             st_u4(dst + half + j * 8, yp);
-            if (STORE && is_k && slot >= 0) {
+            if (STORE == 1 && is_k && slot >= 0) {
               unpack_bf16x8(xp, xo);
               unpack_bf16x8(yp, yo);
+            }
+            if (STORE == 2 && is_k && slot >= 0) {
+              T* kc = reinterpret_cast<T*>(p.k_copy) + slot * p.copy_stride + hh * D;
+              st_u4(kc + j * 8, xp);
+              st_u4(kc + half + j * 8, yp);
             }
           } else {
             if (ElemTraits<T>::code == MCOP_BF16) {
@@ -142,15 +148,26 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
             rotate8<T, PER_OP>(x, y, cc, ss, xo, yo);
             Vec8<T>::store(dst + j * 8, xo);
             Vec8<T>::store(dst + half + j * 8, yo);
+            if (STORE == 2 && is_k && slot >= 0) {
+              T* kc = reinterpret_cast<T*>(p.k_copy) + slot * p.copy_stride + hh * D;
+              Vec8<T>::store(kc + j * 8, xo);
+              Vec8<T>::store(kc + half + j * 8, yo);
+            }
           }
-          if (STORE && is_k && slot >= 0) {
+          if (STORE == 1 && is_k && slot >= 0) {
             const float inv = s_kinv[hh];
             int8_t* kc = p.k_cache + (slot * p.num_kv_heads + hh) * (int64_t)D;
             st_cs_u2(kc + j * 8, quant8(xo, inv));
             st_cs_u2(kc + half + j * 8, quant8(yo, inv));
           }
         }
-        if (STORE && slot >= 0) {
+        if (STORE == 2 && slot >= 0) {
+          // the V row as it came: 16-byte vectors from the stage to the token's row of the buffer
+          const unsigned char* vs = st + q_bytes + k_bytes;
+          unsigned char* vc = reinterpret_cast<unsigned char*>(reinterpret_cast<T*>(p.v_copy) + slot * p.copy_stride);
+          for (uint32_t i = threadIdx.x * 16u; i < v_bytes; i += blockDim.x * 16u) st_u4(vc + i, lds_u4(vs + i));
+        }
+        if (STORE == 1 && slot >= 0) {
           const T* vs = reinterpret_cast<const T*>(st + q_bytes + k_bytes);
           const int vper = D >> 4;
           const int nitems = p.num_kv_heads * vper;
@@ -188,7 +205,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
 }
 
 // Returns MCOP_OK / an error, or 1 when the shape does not fit the pipelined kernel.
-template <typename T, typename CT, bool PER_OP, bool STORE>
+template <typename T, typename CT, bool PER_OP, int STORE>
 int launch_rope_pipe(const RopeParams& p, int64_t tokens, cudaStream_t stream) {
   const int D = p.head_size, hv = D >> 4;
   if (hv < 1 || 256 % hv != 0 || p.num_kv_heads > kRopeMaxKvHeads) return 1;

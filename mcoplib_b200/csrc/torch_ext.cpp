@@ -592,6 +592,7 @@ void store_kv_cache(Tensor k_cache, Tensor v_cache, Tensor out_loc, Tensor k, Te
 // sglang's apply_rope_pos_ids_cos_sin_cache (op/sglang/csrc/elementwise/rope.cu:28-171): RoPE from an fp32 cos||sin cache at
 // explicit positions, written to q_rope / k_rope (which may be q / k), optionally followed by
 // k_buffer[kv_cache_loc[i]] = k_rope[i], v_buffer[kv_cache_loc[i]] = v[i].  fp32 products and sum, one rounding.
+// With the save, NeoX order and rotary_dim == head_dim this is ONE call (mcop_rope_kv_copy); other forms rotate, then copy.
 void apply_rope_pos_ids_cos_sin_cache(Tensor q, Tensor k, Tensor q_rope, Tensor k_rope, Tensor cos_sin_cache, Tensor pos_ids, bool interleave,
                                       bool enable_pdl, const std::optional<Tensor>& v, const std::optional<Tensor>& k_buffer,
                                       const std::optional<Tensor>& v_buffer, const std::optional<Tensor>& kv_cache_loc) {
@@ -626,6 +627,19 @@ void apply_rope_pos_ids_cos_sin_cache(Tensor q, Tensor k, Tensor q_rope, Tensor 
   if (k_rope.data_ptr() != k.data_ptr()) k_rope.copy_(k);
   TORCH_CHECK(q_rope.stride(1) == k_rope.stride(1), "q_rope and k_rope must have one head stride");
   TORCH_CHECK(pos_ids.numel() >= nnz && cos_sin_cache.size(0) > 0);
+  if (save_kv_cache && !interleave && rot == head_dim && q_rope.stride(1) == head_dim && k_rope.stride(1) == head_dim &&
+      v->stride(1) == head_dim && k_buffer->stride(1) == head_dim && k_buffer->strides() == v_buffer->strides() &&
+      k_buffer->size(1) == kv_heads && k_buffer->size(2) == head_dim && v->size(0) == nnz && v->size(1) == kv_heads &&
+      v->size(2) == head_dim && kv_cache_loc->numel() == nnz && v->scalar_type() == q.scalar_type() &&
+      k_buffer->scalar_type() == q.scalar_type() && v_buffer->scalar_type() == q.scalar_type()) {
+    // rotation and save in one call (one launch from 2048 tokens on, like the reference's fused kernel)
+    check_rc(mcop_rope_kv_copy(pos_ids.data_ptr<int64_t>(), q_rope.data_ptr(), k_rope.data_ptr(), v->data_ptr(),
+                               cos_sin_cache.data_ptr<float>(), cos_sin_cache.size(0), k_buffer->data_ptr(), v_buffer->data_ptr(),
+                               kv_cache_loc->data_ptr<int64_t>(), std::min(k_buffer->size(0), v_buffer->size(0)), k_buffer->stride(0), nnz,
+                               heads, kv_heads, head_dim, q_rope.stride(0), k_rope.stride(0), v->stride(0),
+                               dtype_code(q, "apply_rope_pos_ids_cos_sin_cache"), cur_stream()));
+    return;
+  }
   check_rc(mcop_rope_inplace(pos_ids.data_ptr<int64_t>(), q_rope.data_ptr(), k_rope.data_ptr(), cos_sin_cache.data_ptr(), MCOP_F32,
                              cos_sin_cache.size(0), nnz, heads,
                              kv_heads, head_dim, rot, q_rope.stride(0), k_rope.stride(0), q_rope.stride(1), interleave ? 0 : 1,

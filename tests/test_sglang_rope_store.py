@@ -18,6 +18,7 @@ def _cache(max_pos, rot, base=10000.0):
 @pytest.mark.parametrize("n,Hq,Hk,D,rot,interleave,dtype,inplace,save", [
     (77, 8, 2, 128, 128, False, torch.bfloat16, True, False), (77, 8, 2, 128, 128, True, torch.bfloat16, False, True),
     (300, 32, 8, 128, 64, False, torch.float16, True, True), (5000, 16, 4, 64, 64, False, torch.bfloat16, False, True),
+    (20000, 32, 8, 128, 128, False, torch.bfloat16, True, True), (3000, 8, 2, 128, 128, False, torch.float16, True, True),
     (9, 4, 4, 256, 128, True, torch.float16, False, False)])
 def test_apply_rope_pos_ids_cos_sin_cache(n, Hq, Hk, D, rot, interleave, dtype, inplace, save):
     from mcoplib_b200 import op
@@ -48,6 +49,40 @@ def test_apply_rope_pos_ids_cos_sin_cache(n, Hq, Hk, D, rot, interleave, dtype, 
         assert torch.equal(bits(kb[loc].reshape(n, -1)), bits(k_ref)) and torch.equal(vb[loc], v)
         rest = torch.ones(slots, dtype=torch.bool); rest[loc] = False
         assert bool((kb[rest] == 3.0).all()) and bool((vb[rest] == 3.0).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [2500, 64])
+def test_apply_rope_save_skips_bad_rows_of_the_buffers(n):
+    """The fused rotation + save (one launch from 2048 tokens on; the rotation followed by the copy below that): a negative
+    row id rotates the token and stores nothing; a row id past the buffers does the same and records MCOP_DEVERR_SLOT."""
+    from mcoplib_b200 import cabi, op
+    from tests.gpu_util import DEV, bits
+    g = torch.Generator().manual_seed(n)
+    Hq, Hk, D = 8, 2, 128
+    q = torch.randn(n, Hq, D, generator=g).bfloat16(); k = torch.randn(n, Hk, D, generator=g).bfloat16()
+    v = torch.randn(n, Hk, D, generator=g).bfloat16()
+    pos = torch.randint(0, 1024, (n,), generator=g, dtype=torch.int64)
+    cache = _cache(1024, D)
+    q_ref, k_ref = R.rotary_embedding(pos, q.reshape(n, -1), k.reshape(n, -1), D, cache, True)
+    slots = n + 10
+    loc = torch.randperm(slots, generator=g)[:n].to(torch.int64)
+    loc[5] = -1
+    loc[7] = slots + 3
+    kbuf = torch.full((slots, Hk, D), 3.0, dtype=torch.bfloat16, device=DEV); vbuf = torch.full_like(kbuf, 3.0)
+    qd, kd = q.to(DEV), k.to(DEV)
+    lib = cabi.load()
+    torch.cuda.synchronize(); lib.mcop_device_error()
+    op.apply_rope_pos_ids_cos_sin_cache(qd, kd, qd, kd, cache.to(DEV), pos.to(DEV), False, False, v=v.to(DEV), k_buffer=kbuf,
+                                        v_buffer=vbuf, kv_cache_loc=loc.to(DEV))
+    torch.cuda.synchronize()
+    assert lib.mcop_device_error() == cabi.DEVERR_SLOT and lib.mcop_device_error() == 0
+    assert torch.equal(bits(qd.cpu().reshape(n, -1)), bits(q_ref)) and torch.equal(bits(kd.cpu().reshape(n, -1)), bits(k_ref))
+    good = torch.ones(n, dtype=torch.bool); good[5] = False; good[7] = False
+    kb, vb = kbuf.cpu(), vbuf.cpu()
+    assert torch.equal(bits(kb[loc[good]].reshape(int(good.sum()), -1)), bits(k_ref[good])) and torch.equal(vb[loc[good]], v[good])
+    rest = torch.ones(slots, dtype=torch.bool); rest[loc[good]] = False
+    assert bool((kb[rest] == 3.0).all()) and bool((vb[rest] == 3.0).all())
 
 
 @pytest.mark.gpu
