@@ -118,10 +118,16 @@ __device__ __forceinline__ void rotate_bf16x8_packed(const uint4 xr, const uint4
 }
 
 __device__ __forceinline__ uint2 quant8(const float (&v)[8], float inv) {
-  int c[8];
+  uint32_t c[8];
+  const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) c[j] = q_rn_clamp(__fmul_rn(v[j], inv), -127, 127);
-  return pack_i8x8(c);
+  for (int j = 0; j < 8; j += 2) {
+    const float2 pr = mul2_rn(make_float2(v[j], v[j + 1]), inv2);
+    c[j] = (uint32_t)q_rn_clamp(pr.x, -127, 127);
+    c[j + 1] = (uint32_t)q_rn_clamp(pr.y, -127, 127);
+  }
+  // the low bytes of the clamped integers are the codes: three byte permutes per four codes
+  return make_uint2(pack4_low_bytes(c[0], c[1], c[2], c[3]), pack4_low_bytes(c[4], c[5], c[6], c[7]));
 }
 
 // NeoX, rot_dim == head_size, head_size % 16 == 0, all rows 16-byte aligned.
