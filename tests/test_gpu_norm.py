@@ -469,3 +469,47 @@ def test_head_rms_norm_grid_stride_and_corrected_quotients(op, dtype, wdtype, T,
     xin = x.to(DEV)
     op.head_rms_norm(xin, xin, w.to(DEV), 1e-5, off, hn)
     assert torch.equal(bits(xin[:, off:off + hn]), bits(out[:, off:off + hn]))
+
+
+def test_scale_dynamic_quant_adversarial_ties_fp32(op):
+    """The division-free code path against the IEEE division on inputs built to sit on and beside the rounding ties: for a
+    set of scales (random ones, and mantissas of all zeros, all ones, a single low or high bit), a row holds 127 * scale as
+    its maximum and, for every k, the fp32 value nearest to scale * (k + 0.5) with its neighbours one and two ulps either
+    side, in both signs.  fp32 rows with a smooth vector of ones (y = x exactly): the row-per-CTA kernel, which shares
+    `quant8_by_scale` with the pipelined one.  Bit-exact codes and scales."""
+    import numpy as np
+    rng = np.random.default_rng(3)
+    mant = np.concatenate([rng.integers(0, 1 << 23, 200), [0, 0x7fffff, 1, 0x400000, 0x7ffffe, 0x2aaaaa, 0x555555]]).astype(np.uint32)
+    expo = rng.integers(100, 150, mant.size).astype(np.uint32)
+    scales = ((expo << 23) | mant).view(np.float32)
+    H = 2048
+    rows = []
+    for sc in scales:
+        top = np.float32(127.0) * sc
+        k = np.arange(0, 127, dtype=np.float32) + np.float32(0.5)
+        base = (k * sc).astype(np.float32)
+        vals = [base]
+        for d in (1, 2):
+            up, dn = base.copy(), base.copy()
+            for _ in range(d):
+                up = np.nextafter(up, np.float32(np.inf)); dn = np.nextafter(dn, np.float32(0))
+            vals += [up, dn]
+        v = np.concatenate(vals)
+        v = np.concatenate([v, -v])
+        row = np.zeros(H, np.float32)
+        row[0] = top
+        row[1:1 + v.size] = v[: H - 1]
+        rows.append(row)
+    x = torch.from_numpy(np.stack(rows))
+    assert bool(torch.isfinite(x).all())
+    ones = torch.ones(H)
+    q_ref, s_ref = R.scale_dynamic_quant(x, ones)
+    q, s = op.scale_dynamic_quant(x.to(DEV), ones.to(DEV))
+    C.assert_equal(bits(s.cpu()), bits(s_ref.reshape(-1)), "scales")
+    C.assert_equal(q.cpu(), q_ref, "codes")
+    # the same rows as bf16-representable values through the pipelined kernel (rows repeated to reach its 1024-row threshold)
+    xb = x.bfloat16().repeat(6, 1)
+    q_ref, s_ref = R.scale_dynamic_quant(xb, ones)
+    q, s = op.scale_dynamic_quant(xb.to(DEV), ones.to(DEV))
+    C.assert_equal(bits(s.cpu()), bits(s_ref.reshape(-1)), "scales (bf16 rows)")
+    C.assert_equal(q.cpu(), q_ref, "codes (bf16 rows)")
