@@ -513,3 +513,20 @@ def test_scale_dynamic_quant_adversarial_ties_fp32(op):
     q, s = op.scale_dynamic_quant(xb.to(DEV), ones.to(DEV))
     C.assert_equal(bits(s.cpu()), bits(s_ref.reshape(-1)), "scales (bf16 rows)")
     C.assert_equal(q.cpu(), q_ref, "codes (bf16 rows)")
+
+
+@pytest.mark.parametrize("T,heads,D", [(2000, 56, 128), (1500, 16, 64), (300, 12, 256)])
+def test_head_rms_norm_quotients_against_ieee_division_fp32(op, T, heads, D):
+    """The twice-corrected quotient x * (1 / r) of the head kernels against the IEEE division, bit for bit, on fp32 heads
+    (no rounding to a 16-bit type hides a last-bit error): the checker is torch on the GPU with the same formula -
+    the mean of squares in float64 rounded to fp32, r = 1 / sqrt(var + eps), (x / r) * w - whose sqrt and divisions are the
+    IEEE ones.  Heads spread over 40 binades; both the pipelined kernel (T >= 1024) and the grid-stride kernel."""
+    g = torch.Generator(device=DEV).manual_seed(41)
+    x = torch.randn(T, heads, D, generator=g, device=DEV) * torch.exp2(torch.randint(-20, 20, (T, heads, 1), generator=g, device=DEV).float())
+    w = 1 + 0.1 * torch.randn(heads, D, generator=g, device=DEV)
+    var = (x.double() * x.double()).mean(dim=-1, keepdim=True).float()
+    r = 1.0 / torch.sqrt(var + 1e-5)
+    ref = (x / r) * w.unsqueeze(0)
+    out = torch.empty_like(x)
+    op.head_rms_norm(out, x, w, 1e-5, 0, heads)
+    assert torch.equal(bits(out), bits(ref)), f"{int((bits(out) != bits(ref)).sum())} of {out.numel()} elements differ"
