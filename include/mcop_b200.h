@@ -39,7 +39,8 @@ int mcop_version(void);
 const char* mcop_last_error(void);
 /* Device-side status of the current device: one word per device that kernels set and the host reads.
  *   - the row-pipeline kernels bound every wait on an asynchronous copy; a kernel whose wait runs out records
- *     MCOP_DEVERR_WAIT_FIRST .. MCOP_DEVERR_WAIT_LAST (which wait it was), stops issuing copies, drains those in
+ *     MCOP_DEVERR_WAIT_FIRST .. MCOP_DEVERR_WAIT_LAST (which wait it was: 1 / 2 norm + quant row wait / drain, 3 / 4 gather,
+ *     5 / 6 scatter, 7 RoPE, 11 / 12 scale_dynamic_quant, 13 / 14 head_rms_norm), stops issuing copies, drains those in
  *     flight and returns instead of hanging;
  *   - a value read from a caller's tensor is never turned into an address unchecked: a position outside the
  *     cos / sin table, a cache slot or cache position outside the cache make the kernel SKIP that token (nothing of
