@@ -517,6 +517,45 @@ __global__ void __launch_bounds__(256) cache_copy_kernel(CacheCopyParams p) {
   }
 }
 
+// The same with 16-byte vectors and U tokens per thread: a thread moves one vector of K and one of V for each of its U
+// tokens, all 2 * U loads issued before the first store (one token per CTA left one pair of loads per thread in flight
+// behind the slot lookup: 4.7 TB/s at 8 heads of 128).  The CTA's threads are (tokens per pass) x (vectors per token).
+template <int U>
+__global__ void __launch_bounds__(256) cache_copy_vec16_multi(CacheCopyParams p, int64_t tokens, int tokens_per_pass) {
+  const int per_head = p.head_bytes >> 4;
+  const int n = p.kv_heads * per_head;
+  const int tl = threadIdx.x / n, i = threadIdx.x - tl * n;
+  if (tl >= tokens_per_pass) return;
+  const int h = i / per_head, e = i - h * per_head;
+  const int64_t src = (int64_t)h * p.head_bytes + (int64_t)e * 16;
+  const int64_t dst_hd = h * p.head_stride + (int64_t)e * 16;
+  const int64_t t0 = (int64_t)blockIdx.x * tokens_per_pass * U + tl;
+  uint4 kv[U], vv[U];
+  int64_t dst[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int64_t t = t0 + (int64_t)u * tokens_per_pass;
+    dst[u] = -1;
+    if (t >= tokens) continue;
+    const int64_t slot = p.slot_mapping[t];
+    if (slot < 0) continue;
+    if (slot >= p.num_slots) {  // never becomes an address
+      if (i == 0) report_device_error(p.err, MCOP_DEVERR_SLOT);
+      continue;
+    }
+    const int64_t blk = slot / p.block_size, off = slot % p.block_size;
+    dst[u] = blk * p.block_stride + off * p.page_stride + dst_hd;
+    kv[u] = ld_nc_u4(p.key + t * p.key_stride + src);
+    vv[u] = ld_nc_u4(p.value + t * p.value_stride + src);
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (dst[u] < 0) continue;
+    st_u4(p.key_cache + dst[u], kv[u]);
+    st_u4(p.value_cache + dst[u], vv[u]);
+  }
+}
+
 struct CacheSplitParams {
   const void* key; const void* value; int64_t key_stride, value_stride;  // elements
   void* key_cache; void* value_cache;
@@ -553,6 +592,108 @@ __global__ void __launch_bounds__(256) cache_split_kernel(CacheSplitParams p) {
       for (int j = 0; j < p.x; ++j) kc[kdst + j] = key[src + j];
     }
     for (int j = 0; j < p.x; ++j) vc[vdst + (int64_t)j * p.block_size] = value[src + j];
+  }
+}
+
+// The same for 2-byte elements with a window of kSplitWindow consecutive tokens per CTA.  In the V layout
+// [blocks, heads, head_size, block_size] the elements of one token lie block_size elements apart: written token by token
+// every element is a 2-byte store into a 32-byte sector of its own (1024 partial-sector writes per token of 8 heads of
+// 128: 0.9 TB/s with consecutive slots, 0.46 TB/s with scattered ones).  Tokens that follow each other in a prefill
+// mostly have consecutive slots, i.e. consecutive positions of one block, and then the 2-byte pieces of neighbouring
+// tokens are neighbours in memory.  So the CTA copies the V rows of its window into shared memory, splits the window
+// into runs of tokens with consecutive slots inside one block, and every thread writes, for its (head, element) pairs,
+// the run's values as the largest aligned pieces (16, 8, 4, 2 bytes) - a full run of 16 tokens is two 16-byte stores
+// per pair instead of sixteen 2-byte stores.  K moves as before (a group of x elements per store).
+constexpr int kSplitWindow = 16;
+
+template <typename KV>
+__global__ void __launch_bounds__(256) cache_split_tile_kernel(CacheSplitParams p, int64_t tokens) {
+  extern __shared__ __align__(16) unsigned char tile_raw[];
+  uint16_t* tile = reinterpret_cast<uint16_t*>(tile_raw);  // [kSplitWindow][kv_heads * head_size]
+  __shared__ int64_t s_slot[kSplitWindow];
+  const int HD = p.kv_heads * p.head_size;
+  const int64_t t0 = (int64_t)blockIdx.x * kSplitWindow;
+  const int nt = (int)min((int64_t)kSplitWindow, tokens - t0);
+  if (threadIdx.x < kSplitWindow) {
+    int64_t slot = -1;
+    if (threadIdx.x < nt) {
+      slot = p.slot_mapping[t0 + threadIdx.x];
+      if (slot >= p.num_slots) {  // never becomes an address
+        report_device_error(p.err, MCOP_DEVERR_SLOT);
+        slot = -1;
+      }
+    }
+    s_slot[threadIdx.x] = slot;
+  }
+  // V rows of the window -> shared memory, 16 bytes at a time (rows of HD elements, HD % 8 == 0)
+  const uint16_t* value = reinterpret_cast<const uint16_t*>(p.value);
+  const int vec_per_row = HD >> 3;
+  for (int i = threadIdx.x; i < nt * vec_per_row; i += blockDim.x) {
+    const int tk = i / vec_per_row, v = i - tk * vec_per_row;
+    *reinterpret_cast<uint4*>(tile + (size_t)tk * HD + v * 8) = ld_nc_u4(value + (t0 + tk) * p.value_stride + v * 8);
+  }
+  __syncthreads();
+  // K: one group of x elements per store, token by token
+  {
+    const int groups = p.head_size / p.x;
+    const int n = p.kv_heads * groups;
+    const uint16_t* key = reinterpret_cast<const uint16_t*>(p.key);
+    uint16_t* kc = reinterpret_cast<uint16_t*>(p.key_cache);
+    for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
+      const int tk = i / n, r = i - tk * n;
+      const int64_t slot = s_slot[tk];
+      if (slot < 0) continue;
+      const int64_t blk = slot / p.block_size, off = slot % p.block_size;
+      const int h = r / groups, g = r - h * groups;
+      const int64_t src = (t0 + tk) * p.key_stride + (int64_t)h * p.head_size + (int64_t)g * p.x;
+      const int64_t kdst = (((blk * p.kv_heads + h) * groups + g) * p.block_size + off) * p.x;
+      if (sizeof(KV) > sizeof(uint16_t)) {
+        *reinterpret_cast<KV*>(kc + kdst) = *reinterpret_cast<const KV*>(key + src);
+      } else {
+        for (int j = 0; j < p.x; ++j) kc[kdst + j] = key[src + j];
+      }
+    }
+  }
+  // V: runs of tokens with consecutive slots inside one block
+  uint16_t* vc = reinterpret_cast<uint16_t*>(p.value_cache);
+  int a = 0;
+  while (a < nt) {  // the same for every thread of the CTA
+    const int64_t slot0 = s_slot[a];
+    if (slot0 < 0) { ++a; continue; }
+    const int64_t blk = slot0 / p.block_size;
+    const int off0 = (int)(slot0 % p.block_size);
+    int n = 1;
+    while (a + n < nt && s_slot[a + n] == slot0 + n && off0 + n < p.block_size) ++n;
+    for (int hd = threadIdx.x; hd < HD; hd += blockDim.x) {
+      const int h = hd / p.head_size, d = hd - h * p.head_size;
+      uint16_t* dst = vc + ((blk * p.kv_heads + h) * (int64_t)p.head_size + d) * p.block_size + off0;
+      const uint16_t* col = tile + (size_t)a * HD + hd;  // the run's values: col[i * HD]
+      int i = 0;
+      while (i < n) {
+        const uintptr_t addr = reinterpret_cast<uintptr_t>(dst + i);
+        const int left = n - i;
+        if (left >= 8 && (addr & 15u) == 0) {
+          uint32_t w[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) w[q] = (uint32_t)col[(size_t)(i + 2 * q) * HD] | ((uint32_t)col[(size_t)(i + 2 * q + 1) * HD] << 16);
+          *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          i += 8;
+        } else if (left >= 4 && (addr & 7u) == 0) {
+          uint32_t w[2];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) w[q] = (uint32_t)col[(size_t)(i + 2 * q) * HD] | ((uint32_t)col[(size_t)(i + 2 * q + 1) * HD] << 16);
+          *reinterpret_cast<uint2*>(dst + i) = make_uint2(w[0], w[1]);
+          i += 4;
+        } else if (left >= 2 && (addr & 3u) == 0) {
+          *reinterpret_cast<uint32_t*>(dst + i) = (uint32_t)col[(size_t)i * HD] | ((uint32_t)col[(size_t)(i + 1) * HD] << 16);
+          i += 2;
+        } else {
+          dst[i] = col[(size_t)i * HD];
+          i += 1;
+        }
+      }
+    }
+    a += n;
   }
 }
 
@@ -754,7 +895,13 @@ extern "C" int mcop_reshape_and_cache_flash(const void* key, const void* value, 
                    p.key_stride % 16 == 0 && p.value_stride % 16 == 0 && p.block_stride % 16 == 0 && p.page_stride % 16 == 0 &&
                    p.head_stride % 16 == 0;
   cudaStream_t s = (cudaStream_t)stream;
-  if (v16) cache_copy_kernel<uint4><<<(unsigned)tokens, 256, 0, s>>>(p);
+  const int nvec = kv_heads * (p.head_bytes >> 4);  // 16-byte vectors per token and tensor
+  if (v16 && nvec <= 256 && tokens >= 1024) {
+    constexpr int U = 4;
+    const int tpp = 256 / nvec;  // tokens per pass of the CTA
+    const unsigned grid = (unsigned)((tokens + (int64_t)tpp * U - 1) / ((int64_t)tpp * U));
+    cache_copy_vec16_multi<U><<<grid, tpp * nvec, 0, s>>>(p, tokens, tpp);
+  } else if (v16) cache_copy_kernel<uint4><<<(unsigned)tokens, 256, 0, s>>>(p);
   else if (elem_bytes == 4) cache_copy_kernel<uint32_t><<<(unsigned)tokens, 256, 0, s>>>(p);
   else if (elem_bytes == 2) cache_copy_kernel<uint16_t><<<(unsigned)tokens, 256, 0, s>>>(p);
   else cache_copy_kernel<uint8_t><<<(unsigned)tokens, 256, 0, s>>>(p);
@@ -780,6 +927,22 @@ extern "C" int mcop_reshape_and_cache(const void* key, const void* value, int64_
   const bool g16 = gb == 16 && al(key, 16) && al(key_cache, 16) && (key_stride * elem_bytes) % 16 == 0;
   const bool g8 = gb == 8 && al(key, 8) && al(key_cache, 8) && (key_stride * elem_bytes) % 8 == 0;
   if (elem_bytes == 2) {
+    // from a few windows of tokens on, with rows that move as 16-byte vectors and a window that fits shared memory:
+    // the tiled kernel (V written run by run instead of element by element)
+    const size_t tile_bytes = (size_t)kSplitWindow * kv_heads * head_size * 2;
+    if (tokens >= 4 * kSplitWindow && (kv_heads * head_size) % 8 == 0 && al(value, 16) && (value_stride * 2) % 16 == 0 &&
+        al(value_cache, 16) && tile_bytes <= 160 * 1024) {
+      const unsigned wgrid = (unsigned)((tokens + kSplitWindow - 1) / kSplitWindow);
+      auto launch_tile = [&](auto kernel) -> int {
+        const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 200 * 1024);
+        MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "reshape_and_cache: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        kernel<<<wgrid, 256, tile_bytes, s>>>(p, tokens);
+        return check_launch("reshape_and_cache (tiled)");
+      };
+      if (g16) return launch_tile(cache_split_tile_kernel<uint4>);
+      if (g8) return launch_tile(cache_split_tile_kernel<uint2>);
+      return launch_tile(cache_split_tile_kernel<uint16_t>);
+    }
     if (g16) cache_split_kernel<uint16_t, uint4><<<grid, 256, 0, s>>>(p);
     else if (g8) cache_split_kernel<uint16_t, uint2><<<grid, 256, 0, s>>>(p);
     else cache_split_kernel<uint16_t, uint16_t><<<grid, 256, 0, s>>>(p);

@@ -290,6 +290,30 @@ def test_reshape_and_cache_flash(op):
         ns.reshape_and_cache_flash(key.to(DEV), val.to(DEV), kc, vc, slots.to(DEV), "fp8", one, one)
 
 
+@pytest.mark.parametrize("T,Hkv,D,bs,dtype", [(5000, 8, 128, 16, torch.bfloat16), (2049, 2, 64, 8, torch.float16), (1500, 40, 128, 16, torch.bfloat16)])
+def test_reshape_and_cache_flash_many_tokens(op, T, Hkv, D, bs, dtype):
+    """From 1024 tokens on a thread of the flash-layout copy moves one 16-byte vector of K and of V for four tokens (40 heads
+    of 128 are more vectors than a CTA has threads: the row-per-token kernel).  Scattered slots, negative slots, a slot
+    past the cache (skipped, reported); bit-exact against the oracle, untouched cells keep their canary value."""
+    ns = getattr(torch.ops, op.torch_namespace + "_cache_ops")
+    g = torch.Generator().manual_seed(23)
+    nb = (T + bs - 1) // bs + 5
+    key = torch.randn(T, Hkv, D, generator=g).to(dtype); val = torch.randn(T, Hkv, D, generator=g).to(dtype)
+    slots = torch.randperm(nb * bs, generator=g)[:T].to(torch.int64)
+    slots[3] = -1; slots[T - 1] = -1
+    ref_slots = slots.clone()
+    slots[700] = nb * bs + 9; ref_slots[700] = -1
+    kc0 = torch.full((nb, bs, Hkv, D), 7.0, dtype=dtype)
+    kc_ref, vc_ref = R.reshape_and_cache_flash(key, val, kc0, kc0.clone(), ref_slots)
+    kc, vc = kc0.to(DEV), kc0.clone().to(DEV)
+    one = torch.ones(1, device=DEV)
+    _device_error()
+    ns.reshape_and_cache_flash(key.to(DEV), val.to(DEV), kc, vc, slots.to(DEV), "auto", one, one)
+    from mcoplib_b200 import cabi
+    assert _device_error() == cabi.DEVERR_SLOT
+    C.assert_equal(bits(kc), bits(kc_ref), "key cache"); C.assert_equal(bits(vc), bits(vc_ref), "value cache")
+
+
 def test_config4_rope_kv_full_size_properties(op):
     """Benchmark configuration 4's RoPE stage (32768 tokens, 64/8 heads, positions < 131072): properties over
     the whole output, the oracle on a sample of tokens."""
@@ -369,6 +393,39 @@ def test_reshape_and_cache_split_layout(op):
         ns.reshape_and_cache(kview, vview, kc, vc, slots.to(DEV), "fp8", one, one)
     with pytest.raises(RuntimeError):   # a flash-layout cache is not a split-layout cache
         ns.reshape_and_cache(kview, vview, torch.zeros(8, 16, 40, 128, dtype=dtype, device=DEV), vc, slots.to(DEV), "auto", one, one)
+
+
+@pytest.mark.parametrize("dtype,x,Hkv,D,bs", [(torch.bfloat16, 8, 8, 128, 16), (torch.float16, 8, 2, 64, 32), (torch.bfloat16, 4, 3, 128, 8),
+                                              (torch.bfloat16, 8, 40, 128, 16)])
+def test_reshape_and_cache_split_layout_runs_of_consecutive_slots(op, dtype, x, Hkv, D, bs):
+    """The tiled kernel of the split layout writes a run of tokens with consecutive slots inside one block as aligned
+    pieces of up to 16 bytes.  The slot map mixes what a scheduler produces: sequences whose slots run through several
+    blocks starting at any offset of a block and at any token index, single tokens, a negative slot inside a run, a slot
+    past the cache (skipped, reported), and a tail of scattered slots.  Bit-exact against the oracle; cells that no token
+    maps to keep their canary value.  (40 heads of 128: a window does not fit shared memory, the row-per-token kernel.)"""
+    ns = getattr(torch.ops, op.torch_namespace + "_cache_ops")
+    one = torch.ones(1, device=DEV)
+    nb = 64
+    g = torch.Generator().manual_seed(17)
+    runs = [(3, bs + 2), (2 * bs, bs), (5 * bs + bs - 1, 2), (9 * bs + 5, 1), (12 * bs, 3 * bs + 7), (20 * bs + 3, bs - 3), (30 * bs + 1, 29)]
+    slots = torch.cat([torch.arange(s0, s0 + n) for s0, n in runs])
+    used = set(slots.tolist())
+    free = torch.tensor([s_ for s_ in range(nb * bs) if s_ not in used])
+    tail = free[torch.randperm(free.numel(), generator=g)[:45]]
+    slots = torch.cat([slots, tail]).to(torch.int64)
+    slots[10] = -1                       # inside the first run
+    slots[50] = nb * bs + 4              # past the cache: skipped and reported
+    T = slots.numel()
+    key = (torch.randn(T, Hkv, D, generator=g)).to(dtype); val = (torch.randn(T, Hkv, D, generator=g)).to(dtype)
+    kc0 = torch.full((nb, Hkv, D // x, bs, x), 7.0, dtype=dtype); vc0 = torch.full((nb, Hkv, D, bs), 7.0, dtype=dtype)
+    ref_slots = slots.clone(); ref_slots[50] = -1
+    kc_ref, vc_ref = R.reshape_and_cache(key, val, kc0, vc0, ref_slots)
+    kc, vc = kc0.to(DEV), vc0.to(DEV)
+    _device_error()
+    ns.reshape_and_cache(key.to(DEV), val.to(DEV), kc, vc, slots.to(DEV), "auto", one, one)
+    from mcoplib_b200 import cabi
+    assert _device_error() == cabi.DEVERR_SLOT
+    C.assert_equal(bits(kc), bits(kc_ref), "key cache"); C.assert_equal(bits(vc), bits(vc_ref), "value cache")
 
 
 def _device_error():
