@@ -317,11 +317,16 @@ class Part1:
     """The other entry points of parts 1 and 2, each timed on its own on bf16 rows of 7168: fused_add_rms_norm (in place), rms_norm
     with a residual, the 9-argument norm + smooth quant, scale_dynamic_quant, head_rms_norm (56 heads of 128), the unpaged
     int8 store of packed K/V (64 Q + 8 + 8 KV heads of 128, one sequence per 4096 tokens) and sglang's RoPE with the save of the
-    rotated K and of V into token-indexed buffers (same heads, positions below 8192, a random permutation of rows)."""
+    rotated K and of V into token-indexed buffers (same heads, positions below 8192, a random permutation of rows), the packed
+    rotary_embedding of mcoplib.op (positions from the sequence bounds, output to a second tensor) and the two paged copies of
+    K / V rows (8 heads of 128, blocks of 16; flash layout with scattered slots, split layout with the consecutive slots of a
+    prefill - scattered slots cost the split layout one 2-byte store per element by construction)."""
     name = ("other entry points: fused_add_rms_norm, rms_norm (+residual), 9-argument rms_norm_dynamic_per_token_quant, "
-            "scale_dynamic_quant, head_rms_norm, store_kv_cache_cuda_interface, apply_rope_pos_ids_cos_sin_cache with save")
-    kernels = ["fused_add_rms_norm", "rms_norm", "norm_smooth_quant", "scale_dynamic_quant", "head_rms_norm", "store_kv", "rope_kv_save"]
-    launches_per_step = 7
+            "scale_dynamic_quant, head_rms_norm, store_kv_cache_cuda_interface, apply_rope_pos_ids_cos_sin_cache with save, "
+            "rotary_embedding (packed), reshape_and_cache_flash, reshape_and_cache")
+    kernels = ["fused_add_rms_norm", "rms_norm", "norm_smooth_quant", "scale_dynamic_quant", "head_rms_norm", "store_kv", "rope_kv_save",
+               "rotary_embedding_packed", "reshape_and_cache_flash", "reshape_and_cache"]
+    launches_per_step = 10
 
     def __init__(self, tokens, t0=0, device="cuda", gen_device="cuda", **_):
         from mcoplib_b200 import workloads as W
@@ -361,6 +366,19 @@ class Part1:
         self.kv_loc = torch.randperm(tokens, generator=g, device=device).to(torch.int64)
         self.k_buffer = torch.empty(tokens, self.Hkv, self.D, dtype=torch.bfloat16, **o)
         self.v_buffer = torch.empty_like(self.k_buffer)
+        # packed rotary_embedding: cos / sin halves of the same table, an output tensor of the packed shape
+        self.cos_half = self.rope_cache[:, :self.D // 2].contiguous()
+        self.sin_half = self.rope_cache[:, self.D // 2:].contiguous()
+        self.packed_out = torch.empty_like(self.qkv)
+        # paged copies: blocks of 16 slots
+        self.bs = 16
+        nb = (tokens + self.bs - 1) // self.bs
+        self.flash_k = torch.empty(nb, self.bs, self.Hkv, self.D, dtype=torch.bfloat16, **o)
+        self.flash_v = torch.empty_like(self.flash_k)
+        self.split_k = torch.empty(nb, self.Hkv, self.D // 8, self.bs, 8, dtype=torch.bfloat16, **o)
+        self.split_v = torch.empty(nb, self.Hkv, self.D, self.bs, dtype=torch.bfloat16, **o)
+        self.slots_seq = torch.arange(tokens, dtype=torch.int64, **o)
+        self.one = torch.ones(1, **o)
 
     def bytes_per_kernel(self):
         n = self.T * self.H
@@ -373,13 +391,19 @@ class Part1:
                 "store_kv": 2 * kv * 2 + 2 * kv + 8 * self.Hkv * self.D,   # K, V heads read, two int8 caches written
                 # q, k, v read; q, k written in place; rotated k and v written to the buffers; cos || sin row, position, row id
                 "rope_kv_save": self.T * ((self.Hq + 2 * self.Hkv) * self.D * 2 + (self.Hq + self.Hkv) * self.D * 2
-                                          + 2 * self.Hkv * self.D * 2 + 4 * self.D + 16)}
+                                          + 2 * self.Hkv * self.D * 2 + 4 * self.D + 16),
+                # q, k heads read and written to the output tensor, the cos and sin half rows
+                "rotary_embedding_packed": self.T * (2 * (self.Hq + self.Hkv) * self.D * 2 + 4 * self.D),
+                # K and V rows read, written to the caches, the slot
+                "reshape_and_cache_flash": self.T * (4 * self.Hkv * self.D * 2 + 8),
+                "reshape_and_cache": self.T * (4 * self.Hkv * self.D * 2 + 8)}
 
     def stages(self, ops):
         x3 = self.x.view(self.T, 56, 128)
         out3 = self.out.view(self.T, 56, 128)
         q, k = self.qkv[:, :self.Hq], self.qkv[:, self.Hq:self.Hq + self.Hkv]   # rotated in place: norms are kept, values stay put
         v = self.qkv[:, self.Hq + self.Hkv:]
+        cache_ops = getattr(torch.ops, ops.torch_namespace + "_cache_ops")
         return [
             lambda: ops.fused_add_rms_norm(self.x_io, self.res_io, self.w, 1e-6),
             lambda: ops.rms_norm(self.out, self.x, self.w, 1e-6, self.after_res, self.res, False),
@@ -391,6 +415,10 @@ class Part1:
                                                       self.v_cache, self.kv_scale, self.kv_scale, self.nseq, self.Hq, self.Hkv),
             lambda: ops.apply_rope_pos_ids_cos_sin_cache(q, k, q, k, self.rope_cache, self.rope_pos, False, False, v=v,
                                                          k_buffer=self.k_buffer, v_buffer=self.v_buffer, kv_cache_loc=self.kv_loc),
+            lambda: ops.rotary_embedding(self.qkv, self.q_lens, self.accum, self.cache_lens, self.cos_half, self.sin_half, self.packed_out,
+                                         self.Hq, self.Hkv, 0),
+            lambda: cache_ops.reshape_and_cache_flash(k, v, self.flash_k, self.flash_v, self.kv_loc, "auto", self.one, self.one),
+            lambda: cache_ops.reshape_and_cache(k, v, self.split_k, self.split_v, self.slots_seq, "auto", self.one, self.one),
         ]
 
 

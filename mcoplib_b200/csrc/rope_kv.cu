@@ -285,11 +285,14 @@ int launch_rope_t(const RopeParams& p, int64_t tokens, int is_neox, bool vec_ok,
   if (tokens == 0) return MCOP_OK;
   MCOP_REQUIRE(tokens <= 0x7fffffffLL, MCOP_ERR_UNSUPPORTED, "rope: %lld tokens exceed the grid limit", (long long)tokens);
   if constexpr (sizeof(T) == 2) {
-    // the pipelined kernel wants explicit positions, heads packed back to back, a key tensor, and cos || sin as
-    // one contiguous table row; it pays off once there are a few waves of tokens
+    // the pipelined kernel wants positions (explicit, or sequence bounds to derive them from), heads packed back to back, a
+    // key tensor, and the cos / sin halves as 16-byte aligned rows: one table row cos || sin, or two tables of half rows
+    // (those land side by side in the ring stage); it pays off once there are a few waves of tokens
     const bool one_row = reinterpret_cast<const char*>(p.sin) == reinterpret_cast<const char*>(p.cos) + (size_t)(p.rot_dim / 2) * sizeof(CT);
-    if (vec_ok && !p.sin_flip && tokens >= MCOP_ROPE_PIPE_MIN && p.positions && p.k_src && p.num_kv_heads > 0 && p.head_stride == p.head_size &&
-        one_row && p.cs_row_stride == p.rot_dim) {
+    const bool one_table = one_row && p.cs_row_stride == p.rot_dim;
+    const bool two_tables = p.cs_row_stride == p.rot_dim / 2 && ((size_t)(p.rot_dim / 2) * sizeof(CT)) % 16 == 0;
+    if (vec_ok && !p.sin_flip && tokens >= MCOP_ROPE_PIPE_MIN && (p.positions || p.accum_q_lens) && p.k_src && p.num_kv_heads > 0 &&
+        p.head_stride == p.head_size && (one_table || two_tables)) {
       const int rc = launch_rope_pipe<T, CT, PER_OP, STORE>(p, tokens, stream);
       if (rc != 1) return rc;
     }

@@ -56,7 +56,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
   for (int64_t t0 = tok_begin; t0 < tok_end && alive; t0 += chunk) {
     const int ntok = (int)min((int64_t)chunk, tok_end - t0);
     if (threadIdx.x < ntok) {
-      int64_t pos = p.positions[t0 + threadIdx.x];
+      int64_t pos = token_position(p, t0 + threadIdx.x);  // explicit, or from the bounds of the token's sequence
       if (pos < 0 || pos >= p.max_pos) {  // never becomes an address: the token is skipped (marked by -1) and reported
         report_device_error(p.err, MCOP_DEVERR_POSITION);
         pos = -1;
@@ -84,7 +84,13 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
       if (STORE) bulk_g2s(dst + q_bytes + k_bytes, reinterpret_cast<const T*>(p.v_src) + t * p.v_stride, v_bytes, &full[s]);
       // a skipped token still fills its stage (row 0 of the table stands in): the ring stays in step, nothing is used
       const int64_t cs_row = s_pos[pi] < 0 ? 0 : s_pos[pi];
-      bulk_g2s(dst + q_bytes + k_bytes + v_bytes, reinterpret_cast<const CT*>(p.cos) + cs_row * p.cs_row_stride, cs_bytes, &full[s]);
+      unsigned char* cs_dst = dst + q_bytes + k_bytes + v_bytes;
+      if (p.cs_row_stride == p.rot_dim) {  // cos || sin is one row of one table
+        bulk_g2s(cs_dst, reinterpret_cast<const CT*>(p.cos) + cs_row * p.cs_row_stride, cs_bytes, &full[s]);
+      } else {                             // two tables of half rows: they land side by side in the stage
+        bulk_g2s(cs_dst, reinterpret_cast<const CT*>(p.cos) + cs_row * p.cs_row_stride, cs_bytes / 2, &full[s]);
+        bulk_g2s(cs_dst + cs_bytes / 2, reinterpret_cast<const CT*>(p.sin) + cs_row * p.cs_row_stride, cs_bytes / 2, &full[s]);
+      }
       ++issued; ++pi;
       prod.advance(stages);
     };

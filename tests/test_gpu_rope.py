@@ -158,6 +158,39 @@ def test_fused_rope_fwd(op):
         op.fused_rope_fwd(qkv.float().to(DEV), cos.to(DEV), sin.to(DEV), None, False)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_packed_and_plane_rope_through_the_pipelined_kernel(op, dtype):
+    """From 2048 tokens on, mcoplib.op's packed rotary_embedding (positions derived from the sequence bounds, separate fp32 cos
+    and sin tables, output to a second tensor) and fused_rope_fwd (Q and K planes of [S, 3, H, D], cos / sin tables of the
+    element type) take the pipelined kernel: the two half rows of a position land side by side in the ring stage.
+    Bit-exact against the oracle; V heads / the V plane untouched."""
+    g = torch.Generator().manual_seed(33)
+    D = 128
+    cs = W.cos_sin_cache(8192, D, 500000.0)
+    cos, sin = cs[:, :D // 2].contiguous(), cs[:, D // 2:].contiguous()
+    if dtype == torch.bfloat16:   # the packed operator is bf16 only, as in the reference
+        T, Hq, Hkv = 6000, 16, 4
+        packed = torch.randn(T, Hq + 2 * Hkv, D, generator=g).to(dtype)
+        accum = torch.tensor([0, 2500, 2501, 6000], dtype=torch.int32); q_len = torch.tensor([2500, 1, 3499], dtype=torch.int32)
+        cache_lens = torch.tensor([5, 400, 0], dtype=torch.int32)
+        base = torch.full_like(packed, 7.0)
+        ref = R.rotary_embedding_packed(packed, q_len, accum, cache_lens, cos, sin, base, Hq, Hkv)
+        out = base.to(DEV)
+        op.rotary_embedding(packed.to(DEV), q_len.to(DEV), accum.to(DEV), cache_lens.to(DEV), cos.to(DEV), sin.to(DEV), out, Hq, Hkv, 0)
+        assert _device_error() == 0
+        C.assert_equal(bits(out), bits(ref))
+    S, H = 4500, 8
+    qkv = torch.randn(S, 3, H, D, generator=g).to(dtype)
+    cos_t, sin_t = cos.to(dtype).contiguous(), sin.to(dtype).contiguous()
+    idx = torch.randint(0, 8192, (S,), generator=g)
+    for indexes in (None, idx):
+        ref = R.fused_rope_fwd(qkv, cos_t, sin_t, indexes)
+        gq = qkv.to(DEV)
+        op.fused_rope_fwd(gq, cos_t.to(DEV), sin_t.to(DEV), indexes.to(DEV) if indexes is not None else None, False)
+        assert _device_error() == 0
+        C.assert_equal(bits(gq), bits(ref))
+
+
 def test_fused_rope_fwd_force_bf16_attn(op):
     """force_bf16_attn on f16 data (op/fused_rope.cu:44-52): fp32 rotation of the f16 inputs, Q and K rounded once to bf16
     and stored in place, V keeps its f16 bits, the result is the same storage viewed as bf16."""
