@@ -642,8 +642,11 @@ __global__ void __launch_bounds__(256) cache_split_tile_kernel(CacheSplitParams 
     const int n = p.kv_heads * groups;
     const uint16_t* key = reinterpret_cast<const uint16_t*>(p.key);
     uint16_t* kc = reinterpret_cast<uint16_t*>(p.key_cache);
+    // consecutive lanes take consecutive TOKENS of one group: with consecutive slots their 16-byte groups are neighbours
+    // in the cache (a whole 256-byte line of one (head, group) per 16 lanes) instead of 32 half-written sectors: 142 -> 128 us at
+    // 65,536 tokens of 8 heads of 128 (the K rows through shared memory as well: 157 us)
     for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
-      const int tk = i / n, r = i - tk * n;
+      const int r = i / nt, tk = i - r * nt;
       const int64_t slot = s_slot[tk];
       if (slot < 0) continue;
       const int64_t blk = slot / p.block_size, off = slot % p.block_size;
