@@ -67,8 +67,20 @@ __device__ __forceinline__ float row_weight(const GatherParams& p, int64_t t, in
 __device__ __forceinline__ void accumulate8(float (&acc)[8], const uint4 raw, bool weighted, float w) {
   float f[8];
   unpack_bf16x8(raw, f);
+  if (weighted) {
+    // products as packed fp32 pairs (each lane rounded like __fmul_rn), sums scalar: a packed add fed by a packed product
+    // would be fused into one multiply-add and drop the product's rounding
+    const float2 w2 = make_float2(w, w);
 #pragma unroll
-  for (int q = 0; q < 8; ++q) acc[q] = __fadd_rn(acc[q], weighted ? __fmul_rn(w, f[q]) : f[q]);
+    for (int q = 0; q < 8; q += 2) {
+      const float2 pr = mul2_rn(make_float2(f[q], f[q + 1]), w2);
+      acc[q] = __fadd_rn(acc[q], pr.x);
+      acc[q + 1] = __fadd_rn(acc[q + 1], pr.y);
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[q] = __fadd_rn(acc[q], f[q]);
+  }
 }
 
 // Slow path shared by both vector kernels: the token owns more rows than the inverse holds, so row2tok is
