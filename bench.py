@@ -49,7 +49,8 @@ def measured_peak():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs (and, when that region is
+    shorter than the sampler's start-up, while the same replays continue off the clock: time_graph_replays)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -66,7 +67,7 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -651,6 +652,14 @@ def time_graph_replays(step, turn, nsets, steps, warmup, world, device, dist, on
         dist.barrier()
     torch.cuda.synchronize()
     total = g0.elapsed_time(g1)
+    if on_start:
+        # A clock sampler is running (nvidia-smi needs a few hundred ms for its first line, a short timed region would get no
+        # sample at all): the SAME replays continue off the clock until the sampler has seen about 0.7 s of this load.
+        t_end = time.time() + max(0.0, 0.7 - total * 1e-3)
+        while time.time() < t_end:
+            for _ in range(reps):
+                g.replay()
+            torch.cuda.synchronize()
     if world > 1:
         t = torch.tensor([total], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -915,7 +924,8 @@ def run_ours(args):
             oms, opk, ostep, oturn = time_steps([w.stages(ops) for w in osets], steps_o, 3, 1, device, dist)
             oeager = oms / steps_o
             try:
-                gtot, gst = time_graph_replays(ostep, oturn, onsets, steps_o, 3, 1, device, dist)
+                # (on_start given: the replays continue off the clock until the sampler above has seen 0.7 s of this load)
+                gtot, gst = time_graph_replays(ostep, oturn, onsets, steps_o, 3, 1, device, dist, on_start=lambda: None)
                 oms, steps_o = gtot, gst
             except Exception:
                 pass
