@@ -88,7 +88,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons),
+                "window": "the timed replays and, where they take less than 0.5 s, the same replays continued off the clock"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -654,8 +655,8 @@ def time_graph_replays(step, turn, nsets, steps, warmup, world, device, dist, on
     total = g0.elapsed_time(g1)
     if on_start:
         # A clock sampler is running (nvidia-smi needs a few hundred ms for its first line, a short timed region would get no
-        # sample at all): the SAME replays continue off the clock until the sampler has seen about 0.7 s of this load.
-        t_end = time.time() + max(0.0, 0.7 - total * 1e-3)
+        # sample at all): the SAME replays continue off the clock until the sampler has seen about 0.5 s of this load.
+        t_end = time.time() + max(0.0, 0.5 - total * 1e-3)
         while time.time() < t_end:
             for _ in range(reps):
                 g.replay()
@@ -924,7 +925,7 @@ def run_ours(args):
             oms, opk, ostep, oturn = time_steps([w.stages(ops) for w in osets], steps_o, 3, 1, device, dist)
             oeager = oms / steps_o
             try:
-                # (on_start given: the replays continue off the clock until the sampler above has seen 0.7 s of this load)
+                # (on_start given: the replays continue off the clock until the sampler above has seen 0.5 s of this load)
                 gtot, gst = time_graph_replays(ostep, oturn, onsets, steps_o, 3, 1, device, dist, on_start=lambda: None)
                 oms, steps_o = gtot, gst
             except Exception:
