@@ -389,13 +389,12 @@ __device__ __noinline__ void scatter_fold_histogram(const ScatterQuantParams& p,
     for (int e = threadIdx.x; e < E; e += nthreads) { p.counts[e] = s_cnt[e]; p.starts[e] = s_starts[e]; }
 }
 
-// One batch of an item (whole CTA): the tokens holding ranks [lo, lo + nb) of expert e inside tiles [tile_lo, tile_hi),
-// in ascending order, go to s_tok; their routing weights to s_wt; row2tok / tok2row of the rows b0 .. b0 + nb - 1 are
-// written.  Ends with a CTA barrier.  Kept out of line for the same reason as the prologue.
-// The CTA has nothing else to do while this runs, so dependent loads are kept to two round trips: the bitmaps of
-// the (few) tiles are fetched together with their counts, the weights of all slots together with the ids.
-__device__ __noinline__ void scatter_stage_batch(const ScatterQuantParams& p, int e, int tile_lo, int tile_hi, int lo, int nb, int b0,
-                                                 int32_t* s_tok, float* s_wt) {
+// One batch of an item, first half (whole CTA): the tokens holding ranks [lo, lo + nb) of expert e inside tiles
+// [tile_lo, tile_hi), in ascending order, go to s_tok.  Ends with a CTA barrier.  One round trip to memory: the bitmaps
+// of the (few) tiles are fetched together with their counts.
+// Both halves are inlined: as calls they cost the CTA a spill of the live smooth slice to the stack and a reload from
+// L2 afterwards (the L1 that is left beside the ring does not keep the stack) - two more round trips per item.
+__device__ __forceinline__ void scatter_list_tokens(const ScatterQuantParams& p, int e, int tile_lo, int tile_hi, int lo, int nb, int32_t* s_tok) {
   const int E = p.E;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (warp == 0) {
@@ -459,6 +458,11 @@ __device__ __noinline__ void scatter_stage_batch(const ScatterQuantParams& p, in
     }
   }
   __syncthreads();
+}
+
+// Second half: the routing weights of the batch's tokens go to s_wt; row2tok / tok2row of the rows b0 .. b0 + nb - 1 are
+// written.  Ends with a CTA barrier.  One round trip: the weights of all slots are fetched together with the ids.
+__device__ __forceinline__ void scatter_stage_weights(const ScatterQuantParams& p, int e, int nb, int b0, const int32_t* s_tok, float* s_wt) {
   // slot and routing weight of every token of the batch; the row's entries of row2tok / tok2row
   if (threadIdx.x < nb) {
     const int t = s_tok[threadIdx.x];
@@ -574,7 +578,7 @@ __global__ void __launch_bounds__(THREADS, CTAS) scatter_quant_pipe(ScatterQuant
     for (int lo = lo_part; lo < hi_part && alive; lo += kBatchRows) {
       const int nb = min(kBatchRows, hi_part - lo);
       const int b0 = rb_all + lo;  // output row of the batch's first token
-      scatter_stage_batch(p, e, tile_lo, tile_hi, lo, nb, b0, s_tok, s_wt);
+      scatter_list_tokens(p, e, tile_lo, tile_hi, lo, nb, s_tok);
       int pi = 0;  // producer cursor inside the batch (thread 0)
       auto issue_next = [&]() {
         if (pi >= nb) return;
@@ -584,8 +588,10 @@ __global__ void __launch_bounds__(THREADS, CTAS) scatter_quant_pipe(ScatterQuant
         ++issued; ++pi;
         prod.advance(stages);
       };
+      // the first rows are on their way while the ids and weights of the batch are fetched
       if (threadIdx.x == 0)
         for (int s = 0; s < stages; ++s) issue_next();
+      scatter_stage_weights(p, e, nb, b0, s_tok, s_wt);
       for (int i = 0; i < nb; ++i) {
         const int st = cons.s;
         const bool ok = mbar_wait_bounded(&full[st], cons.phase, err, 5);
@@ -637,7 +643,10 @@ __global__ void __launch_bounds__(THREADS, CTAS) scatter_quant_pipe(ScatterQuant
             uint32_t c[8];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              // packed product, scalar rounding adds (a packed add could be fused with the product by the assembler)
+              // packed product, scalar rounding adds.  Measured: a packed add here gets contracted with the packed product
+              // into one fused multiply-add by the assembler (4 % faster, but the codes differ: one rounding instead of
+              // two); a packed fma(pr, 1, magic), which cannot be contracted, is exact and no faster than the scalar adds.
+              // The row's scale written by another warp than the one that issues the copies: no change either.
               const float2 pr = mul2_rn(vv[k][q], mul2);
               c[2 * q] = rn_low_byte(pr.x);
               c[2 * q + 1] = rn_low_byte(pr.y);
