@@ -537,27 +537,36 @@ __global__ void __launch_bounds__(THREADS, CTAS) scatter_quant_pipe(ScatterQuant
   uint32_t it = 0, issued = 0, flip = 0;
   RingPos cons, prod;  // ring positions of the consumer (all threads) and of the producer (thread 0)
   bool alive = true;
-  const int64_t nitems = (int64_t)nsuper * E * p.parts;
+  const int nitems = nsuper * E * p.parts;
   while (alive) {
     // work items (super-tile, expert, part) from an atomic counter, in token-major order: the CTAs move through the
     // tokens together, so the k readers of a token row run close together in time
     // (asking the counter for the next item while this one runs, so that the atomic's round trip hides behind the rows,
-    // measured the same: 1357 / 201 us against 1349-1354 / 199-203 us at 262,144 / 32,768 tokens)
+    // measured the same: 1357 / 201 us against 1349-1354 / 199-203 us at 262,144 / 32,768 tokens.
+    // Preparing the whole next item while the last rows of this one are quantised - the counter asked a dozen rows before
+    // the end, bitmap words and ids / weights brought by asynchronous copies into shared memory, tokens listed, weights
+    // chosen, each step between two rows, and the producer running on into the next item's rows - cut the time from an
+    // item's start to its first row from 11,000 to 3,600 cycles and still lost: 204 against 185 us at 32,768 tokens,
+    // 1470-1600 against 1330-1450 us at 262,144.  With the steps compiled in but switched off it was 201 us: the state
+    // they keep alive costs the row loop its registers, and the two other CTAs of the SM were already covering for a
+    // CTA that sits in its set-up.)
     if (threadIdx.x == 0) s_item = atomicAdd(p.work_counter, 1);
     __syncthreads();
-    const int64_t item = s_item;
+    const int item = s_item;
     __syncthreads();  // s_item may be rewritten only after everybody has read it
     if (item >= nitems) break;
-    const int part = (int)(item % p.parts);
-    const int e = (int)((item / p.parts) % E);
-    const int sup = (int)(item / ((int64_t)p.parts * E));
+    // 32-bit arithmetic throughout (64-bit divisions are long instruction sequences, and the CTA waits for them): the host
+    // keeps the item count below 2^30, a (super-tile, expert) pair holds at most 64 * 512 rows and is cut into at most 64 parts
+    const int part = item % p.parts, pe = item / p.parts;
+    const int e = pe % E;
+    const int sup = pe / E;
     const int tile_lo = sup * p.supertile;
     const int tile_hi = min(tile_lo + p.supertile, ntiles);
     const int off_lo = s_base[sup * E + e];
     const int nall = (sup + 1 < nsuper ? s_base[(sup + 1) * E + e] : s_cnt[e]) - off_lo;
     const int rb_all = s_starts[e] + off_lo;
-    const int lo_part = (int)(((int64_t)nall * part) / p.parts);
-    const int hi_part = (int)(((int64_t)nall * (part + 1)) / p.parts);
+    const int lo_part = nall * part / p.parts;
+    const int hi_part = nall * (part + 1) / p.parts;
     if (hi_part <= lo_part) continue;  // uniform over the CTA
     // the expert's smooth-scale slice stays in registers for the whole item
     // (kept as pairs: the arithmetic below uses the packed fp32x2 multiply of sm_100)
@@ -771,6 +780,7 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   p.parts = parts;
   const int64_t nsuper = (ntiles + supertile - 1) / supertile;
   const int64_t nitems = nsuper * p.E * parts;
+  if (nitems >= (int64_t)1 << 30) return 1;  // the kernel numbers its items with 32 bits
   const int table_bytes = (int)(((2 * (int64_t)p.E + nsuper * p.E) * sizeof(int32_t) + 127) / 128 * 128);
   // each of the CTAS resident CTAs gets its share of the shared memory: barriers, table, ring of row buffers
   const int64_t budget = (227 * 1024) / CTAS - 2 * 1024 - 128 - table_bytes;
