@@ -225,6 +225,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
   for (int64_t t0 = tok_begin; t0 < tok_end && alive; t0 += chunk) {
     const int ntok = (int)min((int64_t)chunk, tok_end - t0);
     // ---- phase A: one thread per token builds the token's ascending row list (and weights)
+    // (the token's ids and weights prefetched into L1 while its rows are fetched, instead of one round trip after the
+    // other: 244 us either way at 32,768 tokens x top-2 - the phase is not what the short runs lose)
     if (threadIdx.x < ntok) {
       const int64_t t = t0 + threadIdx.x;
       int rows[kPipeMaxRows];
