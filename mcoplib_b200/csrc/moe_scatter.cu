@@ -761,7 +761,9 @@ int launch_quant_pipe(ScatterQuantParams p, cudaStream_t stream) {
   // (measured at 8192 tokens x top-8 of 256: items of 16 rows +1 %, of 8 rows -4 % against this rule; at 32,768 tokens x
   // top-2 of 8 items of 12 / 16 / 20 / 24 / 32 / 40 / 56 rows: 213 / 209 / 202 / 199 / 197 / 200 / 220 us - flat around the rule's 25;
   // half-size items for the last quarter / half / all of the super-tiles: 200 / 205 / 214 us there, 1370 / 1449 / 1552 us
-  // against 1347 us at 262,144 tokens - the spread of the CTAs' finishing times is not what the short runs lose)
+  // against 1347 us at 262,144 tokens - the spread of the CTAs' finishing times is not what the short runs lose;
+  // again after the per-item set-up had lost two round trips: 10 / 13 / 16 / 20 / 32 rows at 32,768 tokens 200 / 191 / 189 /
+  // 187 / 185 us against 186 us for the rule, 20 / 26 / 32 / 64 rows at 262,144 tokens 1358 / 1362 / 1375 / 1348 against 1317 us)
   double target = total_rows / ((double)sm_count() * CTAS * 6.0);
   target = target < 16.0 ? 16.0 : (target > 40.0 ? 40.0 : target);
   const double rows_per_tile_expert = (double)kTileTokens * p.topk / p.E;
