@@ -394,7 +394,13 @@ int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t strea
   // every CTA gets an equal contiguous share of the tokens and prepares it in chunks of up to kChunkTokens tokens
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > (tokens + 7) / 8) grid = (tokens + 7) / 8;
-  const int chunk = kChunkTokens;
+  // chunks of a quarter of a CTA's share, between 32 and kChunkTokens tokens: with one chunk per CTA every CTA of the
+  // grid builds its lists at the same moment and then streams at the same moment (32,768 tokens x top-2: 246 us with one
+  // chunk of 110 tokens per CTA, 235 / 228 / 239 / 254 us with chunks of 64 / 32 / 16 / 8); large runs keep the long chunks
+  // (262,144 tokens: 128 and 32 within the noise of each other, 16 and 8 slower: the ring drains at every chunk's end)
+  const int64_t share = (tokens + grid - 1) / grid;
+  int chunk = (int)(((share + 3) / 4 + 7) / 8 * 8);
+  chunk = chunk < 32 ? 32 : (chunk > kChunkTokens ? kChunkTokens : chunk);
   const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&gather_pipe<THREADS, 4>), 200 * 1024);
   MCOP_REQUIRE(e == cudaSuccess, MCOP_ERR_CUDA, "moe_gather: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   (void)launch_pdl(gather_pipe<THREADS, 4>, dim3((unsigned)grid), dim3(THREADS), smem, stream, p, stages, chunk, pipe_error_ptr());
