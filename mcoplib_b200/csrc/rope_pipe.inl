@@ -167,7 +167,7 @@ __global__ void __maxnreg__(80) rope_neox_pipe(RopeParams p, int64_t tokens, int
             st_cs_u2(kc + half + j * 8, quant8(yo, inv));
           }
         }
-        if (STORE == 2 && slot >= 0) {
+        if constexpr (STORE == 2) if (slot >= 0) {
           // the V row as it came: 16-byte vectors from the stage to the token's row of the buffer
           const unsigned char* vs = st + q_bytes + k_bytes;
           unsigned char* vc = reinterpret_cast<unsigned char*>(reinterpret_cast<T*>(p.v_copy) + slot * p.copy_stride);
