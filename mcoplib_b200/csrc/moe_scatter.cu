@@ -503,6 +503,13 @@ __device__ __forceinline__ void scatter_stage_weights(const ScatterQuantParams& 
 }
 
 // Main path, second launch: persistent pipelined quant kernel.
+// What bounds it at 262,144 tokens x top-2 is not the SM: with the multiply and the two rounding adds of pass 2 taken out
+// (a fifth of the instructions) it takes the same 1325-1335 us, and a form that keeps the row's products in tensor
+// memory between the passes (tcgen05.alloc of 64 columns per CTA, tcgen05.st / ld of 8 columns, 128 registers, four
+// CTAs per SM, bit-identical) takes 1395 us against 1325 (199 against 185 us at 32,768 tokens; only below 8192 tokens
+// is it ahead, 39 against 44 us at 4096).  Every token row is read k times, once from DRAM and k - 1 times from L2: at
+// top-2 the SMs take in 5.6 TB/s and put out 2.8 TB/s, 8.4 TB/s through the L2, where the kernels that run at 0.98 of
+// the copy bandwidth move 6.4-6.5 TB/s; the bytes the roofline counts (a token row once) are 5.7 TB/s of that.
 // Dynamic shared memory: 128 bytes of mbarriers; the table (starts [E], counts [E], row offset of every
 // (super-tile, expert) pair [nsuper, E]) rounded up to 128 bytes; then `stages` row buffers.
 template <int THREADS, int NVEC, bool FULL, int CTAS>  // FULL: the row is exactly THREADS * NVEC vectors of 8, no lane is ever idle
