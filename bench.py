@@ -127,6 +127,11 @@ class Chain5:
     def bytes_per_kernel(self):
         return self.W.chain5_bytes(self.T, self.H, self.E, self.k)
 
+    def l2_side_bytes(self):
+        # what the SMs take in and put out for the scatter: a token row is read once per expert that consumes it,
+        # the first time from DRAM and the other k - 1 times from L2 (the algorithmic bytes count it once)
+        return {"scatter": self.W.scatter_bytes(self.T, self.H, self.E, self.k) + (self.k - 1) * self.T * self.H * 2}
+
     def stages(self, ops):
         return [
             lambda: ops.rms_norm_dynamic_per_token_quant_custom(self.codes, self.x, self.w, self.scales, 1e-6, None, self.res),
@@ -205,6 +210,9 @@ class Route3:
         W = self.W
         return {"gate": W.gate_bytes(self.T, 256, 8), "scatter": W.scatter_bytes(self.T, 7168, 256, 8),
                 "gather": W.gather_bytes(self.T, 7168, 8, False)}
+
+    def l2_side_bytes(self):
+        return {"scatter": self.W.scatter_bytes(self.T, 7168, 256, 8) + 7 * self.T * 7168 * 2}
 
     def stages(self, ops):
         return [
@@ -675,6 +683,13 @@ def kernel_table(wl, per_kernel_ms, peak):
         gbs = bpk[name] / (ms * 1e-3) / 1e9
         out[name] = {"ms": ms, "algorithmic_bytes": bpk[name], "gb_per_s": gbs, "frac_of_measured_copy_peak": gbs / peak,
                      "frac_of_8TBps_nominal": gbs / NOMINAL_HBM_GBS}
+    # where a kernel re-reads rows from L2, the rate at which bytes cross between L2 and the SMs is given beside the
+    # algorithmic rate (it is not a roofline fraction: the denominator above is a DRAM copy)
+    side = wl.l2_side_bytes() if hasattr(wl, "l2_side_bytes") else {}
+    for name, b in side.items():
+        if name in out:
+            out[name]["l2_side_bytes"] = b
+            out[name]["l2_side_gb_per_s"] = b / (out[name]["ms"] * 1e-3) / 1e9
     return out
 
 
