@@ -25,7 +25,7 @@ struct GatherParams {
 };
 
 constexpr int kMaxList = 64;    // rows of one token the row-per-CTA kernels handle without the slow scan
-constexpr int kChunkTokens = 128;  // tokens whose row lists a CTA of the pipelined kernel prepares at a time
+constexpr int kChunkTokens = 64;   // tokens whose row lists a CTA of the pipelined kernel prepares at a time (two such tables + the staging of one)
 constexpr int kPipeMaxRows = 16;  // rows per token the pipelined kernel keeps in shared memory
 
 // Inversion pre-pass: the rows of a token form a chain, head[t] -> r1 -> next[r1] -> ... -> -1 (unordered; the gather sorts
@@ -194,13 +194,68 @@ __global__ void __launch_bounds__(THREADS) gather_vec(GatherParams p) {
   }
 }
 
+// One token's ascending row list (and weights) for the pipelined kernel: rows[0..n) and w[0..n), *cnt = n, or -1 when the
+// token owns more rows than the table holds (slow scan).  `staged` (nullable): the token's tok2row, ids and weights rows as
+// an earlier asynchronous copy left them in shared memory (8 words each, topk <= 8) - the same values as in global memory.
+__device__ __forceinline__ void gather_build_list(const GatherParams& p, int64_t t, const uint32_t* staged, int32_t* rows_out, float* w_out,
+                                                  int* cnt) {
+  int rows[kPipeMaxRows];
+  int slot[kPipeMaxRows];  // with tok2row: the routing slot a row came from
+  int n = 0;
+  bool overflow = false;
+  if (p.tok2row) {
+    for (int j = 0; j < p.topk; ++j) {
+      const int r = staged ? (int)staged[j] : p.tok2row[t * p.topk + j];
+      if (r >= 0 && r < p.rows) { rows[n] = r; slot[n] = j; ++n; }
+    }
+  } else {
+    n = gather_walk_chain(p, t, rows, kPipeMaxRows);
+    if (n < 0) { overflow = true; n = 0; }
+  }
+  if (!overflow) {
+    for (int a = 1; a < n; ++a) {  // insertion sort, n <= 16
+      const int key = rows[a], ks = slot[a];
+      int b = a - 1;
+      while (b >= 0 && rows[b] > key) { rows[b + 1] = rows[b]; slot[b + 1] = slot[b]; --b; }
+      rows[b + 1] = key; slot[b + 1] = ks;
+    }
+    for (int j = 0; j < n; ++j) {
+      rows_out[j] = rows[j];
+      if (p.weighted) {
+        float w;
+        if (p.tok2row) {
+          // the row belongs to the expert named by its slot: the weight is that of the FIRST slot of the token that
+          // names this expert - the same value the search over the experts' starts would find, without the search
+          const int32_t* tid = p.topk_ids + t * p.topk;
+          const int e = staged ? (int)staged[8 + slot[j]] : tid[slot[j]];
+          int jf = slot[j];
+          for (int i = 0; i < slot[j]; ++i)
+            if ((staged ? (int)staged[8 + i] : tid[i]) == e) { jf = i; break; }
+          w = staged ? __uint_as_float(staged[16 + jf]) : p.topk_weights[t * p.topk + jf];
+        } else {
+          w = row_weight(p, t, rows[j]);
+        }
+        w_out[j] = w;
+      }
+    }
+  }
+  *cnt = overflow ? -1 : n;
+}
+
 // Persistent pipelined kernel.  Dynamic shared memory: 128 bytes of mbarriers, then `stages` row buffers.
+// The row lists of a chunk of tokens live in one of two halves of the tables below.  With tok2row and topk <= 8 the
+// NEXT chunk's lists are made while the current chunk streams: at the chunk's start one thread per token of the next
+// chunk starts asynchronous copies of that token's tok2row, ids and weights rows into shared memory; half way through
+// the chunk the same threads wait for their copies (long landed), sort and write the lists into the other half; from
+// the next row on the producer runs on into those rows, so the ring neither drains at the chunk's end nor waits for
+// three dependent round trips.  Without tok2row (chains to walk) or with more slots the lists are made between chunks.
 template <int THREADS, int NVEC>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe(GatherParams p, int stages, int chunk, int* err) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int32_t s_rows[kChunkTokens][kPipeMaxRows];
-  __shared__ float s_w[kChunkTokens][kPipeMaxRows];
-  __shared__ int s_cnt[kChunkTokens];   // rows of the token; -1 = more than the table holds (slow scan)
+  __shared__ int32_t s_rows[2][kChunkTokens][kPipeMaxRows];
+  __shared__ float s_w[2][kChunkTokens][kPipeMaxRows];
+  __shared__ int s_cnt[2][kChunkTokens];   // rows of the token; -1 = more than the table holds (slow scan)
+  __shared__ uint32_t s_stage[kChunkTokens][24];  // tok2row | ids | weights of the next chunk's tokens, 8 words each
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   unsigned char* buf = smem + 128;
   const int H = p.hidden_size, nv = H >> 3;
@@ -222,72 +277,72 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
   // walks it in chunks
   const int64_t tok_begin = (p.tokens * (int64_t)blockIdx.x) / gridDim.x;
   const int64_t tok_end = (p.tokens * ((int64_t)blockIdx.x + 1)) / gridDim.x;
+  const bool ahead = p.tok2row != nullptr && p.topk <= 8;
+  int cur = 0;
+  bool have = false;       // the lists of the chunk at t0 are in half `cur` already
+  int qtl = 0, qj = 0;     // thread 0: producer cursor inside the next chunk's lists
   for (int64_t t0 = tok_begin; t0 < tok_end && alive; t0 += chunk) {
     const int ntok = (int)min((int64_t)chunk, tok_end - t0);
+    const int nnext = (int)max((int64_t)0, min((int64_t)chunk, tok_end - (t0 + chunk)));
     // ---- phase A: one thread per token builds the token's ascending row list (and weights)
     // (the token's ids and weights prefetched into L1 while its rows are fetched, instead of one round trip after the
     // other: 244 us either way at 32,768 tokens x top-2 - the phase is not what the short runs lose)
-    if (threadIdx.x < ntok) {
-      const int64_t t = t0 + threadIdx.x;
-      int rows[kPipeMaxRows];
-      int slot[kPipeMaxRows];  // with tok2row: the routing slot a row came from
-      int n = 0;
-      bool overflow = false;
-      if (p.tok2row) {
-        for (int j = 0; j < p.topk; ++j) {
-          const int r = p.tok2row[t * p.topk + j];
-          if (r >= 0 && r < p.rows) { rows[n] = r; slot[n] = j; ++n; }
-        }
-      } else {
-        n = gather_walk_chain(p, t, rows, kPipeMaxRows);
-        if (n < 0) { overflow = true; n = 0; }
-      }
-      if (!overflow) {
-        for (int a = 1; a < n; ++a) {  // insertion sort, n <= 16
-          const int key = rows[a], ks = slot[a];
-          int b = a - 1;
-          while (b >= 0 && rows[b] > key) { rows[b + 1] = rows[b]; slot[b + 1] = slot[b]; --b; }
-          rows[b + 1] = key; slot[b + 1] = ks;
-        }
-        for (int j = 0; j < n; ++j) {
-          s_rows[threadIdx.x][j] = rows[j];
-          if (p.weighted) {
-            float w;
-            if (p.tok2row) {
-              // the row belongs to the expert named by its slot: the weight is that of the FIRST slot of the token that
-              // names this expert - the same value the search over the experts' starts would find, without the search
-              const int32_t* tid = p.topk_ids + t * p.topk;
-              const int e = tid[slot[j]];
-              int jf = slot[j];
-              for (int i = 0; i < slot[j]; ++i)
-                if (tid[i] == e) { jf = i; break; }
-              w = p.topk_weights[t * p.topk + jf];
-            } else {
-              w = row_weight(p, t, rows[j]);
-            }
-            s_w[threadIdx.x][j] = w;
-          }
-        }
-      }
-      s_cnt[threadIdx.x] = overflow ? -1 : n;
+    if (!have) {
+      if (threadIdx.x < ntok)
+        gather_build_list(p, t0 + threadIdx.x, nullptr, s_rows[cur][threadIdx.x], s_w[cur][threadIdx.x], &s_cnt[cur][threadIdx.x]);
+      __syncthreads();
     }
-    __syncthreads();
+    const bool look = ahead && nnext > 0;
+    if (look && threadIdx.x < nnext) {
+      const int64_t tn = t0 + chunk + threadIdx.x;
+      const uint32_t dst = smem_addr(&s_stage[threadIdx.x][0]);
+      for (int j = 0; j < p.topk; ++j) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * j), "l"(p.tok2row + tn * p.topk + j) : "memory");
+        if (p.weighted) {
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 32u + 4u * j), "l"(p.topk_ids + tn * p.topk + j) : "memory");
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 64u + 4u * j), "l"(p.topk_weights + tn * p.topk + j) : "memory");
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     // ---- phase B: stream the rows of the chunk
     int ptl = 0, pj = 0;  // producer cursor (thread 0)
-    auto issue_next = [&]() -> bool {  // issues the next row of the chunk, if any
-      while (ptl < ntok && (s_cnt[ptl] < 0 || pj >= s_cnt[ptl])) { ++ptl; pj = 0; }
-      if (ptl >= ntok) return false;
+    if (have) { ptl = qtl; pj = qj; }
+    qtl = 0; qj = 0;
+    uint32_t ready_after = 0xffffffffu;  // the next chunk's lists may be read once more than this many rows have been consumed
+    bool built = false;
+    auto issue_next = [&]() -> bool {  // issues the next row of the chunk (or, once listed, of the next chunk), if any
+      while (ptl < ntok && (s_cnt[cur][ptl] < 0 || pj >= s_cnt[cur][ptl])) { ++ptl; pj = 0; }
+      int32_t row;
+      if (ptl < ntok) {
+        row = s_rows[cur][ptl][pj++];
+      } else {
+        if (it <= ready_after) return false;
+        while (qtl < nnext && (s_cnt[cur ^ 1][qtl] < 0 || qj >= s_cnt[cur ^ 1][qtl])) { ++qtl; qj = 0; }
+        if (qtl >= nnext) return false;
+        row = s_rows[cur ^ 1][qtl][qj++];
+      }
       const int s = prod.s;
       mbar_expect_tx(&full[s], row_bytes);
-      bulk_g2s(buf + (size_t)s * row_bytes, p.y + (int64_t)s_rows[ptl][pj] * H, row_bytes, &full[s]);
-      ++issued; ++pj;
+      bulk_g2s(buf + (size_t)s * row_bytes, p.y + (int64_t)row * H, row_bytes, &full[s]);
+      ++issued;
       prod.advance(stages);
       return true;
     };
     if (threadIdx.x == 0)
-      for (int s = 0; s < stages; ++s)
+      while ((int)(issued - it) < stages)
         if (!issue_next()) break;
     for (int tl = 0; tl < ntok && alive; ++tl) {
+      if (look && !built && tl >= ntok / 2) {
+        // the next chunk's lists, from the copies started at this chunk's start
+        if (threadIdx.x < nnext) {
+          asm volatile("cp.async.wait_all;" ::: "memory");
+          gather_build_list(p, t0 + chunk + threadIdx.x, s_stage[threadIdx.x], s_rows[cur ^ 1][threadIdx.x], s_w[cur ^ 1][threadIdx.x],
+                            &s_cnt[cur ^ 1][threadIdx.x]);
+        }
+        built = true;
+        ready_after = it;  // readable after the next row barrier
+      }
       const int64_t t = t0 + tl;
       __nv_bfloat16* out = p.out + t * (int64_t)H;
       float acc[NVEC][8];
@@ -301,7 +356,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
           for (int q = 0; q < 8; ++q) acc[k][q] = 0.f;
         }
       }
-      const int n = s_cnt[tl];
+      const int n = s_cnt[cur][tl];
       if (n < 0) {
         accumulate_by_scan<THREADS, NVEC>(p, t, acc);
       } else {
@@ -310,7 +365,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
           const bool ok = mbar_wait_bounded_sleepy(&full[s], cons.phase, err, 3);
           if (ok) {
             const unsigned char* src = buf + (size_t)s * row_bytes;
-            const float w = p.weighted ? s_w[tl][j] : 1.f;
+            const float w = p.weighted ? s_w[cur][tl][j] : 1.f;
 #pragma unroll
             for (int k = 0; k < NVEC; ++k) {
               const int v = threadIdx.x + k * THREADS;
@@ -335,8 +390,11 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 2 : 1)) gather_pipe
         }
       }
     }
-    __syncthreads();  // the row lists are rebuilt for the next chunk
+    __syncthreads();  // the halves of the tables change hands
+    have = look && built;
+    cur ^= 1;
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
   if (!alive && threadIdx.x == 0) {
     // a wait ran out: drain (bounded) the copies still in flight before the CTA gives its shared memory back
     for (uint32_t k = it; k < issued; ++k, cons.advance(stages))
@@ -388,7 +446,7 @@ int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t strea
   int stages = (int)((96 * 1024) / row_bytes);
   stages = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
   const size_t smem = 128 + (size_t)stages * row_bytes;
-  int per_sm = (int)((227 * 1024) / (smem + 18 * 1024));  // + the static row-list tables
+  int per_sm = (int)((227 * 1024) / (smem + 24 * 1024));  // + the static row-list tables and the staging of the next chunk
   per_sm = per_sm < 1 ? 1 : (per_sm > 2048 / THREADS ? 2048 / THREADS : per_sm);
   if (per_sm > 4) per_sm = 4;
   // every CTA gets an equal contiguous share of the tokens and prepares it in chunks of up to kChunkTokens tokens
