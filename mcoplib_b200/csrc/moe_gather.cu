@@ -453,9 +453,10 @@ int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t strea
   int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > (tokens + 7) / 8) grid = (tokens + 7) / 8;
   // chunks of a quarter of a CTA's share, between 32 and kChunkTokens tokens: with one chunk per CTA every CTA of the
-  // grid builds its lists at the same moment and then streams at the same moment (32,768 tokens x top-2: 246 us with one
-  // chunk of 110 tokens per CTA, 235 / 228 / 239 / 254 us with chunks of 64 / 32 / 16 / 8); large runs keep the long chunks
-  // (262,144 tokens: 128 and 32 within the noise of each other, 16 and 8 slower: the ring drains at every chunk's end)
+  // grid builds its lists at the same moment and then streams at the same moment (32,768 tokens x top-2, lists made
+  // between chunks: 246 us with one chunk of 110 tokens per CTA, 235 / 228 / 239 / 254 us with chunks of 64 / 32 / 16 / 8;
+  // with the lists made ahead: 219 / 217 / 220 / 226 / 224 us with chunks of 16 / 24 / 32 / 48 / 64, and no difference
+  // beyond the noise at 262,144 tokens)
   const int64_t share = (tokens + grid - 1) / grid;
   int chunk = (int)(((share + 3) / 4 + 7) / 8 * 8);
   chunk = chunk < 32 ? 32 : (chunk > kChunkTokens ? kChunkTokens : chunk);
