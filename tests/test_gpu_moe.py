@@ -286,6 +286,32 @@ def test_gather_matches_oracle_bit_for_bit(op, T, H, E, k):
         assert float((g_ref.float() - seq.float()).abs().max()) <= 0.02 * float(seq.float().abs().max()) + 1e-3
 
 
+@pytest.mark.parametrize("T,H,E,k,local", [(1024, 7168, 8, 2, 8), (1500, 4096, 16, 4, 16), (4097, 4096, 64, 8, 64),
+                                             (2049, 7168, 8, 1, 8), (9000, 4096, 8, 2, 6), (2500, 7168, 32, 8, 20)])
+def test_gather_pipelined_with_tok2row_matches_oracle(op, T, H, E, k, local):
+    """The pipelined gather (1024 tokens and more, rows of 2056 ... 16,384 elements) with the direct inverse map: every
+    CTA walks its share in several chunks with a ragged last one and makes the next chunk's row lists while the current
+    one streams.  `local` < E drops the rows of the experts beyond it (tok2row = -1 there), so tokens own 0 ... k rows.
+    Plain and weighted, with and without accumulation, bit for bit against the oracle."""
+    w, ids = R.moe_softmax_topk(W.router_inputs(T, E, seed=21)["logits"], k)
+    r2t, cnt, st, t2r = R.moe_scatter_permutation(ids, local)
+    Rn = T * k
+    y = W.per_token("randn", 61, 0, Rn, H, torch.bfloat16)
+    out0 = W.per_token("randn", 62, 0, T, H, torch.bfloat16)
+    if local < E:
+        assert int((t2r < 0).sum()) > 0
+    o = Canary((T, H), torch.bfloat16); o.t.copy_(out0)
+    op.moe_gather(y.to(DEV), r2t.to(DEV), o.t, t2r.to(DEV))
+    torch.cuda.synchronize(); o.check("gather")
+    C.assert_equal(bits(o.t), bits(R.moe_gather(y, r2t, out0)), "gather")
+    for acc in (False, True):
+        ref = R.moe_gather_weighted(y, r2t, ids, w, st, out0, acc)
+        o = Canary((T, H), torch.bfloat16); o.t.copy_(out0)
+        op.moe_gather_weighted(y.to(DEV), r2t.to(DEV), ids.to(DEV), w.to(DEV), st.to(DEV), o.t, acc, t2r.to(DEV))
+        torch.cuda.synchronize(); o.check("weighted gather")
+        C.assert_equal(bits(o.t), bits(ref), f"weighted gather accumulate={acc}")
+
+
 def test_gather_fixed_order_against_legal_orders_of_the_reference_at_top8_hidden_7168(op):
     """The reference sums a token's rows with bf16 atomics in whatever order the hardware takes them; the build sums in
     fp32 in ascending row order and rounds once.  At the DeepSeek-V3 shape (8 rows per token, hidden 7168) the result
