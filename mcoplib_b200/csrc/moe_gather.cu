@@ -462,7 +462,11 @@ int gather_cap(int64_t tokens, int64_t rows) {
 template <int THREADS>
 int launch_gather_pipe(const GatherParams& p, int64_t tokens, cudaStream_t stream) {
   const size_t row_bytes = (size_t)p.hidden_size * 2;
-  int stages = (int)((96 * 1024) / row_bytes);
+  // 256-thread CTAs: the ring that still lets two CTAs share an SM beside their tables - with a fixed 96 KB of ring,
+  // rows of 6144 and 8192 elements got 8 and 6 stages and ONE CTA per SM: 337 and 367 us at 32,768 tokens x top-2 against
+  // 204 and 292 us now (7168: 6 stages and two CTAs either way).  512-thread CTAs are alone on their SM.
+  const size_t ring = THREADS <= 256 ? (227 * 1024) / 2 - 24 * 1024 - 128 : 96 * 1024;
+  int stages = (int)(ring / row_bytes);
   stages = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
   const size_t smem = 128 + (size_t)stages * row_bytes;
   int per_sm = (int)((227 * 1024) / (smem + 24 * 1024));  // + the static row-list tables and the staging of the next chunk
